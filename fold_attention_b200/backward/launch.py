@@ -1,0 +1,171 @@
+"""The backward's host side: bind one call's tensors, return the launch.
+
+Mirrors `prepare_backward` of the reference
+(src/fold_attention/backward/launch.py:75-117): the launch returns `(dq, dk,
+dv)`, the same tensors on every call, and owns its workspace, so two captured
+graphs never share one. All device work goes through the C ABI
+(`fold_bwd_run`): preprocess, main loop, postprocess on the current stream,
+with no host synchronisation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import _lib
+from ..utils import Launch
+from .plan import Plan, plan_dense, plan_varlen
+
+P, I, F, Z = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+_lib.register("fold_bwd_workspace_bytes", [I, I, I, I, I, I, I], Z)
+_lib.register("fold_bwd_workspace_layout", [I, I, I, I, I, I, I, P])
+_lib.register(
+    "fold_bwd_run",
+    [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, P],
+)
+_lib.register("fold_fwd_run", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
+
+KERNELS = {"auto": 0, "mma": 1, "sm100": 2}
+
+
+@dataclass(eq=False)
+class BackwardLaunch(Launch):
+    """`prepare_backward`'s result: calling it returns `(dq, dk, dv)`."""
+
+    plan: Plan | None = None
+    workspace: torch.Tensor | None = None
+    layout: tuple | None = None
+
+
+def _strides(tensors, varlen):
+    """(batch, row, head) element strides of `(B, H, S, D)` views or packed
+    `(total, H, D)` tensors, as a host int64 array."""
+    out = []
+    for t in tensors:
+        if t.stride(-1) != 1:
+            raise ValueError("the head dim must be contiguous")
+        if varlen:
+            out += [0, t.stride(0), t.stride(1)]
+        else:
+            out += [t.stride(0), t.stride(2), t.stride(1)]
+    return (ctypes.c_int64 * len(out))(*out)
+
+
+def prepare_backward(
+    q,
+    k,
+    v,
+    o,
+    do,
+    lse,
+    *,
+    causal,
+    softmax_scale=None,
+    cu_seqlens=None,
+    max_seqlen=None,
+    out_dtype=None,
+    plan: Plan | None = None,
+    kernel: str = "auto",
+):
+    """Bind dQ, dK and dV of causal or full self-attention to one call's
+    tensors, and return the launch that computes them.
+
+    Dense: `(B, H, S, D)` views and `lse` `(B, H, S)`. Varlen: `(total, H, D)`
+    packed by `cu_seqlens` `(B + 1,)` int32, and `lse` `(H, total)`. `lse` is
+    in nats. `kernel` picks the main loop: "auto" (tcgen05 where it applies),
+    "mma" or "sm100".
+    """
+    varlen = cu_seqlens is not None
+    if varlen:
+        total, H, D = q.shape
+        H_KV = k.shape[1]
+        B = cu_seqlens.shape[0] - 1
+        if max_seqlen is None:
+            max_seqlen = int(torch.diff(cu_seqlens).max())
+        S = int(max_seqlen)
+    else:
+        B, H, S, D = q.shape
+        H_KV = k.shape[1]
+        total = B * S
+        if k.shape[2] != S:
+            raise NotImplementedError("the integer grids assume self-attention")
+    if v.shape[-1] != D:
+        raise NotImplementedError("the value head dim must equal the key head dim")
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("q, k and v must be bf16 or fp16")
+    if H % H_KV:
+        raise ValueError("the query heads must be a multiple of the KV heads")
+    if D not in (64, 96, 128):
+        raise NotImplementedError(f"head_dim {D}: 64, 96 and 128 are supported")
+    if out_dtype is not None and out_dtype != q.dtype:
+        raise NotImplementedError("gradients are returned in the inputs' dtype")
+    dev = q.device
+    sm = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    if plan is None:
+        plan = plan_varlen(H, H_KV) if varlen else plan_dense(B, H, H_KV, S, D, bool(causal))
+    if plan.subgroup != H // H_KV or plan.record:
+        raise NotImplementedError("dK and dV are private to a CTA: the plan is the whole group")
+    lse = lse.contiguous()
+    if lse.dtype != torch.float32:
+        raise ValueError("lse must be fp32")
+    dq, dk, dv = (torch.empty_like(x) for x in (q, k, v))
+    nbytes = _lib.lib.fold_bwd_workspace_bytes(B, H, H_KV, S, total, D, int(varlen))
+    workspace = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    lay = (ctypes.c_int64 * 5)()
+    _lib.call("fold_bwd_workspace_layout", B, H, H_KV, S, total, D, int(varlen), lay)
+    tensors = (q, k, v, o, do, dq, dk, dv)
+    strides = _strides(tensors, varlen)
+    cu = cu_seqlens
+    args = (
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+        dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ctypes.addressof(strides),
+        _lib.ptr(cu), B, H, H_KV, S, total, D, int(bool(causal)),
+        int(q.dtype == torch.float16), sm, workspace.data_ptr(), nbytes, KERNELS[kernel],
+    )
+
+    def run():
+        _lib.call("fold_bwd_run", *args, _lib.stream(dev))
+        return dq, dk, dv
+
+    held = (q, k, v, o, do, lse, dq, dk, dv, workspace, cu, strides)
+    return BackwardLaunch(run, held, plan, workspace, tuple(lay))
+
+
+def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, max_seqlen=None):
+    """O and LSE (nats) of self-attention through the library's own forward.
+
+    Dense: `(B, S, H, D)` tensors, lse `(B, H, S)`. Varlen: `(total, H, D)`,
+    lse `(H, total)`. Stands in for the third-party forward the reference
+    calls (src/fold_attention/interface.py:42-44,70-81)."""
+    varlen = cu_seqlens is not None
+    D = q.shape[-1]
+    sm = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    o = torch.empty_like(q)
+    if varlen:
+        total, H, _ = q.shape
+        B = cu_seqlens.shape[0] - 1
+        if max_seqlen is None:
+            max_seqlen = int(torch.diff(cu_seqlens).max())
+        S = int(max_seqlen)
+        lse = torch.empty((H, total), device=q.device, dtype=torch.float32)
+        st = []
+        for t in (q, k, v, o):
+            st += [0, t.stride(0), t.stride(1)]
+    else:
+        B, S, H, _ = q.shape
+        total = B * S
+        lse = torch.empty((B, H, S), device=q.device, dtype=torch.float32)
+        st = []
+        for t in (q, k, v, o):
+            st += [t.stride(0), t.stride(1), t.stride(2)]
+    strides = (ctypes.c_int64 * 12)(*st)
+    _lib.call(
+        "fold_fwd_run", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+        ctypes.addressof(strides), _lib.ptr(cu_seqlens), B, H, k.shape[-2], S, total, D,
+        int(bool(causal)), int(q.dtype == torch.float16), sm, _lib.stream(q.device),
+    )
+    return o, lse

@@ -1,0 +1,155 @@
+// The backward's memory-bound ends.
+//
+// Preprocess (one pass over O and dO, and over K and V once per KV head):
+//   Delta_i = sum_d dO_id O_id, lse * log2(e), a zeroed dQ accumulator, and the
+//   four order-free maxima the integer grid is derived from, published with
+//   atomicMax on float bits: max|K|, max|V|, max ||dO_i||, max |Delta_i| per
+//   (request, KV head). Reference: src/fold_attention/backward/preprocess.py:176-346.
+// Postprocess: dQ = round16( float(acc) * (softmax_scale * 2^-s) ).
+//   Reference: src/fold_attention/backward/postprocess.py:153-154,256-344.
+#include "bwd_common.cuh"
+
+namespace fold {
+
+constexpr int PRE_ROWS = 64;
+constexpr int PRE_THREADS = 256;
+
+template <bool F16>
+__device__ __forceinline__ void load4(const void* p, float (&x)[4]) {
+    uint2 w = __ldg(reinterpret_cast<const uint2*>(p));
+    x[0] = half_bits_to_float<F16>(static_cast<uint16_t>(w.x & 0xFFFF));
+    x[1] = half_bits_to_float<F16>(static_cast<uint16_t>(w.x >> 16));
+    x[2] = half_bits_to_float<F16>(static_cast<uint16_t>(w.y & 0xFFFF));
+    x[3] = half_bits_to_float<F16>(static_cast<uint16_t>(w.y >> 16));
+}
+
+template <bool F16>
+__global__ void __launch_bounds__(PRE_THREADS) bwd_preprocess_kernel(const BwdParams p) {
+    const int mb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const SeqInfo sq = seq_info(p, b);
+    const int len_r = (sq.len + ROW_PAD - 1) / ROW_PAD * ROW_PAD;
+    if (mb * PRE_ROWS >= len_r) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int D = p.D;
+    const bool active = lane * 4 < D;
+    const int hkv = h / p.G;
+    const bool kv_owner = (h % p.G) == 0;
+    float mx_k = 0.f, mx_v = 0.f, mx_dn = 0.f, mx_dl = 0.f;
+    const int64_t wbase = static_cast<int64_t>(h) * p.rows_p + sq.pstart;
+    for (int r = warp; r < PRE_ROWS; r += PRE_THREADS / 32) {
+        const int i = mb * PRE_ROWS + r;
+        float delta = 0.f, lse2 = INFINITY;
+        if (i < sq.len) {
+            float o[4] = {0, 0, 0, 0}, g[4] = {0, 0, 0, 0};
+            if (active) {
+                load4<F16>(row_ptr<const uint16_t>(p.o, b, sq.start + i, h) + lane * 4, o);
+                load4<F16>(row_ptr<const uint16_t>(p.dout, b, sq.start + i, h) + lane * 4, g);
+            }
+            float d = o[0] * g[0] + o[1] * g[1] + o[2] * g[2] + o[3] * g[3];
+            float n2 = g[0] * g[0] + g[1] * g[1] + g[2] * g[2] + g[3] * g[3];
+            d = warp_sum(d);
+            n2 = warp_sum(n2);
+            delta = d;
+            mx_dn = fmaxf(mx_dn, sqrtf(n2));
+            mx_dl = fmaxf(mx_dl, fabsf(d));
+            if (kv_owner && active) {
+                float kk[4], vv[4];
+                load4<F16>(row_ptr<const uint16_t>(p.k, b, sq.start + i, hkv) + lane * 4, kk);
+                load4<F16>(row_ptr<const uint16_t>(p.v, b, sq.start + i, hkv) + lane * 4, vv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    mx_k = fmaxf(mx_k, fabsf(kk[j]));
+                    mx_v = fmaxf(mx_v, fabsf(vv[j]));
+                }
+            }
+            const float l = p.lse[b * p.lse_sb + h * p.lse_sh + sq.start + i];
+            lse2 = (l == -INFINITY) ? 0.f : l * kLog2e;
+        }
+        if (lane == 0) {
+            p.dpsum[wbase + i] = delta;
+            p.lse2[wbase + i] = lse2;
+        }
+        int4* acc = reinterpret_cast<int4*>(p.dq_acc + (wbase + i) * D);
+        for (int c = lane; c < D / 4; c += 32) acc[c] = make_int4(0, 0, 0, 0);
+    }
+    __shared__ float s_red[4][PRE_THREADS / 32];
+    mx_k = warp_max(mx_k);
+    mx_v = warp_max(mx_v);
+    if (lane == 0) {
+        s_red[0][warp] = mx_k;
+        s_red[1][warp] = mx_v;
+        s_red[2][warp] = mx_dn;
+        s_red[3][warp] = mx_dl;
+    }
+    __syncthreads();
+    if (threadIdx.x < 4) {
+        float r = s_red[threadIdx.x][0];
+        for (int w = 1; w < PRE_THREADS / 32; ++w) r = fmaxf(r, s_red[threadIdx.x][w]);
+        // the max of non-negative floats is the max of their bits, and a max
+        // lands the same in any order
+        const int slot = threadIdx.x == 0 ? ST_K : threadIdx.x == 1 ? ST_V : threadIdx.x == 2 ? ST_DO : ST_DELTA;
+        if (threadIdx.x >= 2 || kv_owner)
+            atomicMax(reinterpret_cast<unsigned int*>(p.stats + (static_cast<int64_t>(b) * p.HKV + hkv) * N_STATS + slot),
+                      __float_as_uint(r));
+    }
+}
+
+// element (row r, channel d) of a dQ accumulator tile of 128 rows
+__device__ __forceinline__ int64_t dq_tile_offset(int layout, int r, int d, int D) {
+    if (layout == DQ_LAYOUT_ROW_MAJOR) return static_cast<int64_t>(r) * D + d;
+    // DQ_LAYOUT_SM100: 16-byte chunks of a row are interleaved over the 128
+    // rows of a tile: chunk c of row r sits at (c * 128 + r) * 4 ints
+    return (static_cast<int64_t>(d >> 2) * 128 + (r & 127)) * 4 + (d & 3) + static_cast<int64_t>(r >> 7) * 128 * D;
+}
+
+template <bool F16>
+__global__ void __launch_bounds__(256) bwd_postprocess_dq_kernel(const BwdParams p, int layout) {
+    const int h = blockIdx.y, b = blockIdx.z;
+    const SeqInfo sq = seq_info(p, b);
+    const int D = p.D, cpr = D / 4;  // 4-channel chunks per row
+    const int rows_per_block = 256 / cpr > 0 ? 256 / cpr : 1;
+    const int r0 = blockIdx.x * 64;
+    if (r0 >= sq.len) return;
+    const int s = dq_scale_exp(p.stats + (static_cast<int64_t>(b) * p.HKV + h / p.G) * N_STATS, root_d(D));
+    const float f = __fmul_rn(p.scale, pow2f(-s));
+    const int64_t wbase = (static_cast<int64_t>(h) * p.rows_p + sq.pstart) * D;
+    for (int rr = threadIdx.x / cpr; rr < 64; rr += rows_per_block) {
+        const int i = r0 + rr;
+        const int c = threadIdx.x % cpr;
+        if (i >= sq.len || threadIdx.x >= rows_per_block * cpr) continue;
+        const int4 a = *reinterpret_cast<const int4*>(p.dq_acc + wbase + dq_tile_offset(layout, i, c * 4, D));
+        const float x0 = __fmul_rn(static_cast<float>(a.x), f), x1 = __fmul_rn(static_cast<float>(a.y), f);
+        const float x2 = __fmul_rn(static_cast<float>(a.z), f), x3 = __fmul_rn(static_cast<float>(a.w), f);
+        uint2 w;
+        if (F16) {
+            w.x = pack_f16x2(x0, x1);
+            w.y = pack_f16x2(x2, x3);
+        } else {
+            w.x = pack_bf16x2(x0, x1);
+            w.y = pack_bf16x2(x2, x3);
+        }
+        *reinterpret_cast<uint2*>(row_ptr<uint16_t>(p.dq, b, sq.start + i, h) + c * 4) = w;
+    }
+}
+
+int launch_bwd_preprocess(const BwdParams& p, cudaStream_t st) {
+    cudaMemsetAsync(p.stats, 0, sizeof(int) * N_STATS * p.B * p.HKV, st);
+    const int s_r = (p.S + ROW_PAD - 1) / ROW_PAD * ROW_PAD;
+    dim3 grid(s_r / PRE_ROWS, p.H, p.B);
+    if (p.f16)
+        bwd_preprocess_kernel<true><<<grid, PRE_THREADS, 0, st>>>(p);
+    else
+        bwd_preprocess_kernel<false><<<grid, PRE_THREADS, 0, st>>>(p);
+    return check_launch("bwd_preprocess");
+}
+
+int launch_bwd_postprocess(const BwdParams& p, int layout, cudaStream_t st) {
+    dim3 grid((p.S + 63) / 64, p.H, p.B);
+    if (p.f16)
+        bwd_postprocess_dq_kernel<true><<<grid, 256, 0, st>>>(p, layout);
+    else
+        bwd_postprocess_dq_kernel<false><<<grid, 256, 0, st>>>(p, layout);
+    return check_launch("bwd_postprocess");
+}
+
+}  // namespace fold

@@ -1,0 +1,117 @@
+/* libfold_b200 -- C ABI of the B200 (sm_100a) FoldAttention hot paths.
+ *
+ * Plain pointers and sizes only: every pointer is a CUDA device pointer unless
+ * its comment says "host". Every entry point enqueues on `stream` (a
+ * cudaStream_t passed as void*), never synchronises the host unless stated,
+ * returns 0 on success and a FOLD_ERR_* code otherwise; fold_last_error()
+ * then holds a message for the calling host thread. Nothing here throws.
+ *
+ * Each declaration cites the reference interface it stands in for, by the
+ * reference's path within its project.
+ */
+#ifndef FOLD_B200_H
+#define FOLD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FOLD_B200_ABI_VERSION 1
+
+#define FOLD_OK 0
+#define FOLD_ERR_ARGUMENT 1
+#define FOLD_ERR_LAUNCH 2
+#define FOLD_ERR_TIMEOUT 3
+#define FOLD_ERR_UNSUPPORTED 4
+
+/* Message of the calling thread's last failed call ("" if none). */
+const char* fold_last_error(void);
+int fold_abi_version(void);
+
+/* ---- Path B: cache writes ------------------------------------------------ */
+
+/* Quantise packed prompts into the paged cache.
+ * Replaces: src/fold_attention/decode/write.py:931-1009 (write_prompt) and its
+ * kernels :733-891.
+ *   k, v        (total, n_kv_heads, head_dim) bf16 (is_f16=0) or fp16 (1), packed
+ *   chunk_meta  int32: first[batch+1] padded to a multiple of 4 entries, then
+ *               n_chunks rows (request, first token, first position, count)
+ *               covering each request in 256-token chunks from its start
+ *   page_table  int32 (batch, pages_per_request)
+ *   ka, kb      int8 (rows, head_dim) pool planes; va/vb the V pool: bf16 va and
+ *               vb == NULL, or two e4m3 planes; ek bf16 (rows,) key scales
+ *   vsum, vmean fp32 (batch*n_kv_heads, head_dim)
+ *   scratch     fp32, n_chunks*n_kv_heads*(head_dim+1)+1 elements; its last
+ *               element receives V's scale
+ *   v_fixed     a fixed power-of-two V scale, or 0 to derive it from the
+ *               prompts' largest |v| times v_headroom over 448 */
+int fold_cache_write_prompt(const void* k, const void* v, int is_f16, const int32_t* chunk_meta,
+                            int n_chunks, int batch, const int32_t* page_table,
+                            int pages_per_request, int page_size, int n_kv_heads, int head_dim,
+                            int8_t* ka, int8_t* kb, void* va, void* vb, void* ek, float* vsum,
+                            float* vmean, float* scratch, float v_headroom, float v_fixed,
+                            void* stream);
+
+/* One decode step's writes: query planes (q != NULL) and/or one appended
+ * token per request (k, v != NULL) at position lens_in[b]; lens_out[b] =
+ * lens_in[b] + 1 (lens_out may alias lens_in).
+ * Replaces: src/fold_attention/decode/write.py:380-440 (step_kernel),
+ * :565-673 (prepare_step) and the append half of decode/front.py:255-471.
+ *   q (batch*n_heads, head_dim); k, v (batch, n_kv_heads, head_dim)
+ *   qa, qb int8 (batch*n_heads, head_dim); eq fp32 (batch*n_heads,) */
+int fold_step_append(const void* q, const void* k, const void* v, int is_f16, int batch,
+                     int n_heads, int n_kv_heads, int head_dim, const int32_t* page_table,
+                     int pages_per_request, int page_size, const int32_t* lens_in,
+                     int32_t* lens_out, int8_t* qa, int8_t* qb, float* eq, int8_t* ka, int8_t* kb,
+                     void* va, void* vb, void* ek, float v_scale, float* vsum, float* vmean,
+                     void* stream);
+
+/* ---- Path A: deterministic attention backward ------------------------------ */
+
+#define FOLD_BWD_KERNEL_AUTO 0  /* tcgen05 where it applies, else mma.sync */
+#define FOLD_BWD_KERNEL_MMA 1
+#define FOLD_BWD_KERNEL_SM100 2
+
+/* Tensor arguments of the training entry points are described by `strides`:
+ * three int64 element strides (batch, token row, head) per tensor, channels
+ * contiguous. Dense calls are (B, S, H, D); packed calls (total, H, D) with
+ * batch stride 0 and cu_seqlens (batch+1) int32 on the device. lse is fp32 in
+ * nats, (B, H, S) dense or (H, total) packed. */
+
+/* Bytes of scratch fold_bwd_run needs (the int32 dQ accumulator, Delta,
+ * lse*log2e and the per-(request, KV head) maxima).
+ * Replaces the allocations of src/fold_attention/backward/launch.py:186-216. */
+size_t fold_bwd_workspace_bytes(int batch, int n_heads, int n_kv_heads, int max_seqlen, int total,
+                                int head_dim, int varlen);
+
+/* Byte offsets of the workspace's parts (dq_acc, dpsum, lse2, stats) and the
+ * padded row count per head, for callers that inspect the accumulators. */
+int fold_bwd_workspace_layout(int batch, int n_heads, int n_kv_heads, int max_seqlen, int total,
+                              int head_dim, int varlen, int64_t* out5);
+
+/* dQ, dK, dV of causal or full self-attention: preprocess, main loop and
+ * postprocess on `stream`, no host synchronisation.
+ * Replaces: src/fold_attention/backward/launch.py:75-117 (prepare_backward) and
+ * the run() closure :410-435; kernels backward/preprocess.py, kernel.py,
+ * postprocess.py. strides: q, k, v, o, dout, dq, dk, dv (24 entries). */
+int fold_bwd_run(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                 const float* lse, void* dq, void* dk, void* dv, const int64_t* strides /* host */,
+                 const int32_t* cu_seqlens, int batch, int n_heads, int n_kv_heads, int max_seqlen,
+                 int total, int head_dim, int causal, int is_f16, float softmax_scale,
+                 void* workspace, size_t workspace_bytes, int kernel, void* stream);
+
+/* Attention forward: O and the log-sum-exp (nats) the backward consumes.
+ * Replaces the third-party forward called at src/fold_attention/interface.py:42-44,
+ * :70-81 and kv_cache.py:252-262. strides: q, k, v, o (12 entries). */
+int fold_fwd_run(const void* q, const void* k, const void* v, void* o, float* lse,
+                 const int64_t* strides /* host */, const int32_t* cu_seqlens, int batch,
+                 int n_heads, int n_kv_heads, int max_seqlen, int total, int head_dim, int causal,
+                 int is_f16, float softmax_scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FOLD_B200_H */

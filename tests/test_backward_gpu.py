@@ -1,0 +1,228 @@
+"""The backward: is it attention's gradient, and do its bits depend on
+anything but the request. Mirrors the reference's tests/test_backward.py with
+an FP64 reference as checker; tolerance: rel-L2 <= 3.0e-3 against FP64, the
+level the reference publishes for bf16 (worst 2.525e-3 vs FP32)."""
+
+import ctypes
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import backward as ob  # noqa: E402
+
+TOL = 3.0e-3
+KERNELS = ["mma"]
+
+
+def _api():
+    import fold_attention_b200 as fa
+    from fold_attention_b200.backward import attention_forward, prepare_backward
+
+    return fa, attention_forward, prepare_backward
+
+
+def _packed(lens, H, HKV, D, seed=0, dtype=torch.bfloat16):
+    torch.manual_seed(seed)
+    dev = "cuda"
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=dev, dtype=torch.int32)
+    T = sum(lens)
+    q = torch.randn(T, H, D, device=dev).to(dtype)
+    k = torch.randn(T, HKV, D, device=dev).to(dtype)
+    v = torch.randn(T, HKV, D, device=dev).to(dtype)
+    do = torch.randn(T, H, D, device=dev).to(dtype)
+    return q, k, v, do, cu
+
+
+def _bwd(q, k, v, o, do, lse, cu, S, causal=True, **kw):
+    _, _, prepare_backward = _api()
+    run = prepare_backward(q, k, v, o, do, lse, causal=causal, cu_seqlens=cu, max_seqlen=S, **kw)
+    return tuple(x.clone() for x in run())
+
+
+def _fwd(q, k, v, cu, S, causal=True):
+    _, attention_forward, _ = _api()
+    return attention_forward(q, k, v, causal=causal, cu_seqlens=cu, max_seqlen=S)
+
+
+def _same(a, b):
+    return all(torch.equal(x, y) for x, y in zip(a, b))
+
+
+@pytest.mark.parametrize("H,HKV,D,dtype", [
+    (8, 8, 128, torch.bfloat16), (8, 2, 128, torch.bfloat16), (16, 2, 64, torch.bfloat16),
+    (8, 8, 96, torch.bfloat16), (8, 2, 128, torch.float16),
+])
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_forward_and_gradient_accuracy(H, HKV, D, dtype, kernel):
+    q, k, v, do, cu = _packed([1536], H, HKV, D, dtype=dtype)
+    S = 1536
+    o, lse = _fwd(q, k, v, cu, S)
+    oref, lref = ob.reference_forward(q, k, v)
+    assert ob.rel_l2(o, oref) < 4e-3
+    assert (lse.double() - lref).abs().max().item() < 2e-3
+    ours = _bwd(q, k, v, o, do, lse, cu, S, kernel=kernel)
+    ref = ob.reference_grads(q, k, v, do)
+    for name, a, r in zip("qkv", ours, ref):
+        assert ob.rel_l2(a, r) <= TOL, (name, ob.rel_l2(a, r))
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_config1_dense_mha_d64_twice(kernel):
+    """BASELINE config 1: B2 S512 H8/8 D64 causal, N(0,1) inputs; checked
+    against FP64 autograd, and two runs are the same bits."""
+    fa, _, _ = _api()
+    torch.manual_seed(0)
+    B, S, H, D = 2, 512, 8, 64
+    q, k, v, do = (torch.randn(B, S, H, D, device="cuda").bfloat16() for _ in range(4))
+    grads = []
+    for _ in range(2):
+        qq, kk, vv = (x.clone().requires_grad_() for x in (q, k, v))
+        out = fa.fold_attn_func(qq, kk, vv, causal=True)
+        out.backward(do)
+        grads.append((qq.grad.clone(), kk.grad.clone(), vv.grad.clone()))
+    assert _same(grads[0], grads[1])
+    for b in range(B):
+        ref = ob.reference_grads(q[b], k[b], v[b], do[b])
+        for name, a, r in zip("qkv", grads[0], ref):
+            assert ob.rel_l2(a[b], r) <= TOL, (name, ob.rel_l2(a[b], r))
+
+
+@pytest.mark.parametrize("B,H,HKV,S,D,causal", [
+    (2, 8, 2, 1024, 128, False), (1, 16, 2, 1000, 64, False), (1, 8, 8, 1000, 96, False),
+    (3, 8, 2, 777, 128, True),
+])
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_full_and_ragged_attention(B, H, HKV, S, D, causal, kernel):
+    _, attention_forward, prepare_backward = _api()
+    torch.manual_seed(7)
+    q, do = (torch.randn(B, S, H, D, device="cuda").bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, S, HKV, D, device="cuda").bfloat16() for _ in range(2))
+    o, lse = attention_forward(q, k, v, causal=causal)
+    tr = lambda x: x.transpose(1, 2)
+    run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=causal, kernel=kernel)
+    ours = tuple(tr(x).clone() for x in run())
+    for b in range(B):
+        ref = ob.reference_grads(q[b], k[b], v[b], do[b], causal=causal)
+        for name, a, r in zip("qkv", ours, ref):
+            assert ob.rel_l2(a[b], r) <= TOL, (name, ob.rel_l2(a[b], r))
+    assert _same(ours, tuple(tr(x) for x in run()))
+
+
+@pytest.mark.parametrize("H,HKV,D", [(8, 8, 128), (8, 2, 128), (16, 2, 64), (32, 4, 128)])
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_a_request_does_not_see_its_batch(H, HKV, D, kernel):
+    """A request's gradients alone and packed among others are the same bits."""
+    lens = [1000, 777, 2048, 64, 1500]
+    q, k, v, do, cu = _packed(lens, H, HKV, D)
+    S = max(lens)
+    o, lse = _fwd(q, k, v, cu, S)
+    packed = _bwd(q, k, v, o, do, lse, cu, S, kernel=kernel)
+    a, b = int(cu[2]), int(cu[3])
+    sl = lambda x: x[a:b].contiguous()
+    cu1 = torch.tensor([0, b - a], device="cuda", dtype=torch.int32)
+    o1, lse1 = _fwd(sl(q), sl(k), sl(v), cu1, b - a)
+    assert torch.equal(o1, sl(o))
+    alone = _bwd(sl(q), sl(k), sl(v), o1, sl(do), lse1, cu1, b - a, kernel=kernel)
+    assert all(torch.equal(x, sl(y)) for x, y in zip(alone, packed))
+    # and in another order, inside another batch
+    order = [2, 0, 4]
+    parts = [slice(int(cu[i]), int(cu[i + 1])) for i in order]
+    cat = lambda x: torch.cat([x[p] for p in parts]).contiguous()
+    cu2 = torch.tensor([0] + list(np.cumsum([lens[i] for i in order])), device="cuda", dtype=torch.int32)
+    o2, lse2 = _fwd(cat(q), cat(k), cat(v), cu2, S)
+    other = _bwd(cat(q), cat(k), cat(v), o2, cat(do), lse2, cu2, S, kernel=kernel)
+    assert all(torch.equal(x[: lens[2]], sl(y)) for x, y in zip(other, packed))
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_repeated_calls_and_short_sequences(kernel):
+    _, _, prepare_backward = _api()
+    lens = [17, 0, 129, 65, 257, 1, 191]
+    q, k, v, do, cu = _packed(lens, 8, 2, 128, seed=5)
+    o, lse = _fwd(q, k, v, cu, max(lens))
+    run = prepare_backward(q, k, v, o, do, lse, causal=True, cu_seqlens=cu, max_seqlen=max(lens), kernel=kernel)
+    first = tuple(x.clone() for x in run())
+    for _ in range(3):
+        assert _same(first, run())
+    off = 0
+    for n in lens:
+        if n:
+            ref = ob.reference_grads(q[off:off + n], k[off:off + n], v[off:off + n], do[off:off + n])
+            for name, a, r in zip("qkv", first, ref):
+                assert ob.rel_l2(a[off:off + n], r) <= 2 * TOL, (n, name)
+        off += n
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_varlen_is_dense_to_the_bit(kernel):
+    _, attention_forward, prepare_backward = _api()
+    torch.manual_seed(3)
+    B, S, H, HKV, D = 3, 640, 8, 2, 128
+    q, do = (torch.randn(B, S, H, D, device="cuda").bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, S, HKV, D, device="cuda").bfloat16() for _ in range(2))
+    o, lse = attention_forward(q, k, v, causal=True)
+    tr = lambda x: x.transpose(1, 2)
+    dense = tuple(tr(x).clone() for x in prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True, kernel=kernel)())
+    cu = torch.arange(B + 1, device="cuda", dtype=torch.int32) * S
+    fl = lambda x: x.reshape(B * S, x.shape[2], D)
+    lse_p = lse.permute(1, 0, 2).reshape(H, B * S).contiguous()
+    packed = _bwd(fl(q), fl(k), fl(v), fl(o), fl(do), lse_p, cu, S, kernel=kernel)
+    assert all(torch.equal(fl(a), b) for a, b in zip(dense, packed))
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_grid_exponent_accumulator_and_postprocess(kernel):
+    """The preprocess's maxima and the exponent derived from them are the
+    oracle's; the int32 accumulator never nears saturation; dQ is the one
+    fp32 multiply of the accumulator the postprocess documents."""
+    _, attention_forward, prepare_backward = _api()
+    if kernel != "mma":
+        pytest.skip("row-major accumulator view is the mma kernel's")
+    torch.manual_seed(11)
+    B, S, H, HKV, D = 2, 300, 4, 2, 64
+    G = H // HKV
+    q, do = (torch.randn(B, S, H, D, device="cuda").bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, S, HKV, D, device="cuda").bfloat16() for _ in range(2))
+    k[1] *= 6.0
+    o, lse = attention_forward(q, k, v, causal=True)
+    tr = lambda x: x.transpose(1, 2)
+    run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True, kernel=kernel)
+    dq, dk, dv = run()
+    torch.cuda.synchronize()
+    off_acc, off_dp, off_l2, off_st, rows_p = run.layout
+    ws = run.workspace
+    stats = ws[off_st: off_st + B * HKV * 8 * 4].view(torch.float32).view(B, HKV, 8).cpu()
+    acc = ws[off_acc: off_acc + H * rows_p * D * 4].view(torch.int32).view(H, rows_p, D)
+    S_r = rows_p // B
+    for b in range(B):
+        st = ob.stats(q[b], k[b], v[b], o[b], do[b], G)
+        for h in range(HKV):
+            got = stats[b, h]
+            assert float(got[0]) == st[h][0] and float(got[1]) == st[h][1]
+            assert abs(float(got[2]) - st[h][2]) <= 1e-5 * st[h][2]
+            assert abs(float(got[3]) - st[h][3]) <= 1e-4 * max(st[h][3], 1.0)
+            s = ob.dq_scale_exp(*[float(x) for x in got[:4]], D)
+            for g in range(G):
+                a = acc[h * G + g, b * S_r: b * S_r + S]
+                assert int(a.abs().max()) < 2**30
+                assert int(a.abs().max()) > 2**14
+                f = np.float32(np.float32(1.0 / math.sqrt(D)) * np.float32(2.0**-s))
+                want = (a.float() * float(f)).bfloat16()
+                assert torch.equal(tr(dq)[b, :, h * G + g], want)
+
+
+def test_error_messages():
+    fa, _, _ = _api()
+    q = torch.randn(2, 64, 8, 128, device="cuda").bfloat16()
+    k = torch.randn(2, 64, 3, 128, device="cuda").bfloat16()
+    with pytest.raises(ValueError, match="multiple of the KV heads"):
+        fa.fold_attn_func(q, k, k)
+    with pytest.raises(ValueError, match="bf16 or fp16"):
+        fa.fold_attn_func(q.float(), q.float(), q.float())
+    q32 = torch.randn(2, 64, 8, 32, device="cuda").bfloat16()
+    with pytest.raises(NotImplementedError, match="64, 96 and 128"):
+        fa.fold_attn_func(q32.requires_grad_(), q32, q32).sum().backward()
