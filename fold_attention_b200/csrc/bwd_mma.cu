@@ -45,7 +45,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_main_mma_kernel(const BwdPara
     constexpr int DH = D / 2;         // channels per warp half
 
     const int s_exp = dq_scale_exp(p.stats + (static_cast<int64_t>(b) * p.HKV + hkv) * N_STATS, root_d(D));
-    const float s_bias = static_cast<float>(s_exp);
+    // bf16 has fp32's range, so the softmax carries the grid's exponent
+    // (P~ = P 2^s) and dQ~ leaves the GEMM on the grid. fp16 would overflow:
+    // there P stays unscaled and the partial is multiplied by 2^s (exact)
+    // before it is rounded.
+    const float s_bias = F16 ? 0.f : static_cast<float>(s_exp);
+    const float dq_mul = F16 ? pow2f(s_exp) : 1.f;
     const float c2 = p.scale * kLog2e;
 
     uint8_t* sK = smem + L::OFF_K;
@@ -191,7 +196,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_main_mma_kernel(const BwdPara
                     for (int e = 0; e < 4; ++e) {
                         const int ql = 16 * wk + gid + 8 * (e >> 1);
                         const int d = wd * DH + 8 * nt + 2 * tq + (e & 1);
-                        const int v = __float2int_rn(dq[nt][e]);
+                        const int v = __float2int_rn(dq[nt][e] * dq_mul);
                         if (v != 0) atomicAdd(acc + ql * D + d, v);
                     }
             }
@@ -202,7 +207,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_main_mma_kernel(const BwdPara
 
     // dK = round16(dK~ c 2^-s), dV = round16(dV~ 2^-s): P~ carried 2^s through
     // the whole loop, so both leave scaled by it and are put back exactly.
-    const float un = pow2f(-s_exp);
+    const float un = F16 ? 1.f : pow2f(-s_exp);
     const float fk = p.scale * un;
 #pragma unroll
     for (int nt = 0; nt < NTD; ++nt)

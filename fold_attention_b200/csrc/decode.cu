@@ -1,0 +1,768 @@
+// Quantised paged-KV decode: the mass reference Z, the split-KV kernel and the
+// additive combine.
+//
+// A row group is the G <= 8 query rows that share one KV head of one request.
+// One CTA owns (row group, split) and walks 64-key tiles:
+//   1. plane A of K and the key scales arrive by bulk copy (a tile is
+//      contiguous inside its page) into a 3-slot ring, two tiles ahead;
+//   2. the coarse logit 256 c1 + c2 (int8 mma.sync against both Q planes, Q
+//      fragments held in registers) gives s1 = fma(int, eq ek/256, -Z) and the
+//      verdict bits live / refine-K / refine-V, ORed over the group's rows;
+//   3. the live keys' V rows, the refined keys' plane-B K rows and V plane-B
+//      rows are gathered with 128-bit cp.async through the page table (rows
+//      not selected are zero-filled and move no bytes);
+//   4. one tile later, plane B refines the logits, weights w = exp2(s - Z) are
+//      final at once (Z is fixed before the loop), go to bf16 (value and
+//      rounding error as two terms) and meet V in a bf16 mma.sync; a cut key
+//      adds its weight to the row's dropped mass instead.
+// Partials (numerator, denominator + dropped mass, counts) are plain sums the
+// combine adds in slot order.
+// Reference: src/fold_attention/decode/kernel.py:95-1488, combine.py:10-162,
+// reference.py:120-406 (the arithmetic; the schedule here is B200's own).
+#include "common.cuh"
+#include "fold_b200.h"
+#include "mma_utils.cuh"
+
+namespace fold {
+
+constexpr int BNK = 64;          // keys per tile
+constexpr int DEC_THREADS = 128;
+constexpr int RING = 3;
+constexpr int WAIT_LIMIT = 1 << 22;
+constexpr float E4W = 18446744073709551616.0f;   // 2^64 on the weights of an 8-bit V
+constexpr float E4O = 72057594037927936.0f;      // 2^56 on its accumulator
+
+struct DecodeParams {
+    const int8_t* qa; const int8_t* qb; const float* eq;     // (NBH, G, D), (NBH, G)
+    const int8_t* ka; const int8_t* kb; const uint16_t* ek;  // pool planes, bf16 scales
+    const uint8_t* va; const uint8_t* vb;                    // bf16 or e4m3 (+ plane B)
+    const float* vmean;                                      // (NBH, D) or null
+    const float* z; const float* cut;                        // (NBH, G): reference, depth below it
+    const int* page_table; const int* seq_lens; const int* order;
+    float* o_part; float* den_part; int* cnt_part;
+    int nbh, G, hkv, ppr, page_size, split, chunk_keys, truncate, banded;
+    float rk, rv, band_e0, band_e1, rk1, rk2, rv1, rv2;
+    int* status;
+};
+
+// ---- small PTX wrappers -----------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// A bounded wait: on expiry the status word is set and false returned, so the
+// CTA can leave without hanging the device.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+    for (int i = 0; i < WAIT_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(status, FOLD_ERR_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+// two e4m3 bytes (byte i of w0 -> low half, of w1 -> high half) as bf16x2 * 2^-120
+__device__ __forceinline__ uint32_t e4m3_pair_bf16(uint32_t w0, uint32_t w1, int i) {
+    const uint32_t sel = i | (i << 4) | ((4 + i) << 8) | ((4 + i) << 12);
+    const uint32_t x = __byte_perm(w0, w1, sel);
+    return (x & 0x80008000u) | ((x >> 4) & 0x07F007F0u);
+}
+__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <int D>
+__device__ __forceinline__ int swz(int r) { return D >= 128 ? (r & 7) : ((r >> 1) & 3); }
+
+// where 16-byte unit u of gathered V row r lands in shared memory: an XOR on
+// the low unit bits, so a lane quad reading four rows hits distinct banks
+template <int UNITS>
+__device__ __forceinline__ int vswz(int u, int r) {
+    constexpr int M = (UNITS < 8 ? UNITS : 8) - 1;
+    return (u & ~M) | ((u ^ r) & M);
+}
+
+// ---- the split-KV kernel ------------------------------------------------------
+template <int D, bool V8>
+struct DecSmem {
+    static constexpr int KA = BNK * D, KS = BNK * 2;
+    static constexpr int SLOT = KA + KS;               // plane A tile + its scales
+    static constexpr int VROW = V8 ? D : 2 * D;
+    static constexpr int GKB = BNK * D, GVA = BNK * VROW, GVB = V8 ? BNK * D : 0;
+    static constexpr int GBUF = GKB + GVA + GVB;
+    static constexpr int OFF_RING = 0, OFF_G = RING * SLOT, OFF_LIVE = OFF_G + 2 * GBUF;
+    static constexpr int OFF_BAR = OFF_LIVE + 2 * BNK * 4, OFF_RED = OFF_BAR + 64;
+    static constexpr int OFF_FAIL = OFF_RED + 1024;
+    static constexpr int BYTES = OFF_FAIL + 16;
+};
+
+template <int D, bool V8, bool W2, bool TRUNC>
+__global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams p) {
+    using L = DecSmem<D, V8>;
+    constexpr int NU = D / 16;          // 16-byte units per int8 row
+    constexpr int KSTEPS = D / 32;      // k-steps of the int8 logit
+    constexpr int NT = D / 8;           // 8-channel n-tiles of the value product
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tq = lane & 3;
+    const int slot = blockIdx.x / p.split, sp = blockIdx.x % p.split;
+    const int bh = p.order ? p.order[slot] : slot;
+    const int breq = bh / p.hkv, hkv = bh % p.hkv;
+    const int slen = p.seq_lens[breq];
+    const int G = p.G, PS = p.page_size;
+
+    // this split's tiles: interleaved (tile sp, sp + split, ...) or a fixed chunk
+    int lo, hi, tstep, n_tiles;
+    if (p.chunk_keys > 0) {
+        lo = sp * p.chunk_keys;
+        hi = min(lo + p.chunk_keys, slen);
+        tstep = BNK;
+        n_tiles = hi > lo ? (hi - lo + BNK - 1) / BNK : 0;
+        if (n_tiles == 0) return;   // the combine reads only the splits a request reaches
+    } else {
+        lo = sp * BNK;
+        hi = slen;
+        tstep = p.split * BNK;
+        const int all = (slen + BNK - 1) / BNK;
+        n_tiles = all > sp ? (all - sp + p.split - 1) / p.split : 0;
+    }
+    const int64_t pix = static_cast<int64_t>(bh) * p.split + sp;
+
+    float rk = p.rk, rv = p.rv;
+    if (p.banded) {
+        rk = slen > static_cast<int>(p.band_e1) ? p.rk2 : (slen > static_cast<int>(p.band_e0) ? p.rk1 : p.rk);
+        rv = slen > static_cast<int>(p.band_e1) ? p.rv2 : (slen > static_cast<int>(p.band_e0) ? p.rv1 : p.rv);
+    }
+
+    uint32_t bars[RING];
+#pragma unroll
+    for (int i = 0; i < RING; ++i) bars[i] = smem_u32(smem + L::OFF_BAR + 8 * i);
+    volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_FAIL);
+    if (tid == 0) {
+        *sFail = 0;
+#pragma unroll
+        for (int i = 0; i < RING; ++i) mbar_init(bars[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int* ptab = p.page_table + static_cast<int64_t>(breq) * p.ppr;
+    // pool row of position `pos` of this row group
+    auto pool_row = [&](int pos) -> int64_t {
+        return (static_cast<int64_t>(__ldg(ptab + pos / PS)) * p.hkv + hkv) * PS + pos % PS;
+    };
+    // tile t's plane A and scales into ring slot t % RING, in page segments
+    auto issue_tile = [&](int t) {
+        const int base = lo + t * tstep;
+        const int nrow = min(BNK, hi - base);
+        const int seg = min(PS, BNK);
+        const int nseg = (nrow + seg - 1) / seg;
+        uint8_t* dst = smem + L::OFF_RING + (t % RING) * L::SLOT;
+        const uint32_t bar = bars[t % RING];
+        mbar_expect_tx(bar, nseg * seg * (D + 2));
+        for (int s = 0; s < nseg; ++s) {
+            const int64_t r = pool_row(base + s * seg);
+            bulk_g2s(smem_u32(dst + s * seg * D), p.ka + r * D, seg * D, bar);
+            bulk_g2s(smem_u32(dst + L::KA + s * seg * 2), p.ek + r, seg * 2, bar);
+        }
+    };
+    if (tid == 0) {
+        for (int t = 0; t < min(2, n_tiles); ++t) issue_tile(t);
+    }
+
+    // Q fragments: B operand of m16n8k32, row g = gid, channels 32 ks + 4 tq (+16)
+    uint32_t qfa[KSTEPS][2], qfb[KSTEPS][2];
+    {
+        const bool ok = gid < G;
+        const int64_t qrow = (static_cast<int64_t>(bh) * G + (ok ? gid : 0)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = 32 * ks + 16 * j + 4 * tq;
+                qfa[ks][j] = ok ? *reinterpret_cast<const uint32_t*>(p.qa + qrow + c) : 0u;
+                qfb[ks][j] = ok ? *reinterpret_cast<const uint32_t*>(p.qb + qrow + c) : 0u;
+            }
+    }
+    // the two rows this lane's logit registers belong to
+    float eqr[2], zr[2], cutr[2];
+    bool rowok[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int g = 2 * tq + j;
+        rowok[j] = g < G;
+        const int64_t ix = static_cast<int64_t>(bh) * G + (rowok[j] ? g : 0);
+        eqr[j] = p.eq[ix];
+        zr[j] = p.z[ix];
+        cutr[j] = -p.cut[ix];
+    }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+    float rM[2] = {0.f, 0.f}, rN[2] = {0.f, 0.f};
+    int nlive = 0, nref = 0;
+
+    float s_old[4] = {0, 0, 0, 0}, tk_old[4] = {0, 0, 0, 0};
+    int b_old[2] = {0, 0}, nrow_old = 0;
+    bool failed = false;
+
+    for (int t = 0; t <= n_tiles; ++t) {
+        float s_new[4] = {0, 0, 0, 0}, tk_new[4] = {0, 0, 0, 0};
+        int b_new[2] = {0, 0}, nrow_new = 0;
+        if (t < n_tiles) {
+            const int base = lo + t * tstep;
+            const int nrow = min(BNK, hi - base);
+            nrow_new = nrow;
+            uint8_t* sKa = smem + L::OFF_RING + (t % RING) * L::SLOT;
+            const uint16_t* sKs = reinterpret_cast<const uint16_t*>(sKa + L::KA);
+            if (!mbar_wait(bars[t % RING], (t / RING) & 1, p.status)) *sFail = 1;
+            // ---- coarse logit: 16 keys x 8 rows, both Q planes ----
+            int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+            const int arow = 16 * warp + (lane & 7) + 8 * ((lane >> 3) & 1);
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                uint32_t a[4];
+                const int u = (2 * ks + (lane >> 4)) ^ swz<D>(arow);
+                ldmatrix_x4(a, smem_u32(sKa + arow * D + u * 16));
+                mma_s8(c1, a, qfa[ks][0], qfa[ks][1]);
+                mma_s8(c2, a, qfb[ks][0], qfb[ks][1]);
+            }
+            int pk = TRUNC ? 0 : (1 | (1 << 3));
+            float dg[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int ky = 16 * warp + gid + 8 * (i >> 1);
+                const float ekf = bf16_bits_to_float(sKs[ky]) * (1.0f / 256.0f);
+                const float tk = eqr[i & 1] * ekf;
+                tk_new[i] = tk;
+                float s1 = -INFINITY;
+                if (rowok[i & 1] && ky < nrow) {
+                    s1 = fmaf(static_cast<float>(c1[i] * 256 + c2[i]), tk, -zr[i & 1]);
+                    if (TRUNC && s1 >= cutr[i & 1]) pk |= 1 << (3 * (i >> 1));
+                    dg[i >> 1] = fmaxf(dg[i >> 1], s1);
+                }
+                s_new[i] = s1;
+            }
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                if (dg[hf] >= -rk) pk |= 2 << (3 * hf);
+                if (V8 && dg[hf] >= -rv) pk |= 4 << (3 * hf);
+            }
+            pk |= __shfl_xor_sync(0xffffffffu, pk, 1);
+            pk |= __shfl_xor_sync(0xffffffffu, pk, 2);
+            int b0 = pk & 7, b1 = (pk >> 3) & 7;
+            // a key no row keeps is neither gathered nor refined
+            b0 = (b0 & 1) ? b0 : 0;
+            b1 = (b1 & 1) ? b1 : 0;
+            if (16 * warp + gid >= nrow) b0 = 0;
+            if (16 * warp + gid + 8 >= nrow) b1 = 0;
+            b_new[0] = b0;
+            b_new[1] = b1;
+            int* sLive = reinterpret_cast<int*>(smem + L::OFF_LIVE) + (t & 1) * BNK;
+            if (tq == 0) {
+                sLive[16 * warp + gid] = b0;
+                sLive[16 * warp + gid + 8] = b1;
+            }
+            {   // counts are data, not schedule: live keys and refined keys
+                const unsigned m0 = __ballot_sync(0xffffffffu, tq == 0 && (b0 & 1));
+                const unsigned m1 = __ballot_sync(0xffffffffu, tq == 0 && (b1 & 1));
+                const unsigned r0 = __ballot_sync(0xffffffffu, tq == 0 && (b0 & 2));
+                const unsigned r1 = __ballot_sync(0xffffffffu, tq == 0 && (b1 & 2));
+                nlive += __popc(m0) + __popc(m1);
+                nref += __popc(r0) + __popc(r1);
+            }
+            __syncthreads();
+            // a wait that ran out ends the CTA for every thread alike
+            if (*sFail) { failed = true; }
+            if (failed) break;
+            // every warp has read this ring slot's predecessor: refill it
+            if (tid == 0 && t + 2 < n_tiles) issue_tile(t + 2);
+            // ---- gathers for tile t: two threads per key row ----
+            {
+                uint8_t* g = smem + L::OFF_G + (t & 1) * L::GBUF;
+                const int r = tid >> 1, half = tid & 1;
+                const int bits = sLive[r];
+                const int pos = base + (r < nrow ? r : 0);
+                const int64_t prow = pool_row(pos);
+                // K plane B: stored swizzled by slot, copied unit for unit
+#pragma unroll
+                for (int j = 0; j < NU / 2; ++j) {
+                    const int u = half * (NU / 2) + j;
+                    cp_async16(smem_u32(g + r * D + u * 16), p.kb + prow * D + u * 16, (bits & 2) ? 16 : 0);
+                }
+                // V rows: unit u lands at u ^ (r & 7)
+                constexpr int VU = L::VROW / 16;
+#pragma unroll
+                for (int j = 0; j < VU / 2; ++j) {
+                    const int u = half * (VU / 2) + j;
+                    const int du = vswz<VU>(u, r);
+                    cp_async16(smem_u32(g + L::GKB + r * L::VROW + du * 16), p.va + prow * L::VROW + u * 16,
+                               (bits & 1) ? 16 : 0);
+                }
+                if (V8) {
+#pragma unroll
+                    for (int j = 0; j < NU / 2; ++j) {
+                        const int u = half * (NU / 2) + j;
+                        const int du = vswz<NU>(u, r);
+                        cp_async16(smem_u32(g + L::GKB + L::GVA + r * D + du * 16), p.vb + prow * D + u * 16,
+                                   (bits & 4) ? 16 : 0);
+                    }
+                }
+            }
+        }
+        cp_async_commit();
+        if (t >= 1) {
+            // ---- tile t-1: refine, weights, value product ----
+            cp_async_wait<1>();
+            __syncthreads();
+            uint8_t* g = smem + L::OFF_G + ((t - 1) & 1) * L::GBUF;
+            const uint8_t* sKb = g;
+            const uint8_t* sVa = g + L::GKB;
+            const uint8_t* sVb = g + L::GKB + L::GVA;
+            const unsigned any_ref = __ballot_sync(0xffffffffu, ((b_old[0] | b_old[1]) & 2) != 0);
+            const unsigned any_live = __ballot_sync(0xffffffffu, ((b_old[0] | b_old[1]) & 1) != 0);
+            const unsigned any_rv = __ballot_sync(0xffffffffu, ((b_old[0] | b_old[1]) & 4) != 0);
+            int c3a[4] = {0, 0, 0, 0}, c3b[4] = {0, 0, 0, 0};
+            if (any_ref) {
+                const int arow = 16 * warp + (lane & 7) + 8 * ((lane >> 3) & 1);
+#pragma unroll
+                for (int ks = 0; ks < KSTEPS; ++ks) {
+                    uint32_t a[4];
+                    const int u = (2 * ks + (lane >> 4)) ^ swz<D>(arow);
+                    ldmatrix_x4(a, smem_u32(sKb + arow * D + u * 16));
+                    mma_s8(c3a, a, qfa[ks][0], qfa[ks][1]);
+                    mma_s8(c3b, a, qfb[ks][0], qfb[ks][1]);
+                }
+            }
+            float w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int ky = 16 * warp + gid + 8 * (i >> 1);
+                const bool valid = rowok[i & 1] && ky < nrow_old;
+                const bool live = (b_old[i >> 1] & 1) != 0;
+                float s = s_old[i];
+                if (b_old[i >> 1] & 2)
+                    s = s + (static_cast<float>(c3a[i]) + static_cast<float>(c3b[i]) * (1.0f / 256.0f)) * tk_old[i];
+                const float e = valid ? ex2_approx(s) : 0.f;
+                if (TRUNC) {
+                    // the gather is the group's, so a live key enters every row at
+                    // its true weight; a cut key's weight joins the dropped mass
+                    w[i] = live ? e : 0.f;
+                    rM[i & 1] += live ? 0.f : e;
+                } else {
+                    w[i] = e;
+                }
+            }
+            if (any_live) {
+                uint32_t a[4];
+#pragma unroll
+                for (int hk = 0; hk < 2; ++hk) {
+                    float w0 = w[2 * hk], w1 = w[2 * hk + 1];
+                    if (V8) {
+                        w0 *= E4W;
+                        w1 *= E4W;
+                    }
+                    const uint32_t ph = pack_bf16x2(w0, w1);
+                    const float f0 = __uint_as_float(ph << 16), f1 = __uint_as_float(ph & 0xFFFF0000u);
+                    uint32_t pl = 0;
+                    if (W2) {
+                        pl = pack_bf16x2(w0 - f0, w1 - f1);
+                        rN[0] += w[2 * hk];
+                        rN[1] += w[2 * hk + 1];
+                    } else {
+                        rN[0] += V8 ? f0 * (1.0f / E4W) : f0;
+                        rN[1] += V8 ? f1 * (1.0f / E4W) : f1;
+                    }
+                    // rows of A: 0-7 the weights, 8-15 their rounding errors
+                    a[2 * hk] = movmatrix_t(ph);
+                    a[2 * hk + 1] = movmatrix_t(pl);
+                }
+                const int kb16 = 16 * warp;
+                if (V8) {
+                    const int wo = 4 * (gid & 3);
+#pragma unroll
+                    for (int m = 0; m < D / 32; ++m) {
+                        const int u = 2 * m + (gid >> 2);
+                        uint32_t wa[4], wb[4] = {0, 0, 0, 0};
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const int r = kb16 + 2 * tq + (kk & 1) + 8 * (kk >> 1);
+                            const int off = r * D + (vswz<NU>(u, r) << 4) + wo;
+                            wa[kk] = *reinterpret_cast<const uint32_t*>(sVa + off);
+                            if (any_rv) wb[kk] = *reinterpret_cast<const uint32_t*>(sVb + off);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t b0 = e4m3_pair_bf16(wa[0], wa[1], i);
+                            uint32_t b1 = e4m3_pair_bf16(wa[2], wa[3], i);
+                            if (any_rv) {
+                                // V~ = Va + Vb / 8 (plane B rows not gathered are zero)
+                                b0 = fma_bf16x2(e4m3_pair_bf16(wb[0], wb[1], i), 0x3e003e00u, b0);
+                                b1 = fma_bf16x2(e4m3_pair_bf16(wb[2], wb[3], i), 0x3e003e00u, b1);
+                            }
+                            mma_16816<false>(acc[4 * m + i], a, b0, b1);
+                        }
+                    }
+                } else {
+                    const int krow = kb16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+#pragma unroll
+                    for (int np = 0; np < NT / 2; ++np) {
+                        uint32_t bv[4];
+                        const int u = 2 * np + (lane >> 4);
+                        ldmatrix_x4_trans(bv, smem_u32(sVa + krow * (2 * D) + (vswz<2 * NU>(u, krow) << 4)));
+                        mma_16816<false>(acc[2 * np], a, bv[0], bv[1]);
+                        mma_16816<false>(acc[2 * np + 1], a, bv[2], bv[3]);
+                    }
+                }
+            } else if (!TRUNC) {
+                // unreachable: a dense tile is all live
+            }
+            (void)sVb;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            s_old[i] = s_new[i];
+            tk_old[i] = tk_new[i];
+        }
+        b_old[0] = b_new[0];
+        b_old[1] = b_new[1];
+        nrow_old = nrow_new;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- epilogue: close the rows over lanes and warps in a fixed order ----
+    float* sO = reinterpret_cast<float*>(smem + L::OFF_G);        // [4 warps][8 rows][D]
+    float* sRed = reinterpret_cast<float*>(smem + L::OFF_RED);     // [2][4 warps][8 rows]
+    int* sCnt = reinterpret_cast<int*>(smem + L::OFF_RED + 512);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        float m = rM[j], n = rN[j];
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            m += __shfl_xor_sync(0xffffffffu, m, o);
+            n += __shfl_xor_sync(0xffffffffu, n, o);
+        }
+        if (gid == 0) {
+            sRed[warp * 8 + 2 * tq + j] = m;
+            sRed[32 + warp * 8 + 2 * tq + j] = n;
+        }
+    }
+    if (lane == 0) {
+        sCnt[warp] = nlive;
+        sCnt[4 + warp] = nref;
+    }
+    // channel of accumulator register (n-tile nt, column 2 tq + e)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            int ch;
+            if (V8) ch = 32 * (nt >> 2) + 4 * (2 * tq + e) + (nt & 3);
+            else ch = 8 * nt + 2 * tq + e;
+            sO[(warp * 8 + gid) * D + ch] = acc[nt][e] + acc[nt][2 + e];
+        }
+    __syncthreads();
+    for (int i = tid; i < G * D; i += DEC_THREADS) {
+        const int g = i / D, c = i % D;
+        float x = 0.f, m = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < 4; ++w2) {
+            x += sO[(w2 * 8 + g) * D + c];
+            m += sRed[w2 * 8 + g];
+        }
+        if (V8) x *= E4O;
+        if (TRUNC && p.vmean) x += m * p.vmean[static_cast<int64_t>(bh) * D + c];
+        p.o_part[(pix * G + g) * D + c] = x;
+    }
+    if (tid < G) {
+        float m = 0.f, n = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < 4; ++w2) {
+            m += sRed[w2 * 8 + tid];
+            n += sRed[32 + w2 * 8 + tid];
+        }
+        p.den_part[pix * G + tid] = n + m;
+    }
+    if (tid == 0) {
+        p.cnt_part[pix * 2] = sCnt[0] + sCnt[1] + sCnt[2] + sCnt[3];
+        p.cnt_part[pix * 2 + 1] = sCnt[4] + sCnt[5] + sCnt[6] + sCnt[7];
+    }
+}
+
+// ---- combine: out = (sum_sp O) * e_v / sum_sp den, in slot order ----------------
+template <int OUT>  // 0 fp32, 1 bf16, 2 fp16
+__global__ void decode_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ den_part,
+                                      const int* __restrict__ cnt_part, const int* __restrict__ seq_lens,
+                                      void* out, float* den, int* counts, int G, int D, int hkv,
+                                      int split, int chunk_keys, float evs) {
+    const int bh = blockIdx.x;
+    int ns = split;
+    if (chunk_keys > 0) {
+        const int slen = seq_lens[bh / hkv];
+        ns = min(split, (slen + chunk_keys - 1) / chunk_keys);
+    }
+    for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+        const int g = i / D;
+        float x = 0.f, d = 0.f;
+        for (int s = 0; s < ns; ++s) {
+            const int64_t pix = static_cast<int64_t>(bh) * split + s;
+            x += o_part[pix * G * D + i];
+            d += den_part[pix * G + g];
+        }
+        const float y = x * evs / d;
+        const int64_t oi = static_cast<int64_t>(bh) * G * D + i;
+        if (OUT == 0) static_cast<float*>(out)[oi] = y;
+        else if (OUT == 1) static_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(y);
+        else static_cast<__half*>(out)[oi] = __float2half_rn(y);
+        if (i % D == 0) den[static_cast<int64_t>(bh) * G + g] = d;
+    }
+    if (threadIdx.x < 2) {
+        int c = 0;
+        for (int s = 0; s < ns; ++s) c += cnt_part[(static_cast<int64_t>(bh) * split + s) * 2 + threadIdx.x];
+        counts[bh * 2 + threadIdx.x] = c;
+    }
+}
+
+// ---- the mass reference ---------------------------------------------------------
+// Z_g = M + log2( sum over the sink and the newest 63 keys (exact) + sum over
+// up to 128 stratum centres (samples) + (samples' sum - their 4 largest) *
+// unscored / (samples - 4) ), all on coarse (plane A) logits.
+constexpr int MASS_ROWS = 192, MASS_STRATA = 128, MASS_TRIM = 4, MASS_WINDOW = 63;
+
+template <int D>
+__global__ void __launch_bounds__(DEC_THREADS) mass_z_kernel(
+    const int8_t* __restrict__ qa, const int8_t* __restrict__ qb, const float* __restrict__ eq,
+    const int8_t* __restrict__ ka, const uint16_t* __restrict__ ek, const int* __restrict__ page_table,
+    const int* __restrict__ seq_lens, int G, int hkv, int ppr, int PS, float* __restrict__ z) {
+    __shared__ __align__(16) int8_t sQ[2][8][D];
+    __shared__ float sS[MASS_ROWS][8];
+    __shared__ int sKey[MASS_ROWS];
+    __shared__ int sClass[MASS_ROWS];   // 0 unused, 1 exact, 2 sample
+    const int bh = blockIdx.x, breq = bh / hkv, h = bh % hkv, tid = threadIdx.x;
+    const int n = seq_lens[breq];
+    for (int i = tid; i < G * D / 4; i += DEC_THREADS) {
+        reinterpret_cast<uint32_t*>(&sQ[0][0][0])[i] = reinterpret_cast<const uint32_t*>(qa + static_cast<int64_t>(bh) * G * D)[i];
+        reinterpret_cast<uint32_t*>(&sQ[1][0][0])[i] = reinterpret_cast<const uint32_t*>(qb + static_cast<int64_t>(bh) * G * D)[i];
+    }
+    const int lo = n - MASS_WINDOW;
+    for (int r = tid; r < MASS_ROWS; r += DEC_THREADS) {
+        int key = 0, cls = 0;
+        if (r == 0) {
+            cls = n >= 1 ? 1 : 0;
+        } else if (r <= MASS_WINDOW) {
+            key = n - r;
+            cls = key >= 1 ? 1 : 0;
+        } else {
+            const int j = r - 1 - MASS_WINDOW;
+            key = static_cast<int>((static_cast<int64_t>(2 * j + 1) * n) / (2 * MASS_STRATA));
+            const int prev = j > 0 ? static_cast<int>((static_cast<int64_t>(2 * j - 1) * n) / (2 * MASS_STRATA)) : -1;
+            cls = (key >= 1 && key < lo && key != prev) ? 2 : 0;
+        }
+        sKey[r] = key;
+        sClass[r] = cls;
+    }
+    __syncthreads();
+    constexpr int NU = D / 16;
+    for (int r = tid; r < MASS_ROWS; r += DEC_THREADS) {
+        if (sClass[r] == 0) continue;
+        const int pos = sKey[r];
+        const int64_t prow = (static_cast<int64_t>(__ldg(page_table + static_cast<int64_t>(breq) * ppr + pos / PS)) * hkv + h) * PS + pos % PS;
+        const int off = pos % PS;
+        int c1[8], c2[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) c1[g] = c2[g] = 0;
+        for (int u = 0; u < NU; ++u) {
+            const uint4 kw = *reinterpret_cast<const uint4*>(ka + prow * D + ((u ^ swz<D>(off)) << 4));
+            const uint32_t kk[4] = {kw.x, kw.y, kw.z, kw.w};
+            for (int g = 0; g < G; ++g) {
+                const uint4 a = *reinterpret_cast<const uint4*>(&sQ[0][g][u * 16]);
+                const uint4 b = *reinterpret_cast<const uint4*>(&sQ[1][g][u * 16]);
+                c1[g] = __dp4a(static_cast<int>(kk[0]), static_cast<int>(a.x), c1[g]);
+                c1[g] = __dp4a(static_cast<int>(kk[1]), static_cast<int>(a.y), c1[g]);
+                c1[g] = __dp4a(static_cast<int>(kk[2]), static_cast<int>(a.z), c1[g]);
+                c1[g] = __dp4a(static_cast<int>(kk[3]), static_cast<int>(a.w), c1[g]);
+                c2[g] = __dp4a(static_cast<int>(kk[0]), static_cast<int>(b.x), c2[g]);
+                c2[g] = __dp4a(static_cast<int>(kk[1]), static_cast<int>(b.y), c2[g]);
+                c2[g] = __dp4a(static_cast<int>(kk[2]), static_cast<int>(b.z), c2[g]);
+                c2[g] = __dp4a(static_cast<int>(kk[3]), static_cast<int>(b.w), c2[g]);
+            }
+        }
+        const float ekf = bf16_bits_to_float(ek[prow]) * (1.0f / 256.0f);
+        for (int g = 0; g < G; ++g)
+            sS[r][g] = static_cast<float>(c1[g] * 256 + c2[g]) * (eq[static_cast<int64_t>(bh) * G + g] * ekf);
+    }
+    __syncthreads();
+    // one warp per query row (rows g = warp, warp + 4)
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int g = warp; g < G; g += DEC_THREADS / 32) {
+        float mx = -INFINITY;
+        for (int r = lane; r < MASS_ROWS; r += 32)
+            if (sClass[r]) mx = fmaxf(mx, sS[r][g]);
+        mx = warp_max(mx);
+        float se = 0.f, ss = 0.f;
+        int ne = 0, nsamp = 0;
+        float d[MASS_ROWS / 32];
+#pragma unroll
+        for (int k = 0; k < MASS_ROWS / 32; ++k) {
+            const int r = lane + 32 * k;
+            d[k] = -1.f;
+            if (sClass[r] == 1) {
+                se += exp2f(sS[r][g] - mx);
+                ne++;
+            } else if (sClass[r] == 2) {
+                d[k] = exp2f(sS[r][g] - mx);
+                ss += d[k];
+                nsamp++;
+            }
+        }
+        se = warp_sum(se);
+        ss = warp_sum(ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ne += __shfl_xor_sync(0xffffffffu, ne, o);
+            nsamp += __shfl_xor_sync(0xffffffffu, nsamp, o);
+        }
+        float mass = se + ss;
+        const int uns = n - ne - nsamp;
+        if (nsamp > MASS_TRIM && uns > 0) {
+            float top = 0.f;
+            for (int it = 0; it < MASS_TRIM; ++it) {
+                float best = -1.f;
+                int bk = -1;
+#pragma unroll
+                for (int k = 0; k < MASS_ROWS / 32; ++k)
+                    if (d[k] > best) { best = d[k]; bk = k; }
+                float wbest = warp_max(best);
+                // the lowest lane holding the maximum gives it up
+                const unsigned who = __ballot_sync(0xffffffffu, best == wbest);
+                if (lane == __ffs(who) - 1) {
+#pragma unroll
+                    for (int k = 0; k < MASS_ROWS / 32; ++k)
+                        if (k == bk) d[k] = -1.f;
+                }
+                top += wbest;
+            }
+            mass += (ss - top) * static_cast<float>(uns) / static_cast<float>(nsamp - MASS_TRIM);
+        }
+        if (lane == 0) z[static_cast<int64_t>(bh) * G + g] = mx + log2f(mass);
+    }
+}
+
+}  // namespace fold
+
+using namespace fold;
+
+namespace {
+
+template <int D, bool V8, bool W2, bool TRUNC>
+int launch_decode(const DecodeParams& p, cudaStream_t st) {
+    using L = DecSmem<D, V8>;
+    auto kern = decode_kernel<D, V8, W2, TRUNC>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES);
+    kern<<<p.nbh * p.split, DEC_THREADS, L::BYTES, st>>>(p);
+    return check_launch("fold_decode_run");
+}
+
+template <int D, bool V8>
+int launch_decode_d(const DecodeParams& p, int w2, cudaStream_t st) {
+    if (p.truncate) return w2 ? launch_decode<D, V8, true, true>(p, st) : launch_decode<D, V8, false, true>(p, st);
+    return w2 ? launch_decode<D, V8, true, false>(p, st) : launch_decode<D, V8, false, false>(p, st);
+}
+
+}  // namespace
+
+extern "C" int fold_mass_z(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                           const void* ek, const int32_t* page_table, const int32_t* seq_lens,
+                           int n_groups, int group, int n_kv_heads, int head_dim,
+                           int pages_per_request, int page_size, float* z, void* stream) {
+    FOLD_CHECK_ARG(qa && qb && eq && ka && ek && page_table && seq_lens && z, "fold_mass_z: null pointer");
+    FOLD_CHECK_ARG(group >= 1 && group <= 8, "a row group of %d rows: 1..8 are supported", group);
+    FOLD_CHECK_ARG(head_dim == 64 || head_dim == 128, "head_dim %d: the decode takes 64 or 128", head_dim);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint16_t* ekp = static_cast<const uint16_t*>(ek);
+    if (head_dim == 128)
+        mass_z_kernel<128><<<n_groups, DEC_THREADS, 0, st>>>(qa, qb, eq, ka, ekp, page_table, seq_lens, group, n_kv_heads, pages_per_request, page_size, z);
+    else
+        mass_z_kernel<64><<<n_groups, DEC_THREADS, 0, st>>>(qa, qb, eq, ka, ekp, page_table, seq_lens, group, n_kv_heads, pages_per_request, page_size, z);
+    return check_launch("fold_mass_z");
+}
+
+extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                               const int8_t* kb, const void* ek, const void* va, const void* vb,
+                               const float* vmean, const float* z, const float* cut,
+                               const int32_t* page_table, const int32_t* seq_lens,
+                               const int32_t* order, int n_groups, int group, int n_kv_heads,
+                               int head_dim, int pages_per_request, int page_size, int split,
+                               int chunk_keys, int truncate, int weight_terms, float refine_k,
+                               float refine_v, const float* refine_bands, float v_scale,
+                               float* o_part, float* den_part, int32_t* cnt_part, void* out,
+                               int out_dtype, float* den, int32_t* counts, int32_t* status,
+                               void* stream) {
+    FOLD_CHECK_ARG(qa && qb && eq && ka && kb && ek && va && z && cut && page_table && seq_lens &&
+                       o_part && den_part && cnt_part && out && den && counts && status,
+                   "fold_decode_run: null pointer");
+    FOLD_CHECK_ARG(group >= 1 && group <= 8, "a row group of %d rows: 1..8 are supported", group);
+    FOLD_CHECK_ARG(head_dim == 64 || head_dim == 128, "head_dim %d: the decode takes 64 or 128", head_dim);
+    FOLD_CHECK_ARG(page_size >= 16 && page_size % 16 == 0 && (page_size % 64 == 0 || 64 % page_size == 0),
+                   "page_size %d: a multiple of 64, or 16 or 32", page_size);
+    FOLD_CHECK_ARG(split >= 1, "split %d", split);
+    FOLD_CHECK_ARG(chunk_keys >= 0 && chunk_keys % 64 == 0, "chunk %d is not a multiple of 64", chunk_keys);
+    FOLD_CHECK_ARG(weight_terms == 1 || weight_terms == 2, "weight_terms %d", weight_terms);
+    FOLD_CHECK_ARG(out_dtype >= 0 && out_dtype <= 2, "out_dtype %d", out_dtype);
+    DecodeParams p;
+    p.qa = qa; p.qb = qb; p.eq = eq; p.ka = ka; p.kb = kb;
+    p.ek = static_cast<const uint16_t*>(ek);
+    p.va = static_cast<const uint8_t*>(va); p.vb = static_cast<const uint8_t*>(vb);
+    p.vmean = vmean; p.z = z; p.cut = cut;
+    p.page_table = page_table; p.seq_lens = seq_lens; p.order = order;
+    p.o_part = o_part; p.den_part = den_part; p.cnt_part = cnt_part;
+    p.nbh = n_groups; p.G = group; p.hkv = n_kv_heads; p.ppr = pages_per_request;
+    p.page_size = page_size; p.split = split; p.chunk_keys = chunk_keys; p.truncate = truncate;
+    p.rk = refine_k; p.rv = refine_v;
+    p.banded = refine_bands != nullptr;
+    if (refine_bands) {
+        p.band_e0 = refine_bands[0]; p.band_e1 = refine_bands[1];
+        p.rk1 = refine_bands[2]; p.rk2 = refine_bands[3]; p.rv1 = refine_bands[4]; p.rv2 = refine_bands[5];
+    } else {
+        p.band_e0 = p.band_e1 = p.rk1 = p.rk2 = p.rv1 = p.rv2 = 0.f;
+    }
+    p.status = status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool v8 = vb != nullptr;
+    int rc;
+    if (head_dim == 128) rc = v8 ? launch_decode_d<128, true>(p, weight_terms == 2, st) : launch_decode_d<128, false>(p, weight_terms == 2, st);
+    else rc = v8 ? launch_decode_d<64, true>(p, weight_terms == 2, st) : launch_decode_d<64, false>(p, weight_terms == 2, st);
+    if (rc) return rc;
+    const int threads = 256;
+#define FOLD_COMBINE(OUT) decode_combine_kernel<OUT><<<n_groups, threads, 0, st>>>(o_part, den_part, cnt_part, seq_lens, out, den, counts, group, head_dim, n_kv_heads, split, chunk_keys, v_scale)
+    if (out_dtype == 0) FOLD_COMBINE(0);
+    else if (out_dtype == 1) FOLD_COMBINE(1);
+    else FOLD_COMBINE(2);
+#undef FOLD_COMBINE
+    return check_launch("fold_decode_combine");
+}

@@ -1,0 +1,106 @@
+"""The decode's host side: validation, buffers, the launch closure.
+
+`prepare_fold_decode` mirrors the reference's kernel-level entry
+(src/fold_attention/decode/launch.py:380-500) for the single-level paged
+decode: already-quantised planes plus an explicit reference (`reference=
+"given"`) or the mass estimate (`reference="mass"`). The prepared launch
+returns `(out, den, counts)`, the same tensors every call.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _lib
+from ..utils import Launch
+
+P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_lib.register("fold_mass_z", [P, P, P, P, P, P, P, I, I, I, I, I, I, P, P])
+_lib.register(
+    "fold_decode_run",
+    [P] * 14 + [I] * 10 + [F, F, P, F] + [P, P, P, P, I, P, P, P, P],
+)
+
+_OUT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+class DecodeLaunch(Launch):
+    pass
+
+
+def mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z):
+    """Each query row's estimated log-sum-exp (base 2) into `z` (NBH, G)."""
+    NBH, G, D = qa.shape
+    _lib.call(
+        "fold_mass_z", qa.data_ptr(), qb.data_ptr(), eq.data_ptr(), ka.data_ptr(), ek.data_ptr(),
+        page_table.data_ptr(), seq_lens.data_ptr(), NBH, G, n_kv_heads, D, page_table.shape[1],
+        int(page_size), z.data_ptr(), _lib.stream(qa.device),
+    )
+    return z
+
+
+def prepare_fold_decode(
+    qa, qb, eq, ka, kb, ek, v, z, cut, *,
+    split=1, truncate=False, refine_k=10.0, refine_v=10.0, v8=False, v2=None, v_scale=1.0,
+    vmean=None, page_table, page_size, seq_lens, n_kv_heads, reference="given", weight_terms=1,
+    order=None, out_dtype=torch.float32, refine_bands=(), chunk_keys=0, out=None,
+):
+    """Bind one decode over a paged cache and return its launch.
+
+    `qa`, `qb` int8 `(NBH, G, D)` and `eq` `(NBH, G)` are Q's planes and
+    scales; `ka`, `kb`, `ek`, `v`, `v2` the pool; `z` `(NBH, G)` each row's
+    reference (written by the launch when `reference="mass"`) and `cut` its
+    depth below `z` under which a key is dropped (`truncate`). Calling the
+    launch returns `(out (NBH, G, D), den (NBH, G), counts (NBH, 2))`.
+    """
+    NBH, G, D = qa.shape
+    if G > 8:
+        raise NotImplementedError(f"a row group of {G} rows: 1..8 are supported")
+    if D not in (64, 128):
+        raise NotImplementedError(f"head_dim {D}: the decode takes 64 or 128")
+    if v8 and v2 is None:
+        raise ValueError("an 8-bit V has two planes: pass v2")
+    if not v8 and v.dtype != torch.bfloat16:
+        raise ValueError("a 16-bit V cache is bf16")
+    if reference not in ("given", "mass"):
+        raise ValueError("reference is 'given' or 'mass'")
+    if chunk_keys % 64:
+        raise ValueError(f"chunk={chunk_keys} is not a multiple of 64")
+    dev = qa.device
+    split = int(split)
+    o_part = torch.empty((NBH * split, G, D), device=dev, dtype=torch.float32)
+    den_part = torch.empty((NBH * split, G), device=dev, dtype=torch.float32)
+    cnt_part = torch.empty((NBH * split, 2), device=dev, dtype=torch.int32)
+    out_t = torch.empty((NBH, G, D), device=dev, dtype=out_dtype) if out is None else out
+    den = torch.empty((NBH, G), device=dev, dtype=torch.float32)
+    counts = torch.empty((NBH, 2), device=dev, dtype=torch.int32)
+    status = torch.zeros(1, device=dev, dtype=torch.int32)
+    bands = (ctypes.c_float * 6)(*refine_bands) if refine_bands else None
+    fixed = (
+        qa.data_ptr(), qb.data_ptr(), eq.data_ptr(), ka.data_ptr(), kb.data_ptr(), ek.data_ptr(),
+        v.data_ptr(), _lib.ptr(v2) if v8 else None, _lib.ptr(vmean) if truncate else None,
+        z.data_ptr(), cut.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(), _lib.ptr(order),
+        NBH, G, int(n_kv_heads), D, page_table.shape[1], int(page_size), split, int(chunk_keys),
+        int(bool(truncate)), int(weight_terms), float(refine_k), float(refine_v),
+        ctypes.addressof(bands) if bands is not None else None, float(v_scale),
+        o_part.data_ptr(), den_part.data_ptr(), cnt_part.data_ptr(),
+    )
+    tail = (den.data_ptr(), counts.data_ptr(), status.data_ptr())
+
+    def run(out=None):
+        o = out_t if out is None else out
+        if reference == "mass":
+            mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z)
+        _lib.call("fold_decode_run", *fixed, o.data_ptr(), _OUT[o.dtype], *tail, _lib.stream(dev))
+        return o, den, counts
+
+    launch = DecodeLaunch(
+        run,
+        (qa, qb, eq, ka, kb, ek, v, v2, vmean, z, cut, page_table, seq_lens, order, o_part,
+         den_part, cnt_part, out_t, den, counts, status, bands),
+    )
+    launch.z = z
+    launch.status = status
+    return launch

@@ -1,5 +1,320 @@
-"""Placeholder import target; replaced by the serving cache below."""
+"""One attention layer's serving state: a causal prefill, then the decode over
+a quantised paged cache. Same constructor, methods and tensor attributes as
+the reference's `FoldKVCache` (src/fold_attention/kv_cache.py:65-963) for the
+single-level serving path; every kernel runs in libfold_b200.
+
+Every key carries its own scale, so a key appended later is quantised as
+precisely as the prompt's and nothing is reserved for it. An 8-bit V takes
+one power of two for the layer, fixed at prefill (`v_headroom`).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .backward.launch import attention_forward
+from .decode import write
+from .decode.heuristics import (
+    pick_split,
+    refine_bands_for,
+    refine_for,
+    tail_rank_for,
+    weight_terms_for,
+)
+from .decode.launch import mass_z, prepare_fold_decode
+
+BN = 64  # keys per decode tile: a fixed `chunk` is a multiple of it
 
 
-class FoldKVCache:  # pragma: no cover - replaced
-    pass
+class FoldKVCache:
+    """A paged, quantised KV cache for `batch` requests of one layer, and the
+    decode attention over it.
+
+    `prefill` takes the prompts, packed, and returns their causal attention;
+    `decode` appends one token per request and returns its attention over
+    everything so far (`append` and `attend` do the two halves).
+
+    `depth` is the truncation depth: a key whose weight is under `2^-depth`
+    of its row's mass is dropped (its mass re-enters at V's mean), and None
+    keeps every key. The reference is each row's log-sum-exp, estimated every
+    step from the cache and the step's query alone. `v8` stores V as two e4m3
+    planes rather than bf16 under one power-of-two scale: `v_scale` if given,
+    otherwise set by the prefill from the batch's largest value.
+    `refine_k`, `refine_v` and `weight_terms` trade accuracy for time and
+    default to the reference's gates. `split` fixes the CTAs per row group and
+    `chunk` the keys per split (a multiple of 64); with either, a request's
+    output depends on the request alone.
+
+    The decode tail (`tail` >= 0, a rank-r K->V model of dropped mass on a
+    bf16 V) and `check_range` are not built: `tail` must resolve to None.
+    """
+
+    def __init__(
+        self,
+        batch,
+        n_heads,
+        n_kv_heads,
+        head_dim,
+        max_len,
+        *,
+        depth=None,
+        v8=False,
+        page_size=256,
+        split=None,
+        tail="auto",
+        refine_k=None,
+        refine_v=None,
+        weight_terms=None,
+        v_headroom=2.0,
+        v_scale=None,
+        check_range=False,
+        chunk=None,
+        device="cuda",
+    ):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} query heads do not group over {n_kv_heads} KV heads")
+        self.batch, self.n_heads, self.n_kv_heads, self.head_dim = batch, n_heads, n_kv_heads, head_dim
+        self.group = n_heads // n_kv_heads
+        self.n_groups = batch * n_kv_heads
+        self.page_size = page_size
+        self.max_len = max_len
+        self.depth = depth
+        self.v8 = bool(v8)
+        self.v_headroom = float(v_headroom)
+        self.split = split
+        self.device = torch.device(device)
+        if head_dim not in (64, 128):
+            raise NotImplementedError(f"head_dim {head_dim}: the cache takes 64 or 128")
+        if self.group > 8:
+            raise NotImplementedError(f"a row group of {self.group} rows: 1..8 are supported")
+        if page_size < 16 or page_size % 16 or (page_size % 64 and 64 % page_size):
+            raise ValueError(f"page_size={page_size}: a multiple of 64, or 16 or 32")
+
+        dev, D, HKV, PS = self.device, head_dim, n_kv_heads, page_size
+        pages = -(-max_len // PS)
+        rows = batch * pages * HKV * PS
+        self.page_table = torch.arange(batch * pages, device=dev, dtype=torch.int32).view(batch, pages)
+        self.ka = torch.zeros((rows, D), device=dev, dtype=torch.int8)
+        self.kb = torch.zeros_like(self.ka)
+        if self.v8:
+            self.va = torch.zeros((rows, D), device=dev, dtype=torch.float8_e4m3fn)
+            self.vb = torch.zeros_like(self.va)
+        else:
+            self.va = torch.zeros((rows, D), device=dev, dtype=torch.bfloat16)
+            self.vb = None
+        self.ek = torch.zeros((rows,), device=dev, dtype=torch.bfloat16)
+        if v_scale is not None and 2.0 ** round(math.log2(v_scale)) != v_scale:
+            raise ValueError(f"v_scale={v_scale} is not a power of two")
+        self._fixed_v_scale = v_scale
+        self._v_scale = float(v_scale) if (self.v8 and v_scale is not None) else 1.0
+        self.seq_lens = torch.zeros((batch,), device=dev, dtype=torch.int32)
+        self.lens = [0] * batch
+        self.order = torch.arange(self.n_groups, device=dev, dtype=torch.int32)
+        self.vsum = torch.zeros((self.n_groups, D), device=dev, dtype=torch.float32)
+        self.vmean = torch.zeros_like(self.vsum)
+        self.qa = torch.zeros((self.n_groups, self.group, D), device=dev, dtype=torch.int8)
+        self.qb = torch.zeros_like(self.qa)
+        self.eq = torch.ones((self.n_groups, self.group), device=dev, dtype=torch.float32)
+        self.z = torch.zeros((self.n_groups, self.group), device=dev, dtype=torch.float32)
+        # each row's depth below its reference
+        self.cut = torch.full_like(self.z, 1e4 if depth is None else float(depth))
+        if tail == "auto":
+            tail = tail_rank_for(D, self.group, self.v8) if depth is not None else -1
+            if tail >= 0:
+                tail = None  # the K-predicted tail is not built: dropped mass re-enters at V's mean
+        self.tail_rank = -1 if tail is None else int(tail)
+        if self.tail_rank >= 0:
+            if depth is None:
+                raise ValueError("the tail re-enters truncated mass, and depth=None truncates nothing")
+            if self.v8:
+                raise ValueError("the decode tail needs a bf16 V cache; pass tail=None with v8")
+            raise NotImplementedError("the decode tail is not built: pass tail=None")
+        self._refine_k_fixed = refine_k
+        self._refine_v_fixed = refine_v
+        if check_range:
+            raise NotImplementedError("check_range is not built")
+        self.check_range = False
+        if chunk is not None and (split is not None or chunk % BN):
+            raise ValueError(f"chunk={chunk} is a multiple of {BN} and replaces split")
+        self.chunk = chunk
+        self.den = None
+        self.counts = None
+        self.weight_terms = weight_terms_for(depth) if weight_terms is None else int(weight_terms)
+        self._launches = {}
+
+    @property
+    def v_scale(self) -> float:
+        """V's scale. The prefill leaves it on the device, and the first read
+        after it is where the host takes it."""
+        if torch.is_tensor(self._v_scale):
+            self._v_scale = float(self._v_scale)
+        return self._v_scale
+
+    def prefill(self, q, k, v, cu_seqlens, max_seqlen=None):
+        """Causal attention over `batch` prompts packed along the first axis.
+
+        `q` is `(total, H, D)`, `k` and `v` `(total, H_KV, D)`, `cu_seqlens`
+        `(batch + 1,)` int32 on the device. Returns `(total, H, D)` in q's
+        dtype. The prompts replace the cache's contents.
+        """
+        B = self.batch
+        if cu_seqlens.shape != (B + 1,):
+            raise ValueError(f"cu_seqlens is ({B + 1},) for a batch of {B}")
+        lens = torch.diff(cu_seqlens).tolist()
+        if min(lens) < 1 or max(lens) > self.max_len:
+            raise ValueError(f"prompt lengths {min(lens)}..{max(lens)} are not in 1..{self.max_len}")
+        if max_seqlen is None:
+            max_seqlen = max(lens)
+        out, _ = attention_forward(
+            q, k, v, causal=True, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen,
+            softmax_scale=1.0 / math.sqrt(self.head_dim),
+        )
+        self.write_prompt(k, v, cu_seqlens, lens)
+        return out
+
+    def write_prompt(self, k, v, cu_seqlens, lens=None):
+        """Quantise packed prompts' K and V into the cache, which they replace,
+        without computing their attention. `lens` are the host lengths
+        `cu_seqlens` describes."""
+        if lens is None:
+            lens = torch.diff(cu_seqlens).tolist()
+        if len(lens) != self.batch:
+            raise ValueError(f"{len(lens)} prompts for a batch of {self.batch}")
+        if min(lens) < 1 or max(lens) > self.max_len:
+            raise ValueError(f"prompt lengths {min(lens)}..{max(lens)} are not in 1..{self.max_len}")
+        self._v_scale = write.write_prompt(
+            k, v, lens, self.page_table, self.page_size, self.ka, self.kb, self.va, self.vb,
+            self.ek, self.vsum, self.vmean, v_headroom=self.v_headroom,
+            v_scale=self._fixed_v_scale if self.v8 else None,
+        )
+        self.seq_lens.copy_(torch.tensor(lens, dtype=torch.int32), non_blocking=True)
+        self.lens = list(lens)
+        self._set_order()
+        self._launches.clear()
+
+    def append(self, k, v):
+        """Write one token per request, `(batch, H_KV, D)` each, at its length."""
+        if max(self.lens) >= self.max_len:
+            raise ValueError(f"a request is at max_len={self.max_len}")
+        self._step(None, k, v)
+        self.lens = [x + 1 for x in self.lens]
+
+    def attend(self, q, split=None):
+        """Attention of `q` `(batch, H, D)` over the cache as it stands."""
+        self._step(q, None, None)
+        return self._run(q, split)
+
+    def decode(self, q, k, v, split=None):
+        """One decode step: append `k`, `v` `(batch, H_KV, D)` and attend with
+        `q` `(batch, H, D)`."""
+        if max(self.lens) >= self.max_len:
+            raise ValueError(f"a request is at max_len={self.max_len}")
+        self._step(q, k, v)
+        self.lens = [x + 1 for x in self.lens]
+        return self._run(q, split)
+
+    # ---- internals -------------------------------------------------------
+
+    def _set_order(self):
+        """Give the longest requests the lowest grid slots: a long request
+        placed late has nothing behind it to backfill its tail. It changes no
+        bit, since the slot only chooses which row group a CTA takes."""
+        rank = sorted(range(self.batch), key=lambda b: (-self.lens[b], b))
+        order = [r * self.n_kv_heads + h for r in rank for h in range(self.n_kv_heads)]
+        self.order.copy_(torch.tensor(order, dtype=torch.int32), non_blocking=True)
+
+    def _auto_split(self):
+        mean = sum(self.lens) / self.batch
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        return pick_split(self.n_groups, max(1, int(mean)), max_len=max(self.lens), sms=sms)
+
+    def _resolve_split(self, split):
+        if self.chunk is not None:
+            # every request is cut at the same key offsets whatever its batch;
+            # the batch's longest request only sets how many splits run
+            return max(1, -(-max(self.lens) // self.chunk))
+        if split is None:
+            split = self.split
+        if split is None:
+            split = self._auto_split()
+        return split
+
+    def _banded(self):
+        """Whether the kernel picks the dense gates from each request's length."""
+        return self.depth is None and self._refine_k_fixed is None and self._refine_v_fixed is None
+
+    def _refine(self, seq_len=None):
+        if self._banded():
+            seq_len = 1
+        elif seq_len is None:
+            seq_len = max(self.lens)
+        rk, rv = refine_for(
+            self.depth, self.v8, seq_len=seq_len, head_dim=self.head_dim, group=self.group,
+            tail=self.tail_rank >= 0,
+        )
+        if self._refine_k_fixed is not None:
+            rk = self._refine_k_fixed
+        if self._refine_v_fixed is not None:
+            rv = self._refine_v_fixed
+        return rk, rv
+
+    def refine_gates(self):
+        """Each request's refine gates at its current length, `(refine_k,
+        refine_v)` as `(batch,)` float32 depths below Z."""
+        rk, rv = self._refine()
+        n = torch.tensor(self.lens, dtype=torch.float32)
+        if not self._banded():
+            return torch.full_like(n, float(rk)), torch.full_like(n, float(rv))
+        e0, e1, rk1, rk2, rv1, rv2 = refine_bands_for(self.v8, head_dim=self.head_dim, group=self.group)
+        rk_t = torch.where(n > e1, rk2, torch.where(n > e0, rk1, float(rk)))
+        rv_t = torch.where(n > e1, rv2, torch.where(n > e0, rv1, float(rv)))
+        return rk_t, rv_t
+
+    def _launch(self, split, out_dtype):
+        refine = self._refine()
+        key = (split, out_dtype, refine)
+        if key not in self._launches:
+            truncate = self.depth is not None
+            self._launches[key] = prepare_fold_decode(
+                self.qa, self.qb, self.eq, self.ka, self.kb, self.ek, self.va, self.z, self.cut,
+                split=split, truncate=truncate, refine_k=refine[0], refine_v=refine[1],
+                v8=self.v8, v2=self.vb, v_scale=self.v_scale,
+                vmean=self.vmean if truncate else None, page_table=self.page_table,
+                page_size=self.page_size, seq_lens=self.seq_lens, n_kv_heads=self.n_kv_heads,
+                reference="given", weight_terms=self.weight_terms, order=self.order,
+                out_dtype=out_dtype,
+                refine_bands=(
+                    refine_bands_for(self.v8, head_dim=self.head_dim, group=self.group)
+                    if self._banded() else ()
+                ),
+                chunk_keys=self.chunk or 0,
+            )
+        return self._launches[key]
+
+    def _step(self, q, k, v):
+        """The step's front: Q's planes, the appended token, then each row's
+        reference Z from the cache as it now stands."""
+        qf = None if q is None else q.reshape(-1, self.head_dim)
+        if k is not None and (k.shape != (self.batch, self.n_kv_heads, self.head_dim) or v.shape != k.shape):
+            raise ValueError(f"k and v are ({self.batch}, {self.n_kv_heads}, {self.head_dim})")
+        if qf is not None and qf.shape[0] != self.batch * self.n_heads:
+            raise ValueError(f"q is ({self.batch}, {self.n_heads}, {self.head_dim})")
+        write.step(
+            qf, k, v, self.qa.view(-1, self.head_dim), self.qb.view(-1, self.head_dim),
+            self.eq.view(-1), self.ek, self.page_table, self.page_size, self.seq_lens,
+            self.ka, self.kb, self.va, self.vb, self.v_scale, self.vsum, self.vmean, self.seq_lens,
+        )
+        if q is not None:
+            mass_z(self.qa, self.qb, self.eq, self.ka, self.ek, self.page_table, self.page_size,
+                   self.seq_lens, self.n_kv_heads, self.z)
+
+    def _run(self, q, split):
+        split = self._resolve_split(split)
+        shape = (self.batch, self.n_heads, self.head_dim)
+        out_dtype = q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.float32
+        # a fresh tensor per step: the caller may hold every step's output
+        out = torch.empty((self.n_groups, self.group, self.head_dim), device=q.device, dtype=out_dtype)
+        o, self.den, self.counts = self._launch(split, out_dtype).run(out=out)
+        return o.view(shape).to(q.dtype)

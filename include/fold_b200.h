@@ -69,6 +69,42 @@ int fold_step_append(const void* q, const void* k, const void* v, int is_f16, in
                      void* va, void* vb, void* ek, float v_scale, float* vsum, float* vmean,
                      void* stream);
 
+/* ---- Path B: decode ------------------------------------------------------- */
+
+/* The mass reference: each query row's log-sum-exp estimate Z (base 2) from
+ * the sink, the newest 63 keys and up to 128 stratum centres, on coarse
+ * (plane A) logits. Replaces: src/fold_attention/decode/reference.py:120-535
+ * (mass_estimate, mass_z) and the mass half of decode/front.py:255-471.
+ *   qa, qb int8 (n_groups, group, head_dim); eq, z fp32 (n_groups, group) */
+int fold_mass_z(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                const void* ek, const int32_t* page_table, const int32_t* seq_lens, int n_groups,
+                int group, int n_kv_heads, int head_dim, int pages_per_request, int page_size,
+                float* z, void* stream);
+
+/* Split-KV decode over the paged cache and its additive combine.
+ * Replaces: src/fold_attention/decode/launch.py:509-1252 (_prepare, single
+ * level), decode/kernel.py:95-1562 and decode/combine.py:10-162.
+ *   z, cut        fp32 (n_groups, group): the reference and the depth below it
+ *                 under which a key is cut (used when truncate != 0)
+ *   vmean         fp32 (n_groups, head_dim) or NULL: where dropped mass re-enters
+ *   order         int32 (n_groups,) grid slot -> row group, or NULL
+ *   split         CTAs per row group; chunk_keys > 0 fixes the keys per split
+ *   refine_bands  host: (edge0, edge1, rk1, rk2, rv1, rv2) or NULL
+ *   o_part        fp32 (n_groups*split, group, head_dim) scratch; den_part
+ *                 (n_groups*split, group); cnt_part int32 (n_groups*split, 2)
+ *   out           (n_groups, group, head_dim) as out_dtype: 0 fp32, 1 bf16, 2 fp16
+ *   den           fp32 (n_groups, group); counts int32 (n_groups, 2): live, refined
+ *   status        int32[1]: set non-zero if a device-side wait ran out */
+int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                    const int8_t* kb, const void* ek, const void* va, const void* vb,
+                    const float* vmean, const float* z, const float* cut,
+                    const int32_t* page_table, const int32_t* seq_lens, const int32_t* order,
+                    int n_groups, int group, int n_kv_heads, int head_dim, int pages_per_request,
+                    int page_size, int split, int chunk_keys, int truncate, int weight_terms,
+                    float refine_k, float refine_v, const float* refine_bands /* host */,
+                    float v_scale, float* o_part, float* den_part, int32_t* cnt_part, void* out,
+                    int out_dtype, float* den, int32_t* counts, int32_t* status, void* stream);
+
 /* ---- Path A: deterministic attention backward ------------------------------ */
 
 #define FOLD_BWD_KERNEL_AUTO 0  /* tcgen05 where it applies, else mma.sync */
