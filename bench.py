@@ -1,0 +1,314 @@
+"""Benchmark of the deterministic causal attention backward (and, as extra
+keys, the paged decode) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One JSON line on stdout. A step is one backward (preprocess + main loop +
+postprocess) over BASELINE config 2: batch 4, seqlen 8192, 32 query / 32 KV
+heads, head_dim 128, bf16, causal; inputs iid N(0,1) with 1/sqrt(D) on q, O and
+LSE from the library's own forward, computed before the timed region. At
+N > 1 every rank runs that workload on its own shard (weak scaling; the path
+shards over batch x KV head with no collective on the data path).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+CFG = dict(B=4, S=8192, H=32, HKV=32, D=128)
+WORKLOAD = "config2 causal det. backward B4 S8192 H32/32 D128 bf16"
+METRIC = "det. causal bwd TFLOP/s"
+
+
+def flops(B, S, H, D):
+    """5 GEMMs of the causal half: 5 * B * H * S^2 * D (FA convention)."""
+    return 5.0 * B * H * S * S * D
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(bf16=d["bf16_tflops_sustained"], bf16_burst=d["bf16_tflops"], hbm=d["hbm_gbs"],
+                    which="measured")
+    return dict(bf16=1400.0, bf16_burst=1590.0, hbm=6650.0, which="fallback")
+
+
+class Clocks:
+    """Sample SM clocks and throttle reasons with nvidia-smi while timing."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return None
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for ts, r in self.rows if t0 - 0.05 <= ts <= t1 + 0.15] or [r for _, r in self.rows[-3:]]
+        if not rows:
+            return None
+        mhz = sorted(int(r[0]) for r in rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in rows for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return dict(sm_mhz=mhz[len(mhz) // 2] if mhz else None,
+                    sm_max_mhz=int(rows[0][1]) if rows[0][1].isdigit() else None,
+                    reasons=reasons, samples=len(rows))
+
+
+def make_inputs(cfg, device, seed):
+    B, S, H, HKV, D = (cfg[k] for k in ("B", "S", "H", "HKV", "D"))
+    g = torch.Generator(device=device).manual_seed(seed)
+    q = (torch.randn(B, S, H, D, device=device, generator=g) / D**0.5).bfloat16()
+    k = torch.randn(B, S, HKV, D, device=device, generator=g).bfloat16()
+    v = torch.randn(B, S, HKV, D, device=device, generator=g).bfloat16()
+    do = torch.randn(B, S, H, D, device=device, generator=g).bfloat16()
+    return q, k, v, do
+
+
+def time_backward(cfg, device, steps, warmup, seed, dist):
+    """(ms per step, main-kernel ms per launch, launches per step, run)."""
+    from fold_attention_b200.backward import attention_forward, prepare_backward
+
+    q, k, v, do = make_inputs(cfg, device, seed)
+    o, lse = attention_forward(q, k, v, causal=True)
+    tr = lambda x: x.transpose(1, 2)  # noqa: E731
+    run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True)
+    for _ in range(warmup):
+        run()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    t0 = time.time()
+    for i in range(steps):
+        ev[i][0].record()
+        run.run_phase(1)
+        ev[i][1].record()
+        run.run_phase(2)
+        ev[i][2].record()
+        run.run_phase(4)
+        ev[i][3].record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    total = ev[0][0].elapsed_time(ev[-1][3]) / steps
+    main = sum(e[1].elapsed_time(e[2]) for e in ev) / steps
+    return total, main, 4, (q, k, v, o, do, lse, run), (t0, t1)
+
+
+def time_e2e(cfg, device, steps, state):
+    """The same metric through the public launch with HOST buffers: every step
+    copies q, k, v, o, dO and lse from pinned memory, runs the backward and
+    copies dq, dk, dv back."""
+    q, k, v, o, do, lse, run = state
+    host_in = [t.detach().cpu().pin_memory() for t in (q, k, v, o, do, lse)]
+    dev_in = (q, k, v, o, do, lse)
+    outs = run()
+    host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def step():
+        for d, h in zip(dev_in, host_in):
+            d.copy_(h, non_blocking=True)
+        res = run()
+        for h, d in zip(host_out, res):
+            h.copy_(d, non_blocking=True)
+
+    step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps, h2d, d2h
+
+
+def cpu_reference_tflops(seconds_budget=12.0):
+    """The reference's CPU arithmetic for this path: FP32 gradients of causal
+    softmax attention per request and head (its benchmarks/harness/training.py
+    :124-164), here the oracle's restatement, on the host cores. A bounded
+    sample: batch 1, 4 heads, seqlen 2048, head_dim 128, scaled by FLOPs."""
+    from oracle import backward as ob
+
+    S, H, D = 2048, 4, 128
+    torch.manual_seed(0)
+    q, k, v, do = (torch.randn(S, H, D).bfloat16().float() for _ in range(4))
+    ob.reference_grads(q[:256], k[:256], v[:256], do[:256], dtype=torch.float32)
+    n, t0 = 0, time.time()
+    while True:
+        ob.reference_grads(q, k, v, do, dtype=torch.float32)
+        n += 1
+        if time.time() - t0 > seconds_budget or n >= 8:
+            break
+    dt = (time.time() - t0) / n
+    return flops(1, S, H, D) / dt / 1e12, f"B1 H4 S{S} D{D} causal FP32 autograd x{n}, scaled by FLOPs"
+
+
+def decode_extra(device, steps=8):
+    """Config-5-shaped decode at a reduced batch (extra keys, not the headline):
+    v8, depth 16, GQA 64/8, D128, lengths log-uniform in [4096, 131072]."""
+    import math
+
+    from fold_attention_b200 import FoldKVCache
+
+    B, H, HKV, D = 32, 64, 8, 128
+    g = torch.Generator().manual_seed(5)
+    lens = [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
+    c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, depth=16.0, v8=True, chunk=8192, device=device)
+    gd = torch.Generator(device=device).manual_seed(6)
+    pages = c.page_table.shape[1]
+    perm = torch.randperm(B * pages, device=device, generator=gd).int().view(B, pages)
+    c.page_table.copy_(perm)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=device, dtype=torch.int32)
+    T = sum(lens)
+    k = torch.randn(T, HKV, D, device=device, generator=gd)
+    hot = torch.rand(T, 1, 1, device=device, generator=gd) < 0.01
+    k = torch.where(hot, k * 8, k).bfloat16()
+    v = torch.randn(T, HKV, D, device=device, generator=gd)
+    out = torch.rand(T, HKV, D, device=device, generator=gd) < 0.001
+    v = torch.where(out, v * 20, v).bfloat16()
+    c.write_prompt(k, v, cu, lens)
+    del k, v
+    q = torch.randn(B, H, D, device=device, generator=gd).bfloat16()
+    kn = torch.randn(B, HKV, D, device=device, generator=gd).bfloat16()
+    vn = torch.randn(B, HKV, D, device=device, generator=gd).bfloat16()
+    for _ in range(2):
+        c.decode(q, kn, vn)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        c.decode(q, kn, vn)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / steps * 1e3
+    keys = sum(c.lens) * HKV
+    live = c.counts[:, 0].sum().item() / keys
+    refk = c.counts[:, 1].sum().item() / keys
+    byts = keys * (D + 2 + D * (live + refk))
+    return dict(workload=f"config5-shaped decode v8 depth16 B{B} H64/8 D128 lens logU[4096,131072] chunk8192",
+                us_per_step=us, keys=keys, live_fraction=live, refined_fraction=refk,
+                algorithmic_gbs=byts / us / 1e3, hbm_frac=byts / us / 1e3 / peaks()["hbm"])
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    val, sample = cpu_reference_tflops(20.0)
+    cores = torch.get_num_threads()
+    line = dict(
+        impl="reference", metric=METRIC, value=val, unit="TFLOP/s", n_gpus=args.gpus, steps=args.steps,
+        warmup=args.warmup, ms_per_step=flops(**{k: CFG[k] for k in ("B", "S", "H", "D")}) / val / 1e9,
+        higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+        config=dict(workload=WORKLOAD),
+        cpu_baseline=dict(value=val, unit="TFLOP/s", cores=cores, kind="port", sample=sample),
+        e2e=dict(value=val, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+    )
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-extra", action="store_true", help="skip the decode extra keys")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    clocks = Clocks(local)
+    ms, main_ms, launches, state, (t0, t1) = time_backward(CFG, device, args.steps, args.warmup, 1234 + rank, dist)
+    ck = clocks.stop(t0, t1)
+    fl = flops(CFG["B"], CFG["S"], CFG["H"], CFG["D"])
+    t = torch.tensor([ms, main_ms], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max, main_max = t.tolist()
+    e2e_ms, h2d, d2h = time_e2e(CFG, device, max(2, args.steps // 3), state)
+    t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_max = t.item()
+    del state
+    torch.cuda.empty_cache()
+    pk = peaks()
+    line = dict(
+        metric=METRIC, value=world * fl / ms_max / 1e9, unit="TFLOP/s", n_gpus=world, steps=args.steps,
+        warmup=args.warmup, ms_per_step=ms_max, higher_is_better=True, scaling="weak", vs_baseline=None,
+        dtype="bf16", data="synthetic",
+        config=dict(workload=WORKLOAD, l2="inputs (1.3 GB) larger than L2", shard="batch x KV head, one workload per rank"),
+        e2e=dict(value=world * fl / e2e_max / 1e9, unit="TFLOP/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+        gpu_launches=launches * args.steps,
+        clocks=ck,
+        roofline=dict(bound="tensor", achieved=fl / main_max / 1e9, peak=pk["bf16"], unit="TFLOP/s",
+                      frac=fl / main_max / 1e9 / pk["bf16"], traffic=None,
+                      note=f"main-loop kernel, of {pk['which']} sustained bf16 GEMM; burst peak {pk['bf16_burst']}"),
+    )
+    if rank == 0 and world == 1:
+        val, sample = cpu_reference_tflops()
+        line["cpu_baseline"] = dict(value=val, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port", sample=sample)
+        if not args.no_extra:
+            gqa = dict(CFG, HKV=8)
+            ms_g, main_g, _, st_g, _ = time_backward(gqa, device, max(2, args.steps // 2), 3, 99, None)
+            del st_g
+            torch.cuda.empty_cache()
+            line["extra"] = dict(gqa_32_8=dict(ms_per_step=ms_g, tflops=fl / ms_g / 1e9))
+            try:
+                line["extra"]["decode"] = decode_extra(device)
+            except Exception as e:  # the headline stands on its own
+                line["extra"]["decode"] = dict(error=repr(e))
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

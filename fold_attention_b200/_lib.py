@@ -33,7 +33,7 @@ class FoldLibraryError(RuntimeError):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m fold_attention_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python fold_attention_b200/build.py` "
             "(nvcc, sm_100a). There is no CPU or PyTorch fallback."
         )
     lib = ctypes.CDLL(LIB_PATH)

@@ -27,6 +27,10 @@ _lib.register(
     "fold_bwd_run",
     [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, P],
 )
+_lib.register(
+    "fold_bwd_run_phases",
+    [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, I, P],
+)
 _lib.register("fold_fwd_run", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
 
 KERNELS = {"auto": 0, "mma": 1, "sm100": 2}
@@ -131,8 +135,15 @@ def prepare_backward(
         _lib.call("fold_bwd_run", *args, _lib.stream(dev))
         return dq, dk, dv
 
+    def run_phase(phases):
+        """One or more of the backward's phases (1 preprocess, 2 main loop,
+        4 postprocess), for callers that time them apart."""
+        _lib.call("fold_bwd_run_phases", *args, int(phases), _lib.stream(dev))
+
     held = (q, k, v, o, do, lse, dq, dk, dv, workspace, cu, strides)
-    return BackwardLaunch(run, held, plan, workspace, tuple(lay))
+    launch = BackwardLaunch(run, held, plan, workspace, tuple(lay))
+    launch.run_phase = run_phase
+    return launch
 
 
 def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, max_seqlen=None):

@@ -1,6 +1,8 @@
 """Build libfold_b200.so in-tree with nvcc for sm_100a.
 
-    python -m fold_attention_b200.build [--force] [--verbose]
+    python fold_attention_b200/build.py [--force] [--verbose]
+
+(run it by path: importing the package loads the library)
 
 nvcc cross-compiles without a GPU. The library sits beside this file so it
 travels with the source tree; nothing is installed into site-packages.

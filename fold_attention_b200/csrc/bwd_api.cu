@@ -34,12 +34,12 @@ extern "C" size_t fold_bwd_workspace_bytes(int batch, int n_heads, int n_kv_head
     return ws_layout(batch, n_heads, n_kv_heads, max_seqlen, total, head_dim, varlen != 0).total;
 }
 
-extern "C" int fold_bwd_run(const void* q, const void* k, const void* v, const void* o,
-                            const void* dout, const float* lse, void* dq, void* dk, void* dv,
-                            const int64_t* strides, const int32_t* cu_seqlens, int batch,
-                            int n_heads, int n_kv_heads, int max_seqlen, int total, int head_dim,
-                            int causal, int is_f16, float softmax_scale, void* workspace,
-                            size_t workspace_bytes, int kernel, void* stream) {
+static int bwd_run_phases(const void* q, const void* k, const void* v, const void* o,
+                          const void* dout, const float* lse, void* dq, void* dk, void* dv,
+                          const int64_t* strides, const int32_t* cu_seqlens, int batch,
+                          int n_heads, int n_kv_heads, int max_seqlen, int total, int head_dim,
+                          int causal, int is_f16, float softmax_scale, void* workspace,
+                          size_t workspace_bytes, int kernel, int phases, void* stream) {
     FOLD_CHECK_ARG(q && k && v && o && dout && lse && dq && dk && dv && strides && workspace,
                    "fold_bwd_run: null pointer");
     FOLD_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0,
@@ -99,11 +99,38 @@ extern "C" int fold_bwd_run(const void* q, const void* k, const void* v, const v
     } else {
         FOLD_CHECK_ARG(kernel == FOLD_BWD_KERNEL_MMA, "fold_bwd_run: unknown kernel %d", kernel);
     }
-    int rc = launch_bwd_preprocess(p, st);
+    int rc = FOLD_OK;
+    if (phases & FOLD_BWD_PHASE_PRE) rc = launch_bwd_preprocess(p, st);
     if (rc) return rc;
-    rc = sm100 ? launch_bwd_main_sm100(p, st) : launch_bwd_main_mma(p, st);
+    if (phases & FOLD_BWD_PHASE_MAIN) rc = sm100 ? launch_bwd_main_sm100(p, st) : launch_bwd_main_mma(p, st);
     if (rc) return rc;
-    return launch_bwd_postprocess(p, sm100 ? DQ_LAYOUT_SM100 : DQ_LAYOUT_ROW_MAJOR, st);
+    if (phases & FOLD_BWD_PHASE_POST)
+        rc = launch_bwd_postprocess(p, sm100 ? DQ_LAYOUT_SM100 : DQ_LAYOUT_ROW_MAJOR, st);
+    return rc;
+}
+
+extern "C" int fold_bwd_run(const void* q, const void* k, const void* v, const void* o,
+                            const void* dout, const float* lse, void* dq, void* dk, void* dv,
+                            const int64_t* strides, const int32_t* cu_seqlens, int batch,
+                            int n_heads, int n_kv_heads, int max_seqlen, int total, int head_dim,
+                            int causal, int is_f16, float softmax_scale, void* workspace,
+                            size_t workspace_bytes, int kernel, void* stream) {
+    return bwd_run_phases(q, k, v, o, dout, lse, dq, dk, dv, strides, cu_seqlens, batch, n_heads,
+                          n_kv_heads, max_seqlen, total, head_dim, causal, is_f16, softmax_scale,
+                          workspace, workspace_bytes, kernel,
+                          FOLD_BWD_PHASE_PRE | FOLD_BWD_PHASE_MAIN | FOLD_BWD_PHASE_POST, stream);
+}
+
+extern "C" int fold_bwd_run_phases(const void* q, const void* k, const void* v, const void* o,
+                                   const void* dout, const float* lse, void* dq, void* dk, void* dv,
+                                   const int64_t* strides, const int32_t* cu_seqlens, int batch,
+                                   int n_heads, int n_kv_heads, int max_seqlen, int total,
+                                   int head_dim, int causal, int is_f16, float softmax_scale,
+                                   void* workspace, size_t workspace_bytes, int kernel, int phases,
+                                   void* stream) {
+    return bwd_run_phases(q, k, v, o, dout, lse, dq, dk, dv, strides, cu_seqlens, batch, n_heads,
+                          n_kv_heads, max_seqlen, total, head_dim, causal, is_f16, softmax_scale,
+                          workspace, workspace_bytes, kernel, phases, stream);
 }
 
 // The workspace's views, for tests that inspect the accumulators:

@@ -139,6 +139,20 @@ int fold_bwd_run(const void* q, const void* k, const void* v, const void* o, con
                  int total, int head_dim, int causal, int is_f16, float softmax_scale,
                  void* workspace, size_t workspace_bytes, int kernel, void* stream);
 
+/* fold_bwd_run one phase at a time (a bit mask), so a caller can put events
+ * between the preprocess, the main loop and the postprocess. The phases of
+ * one backward must run in order on one stream with the same arguments.
+ * No counterpart in the reference: its launch closure runs all three. */
+#define FOLD_BWD_PHASE_PRE 1
+#define FOLD_BWD_PHASE_MAIN 2
+#define FOLD_BWD_PHASE_POST 4
+int fold_bwd_run_phases(const void* q, const void* k, const void* v, const void* o,
+                        const void* dout, const float* lse, void* dq, void* dk, void* dv,
+                        const int64_t* strides /* host */, const int32_t* cu_seqlens, int batch,
+                        int n_heads, int n_kv_heads, int max_seqlen, int total, int head_dim,
+                        int causal, int is_f16, float softmax_scale, void* workspace,
+                        size_t workspace_bytes, int kernel, int phases, void* stream);
+
 /* Attention forward: O and the log-sum-exp (nats) the backward consumes.
  * Replaces the third-party forward called at src/fold_attention/interface.py:42-44,
  * :70-81 and kv_cache.py:252-262. strides: q, k, v, o (12 entries). */

@@ -153,7 +153,9 @@ def test_repeated_calls_and_short_sequences(kernel):
         if n:
             ref = ob.reference_grads(q[off:off + n], k[off:off + n], v[off:off + n], do[off:off + n])
             for name, a, r in zip("qkv", first, ref):
-                assert ob.rel_l2(a[off:off + n], r) <= 2 * TOL, (n, name)
+                # a one-token request's dQ and dK are exactly zero
+                err = (a[off:off + n].double() - r).norm().item()
+                assert err <= 2 * TOL * r.norm().item() + 1e-5 * math.sqrt(r.numel()), (n, name)
         off += n
 
 

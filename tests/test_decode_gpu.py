@@ -179,7 +179,9 @@ def test_a_truncated_depth_costs_what_it_says(v8, depth):
     err = _rel(got, want)
     assert err < 2.0 ** (-depth / 3), err
     live = c.counts[:, 0].sum().item() / (sum(lens) * HKV)
-    assert live < 1.0
+    assert live <= 1.0
+    if depth <= 8.0:
+        assert live < 0.9, live  # the cut really drops keys
 
 
 def test_splits_regroup_sums_and_a_fixed_chunk_pins_them():
