@@ -119,7 +119,7 @@ def prepare_backward(
     dq, dk, dv = (torch.empty_like(x) for x in (q, k, v))
     nbytes = _lib.lib.fold_bwd_workspace_bytes(B, H, H_KV, S, total, D, int(varlen))
     workspace = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-    lay = (ctypes.c_int64 * 5)()
+    lay = (ctypes.c_int64 * 6)()
     _lib.call("fold_bwd_workspace_layout", B, H, H_KV, S, total, D, int(varlen), lay)
     tensors = (q, k, v, o, do, dq, dk, dv)
     strides = _strides(tensors, varlen)
@@ -143,6 +143,7 @@ def prepare_backward(
     held = (q, k, v, o, do, lse, dq, dk, dv, workspace, cu, strides)
     launch = BackwardLaunch(run, held, plan, workspace, tuple(lay))
     launch.run_phase = run_phase
+    launch.status = workspace[lay[5]: lay[5] + 4].view(torch.int32)
     return launch
 
 

@@ -22,7 +22,7 @@ WsLayout ws_layout(int B, int H, int HKV, int S, int total, int D, bool varlen) 
     w.dq_acc = off; off = align256(off + sizeof(int) * static_cast<size_t>(H) * w.rows_p * D);
     w.dpsum = off;  off = align256(off + sizeof(float) * static_cast<size_t>(H) * w.rows_p);
     w.lse2 = off;   off = align256(off + sizeof(float) * static_cast<size_t>(H) * w.rows_p);
-    w.stats = off;  off = align256(off + sizeof(int) * N_STATS * static_cast<size_t>(B) * HKV);
+    w.stats = off;  off = align256(off + sizeof(int) * (N_STATS * static_cast<size_t>(B) * HKV + 1));
     w.total = off;
     return w;
 }
@@ -83,6 +83,7 @@ static int bwd_run_phases(const void* q, const void* k, const void* v, const voi
     p.dpsum = reinterpret_cast<float*>(ws + w.dpsum);
     p.lse2 = reinterpret_cast<float*>(ws + w.lse2);
     p.stats = reinterpret_cast<int*>(ws + w.stats);
+    p.status = p.stats + N_STATS * static_cast<size_t>(batch) * n_kv_heads;
     p.rows_p = w.rows_p;
     p.S_r = (max_seqlen + ROW_PAD - 1) / ROW_PAD * ROW_PAD;
 
@@ -105,7 +106,7 @@ static int bwd_run_phases(const void* q, const void* k, const void* v, const voi
     if (phases & FOLD_BWD_PHASE_MAIN) rc = sm100 ? launch_bwd_main_sm100(p, st) : launch_bwd_main_mma(p, st);
     if (rc) return rc;
     if (phases & FOLD_BWD_PHASE_POST)
-        rc = launch_bwd_postprocess(p, sm100 ? DQ_LAYOUT_SM100 : DQ_LAYOUT_ROW_MAJOR, st);
+        rc = launch_bwd_postprocess(p, DQ_LAYOUT_ROW_MAJOR, st);
     return rc;
 }
 
@@ -134,11 +135,13 @@ extern "C" int fold_bwd_run_phases(const void* q, const void* k, const void* v, 
 }
 
 // The workspace's views, for tests that inspect the accumulators:
-// out[0..3] = byte offsets of dq_acc, dpsum, lse2, stats; out[4] = padded rows per head.
+// out[0..3] = byte offsets of dq_acc, dpsum, lse2, stats; out[4] = padded rows per head;
+// out[5] = byte offset of the status word (non-zero after a call whose device-side wait ran out).
 extern "C" int fold_bwd_workspace_layout(int batch, int n_heads, int n_kv_heads, int max_seqlen,
                                          int total, int head_dim, int varlen, int64_t* out) {
     FOLD_CHECK_ARG(out, "fold_bwd_workspace_layout: null pointer");
     const WsLayout w = ws_layout(batch, n_heads, n_kv_heads, max_seqlen, total, head_dim, varlen != 0);
     out[0] = w.dq_acc; out[1] = w.dpsum; out[2] = w.lse2; out[3] = w.stats; out[4] = w.rows_p;
+    out[5] = w.stats + sizeof(int) * N_STATS * static_cast<size_t>(batch) * n_kv_heads;
     return FOLD_OK;
 }

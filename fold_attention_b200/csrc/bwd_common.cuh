@@ -29,6 +29,7 @@ struct BwdParams {
     float* dpsum;   // [H][rows_p]  Delta_i = sum_d dO O
     float* lse2;    // [H][rows_p]  lse * log2(e) - s ; +inf on padded rows
     int* stats;     // [B][HKV][N_STATS] float bits of the order-free maxima
+    int* status;    // one word after the stats: raised if a device-side wait ran out
     int64_t rows_p; // padded rows per head
     int S_r;        // dense: S rounded up to ROW_PAD
 };

@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(256) bwd_postprocess_dq_kernel(const BwdParams
 }
 
 int launch_bwd_preprocess(const BwdParams& p, cudaStream_t st) {
-    cudaMemsetAsync(p.stats, 0, sizeof(int) * N_STATS * p.B * p.HKV, st);
+    cudaMemsetAsync(p.stats, 0, sizeof(int) * (N_STATS * p.B * p.HKV + 1), st);
     const int s_r = (p.S + ROW_PAD - 1) / ROW_PAD * ROW_PAD;
     dim3 grid(s_r / PRE_ROWS, p.H, p.B);
     if (p.f16)

@@ -28,7 +28,7 @@ namespace fold {
 constexpr int BNK = 64;          // keys per tile
 constexpr int DEC_THREADS = 128;
 constexpr int RING = 3;
-constexpr int WAIT_LIMIT = 1 << 22;
+constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 constexpr float E4W = 18446744073709551616.0f;   // 2^64 on the weights of an 8-bit V
 constexpr float E4O = 72057594037927936.0f;      // 2^56 on its accumulator
 
@@ -62,8 +62,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // A bounded wait: on expiry the status word is set and false returned, so the
 // CTA can leave without hanging the device.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-    for (int i = 0; i < WAIT_LIMIT; ++i)
+    const long long t0 = clock64();
+    for (int i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63) == 63 && clock64() - t0 > WAIT_CYCLES) break;
+    }
     atomicExch(status, FOLD_ERR_TIMEOUT);
     return false;
 }

@@ -123,10 +123,12 @@ int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const i
 size_t fold_bwd_workspace_bytes(int batch, int n_heads, int n_kv_heads, int max_seqlen, int total,
                                 int head_dim, int varlen);
 
-/* Byte offsets of the workspace's parts (dq_acc, dpsum, lse2, stats) and the
- * padded row count per head, for callers that inspect the accumulators. */
+/* Byte offsets of the workspace's parts (dq_acc, dpsum, lse2, stats), the
+ * padded row count per head, and the byte offset of the int32 status word
+ * (non-zero after a call in which a device-side wait ran out), for callers
+ * that inspect the accumulators. out6: host, six entries. */
 int fold_bwd_workspace_layout(int batch, int n_heads, int n_kv_heads, int max_seqlen, int total,
-                              int head_dim, int varlen, int64_t* out5);
+                              int head_dim, int varlen, int64_t* out6);
 
 /* dQ, dK, dV of causal or full self-attention: preprocess, main loop and
  * postprocess on `stream`, no host synchronisation.

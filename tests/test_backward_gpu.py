@@ -15,7 +15,13 @@ pytestmark = pytest.mark.gpu
 from oracle import backward as ob  # noqa: E402
 
 TOL = 3.0e-3
-KERNELS = ["mma"]
+KERNELS = ["mma", "sm100"]
+
+
+def _need(kernel, D, dtype=torch.bfloat16):
+    """The tcgen05 kernel serves head_dim 128 in bf16; everything runs on mma.sync."""
+    if kernel == "sm100" and (D != 128 or dtype != torch.bfloat16):
+        pytest.skip("the tcgen05 kernel takes head_dim 128, bf16")
 
 
 def _api():
@@ -58,6 +64,7 @@ def _same(a, b):
 ])
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_forward_and_gradient_accuracy(H, HKV, D, dtype, kernel):
+    _need(kernel, D, dtype)
     q, k, v, do, cu = _packed([1536], H, HKV, D, dtype=dtype)
     S = 1536
     o, lse = _fwd(q, k, v, cu, S)
@@ -72,6 +79,8 @@ def test_forward_and_gradient_accuracy(H, HKV, D, dtype, kernel):
 
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_config1_dense_mha_d64_twice(kernel):
+    if kernel != "mma":
+        pytest.skip("config 1 is head_dim 64: the public API picks the mma.sync kernel")
     """BASELINE config 1: B2 S512 H8/8 D64 causal, N(0,1) inputs; checked
     against FP64 autograd, and two runs are the same bits."""
     fa, _, _ = _api()
@@ -97,6 +106,7 @@ def test_config1_dense_mha_d64_twice(kernel):
 ])
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_full_and_ragged_attention(B, H, HKV, S, D, causal, kernel):
+    _need(kernel, D)
     _, attention_forward, prepare_backward = _api()
     torch.manual_seed(7)
     q, do = (torch.randn(B, S, H, D, device="cuda").bfloat16() for _ in range(2))
@@ -116,6 +126,7 @@ def test_full_and_ragged_attention(B, H, HKV, S, D, causal, kernel):
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_a_request_does_not_see_its_batch(H, HKV, D, kernel):
     """A request's gradients alone and packed among others are the same bits."""
+    _need(kernel, D)
     lens = [1000, 777, 2048, 64, 1500]
     q, k, v, do, cu = _packed(lens, H, HKV, D)
     S = max(lens)
@@ -182,10 +193,8 @@ def test_grid_exponent_accumulator_and_postprocess(kernel):
     oracle's; the int32 accumulator never nears saturation; dQ is the one
     fp32 multiply of the accumulator the postprocess documents."""
     _, attention_forward, prepare_backward = _api()
-    if kernel != "mma":
-        pytest.skip("row-major accumulator view is the mma kernel's")
     torch.manual_seed(11)
-    B, S, H, HKV, D = 2, 300, 4, 2, 64
+    B, S, H, HKV, D = 2, 300, 4, 2, (64 if kernel == "mma" else 128)
     G = H // HKV
     q, do = (torch.randn(B, S, H, D, device="cuda").bfloat16() for _ in range(2))
     k, v = (torch.randn(B, S, HKV, D, device="cuda").bfloat16() for _ in range(2))
@@ -195,7 +204,7 @@ def test_grid_exponent_accumulator_and_postprocess(kernel):
     run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True, kernel=kernel)
     dq, dk, dv = run()
     torch.cuda.synchronize()
-    off_acc, off_dp, off_l2, off_st, rows_p = run.layout
+    off_acc, off_dp, off_l2, off_st, rows_p, _ = run.layout
     ws = run.workspace
     stats = ws[off_st: off_st + B * HKV * 8 * 4].view(torch.float32).view(B, HKV, 8).cpu()
     acc = ws[off_acc: off_acc + H * rows_p * D * 4].view(torch.int32).view(H, rows_p, D)
@@ -215,6 +224,28 @@ def test_grid_exponent_accumulator_and_postprocess(kernel):
                 f = np.float32(np.float32(1.0 / math.sqrt(D)) * np.float32(2.0**-s))
                 want = (a.float() * float(f)).bfloat16()
                 assert torch.equal(tr(dq)[b, :, h * G + g], want)
+    assert int(run.status) == 0
+
+
+def test_the_two_kernels_agree_and_auto_picks_tcgen05():
+    """The tcgen05 and mma.sync main loops are two schedules of one function:
+    same grid exponent, gradients equal to within bf16 rounding; "auto" is the
+    tcgen05 kernel's bits at head_dim 128."""
+    _, attention_forward, prepare_backward = _api()
+    torch.manual_seed(21)
+    B, S, H, HKV, D = 2, 1100, 8, 2, 128
+    q, do = (torch.randn(B, S, H, D, device="cuda").bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, S, HKV, D, device="cuda").bfloat16() for _ in range(2))
+    o, lse = attention_forward(q, k, v, causal=True)
+    tr = lambda x: x.transpose(1, 2)
+    got = {}
+    for kern in ("mma", "sm100", "auto"):
+        run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True, kernel=kern)
+        got[kern] = tuple(x.clone() for x in run())
+        assert int(run.status) == 0
+    assert _same(got["auto"], got["sm100"])
+    for a, b in zip(got["mma"], got["sm100"]):
+        assert ob.rel_l2(a, b.double()) < 1e-3
 
 
 def test_error_messages():
