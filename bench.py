@@ -27,7 +27,7 @@ sys.path.insert(0, ROOT)
 import torch  # noqa: E402
 
 CFG = dict(B=4, S=8192, H=32, HKV=32, D=128)
-WORKLOAD = "config2 causal det. backward B4 S8192 H32/32 D128 bf16"
+WORKLOAD = "config2 causal det. backward B{B} S8192 H32/32 D128 bf16"
 METRIC = "det. causal bwd TFLOP/s"
 
 
@@ -232,7 +232,7 @@ def run_reference(args):
         impl="reference", metric=METRIC, value=val, unit="TFLOP/s", n_gpus=args.gpus, steps=args.steps,
         warmup=args.warmup, ms_per_step=flops(**{k: CFG[k] for k in ("B", "S", "H", "D")}) / val / 1e9,
         higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
-        config=dict(workload=WORKLOAD),
+        config=dict(workload=WORKLOAD.format(B=CFG["B"])),
         cpu_baseline=dict(value=val, unit="TFLOP/s", cores=cores, kind="port", sample=sample),
         e2e=dict(value=val, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
     )
@@ -246,7 +246,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-extra", action="store_true", help="skip the decode extra keys")
+    ap.add_argument("--batch", type=int, default=CFG["B"],
+                    help="batch of the backward workload (config 2 is 4; 1 gives the small case ncu captures)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
+    CFG["B"] = args.batch
     if args.impl == "reference":
         run_reference(args)
         return
@@ -270,7 +274,10 @@ def main():
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max, main_max = t.tolist()
-    e2e_ms, h2d, d2h = time_e2e(CFG, device, max(2, args.steps // 3), state)
+    if args.no_e2e:
+        e2e_ms, h2d, d2h = float("nan"), 0, 0
+    else:
+        e2e_ms, h2d, d2h = time_e2e(CFG, device, max(2, args.steps // 3), state)
     t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -282,7 +289,7 @@ def main():
         metric=METRIC, value=world * fl / ms_max / 1e9, unit="TFLOP/s", n_gpus=world, steps=args.steps,
         warmup=args.warmup, ms_per_step=ms_max, higher_is_better=True, scaling="weak", vs_baseline=None,
         dtype="bf16", data="synthetic",
-        config=dict(workload=WORKLOAD, l2="inputs (1.3 GB) larger than L2", shard="batch x KV head, one workload per rank"),
+        config=dict(workload=WORKLOAD.format(B=CFG["B"]), l2="inputs (1.3 GB) larger than L2", shard="batch x KV head, one workload per rank"),
         e2e=dict(value=world * fl / e2e_max / 1e9, unit="TFLOP/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
         gpu_launches=launches * args.steps,
         clocks=ck,
@@ -290,7 +297,7 @@ def main():
                       frac=fl / main_max / 1e9 / pk["bf16"], traffic=None,
                       note=f"main-loop kernel, of {pk['which']} sustained bf16 GEMM; burst peak {pk['bf16_burst']}"),
     )
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.no_e2e:
         val, sample = cpu_reference_tflops()
         line["cpu_baseline"] = dict(value=val, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port", sample=sample)
         if not args.no_extra:

@@ -57,7 +57,8 @@ enum {
     B_PDS = B_SDP + 2,           // [2]  P~^T in TMEM, dS~^T in shared
     B_DQF = B_PDS + 2,           // [2]  dQ~^T in TMEM (and the step's MMAs retired)
     B_DQE = B_DQF + 2,           // [2]  dQ~^T drained
-    B_COUNT = B_DQE + 2,
+    B_GRP = B_DQE + 2,           // [2]  the step's dQ, dV, dK MMAs have all retired
+    B_COUNT = B_GRP + 2,
 };
 
 // TMEM columns
@@ -202,6 +203,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             mbar_init(sh.bar(B_PDS + i), 128);
             mbar_init(sh.bar(B_DQF + i), 1);
             mbar_init(sh.bar(B_DQE + i), 128);
+            mbar_init(sh.bar(B_GRP + i), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -283,6 +285,12 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 const uint32_t st = base + SM_STAGE + s * STAGE_BYTES;
                 const uint32_t ds = base + SM_DS + bf * 16384;
                 const uint32_t rs = tmem + (bf ? T_RS1 : T_RS0), rd = tmem + (bf ? T_RD1 : T_RD0);
+                // dQ~^T = K^T dS~^T first: 8 steps of 16 keys. Its drain then runs under
+                // dV and dK, so the buffer is free again when the next S^T/dP^T need it.
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_ss(rd, smem_desc(base + SM_K + ks * 2048, 16384, 1024), smem_desc(ds + ks * 2048, 16384, 1024), ID_DQ, ks > 0);
+                tc_commit(sh.bar(B_DQF + bf));
                 // dV += P~^T dO : 4 steps of 16 queries; A = 8 TMEM columns per step
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
@@ -291,12 +299,8 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
                     mma_ss(tmem + T_DK, smem_desc(ds + ks * 32, 16, 1024), smem_desc(st + ST_Q + ks * 2048, 8192, 1024), ID_DK, (i > 0) || (ks > 0));
-                // dQ~^T = K^T dS~^T : 8 steps of 16 keys
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                    mma_ss(rd, smem_desc(base + SM_K + ks * 2048, 16384, 1024), smem_desc(ds + ks * 2048, 16384, 1024), ID_DQ, ks > 0);
                 tc_commit(sh.bar(B_QEMPTY + s));   // the stage's Q, dO are free once these retire
-                tc_commit(sh.bar(B_DQF + bf));
+                tc_commit(sh.bar(B_GRP + bf));
             }
         }
     } else if (warp >= 4 && warp < 12) {
@@ -313,7 +317,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             const int m0 = mb * BM;
             mbar_wait(sh.bar(B_SDP + bf), (i >> 1) & 1, abort_flag, p.status);
             // dS~^T buffer bf was read by step i-2's dK and dQ MMAs
-            if (i >= 2) mbar_wait(sh.bar(B_DQF + bf), ((i >> 1) - 1) & 1, abort_flag, p.status);
+            if (i >= 2) mbar_wait(sh.bar(B_GRP + bf), ((i >> 1) - 1) & 1, abort_flag, p.status);
             tc_fence_after();
             const float* sL = reinterpret_cast<const float*>(smem + SM_STAGE + s * STAGE_BYTES + ST_L);
             const float* sDl = reinterpret_cast<const float*>(smem + SM_STAGE + s * STAGE_BYTES + ST_DL);
@@ -392,11 +396,11 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
     // ================= epilogue: dK, dV out of TMEM =================
     __syncthreads();
     if (warp >= 4 && warp < 12) {
-        // every MMA has retired: the drain saw the last B_DQF, which follows them
+        // every MMA has retired once the last step's group barrier completes
         const int total_steps = total;
         if (total_steps > 0) {
             const int last = total_steps - 1;
-            mbar_wait(sh.bar(B_DQF + (last & 1)), (last >> 1) & 1, abort_flag, p.status);
+            mbar_wait(sh.bar(B_GRP + (last & 1)), (last >> 1) & 1, abort_flag, p.status);
         }
         tc_fence_after();
         const int r = 32 * (warp & 3) + lane;
