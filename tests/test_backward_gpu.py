@@ -259,3 +259,30 @@ def test_error_messages():
     q32 = torch.randn(2, 64, 8, 32, device="cuda").bfloat16()
     with pytest.raises(NotImplementedError, match="64, 96 and 128"):
         fa.fold_attn_func(q32.requires_grad_(), q32, q32).sum().backward()
+
+
+def test_a_shard_of_kv_heads_is_the_full_runs_bits():
+    """Multi-GPU sharding unit: the backward of a slice of (request, KV head)
+    units, run alone as a rank would, equals the full run's slice bit for bit."""
+    from fold_attention_b200 import parallel
+
+    _, attention_forward, prepare_backward = _api()
+    torch.manual_seed(31)
+    B, S, H, HKV, D = 2, 700, 8, 4, 128
+    G = H // HKV
+    q, do = (torch.randn(B, S, H, D, device="cuda").bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, S, HKV, D, device="cuda").bfloat16() for _ in range(2))
+    o, lse = attention_forward(q, k, v, causal=True)
+    tr = lambda x: x.transpose(1, 2)
+    full = tuple(tr(x).clone() for x in prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True)())
+    world = 3
+    for rank in range(world):
+        for b, (lo, hi) in parallel.backward_units(B, HKV, world, rank).items():
+            qs, os_, dos = (x[b:b + 1, :, lo * G:hi * G].contiguous() for x in (q, o, do))
+            ks, vs = (x[b:b + 1, :, lo:hi].contiguous() for x in (k, v))
+            ls = lse[b:b + 1, lo * G:hi * G].contiguous()
+            part = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True)()
+            dq, dk, dv = (tr(x) for x in part)
+            assert torch.equal(dq, full[0][b:b + 1, :, lo * G:hi * G])
+            assert torch.equal(dk, full[1][b:b + 1, :, lo:hi])
+            assert torch.equal(dv, full[2][b:b + 1, :, lo:hi])
