@@ -769,3 +769,81 @@ extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* 
 #undef FOLD_COMBINE
     return check_launch("fold_decode_combine");
 }
+
+// ---- a decode entry point that allocates nothing ------------------------------------
+// Some hosts may not allocate device memory from the code that runs a decode
+// step: an inference server that hands a plugin a fixed memory budget up front
+// and forbids cudaMalloc (or any allocating library call) inside its execution
+// callback, or a process whose device allocator belongs to another runtime.
+// For them the split partials live in this fixed array instead of in buffers
+// the caller provides. The array is part of the library image: every GPU that
+// loads the library holds FOLD_DECODE_STATIC_SCRATCH_BYTES of it until the
+// process exits.
+static __device__ __align__(256) unsigned char g_decode_scratch[FOLD_DECODE_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+// The array's name is only a host-side handle; the device address comes from
+// the runtime, once per device, with that device current.
+int static_scratch(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_error("fold_decode_run_static: cudaGetDevice: %s", cudaGetErrorString(e));
+        return FOLD_ERR_LAUNCH;
+    }
+    if (!g_scratch_ptr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
+        if (e != cudaSuccess || !ptr) {
+            set_error("fold_decode_run_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return FOLD_ERR_LAUNCH;
+        }
+        g_scratch_ptr[dev] = ptr;
+    }
+    *out = g_scratch_ptr[dev];
+    return FOLD_OK;
+}
+}  // namespace
+
+extern "C" size_t fold_decode_static_scratch_needed(int n_groups, int group, int head_dim, int split) {
+    const size_t n = static_cast<size_t>(n_groups) * split;
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    return up(n * group * head_dim * sizeof(float)) + up(n * group * sizeof(float)) + up(n * 2 * sizeof(int));
+}
+
+extern "C" int fold_decode_run_static(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                                      const int8_t* kb, const void* ek, const void* va, const void* vb,
+                                      const float* vmean, const float* z, const float* cut,
+                                      const int32_t* page_table, const int32_t* seq_lens,
+                                      const int32_t* order, int n_groups, int group, int n_kv_heads,
+                                      int head_dim, int pages_per_request, int page_size, int split,
+                                      int chunk_keys, int truncate, int weight_terms, float refine_k,
+                                      float refine_v, const float* refine_bands, float v_scale,
+                                      void* out, int out_dtype, float* den, int32_t* counts,
+                                      int32_t* status, void* stream) {
+    FOLD_CHECK_ARG(n_groups >= 1 && group >= 1 && split >= 1 && head_dim >= 1, "fold_decode_run_static: empty call");
+    const size_t need = fold_decode_static_scratch_needed(n_groups, group, head_dim, split);
+    FOLD_CHECK_ARG(need <= FOLD_DECODE_STATIC_SCRATCH_BYTES,
+                   "fold_decode_run_static: %d row groups x %d splits need %zu bytes of partials, the built-in "
+                   "scratch holds %zu; lower the split or use fold_decode_run with caller-provided buffers",
+                   n_groups, split, need, static_cast<size_t>(FOLD_DECODE_STATIC_SCRATCH_BYTES));
+    void* base = nullptr;
+    const int rc = static_scratch(&base);
+    if (rc) return rc;
+    const size_t n = static_cast<size_t>(n_groups) * split;
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    unsigned char* p = static_cast<unsigned char*>(base);
+    float* o_part = reinterpret_cast<float*>(p);
+    float* den_part = reinterpret_cast<float*>(p + up(n * group * head_dim * sizeof(float)));
+    int32_t* cnt_part = reinterpret_cast<int32_t*>(p + up(n * group * head_dim * sizeof(float)) + up(n * group * sizeof(float)));
+    // Nothing in the partials has to start at zero: every split a request
+    // reaches writes its whole slot before the combine, launched behind it on
+    // the same stream, reads exactly those slots.
+    return fold_decode_run(qa, qb, eq, ka, kb, ek, va, vb, vmean, z, cut, page_table, seq_lens, order,
+                           n_groups, group, n_kv_heads, head_dim, pages_per_request, page_size, split,
+                           chunk_keys, truncate, weight_terms, refine_k, refine_v, refine_bands, v_scale,
+                           o_part, den_part, cnt_part, out, out_dtype, den, counts, status, stream);
+}

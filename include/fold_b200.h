@@ -105,6 +105,33 @@ int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const i
                     float v_scale, float* o_part, float* den_part, int32_t* cnt_part, void* out,
                     int out_dtype, float* den, int32_t* counts, int32_t* status, void* stream);
 
+/* fold_decode_run for callers that may not allocate device memory.
+ * No counterpart in the reference (its launches allocate their partial buffers
+ * with torch). Same arguments as fold_decode_run without o_part, den_part and
+ * cnt_part: the split partials live in a fixed array inside the library
+ * (FOLD_DECODE_STATIC_SCRATCH_BYTES per GPU, held from library load to process
+ * exit). The call allocates nothing: no cudaMalloc, cudaFree or allocating
+ * library routine. A call whose partials would not fit (see
+ * fold_decode_static_scratch_needed) is rejected with FOLD_ERR_ARGUMENT.
+ * The first call on each device looks the array's address up (with that
+ * device current); make that first call before starting any stream capture.
+ * Every call on a device shares the one array and leaves the last call's
+ * partials in it: two calls that overlap on the GPU (different streams,
+ * threads or processes' contexts excepted) race on it, so keep calls on one
+ * device stream-ordered. Nothing in it needs clearing between calls. */
+#define FOLD_DECODE_STATIC_SCRATCH_BYTES (4u << 20)
+size_t fold_decode_static_scratch_needed(int n_groups, int group, int head_dim, int split);
+int fold_decode_run_static(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                           const int8_t* kb, const void* ek, const void* va, const void* vb,
+                           const float* vmean, const float* z, const float* cut,
+                           const int32_t* page_table, const int32_t* seq_lens, const int32_t* order,
+                           int n_groups, int group, int n_kv_heads, int head_dim,
+                           int pages_per_request, int page_size, int split, int chunk_keys,
+                           int truncate, int weight_terms, float refine_k, float refine_v,
+                           const float* refine_bands /* host */, float v_scale, void* out,
+                           int out_dtype, float* den, int32_t* counts, int32_t* status,
+                           void* stream);
+
 /* ---- Path A: deterministic attention backward ------------------------------ */
 
 #define FOLD_BWD_KERNEL_AUTO 0  /* tcgen05 where it applies, else mma.sync */

@@ -38,6 +38,7 @@ def test_bad_arguments_return_a_status_and_a_message():
 
 def test_python_signatures_cover_the_header():
     import fold_attention_b200  # noqa: F401  (registers every signature)
+    import fold_attention_b200.decode.static_scratch  # noqa: F401
     from fold_attention_b200 import _lib
 
     assert set(_declared()) <= set(_lib.exported_symbols())
