@@ -226,6 +226,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS=1; the CPU arm may use every host core
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     val, sample = cpu_reference_tflops(20.0)
     cores = torch.get_num_threads()
     line = dict(
