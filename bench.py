@@ -175,14 +175,14 @@ def cpu_reference_tflops(seconds_budget=12.0):
     return flops(1, S, H, D) / dt / 1e12, f"B1 H4 S{S} D{D} causal FP32 autograd x{n}, scaled by FLOPs"
 
 
-def decode_extra(device, steps=8):
+def decode_extra(device, steps=8, B=32):
     """Config-5-shaped decode at a reduced batch (extra keys, not the headline):
     v8, depth 16, GQA 64/8, D128, lengths log-uniform in [4096, 131072]."""
     import math
 
     from fold_attention_b200 import FoldKVCache
 
-    B, H, HKV, D = 32, 64, 8, 128
+    H, HKV, D = 64, 8, 128
     g = torch.Generator().manual_seed(5)
     lens = [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
     c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, depth=16.0, v8=True, chunk=8192, device=device)
@@ -251,12 +251,19 @@ def main():
     ap.add_argument("--batch", type=int, default=CFG["B"],
                     help="batch of the backward workload (config 2 is 4; 1 gives the small case ncu captures)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="run only the config-5-shaped decode (extra keys) and print its dict")
+    ap.add_argument("--decode-batch", type=int, default=32)
     args = ap.parse_args()
     CFG["B"] = args.batch
     if args.impl == "reference":
         run_reference(args)
         return
     args.warmup = max(args.warmup, 3)
+    if args.decode_only:
+        torch.cuda.set_device(0)
+        print(json.dumps(decode_extra(torch.device("cuda", 0), steps=max(2, args.steps), B=args.decode_batch)), flush=True)
+        return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
