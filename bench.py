@@ -154,6 +154,39 @@ def time_e2e(cfg, device, steps, state):
     return e0.elapsed_time(e1) / steps, h2d, d2h
 
 
+def varlen_extra(device, steps=3):
+    """Config 3: packed causal backward, GQA 32/8, D128, 64K tokens in sequences
+    of length uniform in [256, 8192] (last truncated), int32 cu_seqlens on device."""
+    from fold_attention_b200.backward import attention_forward, prepare_backward
+
+    H, HKV, D, total = 32, 8, 128, 65536
+    g = torch.Generator().manual_seed(3)
+    lens = []
+    while sum(lens) < total:
+        lens.append(min(int(torch.randint(256, 8193, (1,), generator=g)), total - sum(lens)))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=device, dtype=torch.int32)
+    gd = torch.Generator(device=device).manual_seed(4)
+    q = (torch.randn(total, H, D, device=device, generator=gd) / D**0.5).bfloat16()
+    k = torch.randn(total, HKV, D, device=device, generator=gd).bfloat16()
+    v = torch.randn(total, HKV, D, device=device, generator=gd).bfloat16()
+    do = torch.randn(total, H, D, device=device, generator=gd).bfloat16()
+    o, lse = attention_forward(q, k, v, causal=True, cu_seqlens=cu, max_seqlen=max(lens))
+    run = prepare_backward(q, k, v, o, do, lse, causal=True, cu_seqlens=cu, max_seqlen=max(lens))
+    for _ in range(3):
+        run()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    fl = 5.0 * H * D * sum(n * n for n in lens)
+    return dict(workload=f"config3 packed causal backward H32/8 D128 {len(lens)} sequences, {total} tokens",
+                ms_per_step=ms, tflops=fl / ms / 1e9)
+
+
 def cpu_reference_tflops(seconds_budget=12.0):
     """The reference's CPU arithmetic for this path: FP32 gradients of causal
     softmax attention per request and head (its benchmarks/harness/training.py
@@ -175,17 +208,23 @@ def cpu_reference_tflops(seconds_budget=12.0):
     return flops(1, S, H, D) / dt / 1e12, f"B1 H4 S{S} D{D} causal FP32 autograd x{n}, scaled by FLOPs"
 
 
-def decode_extra(device, steps=8, B=32):
+def decode_extra(device, steps=8, B=32, dense=False):
     """Config-5-shaped decode at a reduced batch (extra keys, not the headline):
-    v8, depth 16, GQA 64/8, D128, lengths log-uniform in [4096, 131072]."""
+    v8, depth 16, GQA 64/8, D128, lengths log-uniform in [4096, 131072]; or with
+    `dense` config 4's shape: bf16 V, depth None, GQA 32/8, lengths uniform in
+    [1024, 32768]."""
     import math
 
     from fold_attention_b200 import FoldKVCache
 
-    H, HKV, D = 64, 8, 128
+    H, HKV, D = (32, 8, 128) if dense else (64, 8, 128)
     g = torch.Generator().manual_seed(5)
-    lens = [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
-    c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, depth=16.0, v8=True, chunk=8192, device=device)
+    if dense:
+        lens = torch.randint(1024, 32769, (B,), generator=g).tolist()
+        c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, chunk=4096, device=device)
+    else:
+        lens = [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
+        c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, depth=16.0, v8=True, chunk=8192, device=device)
     gd = torch.Generator(device=device).manual_seed(6)
     pages = c.page_table.shape[1]
     perm = torch.randperm(B * pages, device=device, generator=gd).int().view(B, pages)
@@ -216,8 +255,11 @@ def decode_extra(device, steps=8, B=32):
     keys = sum(c.lens) * HKV
     live = c.counts[:, 0].sum().item() / keys
     refk = c.counts[:, 1].sum().item() / keys
-    byts = keys * (D + 2 + D * (live + refk))
-    return dict(workload=f"config5-shaped decode v8 depth16 B{B} H64/8 D128 lens logU[4096,131072] chunk8192",
+    vb = 2 * D if dense else D
+    byts = keys * (D + 2 + D * refk + vb * live)
+    name = (f"config4-shaped decode bf16 dense B{B} H32/8 D128 lens U[1024,32768] chunk4096" if dense else
+            f"config5-shaped decode v8 depth16 B{B} H64/8 D128 lens logU[4096,131072] chunk8192")
+    return dict(workload=name,
                 us_per_step=us, keys=keys, live_fraction=live, refined_fraction=refk,
                 algorithmic_gbs=byts / us / 1e3, hbm_frac=byts / us / 1e3 / peaks()["hbm"])
 
@@ -254,6 +296,7 @@ def main():
     ap.add_argument("--decode-only", action="store_true",
                     help="run only the config-5-shaped decode (extra keys) and print its dict")
     ap.add_argument("--decode-batch", type=int, default=32)
+    ap.add_argument("--decode-dense", action="store_true", help="config 4's shape instead of config 5's")
     args = ap.parse_args()
     CFG["B"] = args.batch
     if args.impl == "reference":
@@ -262,7 +305,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.decode_only:
         torch.cuda.set_device(0)
-        print(json.dumps(decode_extra(torch.device("cuda", 0), steps=max(2, args.steps), B=args.decode_batch)), flush=True)
+        print(json.dumps(decode_extra(torch.device("cuda", 0), steps=max(2, args.steps), B=args.decode_batch,
+                                      dense=args.decode_dense)), flush=True)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -315,10 +359,14 @@ def main():
             del st_g
             torch.cuda.empty_cache()
             line["extra"] = dict(gqa_32_8=dict(ms_per_step=ms_g, tflops=fl / ms_g / 1e9))
-            try:
-                line["extra"]["decode"] = decode_extra(device)
-            except Exception as e:  # the headline stands on its own
-                line["extra"]["decode"] = dict(error=repr(e))
+            for key, fn in (("varlen_config3", lambda: varlen_extra(device)),
+                            ("decode_config5", lambda: decode_extra(device)),
+                            ("decode_config4", lambda: decode_extra(device, B=128, dense=True))):
+                try:
+                    line["extra"][key] = fn()
+                except Exception as e:  # the headline stands on its own
+                    line["extra"][key] = dict(error=repr(e))
+                torch.cuda.empty_cache()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -286,3 +286,63 @@ def test_a_shard_of_kv_heads_is_the_full_runs_bits():
             assert torch.equal(dq, full[0][b:b + 1, :, lo * G:hi * G])
             assert torch.equal(dk, full[1][b:b + 1, :, lo:hi])
             assert torch.equal(dv, full[2][b:b + 1, :, lo:hi])
+
+
+def test_config2_full_size_repeats_and_matches_a_slice():
+    """BASELINE config 2 (GQA variant) at full size: B4 S8192 H32/8 D128. Two runs
+    are the same bits; one (request, KV head) unit run alone is the full run's
+    slice (size-independent property); that unit's gradients match FP32 autograd."""
+    _, attention_forward, prepare_backward = _api()
+    torch.manual_seed(2)
+    B, S, H, HKV, D = 4, 8192, 32, 8, 128
+    G = H // HKV
+    q = (torch.randn(B, S, H, D, device="cuda") / D**0.5).bfloat16()
+    do = torch.randn(B, S, H, D, device="cuda").bfloat16()
+    k, v = (torch.randn(B, S, HKV, D, device="cuda").bfloat16() for _ in range(2))
+    o, lse = attention_forward(q, k, v, causal=True)
+    tr = lambda x: x.transpose(1, 2)
+    run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True)
+    first = tuple(x.clone() for x in run())
+    assert _same(first, run())
+    assert int(run.status) == 0
+    b, hk = 2, 5
+    qs, os_, dos = (x[b:b + 1, :, hk * G:(hk + 1) * G].contiguous() for x in (q, o, do))
+    ks, vs = (x[b:b + 1, :, hk:hk + 1].contiguous() for x in (k, v))
+    ls = lse[b:b + 1, hk * G:(hk + 1) * G].contiguous()
+    dq, dk, dv = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True)()
+    assert torch.equal(dq, first[0][b:b + 1, hk * G:(hk + 1) * G])
+    assert torch.equal(dk, first[1][b:b + 1, hk:hk + 1])
+    assert torch.equal(dv, first[2][b:b + 1, hk:hk + 1])
+    ref = ob.reference_grads(qs[0, :, :1], ks[0], vs[0], dos[0, :, :1], scale=1.0 / math.sqrt(D), dtype=torch.float32)
+    assert ob.rel_l2(tr(dq)[0, :, :1], ref[0]) <= TOL
+
+
+def test_config3_packed_64k_tokens_invariance():
+    """BASELINE config 3: 64K tokens, lengths uniform in [256, 8192], GQA 32/8,
+    D128. A sequence's gradients are the same bits packed, alone, and in a
+    reversed packing."""
+    lens, total = [], 65536
+    g = torch.Generator().manual_seed(3)
+    while sum(lens) < total:
+        lens.append(min(int(torch.randint(256, 8193, (1,), generator=g)), total - sum(lens)))
+    H, HKV, D = 32, 8, 128
+    q, k, v, do, cu = _packed(lens, H, HKV, D, seed=9)
+    S = max(lens)
+    o, lse = _fwd(q, k, v, cu, S)
+    packed = _bwd(q, k, v, o, do, lse, cu, S)
+    assert _same(packed, _bwd(q, k, v, o, do, lse, cu, S))
+    i = 3
+    a, e = int(cu[i]), int(cu[i + 1])
+    sl = lambda x: x[a:e].contiguous()
+    cu1 = torch.tensor([0, e - a], device="cuda", dtype=torch.int32)
+    o1, lse1 = _fwd(sl(q), sl(k), sl(v), cu1, e - a)
+    alone = _bwd(sl(q), sl(k), sl(v), o1, sl(do), lse1, cu1, e - a)
+    assert all(torch.equal(x, sl(y)) for x, y in zip(alone, packed))
+    order = list(range(len(lens)))[::-1]
+    parts = [slice(int(cu[j]), int(cu[j + 1])) for j in order]
+    cat = lambda x: torch.cat([x[p] for p in parts]).contiguous()
+    cu2 = torch.tensor([0] + list(np.cumsum([lens[j] for j in order])), device="cuda", dtype=torch.int32)
+    o2, lse2 = _fwd(cat(q), cat(k), cat(v), cu2, S)
+    rev = _bwd(cat(q), cat(k), cat(v), o2, cat(do), lse2, cu2, S)
+    pos = sum(lens[j] for j in order[: order.index(i)])
+    assert all(torch.equal(x[pos:pos + lens[i]], sl(y)) for x, y in zip(rev, packed))
