@@ -770,6 +770,23 @@ extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* 
     return check_launch("fold_decode_combine");
 }
 
+// The combine alone, for decode kernels that fill the same partial buffers.
+extern "C" int fold_decode_combine(const float* o_part, const float* den_part, const int32_t* cnt_part,
+                                   const int32_t* seq_lens, void* out, int out_dtype, float* den, int32_t* counts,
+                                   int n_groups, int group, int head_dim, int n_kv_heads, int split, int chunk_keys,
+                                   float v_scale, void* stream) {
+    FOLD_CHECK_ARG(o_part && den_part && cnt_part && seq_lens && out && den && counts, "fold_decode_combine: null pointer");
+    FOLD_CHECK_ARG(out_dtype >= 0 && out_dtype <= 2, "out_dtype %d", out_dtype);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (out_dtype == 0)
+        decode_combine_kernel<0><<<n_groups, 256, 0, st>>>(o_part, den_part, cnt_part, seq_lens, out, den, counts, group, head_dim, n_kv_heads, split, chunk_keys, v_scale);
+    else if (out_dtype == 1)
+        decode_combine_kernel<1><<<n_groups, 256, 0, st>>>(o_part, den_part, cnt_part, seq_lens, out, den, counts, group, head_dim, n_kv_heads, split, chunk_keys, v_scale);
+    else
+        decode_combine_kernel<2><<<n_groups, 256, 0, st>>>(o_part, den_part, cnt_part, seq_lens, out, den, counts, group, head_dim, n_kv_heads, split, chunk_keys, v_scale);
+    return check_launch("fold_decode_combine");
+}
+
 // ---- a decode entry point that allocates nothing ------------------------------------
 // Some hosts may not allocate device memory from the code that runs a decode
 // step: an inference server that hands a plugin a fixed memory budget up front

@@ -1,0 +1,885 @@
+// Quantised paged-KV decode on Blackwell tensor cores (tcgen05 + TMEM), for an
+// 8-bit V (two E4M3 planes), head dim 128, pages of a multiple of 128 keys.
+//
+// The warp-level kernel in decode.cu spends 49 warp instructions per key and is
+// issue-bound at about a third of HBM bandwidth. Here a tile is 128 keys, the
+// cache's planes stream through a ring of shared-memory stages by bulk copy
+// and TMA with nothing in the way that depends on a verdict, and every product
+// is one tcgen05.mma per 32 keys:
+//   L  = Ka Q^T    kind::i8      M=128 keys, N=16 (Qa rows | Qb rows), K=32   -> TMEM int32
+//   O^T += Va^T W  kind::f8f6f4  M=128 channels, N=32, K=32 keys; A = E4M3 V as stored,
+//                                B = the weights as four E5M2 terms per query row
+// so V is never converted: the tensor core reads the cache's own bytes. A key is
+// one TMEM lane, so its 8 logits sit in one thread and the verdict (live /
+// refine-K / refine-V, ORed over the group) needs no shuffle. Plane A of V is read
+// for every key of a tile (a dropped key meets a zero weight): at the depths this
+// kernel is chosen for nearly every key is live, and a stream has no gather latency.
+//
+// A weight w = exp2(s - Z) >= 0 is carried as 64 w = t1 + t2/8 + t3/64 + t4/512
+// with every t an E5M2 number (each term is the rounding error of the sum before
+// it, times 8): 12 bits of mantissa with E5M2's 32 binades of range; the
+// denominator takes the fp32 weight.
+//
+// Plane B of V, where a 32-key quarter of a tile holds at least DENSE_MIN keys inside
+// the refine-V gate, is fetched whole for that quarter (4 KB by TMA, two tiles ahead
+// of its use) and meets the same weights, masked to those keys, in a second
+// accumulator:  O2^T += Vb^T W2  (scaled by 1/8 at the end).
+//
+// The keys that need more than that leave the tensor-core path: a key inside the
+// refine-K gate (its logits need plane B of K), a key inside the refine-V gate in a
+// quarter with few of them, or a key whose weight could pass 2^8 (E5M2 ends at
+// 57344) gets weight zero in W and is handed, tile by tile through bit masks in
+// shared memory, to four helper warps. A helper
+// recomputes the key's logits from both planes with dp4a, takes the weight in
+// fp32 and adds w (Va + Vb/8) into its own fp32 accumulators; tile t always goes
+// to helper t mod 4 and keys are taken in position order, so the sums are the
+// same on every run. The partial is the tensor-core sum plus the four helpers' sums.
+//
+// Warps: 0 and 2 producers (two 5-slot rings: K's plane A by bulk copy; plane A of V
+// by TMA with the 128-byte swizzle, with the key scales), 1 MMA issuer (owns 128 TMEM
+// columns), 4-7 and 8-11 one thread per key of the even and of the odd tiles, 12-15
+// helpers. A K slot is free again as soon as its logits are out, a V slot when its
+// value product has retired. Every wait is bounded (about a second); on expiry
+// a status word is raised, nobody waits any more, TMEM is freed and the kernel returns.
+// Arithmetic contract: src/fold_attention/decode/kernel.py:774-870, 1032-1201,
+// 1400-1476 (the schedule and the weight format are this kernel's own).
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "fold_b200.h"
+
+namespace fold {
+namespace dsm100 {
+
+constexpr int TK = 128;          // keys per tile
+constexpr int HD = 128;
+constexpr int NA = 5;            // ring slots of K's plane A
+constexpr int NV = 5;            // ring slots of V's plane A and the key scales
+constexpr int QD = 8;            // tiles of helper masks in flight
+constexpr int NHELP = 4;
+constexpr int NBQ = 8;            // tiles of quarter flags (and their barrier) in flight: more than the key threads can lead by
+constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weights) in flight
+constexpr int DENSE_MIN = 4;     // refine-V keys in a 32-key quarter from which the quarter's plane B is fetched whole
+constexpr int NTHREADS = 512;
+constexpr long long WAIT_CYCLES = 1ll << 31;
+constexpr float BIG_TOP = 8.0f;  // a key whose weight could pass 2^8 is summed in fp32 by a helper
+constexpr int W_BIAS = 6;        // weights are stored times 2^6: under 2^14 on the tensor-core path
+
+// shared memory map (1024-aligned base)
+constexpr int SM_Q = 0;                               // [16 rows][128 B] int8, SW128
+constexpr int SM_KA = 2048;                           // NA x Ka [128 keys][128 B]
+constexpr int SM_VA = SM_KA + NA * 16384;             // NV x Va [128 keys][128 B]
+constexpr int SM_VB = SM_VA + NV * 16384;             // NB2 x Vb [128 keys][128 B], fetched by quarters
+constexpr int SM_KS = SM_VB + NB2 * 16384;            // NV x 128 bf16 scales
+constexpr int SM_W = SM_KS + NV * 256;                // 2 x [2 units][128 keys][16 B] E5M2
+constexpr int SM_W2 = SM_W + 2 * 4096;                // NB2 x the same, masked to the dense refine-V keys
+constexpr int SM_QM = SM_W2 + NB2 * 4096;             // QD x { refine-K, refine-V, helper } x 4 mask words
+constexpr int SM_QF = SM_QM + QD * 48;                // NBQ x 4 quarter flags
+constexpr int SM_EQZ = SM_QF + NBQ * 16;              // eq[8], z[8] of the row group
+constexpr int SM_BAR = SM_EQZ + 64;
+// after the last MMA the rings are dead and hold the final reduction: 256 x 16 row sums,
+// 8 x 16 partial and 16 full column sums, per-warp counters; and the helpers' sums
+constexpr int SM_RED = SM_KA;
+constexpr int SM_CNT = SM_KA + (256 + 8 + 1) * 16 * 4;
+constexpr int SM_HOUT = SM_VA;                        // NHELP x { [8 rows][128 channels], [8] } floats
+constexpr int HOUT = (8 * 128 + 8) * 4;
+constexpr int SMEM_BYTES = SM_BAR + 512;
+
+enum {
+    B_AFULL = 0,                 // [NA] K's plane A has landed
+    B_LFULL = B_AFULL + NA,      // [NA] the tile's logit MMAs retired: its logits are in TMEM slot t % NA, its K slot is free
+    B_VFULL = B_LFULL + NA,      // [NV] V's plane A and the scales have landed
+    B_VEMPTY = B_VFULL + NV,     // [NV] the tile's value MMAs retired: its V slot and its weight buffer are free
+    B_WREADY = B_VEMPTY + NV,    // [2] 128 arrivals: the tile's weights are in shared memory
+    B_QFULL = B_WREADY + 2,      // [QD] 4 arrivals: the tile's masks are written
+    B_QFREE = B_QFULL + QD,      // [QD] its helper has read them
+    B_BFULL = B_QFREE + QD,      // [NBQ] 4 arrivals (+ bytes): the tile's quarters of plane B have landed
+    B_BFREE = B_BFULL + NBQ,     // [NB2] its plane-B MMAs retired
+    B_ALLDONE = B_BFREE + NB2,   // the last value MMAs retired
+    B_COUNT = B_ALLDONE + 1,
+};
+
+constexpr uint32_t T_L = 0, T_ACC = 96, T_ACC2 = 128;   // TMEM columns: NA logit buffers of 16, then the accumulators
+
+struct Params {
+    const int8_t* qa; const int8_t* qb; const float* eq;
+    const int8_t* ka; const int8_t* kb; const uint16_t* ek;
+    const uint8_t* va; const uint8_t* vb;
+    const float* vmean; const float* z; const float* cut;
+    const int* page_table; const int* seq_lens; const int* order;
+    float* o_part; float* den_part; int* cnt_part;
+    int nbh, G, hkv, ppr, page_size, split, chunk_keys, truncate, banded;
+    float rk, rv, band_e0, band_e1, rk1, rk2, rv1, rv2;
+    int* status;
+};
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try(bar, parity)) return;   // the usual case costs one instruction
+    if (*abort_flag) return;
+    const long long t0 = clock64();
+    for (int i = 0;; ++i) {
+        if (mbar_try(bar, parity)) return;
+        if ((i & 63) == 63) {
+            if (*abort_flag) return;
+            if (clock64() - t0 > WAIT_CYCLES) break;
+        }
+    }
+    *abort_flag = 1;
+    atomicExch(status, FOLD_ERR_TIMEOUT);
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_i8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p; }"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p; }"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+// four MMAs over a tile's K steps in one go: the first overwrites or accumulates as `acc0`
+// says, the rest accumulate; the descriptors advance by DA, DB (16-byte units) per step
+template <int DA, int DB>
+__device__ __forceinline__ void mma4_i8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc0) {
+    asm volatile(
+        "{ .reg .pred p0, p1; .reg .b64 a1, b1;\n"
+        "setp.ne.b32 p0, %4, 0; setp.eq.b32 p1, %4, %4;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p0;\n"
+        "add.u64 a1, %1, %5; add.u64 b1, %2, %6;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], a1, b1, %3, p1;\n"
+        "add.u64 a1, a1, %5; add.u64 b1, b1, %6;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], a1, b1, %3, p1;\n"
+        "add.u64 a1, a1, %5; add.u64 b1, b1, %6;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], a1, b1, %3, p1; }"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc0), "n"(DA), "n"(DB) : "memory");
+}
+template <int DA, int DB>
+__device__ __forceinline__ void mma4_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc0) {
+    asm volatile(
+        "{ .reg .pred p0, p1; .reg .b64 a1, b1;\n"
+        "setp.ne.b32 p0, %4, 0; setp.eq.b32 p1, %4, %4;\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p0;\n"
+        "add.u64 a1, %1, %5; add.u64 b1, %2, %6;\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a1, b1, %3, p1;\n"
+        "add.u64 a1, a1, %5; add.u64 b1, b1, %6;\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a1, b1, %3, p1;\n"
+        "add.u64 a1, a1, %5; add.u64 b1, b1, %6;\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a1, b1, %3, p1; }"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc0), "n"(DA), "n"(DB) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// two floats -> packed E5M2 pair (lo in the low byte), round to nearest, saturating
+__device__ __forceinline__ uint32_t cvt_e5m2x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// an E5M2 byte is the high byte of an fp16
+__device__ __forceinline__ float e5m2_to_float(uint32_t b) {
+    return __half2float(__ushort_as_half(static_cast<uint16_t>((b & 0xFFu) << 8)));
+}
+
+// four E4M3 bytes -> floats
+__device__ __forceinline__ void e4m3x4_to_float(uint32_t v, float (&f)[4]) {
+    uint32_t lo, hi;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"(static_cast<uint16_t>(v & 0xFFFFu)));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"(static_cast<uint16_t>(v >> 16)));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+// shared-memory matrix descriptor; layout 2 = 128-byte swizzle, 0 = none
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFF) << 16;
+    d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFF) << 32;
+    d |= 1ull << 46;
+    d |= static_cast<uint64_t>(layout) << 61;
+    return d;
+}
+// instruction descriptor: c_fmt (1 f32, 2 s32), a/b formats, majors (0 K, 1 MN), N, M
+__host__ __device__ constexpr uint32_t instr_desc(int c_fmt, int a_fmt, int b_fmt, int a_mn, int b_mn, int N, int M) {
+    return (static_cast<uint32_t>(c_fmt) << 4) | (static_cast<uint32_t>(a_fmt) << 7) |
+           (static_cast<uint32_t>(b_fmt) << 10) | (static_cast<uint32_t>(a_mn) << 15) |
+           (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+           (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+template <bool TRUNC>
+__global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params p, const __grid_constant__ CUtensorMap vmap,
+                                                                   const __grid_constant__ CUtensorMap vbmap) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    auto bar = [&](int i) { return base + SM_BAR + 8 * i; };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_BAR + 8 * B_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 8 * B_COUNT + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int slot = blockIdx.x / p.split, sp = blockIdx.x % p.split;
+    const int bh = p.order ? p.order[slot] : slot;
+    const int breq = bh / p.hkv, hkv = bh % p.hkv;
+    const int slen = p.seq_lens[breq];
+    const int G = p.G, PS = p.page_size;
+
+    int lo, hi, tstep, n_tiles;
+    if (p.chunk_keys > 0) {
+        lo = sp * p.chunk_keys;
+        hi = min(lo + p.chunk_keys, slen);
+        tstep = TK;
+        n_tiles = hi > lo ? (hi - lo + TK - 1) / TK : 0;
+        if (n_tiles == 0) return;
+    } else {
+        lo = sp * TK;
+        hi = slen;
+        tstep = p.split * TK;
+        const int all = (slen + TK - 1) / TK;
+        n_tiles = all > sp ? (all - sp + p.split - 1) / p.split : 0;
+    }
+    if (base & 1023u) {
+        if (tid == 0) atomicExch(p.status, FOLD_ERR_LAUNCH);
+        return;
+    }
+    const int64_t pix = static_cast<int64_t>(bh) * p.split + sp;
+    float rk = p.rk, rv = p.rv;
+    if (p.banded) {
+        rk = slen > static_cast<int>(p.band_e1) ? p.rk2 : (slen > static_cast<int>(p.band_e0) ? p.rk1 : p.rk);
+        rv = slen > static_cast<int>(p.band_e1) ? p.rv2 : (slen > static_cast<int>(p.band_e0) ? p.rv1 : p.rv);
+    }
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < NA; ++i) {
+            mbar_init(bar(B_AFULL + i), 1);
+            mbar_init(bar(B_LFULL + i), 1);
+        }
+        for (int i = 0; i < NV; ++i) {
+            mbar_init(bar(B_VFULL + i), 1);
+            mbar_init(bar(B_VEMPTY + i), 1);
+        }
+        for (int i = 0; i < 2; ++i) mbar_init(bar(B_WREADY + i), 128);
+        for (int i = 0; i < QD; ++i) {
+            mbar_init(bar(B_QFULL + i), 4);
+            mbar_init(bar(B_QFREE + i), 1);
+        }
+        for (int i = 0; i < NBQ; ++i) mbar_init(bar(B_BFULL + i), 4);
+        for (int i = 0; i < NB2; ++i) mbar_init(bar(B_BFREE + i), 1);
+        mbar_init(bar(B_ALLDONE), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Q planes -> shared, 16 rows of 128 bytes with the 128-byte swizzle; rows
+    // 0-7 plane A of query rows 0-7, rows 8-15 plane B; rows past G are zero
+    if (tid < 128) {
+        const int row = tid >> 3, u = tid & 7;          // 16 rows x 8 sixteen-byte units
+        const int g = row & 7;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (g < G) {
+            const int8_t* src = (row < 8 ? p.qa : p.qb) + (static_cast<int64_t>(bh) * G + g) * HD + u * 16;
+            val = *reinterpret_cast<const uint4*>(src);
+        }
+        *reinterpret_cast<uint4*>(smem + SM_Q + row * 128 + ((u ^ (row & 7)) << 4)) = val;
+    }
+    if (tid >= 128 && tid < 144) {
+        const int g = tid & 7;
+        const int64_t ix = static_cast<int64_t>(bh) * G + (g < G ? g : 0);
+        reinterpret_cast<float*>(smem + SM_EQZ)[tid - 128] = tid < 136 ? p.eq[ix] : p.z[ix];
+    }
+    fence_async_smem();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;"
+                     ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(tmem_slot))) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const int* ptab = p.page_table + static_cast<int64_t>(breq) * p.ppr;
+    // first pool row of the tile that starts at position `pos` (a tile lies inside one page)
+    auto tile_row = [&](int pos) -> int64_t {
+        const int pg = pos / PS;
+        return (static_cast<int64_t>(__ldg(ptab + pg)) * p.hkv + hkv) * PS + (pos - pg * PS);
+    };
+
+    if (warp == 0) {
+        // ================= producer: K's plane A =================
+        if (lane == 0) {
+            for (int t = 0; t < n_tiles; ++t) {
+                const int s = t % NA;
+                if (t >= NA) mbar_wait(bar(B_LFULL + s), ((t / NA) - 1) & 1, abort_flag, p.status);
+                const int64_t r = tile_row(lo + t * tstep);
+                mbar_expect_tx(bar(B_AFULL + s), 16384);
+                bulk_load(base + SM_KA + s * 16384, p.ka + r * HD, 16384, bar(B_AFULL + s));
+            }
+        }
+    } else if (warp == 2) {
+        // ================= producer: V's plane A and the key scales =================
+        if (lane == 0) {
+            for (int t = 0; t < n_tiles; ++t) {
+                const int s = t % NV;
+                if (t >= NV) mbar_wait(bar(B_VEMPTY + s), ((t / NV) - 1) & 1, abort_flag, p.status);
+                const int64_t r = tile_row(lo + t * tstep);
+                mbar_expect_tx(bar(B_VFULL + s), 16384 + 256);
+                bulk_load(base + SM_KS + s * 256, p.ek + r, 256, bar(B_VFULL + s));
+                tma_load_2d(base + SM_VA + s * 16384, &vmap, 0, static_cast<int>(r), bar(B_VFULL + s));
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            constexpr uint32_t ID_L = instr_desc(2, 1, 1, 0, 0, 16, 128);    // s8 x s8 -> s32
+            constexpr uint32_t ID_V = instr_desc(1, 0, 1, 1, 1, 32, 128);    // e4m3 x e5m2 -> f32, both MN-major
+            // descriptors of slot 0 of every buffer; a slot or K step further is an addition
+            const uint64_t dq = smem_desc(base + SM_Q, 16, 1024, 2);
+            const uint64_t dka = smem_desc(base + SM_KA, 16, 1024, 2);
+            const uint64_t dva = smem_desc(base + SM_VA, 16384, 1024, 2);
+            const uint64_t dvb = smem_desc(base + SM_VB, 16384, 1024, 2);
+            const uint64_t dw = smem_desc(base + SM_W, 128, 2048, 0);
+            const uint64_t dw2 = smem_desc(base + SM_W2, 128, 2048, 0);
+            bool acc2_started = false;
+            auto issue_logits = [&](int t) {
+                const int s = t % NA;
+                mbar_wait(bar(B_AFULL + s), (t / NA) & 1, abort_flag, p.status);
+                tc_fence_after();
+                mma4_i8<2, 2>(tmem + T_L + 16 * s, dka + s * 1024, dq, ID_L, 0u);   // 32 bytes per K step
+                tc_commit(bar(B_LFULL + s));
+            };
+            if (n_tiles > 0) issue_logits(0);
+            if (n_tiles > 1) issue_logits(1);
+            // iteration j: logits of tile j+2, value product of tile j-1, plane B of V of tile j-2
+            for (int j = 0; j <= n_tiles + 1; ++j) {
+                if (j + 2 < n_tiles) issue_logits(j + 2);
+                if (j >= 1 && j - 1 < n_tiles) {
+                    const int t = j - 1, s = t % NV;
+                    mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status);
+                    mbar_wait(bar(B_WREADY + (t & 1)), (t >> 1) & 1, abort_flag, p.status);
+                    tc_fence_after();
+                    // 32 keys per K step: 4096 bytes of V, 512 bytes of weights
+                    mma4_f8<256, 32>(tmem + T_ACC, dva + s * 1024, dw + (t & 1) * 256, ID_V, t > 0 ? 1u : 0u);
+                    tc_commit(bar(B_VEMPTY + s));
+                }
+                if (j >= 2) {
+                    const int t = j - 2, b2 = t % NB2;
+                    mbar_wait(bar(B_BFULL + t % NBQ), (t / NBQ) & 1, abort_flag, p.status);
+                    const volatile uint32_t* qfp = reinterpret_cast<const volatile uint32_t*>(smem + SM_QF + (t % NBQ) * 16);
+                    const uint32_t f[4] = {qfp[0], qfp[1], qfp[2], qfp[3]};
+                    if (f[0] | f[1] | f[2] | f[3]) {
+                        tc_fence_after();
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            if (f[ks]) {
+                                mma_f8(tmem + T_ACC2, dvb + b2 * 1024 + ks * 256, dw2 + b2 * 256 + ks * 32, ID_V, acc2_started);
+                                acc2_started = true;
+                            }
+                        }
+                    }
+                    tc_commit(bar(B_BFREE + b2));
+                    if (t == n_tiles - 1) tc_commit(bar(B_ALLDONE));
+                }
+            }
+        }
+    } else if (warp >= 4 && warp < 12) {
+        // ================= one thread per key; two groups take the even and the odd tiles =================
+        const int wg = (warp - 4) >> 2;
+        const int k = (tid - 128) & 127;                 // key in the tile = TMEM lane
+        const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+        float eqr[8], zr[8], cutr[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const int64_t ix = static_cast<int64_t>(bh) * G + (g < G ? g : 0);
+            eqr[g] = p.eq[ix];
+            zr[g] = p.z[ix];
+            cutr[g] = -p.cut[ix];
+        }
+        float rN[8], rM[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) rN[g] = rM[g] = 0.f;
+        int nlive = 0, nref = 0;
+        bool any_dense = false;
+        uint32_t* qm = reinterpret_cast<uint32_t*>(smem + SM_QM);
+        for (int t = wg; t < n_tiles; t += 2) {
+            const int s = t % NV;
+            const int tb = lo + t * tstep;
+            const int nrow = min(TK, hi - tb);
+            mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status);   // the scales ride with V
+            mbar_wait(bar(B_LFULL + t % NA), (t / NA) & 1, abort_flag, p.status);
+            tc_fence_after();
+            uint32_t c[16];
+            tmem_ld16(tmem + lane_addr + T_L + 16 * (t % NA), c);
+            tmem_wait_ld();
+            tc_fence_before();
+            const bool valid = k < nrow;
+            const float ek = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(smem + SM_KS + s * 256)[k]) * (1.0f / 256.0f);
+            float s1[8];
+            float top = -INFINITY;
+            bool live = !TRUNC;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                s1[g] = -INFINITY;
+                if (g < G && valid) {
+                    const float tk = eqr[g] * ek;
+                    s1[g] = fmaf(static_cast<float>(static_cast<int>(c[g]) * 256 + static_cast<int>(c[8 + g])), tk, -zr[g]);
+                    if (TRUNC && s1[g] >= cutr[g]) live = true;
+                    top = fmaxf(top, s1[g]);
+                }
+            }
+            live = live && valid;
+            const bool refk = live && top >= -rk;
+            const bool refv = live && top >= -rv;
+            const bool big = live && top >= BIG_TOP;
+            // a quarter (this warp's 32 keys) with enough refine-V keys fetches its plane B whole;
+            // the last, partial tile does not (rows past the range are not V's to read)
+            const bool dv = refv && !refk && !big;
+            const bool dense = nrow == TK && __popc(__ballot_sync(0xffffffffu, dv)) >= DENSE_MIN;
+            any_dense = any_dense || dense;
+            const bool helped = refk || big || (refv && !dense);
+            nlive += live ? 1 : 0;
+            nref += refk ? 1 : 0;
+            // a helper will want this key's second planes some tiles from now: start them towards L2
+            if (refk || refv) {
+                const int64_t row = tile_row(tb) + k;
+                if (refk) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kb + row * HD));
+                if (refv && !dense) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vb + row * HD));
+            }
+            const unsigned mk = __ballot_sync(0xffffffffu, refk);
+            const unsigned mv = __ballot_sync(0xffffffffu, refv);
+            const unsigned mh = __ballot_sync(0xffffffffu, helped);
+            if (t >= 2) mbar_wait(bar(B_VEMPTY + (t - 2) % NV), ((t - 2) / NV) & 1, abort_flag, p.status);   // the weight buffer is free
+            float w[8];
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const float e = (g < G && valid) ? ex2f(s1[g]) : 0.f;
+                if (TRUNC) rM[g] += live ? 0.f : e;
+                w[g] = (live && !helped) ? e : 0.f;
+                rN[g] += w[g];
+            }
+            // four E5M2 terms per weight: bytes [term][row]. The chain runs in fp16, two rows
+            // at a time: an E5M2 number is the high byte of an fp16, the differences are exact
+            uint32_t wb[8];
+#pragma unroll
+            for (int g = 0; g < 8; g += 2) {
+                __half2 r = __floats2half2_rn(w[g] * static_cast<float>(1 << W_BIAS), w[g + 1] * static_cast<float>(1 << W_BIAS));
+#pragma unroll
+                for (int term = 0; term < 4; ++term) {
+                    uint16_t pk;
+                    asm("cvt.rn.satfinite.e5m2x2.f16x2 %0, %1;" : "=h"(pk) : "r"(*reinterpret_cast<const uint32_t*>(&r)));
+                    const int word = term * 2 + (g >> 2), sh = (g & 3) * 8;   // byte term*8 + g (and g+1)
+                    if (g == 0 || g == 4) wb[word] = static_cast<uint32_t>(pk) << sh; else wb[word] |= static_cast<uint32_t>(pk) << sh;
+                    const uint32_t qb = __byte_perm(static_cast<uint32_t>(pk), 0u, 0x1404);
+                    r = __hmul2(__hsub2(r, *reinterpret_cast<const __half2*>(&qb)), __floats2half2_rn(8.0f, 8.0f));
+                }
+            }
+            uint8_t* wdst = smem + SM_W + (t & 1) * 4096 + k * 16;
+            *reinterpret_cast<uint4*>(wdst) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+            *reinterpret_cast<uint4*>(wdst + 2048) = make_uint4(wb[4], wb[5], wb[6], wb[7]);
+            if (!valid) {
+                // rows past the range hold whatever the pool holds (an E4M3 NaN times a zero
+                // weight is a NaN): clear them
+                uint4* vrow = reinterpret_cast<uint4*>(smem + SM_VA + s * 16384 + k * 128);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) vrow[u] = make_uint4(0, 0, 0, 0);
+            }
+            fence_async_smem();
+            mbar_arrive(bar(B_WREADY + (t & 1)));
+            // plane B of V for this quarter, and the weights it meets. The flags and their barrier
+            // have more slots than the key threads can run ahead of the MMA issuer (they need its
+            // logits); only the data buffers, two tiles deep, are waited for, and only when used
+            {
+                const int b2 = t % NB2, bq = t % NBQ;
+                if (dense) {
+                    if (lane == 0 && t >= NB2) mbar_wait(bar(B_BFREE + b2), ((t / NB2) - 1) & 1, abort_flag, p.status);
+                    __syncwarp();
+                    uint8_t* w2dst = smem + SM_W2 + b2 * 4096 + k * 16;
+                    *reinterpret_cast<uint4*>(w2dst) = dv ? make_uint4(wb[0], wb[1], wb[2], wb[3]) : make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(w2dst + 2048) = dv ? make_uint4(wb[4], wb[5], wb[6], wb[7]) : make_uint4(0, 0, 0, 0);
+                    fence_async_smem();
+                    __syncwarp();
+                }
+                if (lane == 0) {
+                    reinterpret_cast<volatile int*>(smem + SM_QF + bq * 16)[warp & 3] = dense ? 1 : 0;
+                    if (dense) {
+                        mbar_expect_tx(bar(B_BFULL + bq), 4096);
+                        tma_load_2d(base + SM_VB + b2 * 16384 + 4096 * (warp & 3), &vbmap, 0,
+                                    static_cast<int>(tile_row(tb)) + 32 * (warp & 3), bar(B_BFULL + bq));
+                    } else {
+                        mbar_arrive(bar(B_BFULL + bq));
+                    }
+                }
+            }
+            // hand the keys that need fp32 to the tile's helper
+            if (lane == 0) {
+                const int q = t % QD;
+                if (t >= QD) mbar_wait(bar(B_QFREE + q), ((t / QD) - 1) & 1, abort_flag, p.status);
+                qm[q * 12 + (warp & 3)] = mk;
+                qm[q * 12 + 4 + (warp & 3)] = mv;
+                qm[q * 12 + 8 + (warp & 3)] = mh;
+                mbar_arrive(bar(B_QFULL + q));
+            }
+            __syncwarp();
+        }
+
+        // ---- epilogue: the first group's thread k is channel k of the output ----
+        if (n_tiles > 0) mbar_wait(bar(B_ALLDONE), 0, abort_flag, p.status);
+        tc_fence_after();
+        float* sRed = reinterpret_cast<float*>(smem + SM_RED);
+        const int kk2 = wg * 128 + k;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            sRed[kk2 * 16 + g] = rN[g];
+            sRed[kk2 * 16 + 8 + g] = rM[g];
+        }
+        int* sCnt = reinterpret_cast<int*>(smem + SM_CNT);   // per key warp: live, refined, any dense quarter
+        {
+            const int a = __reduce_add_sync(0xffffffffu, nlive), b = __reduce_add_sync(0xffffffffu, nref);
+            if (lane == 0) {
+                sCnt[3 * (warp - 4)] = a;
+                sCnt[3 * (warp - 4) + 1] = b;
+                sCnt[3 * (warp - 4) + 2] = any_dense ? 1 : 0;
+            }
+        }
+        asm volatile("bar.sync 2, 384;" ::: "memory");   // both groups' sums, and the helpers'
+        if (wg == 0) {
+            // column sums in a fixed order: 8 runs of 32 entries, then the 8 partial sums
+            {
+                const int col = k & 15, part = k >> 4;
+                float sum = 0.f;
+                for (int i = 0; i < 32; ++i) sum += sRed[(part * 32 + i) * 16 + col];
+                sRed[(256 + part) * 16 + col] = sum;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (k < 16) {
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum += sRed[(256 + i) * 16 + k];
+                sRed[(256 + 8) * 16 + k] = sum;
+            }
+            bool use_b = false;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) use_b = use_b || sCnt[3 * i + 2] != 0;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            uint32_t a0[16], a1[16], b0[16], b1[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) a0[i] = a1[i] = b0[i] = b1[i] = 0u;   // an empty range never wrote the accumulators
+            if (n_tiles > 0) {
+                tmem_ld16(tmem + lane_addr + T_ACC, a0);
+                tmem_ld16(tmem + lane_addr + T_ACC + 16, a1);
+                if (use_b) {
+                    tmem_ld16(tmem + lane_addr + T_ACC2, b0);
+                    tmem_ld16(tmem + lane_addr + T_ACC2 + 16, b1);
+                }
+                tmem_wait_ld();
+            }
+            tc_fence_before();
+            const float* hout = reinterpret_cast<const float*>(smem + SM_HOUT);
+            const float vm = (TRUNC && p.vmean) ? p.vmean[static_cast<int64_t>(bh) * HD + k] : 0.f;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                if (g < G) {
+                    float x = __uint_as_float(a0[g]) + __uint_as_float(a0[8 + g]) * 0.125f +
+                              __uint_as_float(a1[g]) * (1.0f / 64.0f) + __uint_as_float(a1[8 + g]) * (1.0f / 512.0f);
+                    x += 0.125f * (__uint_as_float(b0[g]) + __uint_as_float(b0[8 + g]) * 0.125f +
+                                   __uint_as_float(b1[g]) * (1.0f / 64.0f) + __uint_as_float(b1[8 + g]) * (1.0f / 512.0f));
+                    x *= 1.0f / static_cast<float>(1 << W_BIAS);
+#pragma unroll
+                    for (int h = 0; h < NHELP; ++h) x += hout[h * (HOUT / 4) + g * 128 + k];
+                    x += sRed[(256 + 8) * 16 + 8 + g] * vm;
+                    p.o_part[(pix * G + g) * HD + k] = x;
+                }
+            }
+            if (k < G) {
+                float d = sRed[(256 + 8) * 16 + k] + sRed[(256 + 8) * 16 + 8 + k];
+#pragma unroll
+                for (int h = 0; h < NHELP; ++h) d += hout[h * (HOUT / 4) + 8 * 128 + k];
+                p.den_part[pix * G + k] = d;
+            }
+            if (k == 0) {
+                int a = 0, bcount = 0;
+                for (int i = 0; i < 8; ++i) { a += sCnt[3 * i]; bcount += sCnt[3 * i + 1]; }
+                p.cnt_part[pix * 2] = a;
+                p.cnt_part[pix * 2 + 1] = bcount;
+            }
+        }
+    } else if (warp >= 12) {
+        // ================= helpers: the keys that need both planes or an fp32 weight =================
+        // The whole warp works on one key. For the logits lane l is query row l & 7 and the
+        // quarter l >> 3 of the 128 channels: it holds that part of Q's two planes, multiplies
+        // it with the key's, and two shuffles sum the quarters. For the value sum every lane
+        // takes the eight weights and adds them into its four channels. The next key's words
+        // are in flight while this one is worked on.
+        const int h = warp - 12;
+        const int hg = lane & 7, part = lane >> 3;
+        int qaw[8], qbw[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int lu = 2 * part + (i >> 2);   // logical 16-byte unit, word i & 3 of it
+            const int off = ((lu ^ hg) << 4) + 4 * (i & 3);
+            qaw[i] = *reinterpret_cast<const int*>(smem + SM_Q + hg * 128 + off);
+            qbw[i] = *reinterpret_cast<const int*>(smem + SM_Q + (8 + hg) * 128 + off);
+        }
+        const float* eqz = reinterpret_cast<const float*>(smem + SM_EQZ);
+        const float eq_l = eqz[hg], z_l = eqz[8 + hg];
+        float acc[8][4], hden = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) acc[g][cc] = 0.f;
+        }
+        const uint32_t* qm = reinterpret_cast<const uint32_t*>(smem + SM_QM);
+        for (int t = h; t < n_tiles; t += NHELP) {
+            const int q = t % QD;
+            mbar_wait(bar(B_QFULL + q), (t / QD) & 1, abort_flag, p.status);
+            uint32_t mK[4], mV[4], mH[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                mK[i] = qm[q * 12 + i];
+                mV[i] = qm[q * 12 + 4 + i];
+                mH[i] = qm[q * 12 + 8 + i];
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_QFREE + q));
+            if (*abort_flag) break;
+            if ((mH[0] | mH[1] | mH[2] | mH[3]) == 0u) continue;
+            const int64_t row0 = tile_row(lo + t * tstep);
+            // the marked keys in position order
+            int wi = 0;
+            uint32_t rem = mH[0];
+            auto next_key = [&]() -> int {
+                while (rem == 0u && wi < 3) {
+                    ++wi;
+                    rem = wi == 1 ? mH[1] : (wi == 2 ? mH[2] : mH[3]);
+                }
+                if (rem == 0u) return -1;
+                const int b = __ffs(rem) - 1;
+                rem &= rem - 1;
+                return 32 * wi + b;
+            };
+            struct Words { uint4 ka0, ka1, kb0, kb1; uint32_t va, vb; uint16_t ek; bool isK; };
+            auto fetch = [&](int kk) -> Words {
+                Words x;
+                const uint32_t bit = 1u << (kk & 31);
+                const uint32_t wK = kk < 32 ? mK[0] : (kk < 64 ? mK[1] : (kk < 96 ? mK[2] : mK[3]));
+                const uint32_t wV = kk < 32 ? mV[0] : (kk < 64 ? mV[1] : (kk < 96 ? mV[2] : mV[3]));
+                x.isK = (wK & bit) != 0u;
+                const int64_t row = row0 + kk;
+                // K's planes are stored with their 16-byte units swizzled by slot
+                const int u0 = ((2 * part) ^ (kk & 7)) << 4, u1 = ((2 * part + 1) ^ (kk & 7)) << 4;
+                x.ka0 = __ldg(reinterpret_cast<const uint4*>(p.ka + row * HD + u0));
+                x.ka1 = __ldg(reinterpret_cast<const uint4*>(p.ka + row * HD + u1));
+                x.kb0 = x.kb1 = make_uint4(0, 0, 0, 0);
+                if (x.isK) {
+                    x.kb0 = __ldg(reinterpret_cast<const uint4*>(p.kb + row * HD + u0));
+                    x.kb1 = __ldg(reinterpret_cast<const uint4*>(p.kb + row * HD + u1));
+                }
+                x.va = __ldg(reinterpret_cast<const uint32_t*>(p.va + row * HD) + lane);
+                x.vb = (wV & bit) ? __ldg(reinterpret_cast<const uint32_t*>(p.vb + row * HD) + lane) : 0u;
+                x.ek = __ldg(p.ek + row);
+                return x;
+            };
+            auto dot8 = [&](const uint4& lo4, const uint4& hi4, const int (&qw)[8]) -> int {
+                int c = __dp4a(static_cast<int>(lo4.x), qw[0], 0);
+                c = __dp4a(static_cast<int>(lo4.y), qw[1], c);
+                c = __dp4a(static_cast<int>(lo4.z), qw[2], c);
+                c = __dp4a(static_cast<int>(lo4.w), qw[3], c);
+                c = __dp4a(static_cast<int>(hi4.x), qw[4], c);
+                c = __dp4a(static_cast<int>(hi4.y), qw[5], c);
+                c = __dp4a(static_cast<int>(hi4.z), qw[6], c);
+                c = __dp4a(static_cast<int>(hi4.w), qw[7], c);
+                c += __shfl_xor_sync(0xffffffffu, c, 8);
+                c += __shfl_xor_sync(0xffffffffu, c, 16);
+                return c;
+            };
+            int kk = next_key();
+            Words cur = fetch(kk);
+            while (kk >= 0) {
+                const int kn = next_key();
+                Words nxt = cur;
+                if (kn >= 0) nxt = fetch(kn);
+                const float tk = eq_l * (bf16_bits_to_float(cur.ek) * (1.0f / 256.0f));
+                const int c1 = dot8(cur.ka0, cur.ka1, qaw), c2 = dot8(cur.ka0, cur.ka1, qbw);
+                float sv = fmaf(static_cast<float>(c1 * 256 + c2), tk, -z_l);
+                if (cur.isK) {
+                    const int c3a = dot8(cur.kb0, cur.kb1, qaw), c3b = dot8(cur.kb0, cur.kb1, qbw);
+                    sv = sv + (static_cast<float>(c3a) + static_cast<float>(c3b) * (1.0f / 256.0f)) * tk;
+                }
+                const float wl = hg < G ? ex2f(sv) : 0.f;   // row hg's weight, in all four quarters' lanes
+                hden += wl;
+                float fa[4], fb[4];
+                e4m3x4_to_float(cur.va, fa);
+                e4m3x4_to_float(cur.vb, fb);
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) fa[cc] = fmaf(fb[cc], 0.125f, fa[cc]);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float wg_ = __shfl_sync(0xffffffffu, wl, g);
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) acc[g][cc] = fmaf(wg_, fa[cc], acc[g][cc]);
+                }
+                kk = kn;
+                cur = nxt;
+            }
+        }
+        // the sums go where V's ring was: wait until nothing reads or fills it any more
+        if (n_tiles > 0) mbar_wait(bar(B_ALLDONE), 0, abort_flag, p.status);
+        float* hout = reinterpret_cast<float*>(smem + SM_HOUT) + h * (HOUT / 4);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            *reinterpret_cast<float4*>(hout + g * 128 + 4 * lane) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+            if (lane == g) hout[8 * 128 + g] = hden;   // lane g sums row g's weights
+        }
+        asm volatile("bar.sync 2, 384;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
+    }
+}
+
+}  // namespace dsm100
+}  // namespace fold
+
+using namespace fold;
+
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(ptr);
+    }
+    return fn;
+}
+
+// A plane of V in the pool as rows of 128 bytes; a box is `box_rows` rows, swizzled on
+// its way into shared memory. The call does not know the pool's size: the row count
+// only bounds the coordinates, and every tile asked for lies inside a page.
+bool make_v_map(CUtensorMap* m, const void* va, int box_rows) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {128, 1ull << 30};
+    cuuint64_t strides[1] = {128};
+    cuuint32_t box[2] = {128, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(va), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" int fold_decode_combine(const float* o_part, const float* den_part, const int32_t* cnt_part,
+                                   const int32_t* seq_lens, void* out, int out_dtype, float* den, int32_t* counts,
+                                   int n_groups, int group, int head_dim, int n_kv_heads, int split, int chunk_keys,
+                                   float v_scale, void* stream);
+
+extern "C" int fold_decode_sm100_supported(int group, int head_dim, int page_size, int chunk_keys, int v8) {
+    return v8 && head_dim == 128 && group >= 1 && group <= 8 && page_size % 128 == 0 && chunk_keys % 128 == 0 &&
+           encode_fn() != nullptr;
+}
+
+extern "C" int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                                     const int8_t* kb, const void* ek, const void* va, const void* vb,
+                                     const float* vmean, const float* z, const float* cut,
+                                     const int32_t* page_table, const int32_t* seq_lens,
+                                     const int32_t* order, int n_groups, int group, int n_kv_heads,
+                                     int head_dim, int pages_per_request, int page_size, int split,
+                                     int chunk_keys, int truncate, float refine_k, float refine_v,
+                                     const float* refine_bands, float v_scale, float* o_part,
+                                     float* den_part, int32_t* cnt_part, void* out, int out_dtype,
+                                     float* den, int32_t* counts, int32_t* status, void* stream) {
+    FOLD_CHECK_ARG(qa && qb && eq && ka && kb && ek && va && vb && z && cut && page_table && seq_lens &&
+                       o_part && den_part && cnt_part && out && den && counts && status,
+                   "fold_decode_run_sm100: null pointer");
+    if (!fold_decode_sm100_supported(group, head_dim, page_size, chunk_keys, 1)) {
+        set_error("the tcgen05 decode takes an 8-bit V, head_dim 128, groups of 1..8 rows, pages and chunks of a multiple of 128 keys");
+        return FOLD_ERR_UNSUPPORTED;
+    }
+    FOLD_CHECK_ARG(split >= 1 && out_dtype >= 0 && out_dtype <= 2, "fold_decode_run_sm100: bad split or out_dtype");
+    dsm100::Params p;
+    p.qa = qa; p.qb = qb; p.eq = eq; p.ka = ka; p.kb = kb;
+    p.ek = static_cast<const uint16_t*>(ek);
+    p.va = static_cast<const uint8_t*>(va); p.vb = static_cast<const uint8_t*>(vb);
+    p.vmean = truncate ? vmean : nullptr; p.z = z; p.cut = cut;
+    p.page_table = page_table; p.seq_lens = seq_lens; p.order = order;
+    p.o_part = o_part; p.den_part = den_part; p.cnt_part = cnt_part;
+    p.nbh = n_groups; p.G = group; p.hkv = n_kv_heads; p.ppr = pages_per_request;
+    p.page_size = page_size; p.split = split; p.chunk_keys = chunk_keys; p.truncate = truncate;
+    p.rk = refine_k; p.rv = refine_v;
+    p.banded = refine_bands != nullptr;
+    if (refine_bands) {
+        p.band_e0 = refine_bands[0]; p.band_e1 = refine_bands[1];
+        p.rk1 = refine_bands[2]; p.rk2 = refine_bands[3]; p.rv1 = refine_bands[4]; p.rv2 = refine_bands[5];
+    } else {
+        p.band_e0 = p.band_e1 = p.rk1 = p.rk2 = p.rv1 = p.rv2 = 0.f;
+    }
+    p.status = status;
+    CUtensorMap vmap, vbmap;
+    if (!make_v_map(&vmap, va, 128) || !make_v_map(&vbmap, vb, 32)) {
+        set_error("fold_decode_run_sm100: cuTensorMapEncodeTiled failed");
+        return FOLD_ERR_LAUNCH;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (truncate) {
+        auto kern = dsm100::decode_sm100_kernel<true>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dsm100::SMEM_BYTES);
+        kern<<<n_groups * split, dsm100::NTHREADS, dsm100::SMEM_BYTES, st>>>(p, vmap, vbmap);
+    } else {
+        auto kern = dsm100::decode_sm100_kernel<false>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dsm100::SMEM_BYTES);
+        kern<<<n_groups * split, dsm100::NTHREADS, dsm100::SMEM_BYTES, st>>>(p, vmap, vbmap);
+    }
+    int rc = check_launch("fold_decode_run_sm100");
+    if (rc) return rc;
+    return fold_decode_combine(o_part, den_part, cnt_part, seq_lens, out, out_dtype, den, counts, n_groups, group,
+                               head_dim, n_kv_heads, split, chunk_keys, v_scale, stream);
+}

@@ -23,7 +23,15 @@ _lib.register(
     [P] * 14 + [I] * 10 + [F, F, P, F] + [P, P, P, P, I, P, P, P, P],
 )
 
+_lib.register("fold_decode_sm100_supported", [I, I, I, I, I])
+_lib.register(
+    "fold_decode_run_sm100",
+    [P] * 14 + [I] * 9 + [F, F, P, F] + [P, P, P, P, I, P, P, P, P],
+)
+_lib.register("fold_decode_combine", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P])
+
 _OUT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+KERNELS = ("auto", "mma", "sm100")
 
 
 class DecodeLaunch(Launch):
@@ -45,7 +53,7 @@ def prepare_fold_decode(
     qa, qb, eq, ka, kb, ek, v, z, cut, *,
     split=1, truncate=False, refine_k=10.0, refine_v=10.0, v8=False, v2=None, v_scale=1.0,
     vmean=None, page_table, page_size, seq_lens, n_kv_heads, reference="given", weight_terms=1,
-    order=None, out_dtype=torch.float32, refine_bands=(), chunk_keys=0, out=None,
+    order=None, out_dtype=torch.float32, refine_bands=(), chunk_keys=0, out=None, kernel="mma",
 ):
     """Bind one decode over a paged cache and return its launch.
 
@@ -54,6 +62,9 @@ def prepare_fold_decode(
     reference (written by the launch when `reference="mass"`) and `cut` its
     depth below `z` under which a key is dropped (`truncate`). Calling the
     launch returns `(out (NBH, G, D), den (NBH, G), counts (NBH, 2))`.
+    `kernel` picks the split-KV kernel: "mma" (warp-level, every shape), "sm100"
+    (tcgen05; an 8-bit V, D = 128, pages and chunks of a multiple of 128 keys;
+    its weights are four E5M2 terms whatever `weight_terms` says) or "auto".
     """
     NBH, G, D = qa.shape
     if G > 8:
@@ -68,6 +79,13 @@ def prepare_fold_decode(
         raise ValueError("reference is 'given' or 'mass'")
     if chunk_keys % 64:
         raise ValueError(f"chunk={chunk_keys} is not a multiple of 64")
+    if kernel not in KERNELS:
+        raise ValueError(f"kernel is one of {KERNELS}")
+    can = bool(_lib.lib.fold_decode_sm100_supported(G, D, int(page_size), int(chunk_keys), int(bool(v8))))
+    if kernel == "sm100" and not can:
+        raise NotImplementedError(
+            "the tcgen05 decode takes an 8-bit V, head_dim 128, pages and chunks of a multiple of 128 keys")
+    use_sm100 = can and kernel in ("auto", "sm100")
     dev = qa.device
     split = int(split)
     o_part = torch.empty((NBH * split, G, D), device=dev, dtype=torch.float32)
@@ -88,12 +106,16 @@ def prepare_fold_decode(
         o_part.data_ptr(), den_part.data_ptr(), cnt_part.data_ptr(),
     )
     tail = (den.data_ptr(), counts.data_ptr(), status.data_ptr())
+    fixed_sm100 = fixed[:23] + fixed[24:]   # the same arguments without weight_terms
 
     def run(out=None):
         o = out_t if out is None else out
         if reference == "mass":
             mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z)
-        _lib.call("fold_decode_run", *fixed, o.data_ptr(), _OUT[o.dtype], *tail, _lib.stream(dev))
+        if use_sm100:
+            _lib.call("fold_decode_run_sm100", *fixed_sm100, o.data_ptr(), _OUT[o.dtype], *tail, _lib.stream(dev))
+        else:
+            _lib.call("fold_decode_run", *fixed, o.data_ptr(), _OUT[o.dtype], *tail, _lib.stream(dev))
         return o, den, counts
 
     launch = DecodeLaunch(

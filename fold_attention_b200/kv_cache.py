@@ -72,6 +72,7 @@ class FoldKVCache:
         check_range=False,
         chunk=None,
         device="cuda",
+        kernel="mma",
     ):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads do not group over {n_kv_heads} KV heads")
@@ -85,6 +86,8 @@ class FoldKVCache:
         self.v_headroom = float(v_headroom)
         self.split = split
         self.device = torch.device(device)
+        # the split-KV kernel (not a reference argument): "mma", "sm100" or "auto"
+        self.kernel = kernel
         if head_dim not in (64, 128):
             raise NotImplementedError(f"head_dim {head_dim}: the cache takes 64 or 128")
         if self.group > 8:
@@ -274,7 +277,7 @@ class FoldKVCache:
 
     def _launch(self, split, out_dtype):
         refine = self._refine()
-        key = (split, out_dtype, refine)
+        key = (split, out_dtype, refine, self.kernel)
         if key not in self._launches:
             truncate = self.depth is not None
             self._launches[key] = prepare_fold_decode(
@@ -290,6 +293,7 @@ class FoldKVCache:
                     if self._banded() else ()
                 ),
                 chunk_keys=self.chunk or 0,
+                kernel=self.kernel,
             )
         return self._launches[key]
 

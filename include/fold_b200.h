@@ -105,6 +105,35 @@ int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const i
                     float v_scale, float* o_part, float* den_part, int32_t* cnt_part, void* out,
                     int out_dtype, float* den, int32_t* counts, int32_t* status, void* stream);
 
+/* The same decode on tcgen05 tensor cores (TMEM accumulators, the E4M3 V planes
+ * read by the tensor core as stored; weights carried as four E5M2 terms). K's
+ * and V's first planes stream whole through shared memory; V's second plane is
+ * fetched by 32-key quarters where enough keys pass the refine-V gate; the
+ * remaining refined keys, and keys whose weight passes 2^8, are summed in fp32
+ * by helper warps in a fixed order. For an 8-bit V, head_dim 128, groups of
+ * 1..8 rows, page_size and chunk_keys multiples of 128
+ * (fold_decode_sm100_supported, which also wants the driver's tensor-map
+ * encoder). Arguments as fold_decode_run without weight_terms; `va` and `vb`
+ * 16-byte aligned. Replaces the same reference code as fold_decode_run. */
+int fold_decode_sm100_supported(int group, int head_dim, int page_size, int chunk_keys, int v8);
+int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                          const int8_t* kb, const void* ek, const void* va, const void* vb,
+                          const float* vmean, const float* z, const float* cut,
+                          const int32_t* page_table, const int32_t* seq_lens, const int32_t* order,
+                          int n_groups, int group, int n_kv_heads, int head_dim,
+                          int pages_per_request, int page_size, int split, int chunk_keys,
+                          int truncate, float refine_k, float refine_v,
+                          const float* refine_bands /* host */, float v_scale, float* o_part,
+                          float* den_part, int32_t* cnt_part, void* out, int out_dtype, float* den,
+                          int32_t* counts, int32_t* status, void* stream);
+
+/* The combine step alone: out = (sum over splits of o_part) * v_scale / (sum of
+ * den_part), in slot order. Replaces src/fold_attention/decode/combine.py:10-162. */
+int fold_decode_combine(const float* o_part, const float* den_part, const int32_t* cnt_part,
+                        const int32_t* seq_lens, void* out, int out_dtype, float* den,
+                        int32_t* counts, int n_groups, int group, int head_dim, int n_kv_heads,
+                        int split, int chunk_keys, float v_scale, void* stream);
+
 /* fold_decode_run for callers that may not allocate device memory.
  * No counterpart in the reference (its launches allocate their partial buffers
  * with torch). Same arguments as fold_decode_run without o_part, den_part and

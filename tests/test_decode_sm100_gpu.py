@@ -1,0 +1,134 @@
+"""The tcgen05 split-KV decode kernel (`kernel="sm100"`) against the float64
+model of the cache's own planes (oracle/decode.py), against the warp-level
+kernel, and against itself (bit-repeatability, batch invariance under a fixed
+chunk). Gates are chosen so that each of its paths carries keys: the tensor-core
+stream, the whole-quarter plane B of V, and the helper warps (refine-K keys,
+sparse refine-V keys, weights past the E5M2 range)."""
+import pytest
+import torch
+
+from oracle import decode as od
+from test_decode_gpu import _cache, _layer, _planes, _rel
+
+pytestmark = pytest.mark.gpu
+
+# (refine_k, refine_v): the defaults' shape, tight gates, plane B of V nearly everywhere
+# (whole quarters), no refinement at all (a weight far past 2^8 still has to come out right)
+GATES = [(10.0, 10.0), (3.0, 3.0), (2.0, 14.0), (-1e9, 1e9), (-1e9, -1e9)]
+
+
+def _launch(c, z, *, depth, rk, rv, split, chunk, HKV, ps, kernel):
+    from fold_attention_b200.decode.launch import prepare_fold_decode
+
+    return prepare_fold_decode(
+        c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, c.cut, split=split,
+        truncate=depth is not None, refine_k=rk, refine_v=rv, v8=True, v2=c.vb, v_scale=c.v_scale,
+        vmean=c.vmean, page_table=c.page_table, page_size=ps, seq_lens=c.seq_lens,
+        n_kv_heads=HKV, weight_terms=2, chunk_keys=chunk, kernel=kernel,
+    )
+
+
+@pytest.mark.parametrize("depth", [None, 16.0, 8.0])
+@pytest.mark.parametrize("ps,G,lens,split,chunk", [
+    (256, 8, [1500, 700, 64, 2049], 1, 0),
+    (256, 8, [1500, 700, 64, 2049], 3, 0),     # ranges without a key: 64 keys over 3 splits
+    (128, 4, [300, 1, 129, 1000], 2, 0),
+    (256, 1, [513, 2000], 0, 512),
+    (256, 2, [5000, 100], 0, 1024),
+])
+def test_the_tcgen05_kernel_is_the_model(depth, ps, G, lens, split, chunk):
+    HKV, D = 2, 128
+    B = len(lens)
+    q, k, v, cu = _layer(B, HKV * G, HKV, D, lens, seed=2, vmu=0.5)
+    c = _cache(B, HKV * G, HKV, D, lens, ps=ps, v8=True, depth=depth)
+    c.write_prompt(k, v, cu, lens)
+    c.attend(q)
+    z = (torch.ceil(c.z * 16) / 16).contiguous()
+    sp = split if not chunk else -(-max(lens) // chunk)
+    for rk, rv in GATES:
+        run = _launch(c, z, depth=depth, rk=rk, rv=rv, split=sp, chunk=chunk, HKV=HKV, ps=ps, kernel="sm100")
+        out, den, counts = run()
+        torch.cuda.synchronize()
+        assert int(run.status) == 0
+        first = (out.clone(), den.clone(), counts.clone())
+        out, den, counts = run()
+        torch.cuda.synchronize()
+        assert torch.equal(out, first[0]) and torch.equal(den, first[1]) and torch.equal(counts, first[2])
+        ref = _launch(c, z, depth=depth, rk=rk, rv=rv, split=sp, chunk=chunk, HKV=HKV, ps=ps, kernel="mma")
+        _, _, counts_mma = ref()
+        torch.cuda.synchronize()
+        assert torch.equal(counts, counts_mma)
+        for b in range(B):
+            for h in range(HKV):
+                bh = b * HKV + h
+                ka, kb, ek, va, vb = _planes(c, b, h, lens[b])
+                want, wden, nlive, nref = od.decode_model(
+                    c.qa[bh], c.qb[bh], c.eq[bh], ka, kb, ek, va, vb, c.v_scale, z[bh], depth,
+                    rk, rv, lens[b], vmean=c.vmean[bh] if depth is not None else None)
+                assert counts[bh].tolist() == [nlive, nref], (rk, rv, b, h)
+                # weights are 12-bit (four E5M2 terms off an fp16): 2^-11 each, less in the sum
+                assert _rel(out[bh], want) < 1e-3, (rk, rv, b, h, _rel(out[bh], want))
+                assert ((den[bh].double() - wden).abs() / wden).max().item() < 1e-3
+
+
+def test_the_cache_serves_through_either_kernel():
+    """FoldKVCache with kernel="sm100": append + attend tracks the softmax, a
+    request's output under a fixed chunk is the same bits alone and in a batch."""
+    lens = [3000, 1000, 5000]
+    B, H, HKV, D = len(lens), 16, 2, 128
+    q, k, v, cu = _layer(B, H, HKV, D, lens, seed=6)
+    kw = dict(ps=128, v8=True, depth=16.0, chunk=1024, v_scale=0.03125)
+    full = _cache(B, H, HKV, D, lens, kernel="sm100", **kw)
+    full.write_prompt(k, v, cu, lens)
+    o_full = full.attend(q)
+    cnt_full = full.counts.clone()
+    other = _cache(B, H, HKV, D, lens, kernel="mma", seed=3, **kw)
+    other.write_prompt(k, v, cu, lens)
+    o_mma = other.attend(q)
+    assert torch.equal(cnt_full, other.counts)
+    assert _rel(o_full.float(), o_mma.float()) < 2e-3
+    for b in range(B):
+        one = _cache(1, H, HKV, D, [lens[b]], seed=b, kernel="sm100", **kw)
+        a, e = int(cu[b]), int(cu[b + 1])
+        one.write_prompt(k[a:e], v[a:e], torch.tensor([0, lens[b]], device="cuda", dtype=torch.int32), [lens[b]])
+        o_one = one.attend(q[b:b + 1])
+        assert torch.equal(o_one[0], o_full[b])
+        assert torch.equal(one.counts, cnt_full[b * HKV:(b + 1) * HKV])
+    # serving steps: the appended token lands in a page the next attend streams
+    G = H // HKV
+    ks = [k[int(cu[b]):int(cu[b + 1])].float() for b in range(B)]
+    vs = [v[int(cu[b]):int(cu[b + 1])].float() for b in range(B)]
+    c = _cache(B, H, HKV, D, [n + 8 for n in lens], ps=128, v8=True, depth=16.0, kernel="sm100")
+    c.write_prompt(k, v, cu, lens)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    for step in range(6):
+        qn = torch.randn(B, H, D, device="cuda", generator=g).bfloat16()
+        kn = torch.randn(B, HKV, D, device="cuda", generator=g).bfloat16()
+        vn = torch.randn(B, HKV, D, device="cuda", generator=g).bfloat16()
+        got = c.decode(qn, kn, vn)
+        for b in range(B):
+            ks[b] = torch.cat([ks[b], kn[b].float()[None]])
+            vs[b] = torch.cat([vs[b], vn[b].float()[None]])
+    want = torch.stack([
+        torch.cat([od.attend_fp32(qn[b, h * G:(h + 1) * G].float(), ks[b][:, h], vs[b][:, h]) for h in range(HKV)])
+        for b in range(B)])
+    assert _rel(got.float(), want) < 2.0 ** (-16.0 / 3)   # the bound the depth test uses
+
+
+def test_what_the_tcgen05_kernel_does_not_take():
+    from fold_attention_b200.decode.launch import prepare_fold_decode
+
+    lens = [300]
+    q, k, v, cu = _layer(1, 8, 2, 128, lens, seed=1)
+    c = _cache(1, 8, 2, 128, lens, ps=64, v8=True)   # pages of 64 keys
+    c.write_prompt(k, v, cu, lens)
+    c.attend(q)
+    with pytest.raises(NotImplementedError, match="multiple of 128"):
+        _launch(c, c.z, depth=None, rk=10.0, rv=10.0, split=1, chunk=0, HKV=2, ps=64, kernel="sm100")
+    with pytest.raises(ValueError, match="kernel is one of"):
+        _launch(c, c.z, depth=None, rk=10.0, rv=10.0, split=1, chunk=0, HKV=2, ps=64, kernel="wgmma")
+    # "auto" falls back to the warp-level kernel where the tcgen05 one does not apply
+    run = _launch(c, c.z, depth=None, rk=10.0, rv=10.0, split=1, chunk=0, HKV=2, ps=64, kernel="auto")
+    run()
+    torch.cuda.synchronize()
+    assert int(run.status) == 0
