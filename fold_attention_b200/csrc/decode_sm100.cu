@@ -36,7 +36,7 @@
 // same on every run. The partial is the tensor-core sum plus the four helpers' sums.
 //
 // Warps: 0 and 2 producers (two 5-slot rings: K's plane A by bulk copy; plane A of V
-// by TMA with the 128-byte swizzle, with the key scales), 1 MMA issuer (owns 128 TMEM
+// by TMA with the 128-byte swizzle, with the key scales), 1 and 3 MMA issuers (logits; values. 256 TMEM
 // columns), 4-7 and 8-11 one thread per key of the even and of the odd tiles, 12-15
 // helpers. A K slot is free again as soon as its logits are out, a V slot when its
 // value product has retired. Every wait is bounded (about a second); on expiry
@@ -55,7 +55,7 @@ namespace dsm100 {
 constexpr int TK = 128;          // keys per tile
 constexpr int HD = 128;
 constexpr int NA = 5;            // ring slots of K's plane A
-constexpr int NV = 5;            // ring slots of V's plane A and the key scales
+constexpr int NV = NA;           // ring slots of V's plane A and the key scales
 constexpr int QD = 8;            // tiles of helper masks in flight
 constexpr int NHELP = 4;
 constexpr int NBQ = 8;            // tiles of quarter flags (and their barrier) in flight: more than the key threads can lead by
@@ -367,39 +367,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             }
         }
     } else if (warp == 1) {
-        // ================= MMA issuer =================
+        // ================= MMA issuer: logits =================
         if (lane == 0) {
             constexpr uint32_t ID_L = instr_desc(2, 1, 1, 0, 0, 16, 128);    // s8 x s8 -> s32
-            constexpr uint32_t ID_V = instr_desc(1, 0, 1, 1, 1, 32, 128);    // e4m3 x e5m2 -> f32, both MN-major
-            // descriptors of slot 0 of every buffer; a slot or K step further is an addition
+            // descriptors of slot 0; a slot or K step further is an addition
             const uint64_t dq = smem_desc(base + SM_Q, 16, 1024, 2);
             const uint64_t dka = smem_desc(base + SM_KA, 16, 1024, 2);
+            for (int t = 0; t < n_tiles; ++t) {
+                const int s = t % NA;
+                // the TMEM slot was tile t-NA's: its value MMAs retired, so its weights were done and
+                // its logits read (NA == NV: the same slot number)
+                if (t >= NA) mbar_wait(bar(B_VEMPTY + s), ((t / NA) - 1) & 1, abort_flag, p.status);
+                mbar_wait(bar(B_AFULL + s), (t / NA) & 1, abort_flag, p.status);
+                tc_fence_after();
+                mma4_i8<2, 2>(tmem + T_L + 16 * s, dka + s * 1024, dq, ID_L, 0u);   // 32 bytes per K step
+                tc_commit(bar(B_LFULL + s));
+            }
+        }
+    } else if (warp == 3) {
+        // ================= MMA issuer: values =================
+        if (lane == 0) {
+            constexpr uint32_t ID_V = instr_desc(1, 0, 1, 1, 1, 32, 128);    // e4m3 x e5m2 -> f32, both MN-major
             const uint64_t dva = smem_desc(base + SM_VA, 16384, 1024, 2);
             const uint64_t dvb = smem_desc(base + SM_VB, 16384, 1024, 2);
             const uint64_t dw = smem_desc(base + SM_W, 128, 2048, 0);
             const uint64_t dw2 = smem_desc(base + SM_W2, 128, 2048, 0);
             bool acc2_started = false;
-            auto issue_logits = [&](int t) {
-                const int s = t % NA;
-                mbar_wait(bar(B_AFULL + s), (t / NA) & 1, abort_flag, p.status);
-                tc_fence_after();
-                mma4_i8<2, 2>(tmem + T_L + 16 * s, dka + s * 1024, dq, ID_L, 0u);   // 32 bytes per K step
-                tc_commit(bar(B_LFULL + s));
-            };
-            if (n_tiles > 0) issue_logits(0);
-            if (n_tiles > 1) issue_logits(1);
-            // iteration j: logits of tile j+2, value product of tile j-1, plane B of V of tile j-2
-            for (int j = 0; j <= n_tiles + 1; ++j) {
-                if (j + 2 < n_tiles) issue_logits(j + 2);
-                if (j >= 1 && j - 1 < n_tiles) {
-                    const int t = j - 1, s = t % NV;
-                    mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status);
-                    mbar_wait(bar(B_WREADY + (t & 1)), (t >> 1) & 1, abort_flag, p.status);
-                    tc_fence_after();
-                    // 32 keys per K step: 4096 bytes of V, 512 bytes of weights
-                    mma4_f8<256, 32>(tmem + T_ACC, dva + s * 1024, dw + (t & 1) * 256, ID_V, t > 0 ? 1u : 0u);
-                    tc_commit(bar(B_VEMPTY + s));
-                }
+            // iteration j: plane B of V of tile j-2 (its quarters were asked for two tiles ago), then
+            // the value product of tile j. The order matters: a key thread of tile t waits for the
+            // value MMAs of t-2 and then, by parity, for the plane-B buffer of t-2; the commit for
+            // t-4's buffer must be the older of the two or that parity test passes a phase early
+            for (int j = 0; j < n_tiles + 2; ++j) {
                 if (j >= 2) {
                     const int t = j - 2, b2 = t % NB2;
                     mbar_wait(bar(B_BFULL + t % NBQ), (t / NBQ) & 1, abort_flag, p.status);
@@ -416,9 +414,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                         }
                     }
                     tc_commit(bar(B_BFREE + b2));
-                    if (t == n_tiles - 1) tc_commit(bar(B_ALLDONE));
+                }
+                if (j < n_tiles) {
+                    const int t = j, s = t % NV;
+                    mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status);
+                    mbar_wait(bar(B_WREADY + (t & 1)), (t >> 1) & 1, abort_flag, p.status);
+                    tc_fence_after();
+                    // 32 keys per K step: 4096 bytes of V, 512 bytes of weights
+                    mma4_f8<256, 32>(tmem + T_ACC, dva + s * 1024, dw + (t & 1) * 256, ID_V, t > 0 ? 1u : 0u);
+                    tc_commit(bar(B_VEMPTY + s));
                 }
             }
+            tc_commit(bar(B_ALLDONE));
         }
     } else if (warp >= 4 && warp < 12) {
         // ================= one thread per key; two groups take the even and the odd tiles =================

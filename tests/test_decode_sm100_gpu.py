@@ -51,9 +51,10 @@ def test_the_tcgen05_kernel_is_the_model(depth, ps, G, lens, split, chunk):
         torch.cuda.synchronize()
         assert int(run.status) == 0
         first = (out.clone(), den.clone(), counts.clone())
-        out, den, counts = run()
-        torch.cuda.synchronize()
-        assert torch.equal(out, first[0]) and torch.equal(den, first[1]) and torch.equal(counts, first[2])
+        for _ in range(8):   # the same bits on every run, whatever the warps' timing
+            out, den, counts = run()
+            torch.cuda.synchronize()
+            assert torch.equal(out, first[0]) and torch.equal(den, first[1]) and torch.equal(counts, first[2])
         ref = _launch(c, z, depth=depth, rk=rk, rv=rv, split=sp, chunk=chunk, HKV=HKV, ps=ps, kernel="mma")
         _, _, counts_mma = ref()
         torch.cuda.synchronize()
