@@ -208,7 +208,7 @@ def cpu_reference_tflops(seconds_budget=12.0):
     return flops(1, S, H, D) / dt / 1e12, f"B1 H4 S{S} D{D} causal FP32 autograd x{n}, scaled by FLOPs"
 
 
-def decode_extra(device, steps=8, B=32, dense=False, kernel="mma"):
+def decode_extra(device, steps=8, B=32, dense=False, kernel="auto"):
     """Config-5-shaped decode at a reduced batch (extra keys, not the headline):
     v8, depth 16, GQA 64/8, D128, lengths log-uniform in [4096, 131072]; or with
     `dense` config 4's shape: bf16 V, depth None, GQA 32/8, lengths uniform in
@@ -259,7 +259,7 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="mma"):
     byts = keys * (D + 2 + D * refk + vb * live)
     name = (f"config4-shaped decode bf16 dense B{B} H32/8 D128 lens U[1024,32768] chunk4096" if dense else
             f"config5-shaped decode v8 depth16 B{B} H64/8 D128 lens logU[4096,131072] chunk8192")
-    return dict(workload=name, kernel=kernel,
+    return dict(workload=name, kernel="/".join(sorted({l.kernel for l in c._launches.values()})),
                 us_per_step=us, keys=keys, live_fraction=live, refined_fraction=refk,
                 algorithmic_gbs=byts / us / 1e3, hbm_frac=byts / us / 1e3 / peaks()["hbm"])
 
@@ -296,7 +296,7 @@ def main():
     ap.add_argument("--decode-only", action="store_true",
                     help="run only the config-5-shaped decode (extra keys) and print its dict")
     ap.add_argument("--decode-batch", type=int, default=32)
-    ap.add_argument("--decode-kernel", default="mma", choices=("auto", "mma", "sm100"))
+    ap.add_argument("--decode-kernel", default="auto", choices=("auto", "mma", "sm100"))
     ap.add_argument("--decode-dense", action="store_true", help="config 4's shape instead of config 5's")
     args = ap.parse_args()
     CFG["B"] = args.batch

@@ -55,9 +55,11 @@ namespace dsm100 {
 constexpr int TK = 128;          // keys per tile
 constexpr int HD = 128;
 constexpr int NA = 5;            // ring slots of K's plane A
-constexpr int NV = NA;           // ring slots of V's plane A and the key scales
+constexpr int NV = 5;            // ring slots of V's plane A and the key scales
 constexpr int QD = 8;            // tiles of helper masks in flight
 constexpr int NHELP = 4;
+constexpr int HD_KEYS = 4;       // keys whose rows a helper has in flight into its staging slots
+constexpr int HSLOT = 528;       // a staging slot: Ka, Kb, Va, Vb rows of 128 bytes, the scale's word, the key's note
 constexpr int NBQ = 8;            // tiles of quarter flags (and their barrier) in flight: more than the key threads can lead by
 constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weights) in flight
 constexpr int DENSE_MIN = 4;     // refine-V keys in a 32-key quarter from which the quarter's plane B is fetched whole
@@ -77,7 +79,8 @@ constexpr int SM_W2 = SM_W + 2 * 4096;                // NB2 x the same, masked 
 constexpr int SM_QM = SM_W2 + NB2 * 4096;             // QD x { refine-K, refine-V, helper } x 4 mask words
 constexpr int SM_QF = SM_QM + QD * 48;                // NBQ x 4 quarter flags
 constexpr int SM_EQZ = SM_QF + NBQ * 16;              // eq[8], z[8] of the row group
-constexpr int SM_BAR = SM_EQZ + 64;
+constexpr int SM_HST = (SM_EQZ + 64 + 15) / 16 * 16;  // NHELP x HD_KEYS staging slots
+constexpr int SM_BAR = SM_HST + NHELP * HD_KEYS * HSLOT;
 // after the last MMA the rings are dead and hold the final reduction: 256 x 16 row sums,
 // 8 x 16 partial and 16 full column sums, per-warp counters; and the helpers' sums
 constexpr int SM_RED = SM_KA;
@@ -150,6 +153,12 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async(uint32_t dst, const void* src, int bytes /* 16 or 0: zero fill */) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -376,8 +385,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             for (int t = 0; t < n_tiles; ++t) {
                 const int s = t % NA;
                 // the TMEM slot was tile t-NA's: its value MMAs retired, so its weights were done and
-                // its logits read (NA == NV: the same slot number)
-                if (t >= NA) mbar_wait(bar(B_VEMPTY + s), ((t / NA) - 1) & 1, abort_flag, p.status);
+                // its logits read
+                if (t >= NA) mbar_wait(bar(B_VEMPTY + (t - NA) % NV), ((t - NA) / NV) & 1, abort_flag, p.status);
                 mbar_wait(bar(B_AFULL + s), (t / NA) & 1, abort_flag, p.status);
                 tc_fence_after();
                 mma4_i8<2, 2>(tmem + T_L + 16 * s, dka + s * 1024, dq, ID_L, 0u);   // 32 bytes per K step
@@ -650,11 +659,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
         }
     } else if (warp >= 12) {
         // ================= helpers: the keys that need both planes or an fp32 weight =================
-        // The whole warp works on one key. For the logits lane l is query row l & 7 and the
-        // quarter l >> 3 of the 128 channels: it holds that part of Q's two planes, multiplies
-        // it with the key's, and two shuffles sum the quarters. For the value sum every lane
-        // takes the eight weights and adds them into its four channels. The next key's words
-        // are in flight while this one is worked on.
+        // The whole warp works on one key. Its four rows (both planes of K and of V) come into a
+        // staging slot with one 16-byte copy per lane, four keys ahead of their use. For the
+        // logits lane l is query row l & 7 and the quarter l >> 3 of the 128 channels: it holds
+        // that part of Q's two planes, multiplies it with the key's, and two shuffles sum the
+        // quarters. For the value sum every lane takes the eight weights and adds them into its
+        // four channels. Keys are taken in (tile, position) order whatever the timing.
         const int h = warp - 12;
         const int hg = lane & 7, part = lane >> 3;
         int qaw[8], qbw[8];
@@ -674,98 +684,128 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             for (int cc = 0; cc < 4; ++cc) acc[g][cc] = 0.f;
         }
         const uint32_t* qm = reinterpret_cast<const uint32_t*>(smem + SM_QM);
-        for (int t = h; t < n_tiles; t += NHELP) {
-            const int q = t % QD;
-            mbar_wait(bar(B_QFULL + q), (t / QD) & 1, abort_flag, p.status);
-            uint32_t mK[4], mV[4], mH[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                mK[i] = qm[q * 12 + i];
-                mV[i] = qm[q * 12 + 4 + i];
-                mH[i] = qm[q * 12 + 8 + i];
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(B_QFREE + q));
-            if (*abort_flag) break;
-            if ((mH[0] | mH[1] | mH[2] | mH[3]) == 0u) continue;
-            const int64_t row0 = tile_row(lo + t * tstep);
-            // the marked keys in position order
-            int wi = 0;
-            uint32_t rem = mH[0];
-            auto next_key = [&]() -> int {
+        uint8_t* stage = smem + SM_HST + h * HD_KEYS * HSLOT;
+        const uint32_t stage_a = base + SM_HST + h * HD_KEYS * HSLOT;
+        const uint8_t* plane_l = part == 0 ? reinterpret_cast<const uint8_t*>(p.ka)
+                               : part == 1 ? reinterpret_cast<const uint8_t*>(p.kb)
+                               : part == 2 ? p.va : p.vb;   // the plane this lane copies from
+
+        // issue side: the tile whose marked keys are being handed out
+        int it = h;                       // next tile to open
+        uint32_t mK[4] = {0, 0, 0, 0}, mV[4] = {0, 0, 0, 0}, mH[4] = {0, 0, 0, 0};
+        int wi = 4;                       // word of mH in hand (4: none left)
+        uint32_t rem = 0u;
+        int64_t row0 = 0;
+        int issued = 0, taken = 0;        // keys copied for, keys summed
+        bool open_tiles = n_tiles > h;
+
+        // one more key's rows on their way, if a key is to be had without waiting (or with, when
+        // `block` says nothing else is left to do); false when no key came
+        auto issue_one = [&](bool block) -> bool {
+            while (true) {
                 while (rem == 0u && wi < 3) {
                     ++wi;
                     rem = wi == 1 ? mH[1] : (wi == 2 ? mH[2] : mH[3]);
                 }
-                if (rem == 0u) return -1;
-                const int b = __ffs(rem) - 1;
-                rem &= rem - 1;
-                return 32 * wi + b;
-            };
-            struct Words { uint4 ka0, ka1, kb0, kb1; uint32_t va, vb; uint16_t ek; bool isK; };
-            auto fetch = [&](int kk) -> Words {
-                Words x;
-                const uint32_t bit = 1u << (kk & 31);
-                const uint32_t wK = kk < 32 ? mK[0] : (kk < 64 ? mK[1] : (kk < 96 ? mK[2] : mK[3]));
-                const uint32_t wV = kk < 32 ? mV[0] : (kk < 64 ? mV[1] : (kk < 96 ? mV[2] : mV[3]));
-                x.isK = (wK & bit) != 0u;
-                const int64_t row = row0 + kk;
-                // K's planes are stored with their 16-byte units swizzled by slot
-                const int u0 = ((2 * part) ^ (kk & 7)) << 4, u1 = ((2 * part + 1) ^ (kk & 7)) << 4;
-                x.ka0 = __ldg(reinterpret_cast<const uint4*>(p.ka + row * HD + u0));
-                x.ka1 = __ldg(reinterpret_cast<const uint4*>(p.ka + row * HD + u1));
-                x.kb0 = x.kb1 = make_uint4(0, 0, 0, 0);
-                if (x.isK) {
-                    x.kb0 = __ldg(reinterpret_cast<const uint4*>(p.kb + row * HD + u0));
-                    x.kb1 = __ldg(reinterpret_cast<const uint4*>(p.kb + row * HD + u1));
+                if (rem != 0u) break;
+                if (!open_tiles) return false;
+                // open the next tile's masks
+                const int q = it % QD;
+                if (!mbar_try(bar(B_QFULL + q), (it / QD) & 1)) {
+                    if (!block) return false;
+                    mbar_wait(bar(B_QFULL + q), (it / QD) & 1, abort_flag, p.status);
+                    if (*abort_flag) { open_tiles = false; return false; }
                 }
-                x.va = __ldg(reinterpret_cast<const uint32_t*>(p.va + row * HD) + lane);
-                x.vb = (wV & bit) ? __ldg(reinterpret_cast<const uint32_t*>(p.vb + row * HD) + lane) : 0u;
-                x.ek = __ldg(p.ek + row);
-                return x;
-            };
-            auto dot8 = [&](const uint4& lo4, const uint4& hi4, const int (&qw)[8]) -> int {
-                int c = __dp4a(static_cast<int>(lo4.x), qw[0], 0);
-                c = __dp4a(static_cast<int>(lo4.y), qw[1], c);
-                c = __dp4a(static_cast<int>(lo4.z), qw[2], c);
-                c = __dp4a(static_cast<int>(lo4.w), qw[3], c);
-                c = __dp4a(static_cast<int>(hi4.x), qw[4], c);
-                c = __dp4a(static_cast<int>(hi4.y), qw[5], c);
-                c = __dp4a(static_cast<int>(hi4.z), qw[6], c);
-                c = __dp4a(static_cast<int>(hi4.w), qw[7], c);
-                c += __shfl_xor_sync(0xffffffffu, c, 8);
-                c += __shfl_xor_sync(0xffffffffu, c, 16);
-                return c;
-            };
-            int kk = next_key();
-            Words cur = fetch(kk);
-            while (kk >= 0) {
-                const int kn = next_key();
-                Words nxt = cur;
-                if (kn >= 0) nxt = fetch(kn);
-                const float tk = eq_l * (bf16_bits_to_float(cur.ek) * (1.0f / 256.0f));
-                const int c1 = dot8(cur.ka0, cur.ka1, qaw), c2 = dot8(cur.ka0, cur.ka1, qbw);
-                float sv = fmaf(static_cast<float>(c1 * 256 + c2), tk, -z_l);
-                if (cur.isK) {
-                    const int c3a = dot8(cur.kb0, cur.kb1, qaw), c3b = dot8(cur.kb0, cur.kb1, qbw);
-                    sv = sv + (static_cast<float>(c3a) + static_cast<float>(c3b) * (1.0f / 256.0f)) * tk;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    mK[i] = qm[q * 12 + i];
+                    mV[i] = qm[q * 12 + 4 + i];
+                    mH[i] = qm[q * 12 + 8 + i];
                 }
-                const float wl = hg < G ? ex2f(sv) : 0.f;   // row hg's weight, in all four quarters' lanes
-                hden += wl;
-                float fa[4], fb[4];
-                e4m3x4_to_float(cur.va, fa);
-                e4m3x4_to_float(cur.vb, fb);
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc) fa[cc] = fmaf(fb[cc], 0.125f, fa[cc]);
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float wg_ = __shfl_sync(0xffffffffu, wl, g);
-#pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) acc[g][cc] = fmaf(wg_, fa[cc], acc[g][cc]);
-                }
-                kk = kn;
-                cur = nxt;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_QFREE + q));
+                row0 = tile_row(lo + it * tstep);
+                wi = 0;
+                rem = mH[0];
+                it += NHELP;
+                open_tiles = it < n_tiles;
             }
+            const int b = __ffs(rem) - 1;
+            rem &= rem - 1;
+            const int kk = 32 * wi + b;
+            const uint32_t bit = 1u << b;
+            const uint32_t wK = wi == 0 ? mK[0] : (wi == 1 ? mK[1] : (wi == 2 ? mK[2] : mK[3]));
+            const uint32_t wV = wi == 0 ? mV[0] : (wi == 1 ? mV[1] : (wi == 2 ? mV[2] : mV[3]));
+            const bool isK = (wK & bit) != 0u, isV = (wV & bit) != 0u;
+            const int64_t row = row0 + kk;
+            const int slot_i = issued % HD_KEYS;
+            const uint32_t dst = stage_a + slot_i * HSLOT;
+            // lane l copies unit l & 7 of plane l >> 3; a plane the key does not need is zero-filled
+            const int need = part == 1 ? (isK ? 16 : 0) : (part == 3 ? (isV ? 16 : 0) : 16);
+            cp_async(dst + 128 * part + 16 * hg, plane_l + row * HD + 16 * hg, need);
+            if (lane == 0) {
+                const uint16_t* e = p.ek + row;
+                cp_async4(dst + 512, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(e) & ~uintptr_t(3)));
+                // the key's note: swizzle of K's units, needs plane B of K, which half of the scale's word
+                *reinterpret_cast<uint32_t*>(stage + slot_i * HSLOT + 516) =
+                    static_cast<uint32_t>(kk & 7) | (isK ? 8u : 0u) | ((reinterpret_cast<uintptr_t>(e) & 2) ? 16u : 0u);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            ++issued;
+            return true;
+        };
+        auto dot8 = [&](const uint4& lo4, const uint4& hi4, const int (&qw)[8]) -> int {
+            int c = __dp4a(static_cast<int>(lo4.x), qw[0], 0);
+            c = __dp4a(static_cast<int>(lo4.y), qw[1], c);
+            c = __dp4a(static_cast<int>(lo4.z), qw[2], c);
+            c = __dp4a(static_cast<int>(lo4.w), qw[3], c);
+            c = __dp4a(static_cast<int>(hi4.x), qw[4], c);
+            c = __dp4a(static_cast<int>(hi4.y), qw[5], c);
+            c = __dp4a(static_cast<int>(hi4.z), qw[6], c);
+            c = __dp4a(static_cast<int>(hi4.w), qw[7], c);
+            c += __shfl_xor_sync(0xffffffffu, c, 8);
+            c += __shfl_xor_sync(0xffffffffu, c, 16);
+            return c;
+        };
+        while (true) {
+            // keep the slots full as far as keys are to be had now; wait for one only when idle
+            while (issued - taken < HD_KEYS && issue_one(false)) {}
+            if (issued == taken && !issue_one(true)) break;
+            // the oldest key's rows: all copies but the younger ones have landed
+            if (issued - taken == HD_KEYS) asm volatile("cp.async.wait_group %0;" ::"n"(HD_KEYS - 1) : "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncwarp();
+            const uint8_t* sb = stage + (taken % HD_KEYS) * HSLOT;
+            const uint32_t note = *reinterpret_cast<const volatile uint32_t*>(sb + 516);
+            const int sw = note & 7;
+            const bool isK = (note & 8u) != 0u;
+            const uint32_t ekw = *reinterpret_cast<const uint32_t*>(sb + 512);
+            const float tk = eq_l * (bf16_bits_to_float(static_cast<uint16_t>((note & 16u) ? (ekw >> 16) : (ekw & 0xFFFFu))) * (1.0f / 256.0f));
+            // K's planes are stored with their 16-byte units swizzled by slot
+            const int u0 = ((2 * part) ^ sw) << 4, u1 = ((2 * part + 1) ^ sw) << 4;
+            const uint4 ka0 = *reinterpret_cast<const uint4*>(sb + u0), ka1 = *reinterpret_cast<const uint4*>(sb + u1);
+            const int c1 = dot8(ka0, ka1, qaw), c2 = dot8(ka0, ka1, qbw);
+            float sv = fmaf(static_cast<float>(c1 * 256 + c2), tk, -z_l);
+            if (isK) {
+                const uint4 kb0 = *reinterpret_cast<const uint4*>(sb + 128 + u0), kb1 = *reinterpret_cast<const uint4*>(sb + 128 + u1);
+                const int c3a = dot8(kb0, kb1, qaw), c3b = dot8(kb0, kb1, qbw);
+                sv = sv + (static_cast<float>(c3a) + static_cast<float>(c3b) * (1.0f / 256.0f)) * tk;
+            }
+            const float wl = hg < G ? ex2f(sv) : 0.f;   // row hg's weight, in all four quarters' lanes
+            hden += wl;
+            float fa[4], fb[4];
+            e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb + 256 + 4 * lane), fa);
+            e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb + 384 + 4 * lane), fb);
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) fa[cc] = fmaf(fb[cc], 0.125f, fa[cc]);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const float wg_ = __shfl_sync(0xffffffffu, wl, g);
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) acc[g][cc] = fmaf(wg_, fa[cc], acc[g][cc]);
+            }
+            __syncwarp();   // the slot is read out before the next copy may land in it
+            ++taken;
         }
         // the sums go where V's ring was: wait until nothing reads or fills it any more
         if (n_tiles > 0) mbar_wait(bar(B_ALLDONE), 0, abort_flag, p.status);

@@ -125,4 +125,5 @@ def prepare_fold_decode(
     )
     launch.z = z
     launch.status = status
+    launch.kernel = "sm100" if use_sm100 else "mma"
     return launch

@@ -47,6 +47,15 @@ class FoldKVCache:
     `chunk` the keys per split (a multiple of 64); with either, a request's
     output depends on the request alone.
 
+    `kernel` (not a reference argument) picks the split-KV kernel: "mma" is
+    the warp-level one, which takes every shape; "sm100" the tcgen05 one (an
+    8-bit V, head_dim 128, pages and chunks of a multiple of 128 keys), which
+    streams the first planes whole and is the faster the longer the contexts
+    are; "auto" takes "sm100" where it applies, the cache truncates, and at
+    least half of the batch's keys sit in requests of 12288 keys or more
+    (shorter requests keep too many keys inside the refine gates, and those
+    leave its tensor-core path).
+
     The decode tail (`tail` >= 0, a rank-r K->V model of dropped mass on a
     bf16 V) and `check_range` are not built: `tail` must resolve to None.
     """
@@ -72,7 +81,7 @@ class FoldKVCache:
         check_range=False,
         chunk=None,
         device="cuda",
-        kernel="mma",
+        kernel="auto",
     ):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads do not group over {n_kv_heads} KV heads")
@@ -221,10 +230,14 @@ class FoldKVCache:
     # ---- internals -------------------------------------------------------
 
     def _set_order(self):
-        """Give the longest requests the lowest grid slots: a long request
-        placed late has nothing behind it to backfill its tail. It changes no
-        bit, since the slot only chooses which row group a CTA takes."""
-        rank = sorted(range(self.batch), key=lambda b: (-self.lens[b], b))
+        """Which row group each grid slot takes; it changes no bit. Without a
+        chunk a CTA walks a whole request, so the longest requests get the
+        lowest slots: a long request placed late has nothing behind it to
+        backfill its tail. Under a fixed chunk every CTA's work is bounded, and
+        the short requests go first instead: their tiles hold the most refined
+        keys and are the slowest, and should not be what the grid ends on."""
+        sign = 1 if self.chunk else -1
+        rank = sorted(range(self.batch), key=lambda b: (sign * self.lens[b], b))
         order = [r * self.n_kv_heads + h for r in rank for h in range(self.n_kv_heads)]
         self.order.copy_(torch.tensor(order, dtype=torch.int32), non_blocking=True)
 
@@ -277,7 +290,11 @@ class FoldKVCache:
 
     def _launch(self, split, out_dtype):
         refine = self._refine()
-        key = (split, out_dtype, refine, self.kernel)
+        kernel = self.kernel
+        if kernel == "auto":
+            long_keys = sum(n for n in self.lens if n >= 12288)
+            kernel = "auto" if self.depth is not None and 2 * long_keys >= sum(self.lens) else "mma"
+        key = (split, out_dtype, refine, kernel)
         if key not in self._launches:
             truncate = self.depth is not None
             self._launches[key] = prepare_fold_decode(
@@ -293,7 +310,7 @@ class FoldKVCache:
                     if self._banded() else ()
                 ),
                 chunk_keys=self.chunk or 0,
-                kernel=self.kernel,
+                kernel=kernel,
             )
         return self._launches[key]
 
