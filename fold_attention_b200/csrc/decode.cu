@@ -727,7 +727,7 @@ extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* 
                                int out_dtype, float* den, int32_t* counts, int32_t* status,
                                void* stream) {
     FOLD_CHECK_ARG(qa && qb && eq && ka && kb && ek && va && z && cut && page_table && seq_lens &&
-                       o_part && den_part && cnt_part && out && den && counts && status,
+                       o_part && den_part && cnt_part && status && (!out || (den && counts)),
                    "fold_decode_run: null pointer");
     FOLD_CHECK_ARG(group >= 1 && group <= 8, "a row group of %d rows: 1..8 are supported", group);
     FOLD_CHECK_ARG(head_dim == 64 || head_dim == 128, "head_dim %d: the decode takes 64 or 128", head_dim);
@@ -761,6 +761,7 @@ extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* 
     if (head_dim == 128) rc = v8 ? launch_decode_d<128, true>(p, weight_terms == 2, st) : launch_decode_d<128, false>(p, weight_terms == 2, st);
     else rc = v8 ? launch_decode_d<64, true>(p, weight_terms == 2, st) : launch_decode_d<64, false>(p, weight_terms == 2, st);
     if (rc) return rc;
+    if (!out) return FOLD_OK;   // partials only: the caller combines
     const int threads = 256;
 #define FOLD_COMBINE(OUT) decode_combine_kernel<OUT><<<n_groups, threads, 0, st>>>(o_part, den_part, cnt_part, seq_lens, out, den, counts, group, head_dim, n_kv_heads, split, chunk_keys, v_scale)
     if (out_dtype == 0) FOLD_COMBINE(0);

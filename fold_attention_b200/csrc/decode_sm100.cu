@@ -885,7 +885,7 @@ extern "C" int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const f
                                      float* den_part, int32_t* cnt_part, void* out, int out_dtype,
                                      float* den, int32_t* counts, int32_t* status, void* stream) {
     FOLD_CHECK_ARG(qa && qb && eq && ka && kb && ek && va && vb && z && cut && page_table && seq_lens &&
-                       o_part && den_part && cnt_part && out && den && counts && status,
+                       o_part && den_part && cnt_part && status && (!out || (den && counts)),
                    "fold_decode_run_sm100: null pointer");
     if (!fold_decode_sm100_supported(group, head_dim, page_size, chunk_keys, 1)) {
         set_error("the tcgen05 decode takes an 8-bit V, head_dim 128, groups of 1..8 rows, pages and chunks of a multiple of 128 keys");
@@ -927,6 +927,7 @@ extern "C" int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const f
     }
     int rc = check_launch("fold_decode_run_sm100");
     if (rc) return rc;
+    if (!out) return FOLD_OK;   // partials only: the caller combines
     return fold_decode_combine(o_part, den_part, cnt_part, seq_lens, out, out_dtype, den, counts, n_groups, group,
                                head_dim, n_kv_heads, split, chunk_keys, v_scale, stream);
 }

@@ -54,6 +54,7 @@ def prepare_fold_decode(
     split=1, truncate=False, refine_k=10.0, refine_v=10.0, v8=False, v2=None, v_scale=1.0,
     vmean=None, page_table, page_size, seq_lens, n_kv_heads, reference="given", weight_terms=1,
     order=None, out_dtype=torch.float32, refine_bands=(), chunk_keys=0, out=None, kernel="mma",
+    short_slots=0,
 ):
     """Bind one decode over a paged cache and return its launch.
 
@@ -65,6 +66,9 @@ def prepare_fold_decode(
     `kernel` picks the split-KV kernel: "mma" (warp-level, every shape), "sm100"
     (tcgen05; an 8-bit V, D = 128, pages and chunks of a multiple of 128 keys;
     its weights are four E5M2 terms whatever `weight_terms` says) or "auto".
+    With an `order`, its first `short_slots` slots stay on the warp-level kernel
+    when the tcgen05 one takes the rest (requests too short for it to pay), and
+    one combine follows both.
     """
     NBH, G, D = qa.shape
     if G > 8:
@@ -105,17 +109,40 @@ def prepare_fold_decode(
         ctypes.addressof(bands) if bands is not None else None, float(v_scale),
         o_part.data_ptr(), den_part.data_ptr(), cnt_part.data_ptr(),
     )
-    tail = (den.data_ptr(), counts.data_ptr(), status.data_ptr())
-    fixed_sm100 = fixed[:23] + fixed[24:]   # the same arguments without weight_terms
+    short_slots = int(short_slots) if (use_sm100 and order is not None) else 0
+    if not 0 <= short_slots <= NBH:
+        raise ValueError(f"short_slots={short_slots} of {NBH} slots")
+    if short_slots == NBH:
+        use_sm100, short_slots = False, 0
+
+    def args(first, count, sm100, o):
+        """One call's arguments over `count` slots from slot `first`; `o` None: partials only."""
+        a = list(fixed)
+        if first or count != NBH:
+            a[13] = order.data_ptr() + 4 * first
+            a[14] = count
+        if sm100:
+            del a[23]   # the tcgen05 kernel has no weight_terms
+        a += [o.data_ptr() if o is not None else None, _OUT[out_t.dtype] if o is None else _OUT[o.dtype],
+              den.data_ptr(), counts.data_ptr(), status.data_ptr(), _lib.stream(dev)]
+        return a
 
     def run(out=None):
         o = out_t if out is None else out
         if reference == "mass":
             mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z)
-        if use_sm100:
-            _lib.call("fold_decode_run_sm100", *fixed_sm100, o.data_ptr(), _OUT[o.dtype], *tail, _lib.stream(dev))
+        if use_sm100 and short_slots:
+            _lib.call("fold_decode_run_sm100", *args(short_slots, NBH - short_slots, True, None))
+            _lib.call("fold_decode_run", *args(0, short_slots, False, None))
+            _lib.call(
+                "fold_decode_combine", o_part.data_ptr(), den_part.data_ptr(), cnt_part.data_ptr(),
+                seq_lens.data_ptr(), o.data_ptr(), _OUT[o.dtype], den.data_ptr(), counts.data_ptr(), NBH, G, D,
+                int(n_kv_heads), split, int(chunk_keys), float(v_scale), _lib.stream(dev),
+            )
+        elif use_sm100:
+            _lib.call("fold_decode_run_sm100", *args(0, NBH, True, o))
         else:
-            _lib.call("fold_decode_run", *fixed, o.data_ptr(), _OUT[o.dtype], *tail, _lib.stream(dev))
+            _lib.call("fold_decode_run", *args(0, NBH, False, o))
         return o, den, counts
 
     launch = DecodeLaunch(
@@ -125,5 +152,5 @@ def prepare_fold_decode(
     )
     launch.z = z
     launch.status = status
-    launch.kernel = "sm100" if use_sm100 else "mma"
+    launch.kernel = ("sm100+mma" if short_slots else "sm100") if use_sm100 else "mma"
     return launch

@@ -51,14 +51,19 @@ class FoldKVCache:
     the warp-level one, which takes every shape; "sm100" the tcgen05 one (an
     8-bit V, head_dim 128, pages and chunks of a multiple of 128 keys), which
     streams the first planes whole and is the faster the longer the contexts
-    are; "auto" takes "sm100" where it applies, the cache truncates, and at
-    least half of the batch's keys sit in requests of 12288 keys or more
-    (shorter requests keep too many keys inside the refine gates, and those
-    leave its tensor-core path).
+    are; "auto" takes "sm100" where it applies and the cache truncates, for
+    the requests of 12288 keys or more (shorter requests keep too many keys
+    inside the refine gates, and those leave its tensor-core path): the batch
+    goes where most of its keys would. With `mix_kernels` set (and a `chunk`)
+    the short requests of a batch go to "mma" and the long ones to "sm100" in
+    the same step; on one B200 that measured slower up to 128 requests (the
+    short requests' launch cannot fill the GPU by itself), so it is off.
 
     The decode tail (`tail` >= 0, a rank-r K->V model of dropped mass on a
     bf16 V) and `check_range` are not built: `tail` must resolve to None.
     """
+
+    SM100_MIN_KEYS = 12288   # requests shorter than this stay on the warp-level kernel under kernel="auto"
 
     def __init__(
         self,
@@ -97,6 +102,7 @@ class FoldKVCache:
         self.device = torch.device(device)
         # the split-KV kernel (not a reference argument): "mma", "sm100" or "auto"
         self.kernel = kernel
+        self.mix_kernels = False
         if head_dim not in (64, 128):
             raise NotImplementedError(f"head_dim {head_dim}: the cache takes 64 or 128")
         if self.group > 8:
@@ -290,11 +296,16 @@ class FoldKVCache:
 
     def _launch(self, split, out_dtype):
         refine = self._refine()
-        kernel = self.kernel
+        kernel, short = self.kernel, 0
         if kernel == "auto":
-            long_keys = sum(n for n in self.lens if n >= 12288)
-            kernel = "auto" if self.depth is not None and 2 * long_keys >= sum(self.lens) else "mma"
-        key = (split, out_dtype, refine, kernel)
+            if self.depth is None:
+                kernel = "mma"
+            elif self.chunk and self.mix_kernels:
+                # the slot order is by length (_set_order): the short requests are its first slots
+                short = self.n_kv_heads * sum(1 for n in self.lens if n < self.SM100_MIN_KEYS)
+            elif 2 * sum(n for n in self.lens if n >= self.SM100_MIN_KEYS) < sum(self.lens):
+                kernel = "mma"
+        key = (split, out_dtype, refine, kernel, short)
         if key not in self._launches:
             truncate = self.depth is not None
             self._launches[key] = prepare_fold_decode(
@@ -311,6 +322,7 @@ class FoldKVCache:
                 ),
                 chunk_keys=self.chunk or 0,
                 kernel=kernel,
+                short_slots=short,
             )
         return self._launches[key]
 

@@ -87,12 +87,17 @@ int fold_mass_z(const int8_t* qa, const int8_t* qb, const float* eq, const int8_
  *   z, cut        fp32 (n_groups, group): the reference and the depth below it
  *                 under which a key is cut (used when truncate != 0)
  *   vmean         fp32 (n_groups, head_dim) or NULL: where dropped mass re-enters
- *   order         int32 (n_groups,) grid slot -> row group, or NULL
+ *   order         int32 (n_groups,) grid slot -> row group, or NULL. With an
+ *                 order, n_groups is the number of slots this call takes: a call
+ *                 may cover a subset of the row groups (the partial buffers are
+ *                 indexed by row group), e.g. the long requests on one kernel and
+ *                 the short ones on the other, combined once afterwards
  *   split         CTAs per row group; chunk_keys > 0 fixes the keys per split
  *   refine_bands  host: (edge0, edge1, rk1, rk2, rv1, rv2) or NULL
  *   o_part        fp32 (n_groups*split, group, head_dim) scratch; den_part
  *                 (n_groups*split, group); cnt_part int32 (n_groups*split, 2)
- *   out           (n_groups, group, head_dim) as out_dtype: 0 fp32, 1 bf16, 2 fp16
+ *   out           (n_groups, group, head_dim) as out_dtype: 0 fp32, 1 bf16, 2 fp16;
+ *                 NULL leaves the partials uncombined (fold_decode_combine)
  *   den           fp32 (n_groups, group); counts int32 (n_groups, 2): live, refined
  *   status        int32[1]: set non-zero if a device-side wait ran out */
 int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,

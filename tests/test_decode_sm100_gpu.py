@@ -133,3 +133,37 @@ def test_what_the_tcgen05_kernel_does_not_take():
     run()
     torch.cuda.synchronize()
     assert int(run.status) == 0
+
+
+def test_a_batch_splits_between_the_kernels_by_request_length():
+    """kernel="auto" with mix_kernels under a chunk: the short requests' slots go to
+    the warp-level kernel, the long ones' to the tcgen05 kernel, one combine after
+    both; every request's output is the bits its own kernel gives it alone."""
+    from fold_attention_b200 import FoldKVCache
+
+    lens = [13000, 500, 12288, 4000]
+    B, H, HKV, D = len(lens), 16, 2, 128
+    q, k, v, cu = _layer(B, H, HKV, D, lens, seed=11)
+    kw = dict(ps=128, v8=True, depth=16.0, chunk=2048, v_scale=0.03125)
+    both = _cache(B, H, HKV, D, lens, kernel="auto", **kw)
+    both.mix_kernels = True
+    both.write_prompt(k, v, cu, lens)
+    o = both.attend(q)
+    launch = next(iter(both._launches.values()))
+    assert launch.kernel == "sm100+mma" and int(launch.status) == 0
+    assert both.order.tolist()[:4] == [2, 3, 6, 7]   # the two short requests' row groups first
+    for b in range(B):
+        kern = "sm100" if lens[b] >= FoldKVCache.SM100_MIN_KEYS else "mma"
+        one = _cache(1, H, HKV, D, [lens[b]], seed=b, kernel=kern, **kw)
+        a, e = int(cu[b]), int(cu[b + 1])
+        one.write_prompt(k[a:e], v[a:e], torch.tensor([0, lens[b]], device="cuda", dtype=torch.int32), [lens[b]])
+        o_one = one.attend(q[b:b + 1])
+        assert torch.equal(o_one[0], o[b]), b
+        assert torch.equal(one.counts, both.counts[b * HKV:(b + 1) * HKV])
+    # a batch of short requests only: the warp-level kernel takes all of it
+    short = _cache(2, H, HKV, D, [500, 4000], kernel="auto", **kw)
+    short.mix_kernels = True
+    short.write_prompt(torch.cat([k[13000:13500], k[-4000:]]), torch.cat([v[13000:13500], v[-4000:]]),
+                       torch.tensor([0, 500, 4500], device="cuda", dtype=torch.int32), [500, 4000])
+    short.attend(q[[1, 3]])
+    assert next(iter(short._launches.values())).kernel == "mma"
