@@ -208,7 +208,7 @@ def cpu_reference_tflops(seconds_budget=12.0):
     return flops(1, S, H, D) / dt / 1e12, f"B1 H4 S{S} D{D} causal FP32 autograd x{n}, scaled by FLOPs"
 
 
-def decode_extra(device, steps=8, B=32, dense=False, kernel="auto"):
+def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
     """Config-5-shaped decode at a reduced batch (extra keys, not the headline):
     v8, depth 16, GQA 64/8, D128, lengths log-uniform in [4096, 131072]; or with
     `dense` config 4's shape: bf16 V, depth None, GQA 32/8, lengths uniform in
@@ -218,14 +218,14 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto"):
     from fold_attention_b200 import FoldKVCache
 
     H, HKV, D = (32, 8, 128) if dense else (64, 8, 128)
-    g = torch.Generator().manual_seed(5)
+    g = torch.Generator().manual_seed(seed)
     if dense:
         lens = torch.randint(1024, 32769, (B,), generator=g).tolist()
         c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, chunk=4096, device=device)
     else:
         lens = [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
         c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, depth=16.0, v8=True, chunk=8192, device=device, kernel=kernel)
-    gd = torch.Generator(device=device).manual_seed(6)
+    gd = torch.Generator(device=device).manual_seed(seed + 1)
     pages = c.page_table.shape[1]
     perm = torch.randperm(B * pages, device=device, generator=gd).int().view(B, pages)
     c.page_table.copy_(perm)
@@ -368,6 +368,26 @@ def main():
                 except Exception as e:  # the headline stands on its own
                     line["extra"][key] = dict(error=repr(e))
                 torch.cuda.empty_cache()
+    if world > 1 and not args.no_extra:
+        # the decode path sharded over requests: config 5's shape, 32 requests per rank (8 ranks hold
+        # its 256), every rank its own lengths; the step time is the slowest rank's
+        try:
+            d = decode_extra(device, seed=5 + 2 * rank)
+            t = torch.tensor([d["us_per_step"], 0.0], device=device, dtype=torch.float64)
+            u = torch.tensor([d["keys"], d["algorithmic_gbs"] * d["us_per_step"]], device=device, dtype=torch.float64)
+        except Exception as e:
+            d = dict(error=repr(e))
+            t = torch.tensor([float("inf"), 1.0], device=device, dtype=torch.float64)
+            u = torch.zeros(2, device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(u, op=dist.ReduceOp.SUM)
+        if t[1].item() == 0.0:
+            us = t[0].item()
+            line["extra"] = dict(decode_config5=dict(
+                workload=d["workload"].replace("B32", f"B{32 * world} (32 per rank)"), kernel=d["kernel"], us_per_step=us,
+                keys=int(u[0].item()), algorithmic_gbs=u[1].item() / us, hbm_frac_per_gpu=u[1].item() / us / world / pk["hbm"]))
+        else:
+            line["extra"] = dict(decode_config5=d if "error" in d else dict(error="a rank failed"))
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
