@@ -60,7 +60,9 @@ class FoldKVCache:
     short requests' launch cannot fill the GPU by itself), so it is off.
 
     The decode tail (`tail` >= 0, a rank-r K->V model of dropped mass on a
-    bf16 V) and `check_range` are not built: `tail` must resolve to None.
+    bf16 V) is not built: `tail` must resolve to None. `check_range` reads each
+    step's denominators on the host and reruns the rows whose reference sat
+    outside `[0.5, 2^60]` (`2^100` on a bf16 V) of their mass.
     """
 
     SM100_MIN_KEYS = 12288   # requests shorter than this stay on the warp-level kernel under kernel="auto"
@@ -151,9 +153,10 @@ class FoldKVCache:
             raise NotImplementedError("the decode tail is not built: pass tail=None")
         self._refine_k_fixed = refine_k
         self._refine_v_fixed = refine_v
-        if check_range:
-            raise NotImplementedError("check_range is not built")
-        self.check_range = False
+        # after a step, look at every row's denominator and run the flagged rows again from a
+        # reference moved to their log-sum-exp (one host sync per step; kv_cache.py:704-744)
+        self.check_range = bool(check_range)
+        self._z_given = None
         if chunk is not None and (split is not None or chunk % BN):
             raise ValueError(f"chunk={chunk} is a multiple of {BN} and replaces split")
         self.chunk = chunk
@@ -294,7 +297,8 @@ class FoldKVCache:
         rv_t = torch.where(n > e1, rv2, torch.where(n > e0, rv1, float(rv)))
         return rk_t, rv_t
 
-    def _launch(self, split, out_dtype):
+    def _launch(self, split, out_dtype, given=False):
+        """The step's decode launch; `given`: the one that reads `_z_given` instead of the mass reference."""
         refine = self._refine()
         kernel, short = self.kernel, 0
         if kernel == "auto":
@@ -305,11 +309,14 @@ class FoldKVCache:
                 short = self.n_kv_heads * sum(1 for n in self.lens if n < self.SM100_MIN_KEYS)
             elif 2 * sum(n for n in self.lens if n >= self.SM100_MIN_KEYS) < sum(self.lens):
                 kernel = "mma"
-        key = (split, out_dtype, refine, kernel, short)
+        key = (split, out_dtype, refine, kernel, short, given)
+        if given and self._z_given is None:
+            self._z_given = torch.empty_like(self.z)
         if key not in self._launches:
             truncate = self.depth is not None
             self._launches[key] = prepare_fold_decode(
-                self.qa, self.qb, self.eq, self.ka, self.kb, self.ek, self.va, self.z, self.cut,
+                self.qa, self.qb, self.eq, self.ka, self.kb, self.ek, self.va,
+                self._z_given if given else self.z, self.cut,
                 split=split, truncate=truncate, refine_k=refine[0], refine_v=refine[1],
                 v8=self.v8, v2=self.vb, v_scale=self.v_scale,
                 vmean=self.vmean if truncate else None, page_table=self.page_table,
@@ -350,4 +357,41 @@ class FoldKVCache:
         # a fresh tensor per step: the caller may hold every step's output
         out = torch.empty((self.n_groups, self.group, self.head_dim), device=q.device, dtype=out_dtype)
         o, self.den, self.counts = self._launch(split, out_dtype).run(out=out)
+        if self.check_range:
+            bad = self._out_of_range(o, self.den)
+            if bool(bad.any()):
+                o, self.den, self.counts = self._rerun(bad, self.den, split, out_dtype, out)
         return o.view(shape).to(q.dtype)
+
+    def _range_window(self):
+        """`(lo, hi)` for a row's denominator `2^(LSE - Z)`: under `hi` no weight or sum overflows
+        (the reference's 8-bit V path carries 2^64 in its weights, which lowers it); over `lo` Z is
+        within a binade of the log-sum-exp, so a gate or cut at depth T below Z is at least T - 1
+        below the row's mass (kv_cache.py:704-713)."""
+        return 0.5, 2.0 ** (60 if self.v8 else 100)
+
+    def _out_of_range(self, o, den):
+        lo, hi = self._range_window()
+        ok = (den >= lo) & (den <= hi)
+        ok &= torch.isfinite(o.view(self.n_groups, self.group, self.head_dim)).all(-1)
+        return ~ok
+
+    def _rerun(self, bad, den, split, out_dtype, out):
+        """The step's decode again with every flagged row's reference moved to its log-sum-exp
+        (`Z + log2(den)`); an empty or infinite denominator moves it by 64 binades and tries again,
+        four times at most (kv_cache.py:721-744)."""
+        z = self.z.clone()
+        launch = self._launch(split, out_dtype, given=True)
+        tiny = torch.finfo(torch.float32).tiny
+        for _ in range(4):
+            shift = torch.where(
+                torch.isfinite(den) & (den > 0), torch.log2(den.clamp_min(tiny)),
+                torch.where(den == 0, torch.full_like(den, -64.0), torch.full_like(den, 64.0)))
+            z = torch.where(bad, z + shift, z)
+            self._z_given.copy_(z)
+            o, den2, counts = launch.run(out=out)
+            bad2 = self._out_of_range(o, den2)
+            if not bool(bad2.any()):
+                return o, den2, counts
+            bad, den = bad2, den2
+        raise FloatingPointError("a row's reference left the exponent range after four moves")

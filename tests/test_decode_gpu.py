@@ -266,3 +266,37 @@ def test_error_messages():
     q = torch.randn(2, 8, 128, device="cuda").bfloat16()
     with pytest.raises(ValueError, match="both given or both left out"):
         fa.fold_attn_with_kvcache(q, c, k[:2])
+
+
+@pytest.mark.parametrize("v8,depth,kernel", [(False, None, "mma"), (True, 16.0, "mma"), (True, 16.0, "sm100")])
+def test_check_range_reruns_the_rows_whose_reference_was_off(v8, depth, kernel):
+    """A reference moved off a row's mass leaves the window [0.5, 2^60 or 2^100] of the
+    denominator; with check_range the step is run again from Z + log2(den) and lands where
+    the undisturbed step does (reference kv_cache.py:704-744)."""
+    lens = [2000, 700]
+    B, H, HKV, D = len(lens), 8, 2, 128
+    q, k, v, cu = _layer(B, H, HKV, D, lens, seed=12)
+    c = _cache(B, H, HKV, D, lens, ps=128, v8=v8, depth=depth, check_range=True, kernel=kernel)
+    c.write_prompt(k, v, cu, lens)
+    want = torch.stack([_attend_ref(q, k, v, cu, b, HKV, H // HKV) for b in range(B)])
+    plain = c.attend(q)
+    tol = 4e-3 if depth is None else 2.0 ** (-depth / 3)
+    assert _rel(plain, want) < tol
+    lo, hi = c._range_window()
+    assert hi == (2.0 ** 60 if v8 else 2.0 ** 100)
+    for move in (6.0, -70.0 if v8 else -110.0):
+        c._step(q, None, None)        # Q's planes and the mass reference, as attend does
+        z_mass = c.z.clone()
+        c.z[1::2] += move             # every other row group's reference off its mass
+        got = c._run(q, None)
+        assert bool(((c.den >= lo) & (c.den <= hi)).all())
+        assert _rel(got, want) < tol, (move, _rel(got, want))
+        # the rows that were not flagged kept their reference: the same bits as the plain step
+        assert torch.equal(got.view(B * HKV, -1)[0::2], plain.view(B * HKV, -1)[0::2])
+        assert torch.equal(c.z[0::2], z_mass[0::2])
+    off = _cache(B, H, HKV, D, lens, ps=128, v8=v8, depth=depth, kernel=kernel)   # without the check
+    off.write_prompt(k, v, cu, lens)
+    off._step(q, None, None)
+    off.z[1::2] += 6.0
+    off._run(q, None)
+    assert bool((off.den[1::2] < lo).any())   # without the check such rows stay as they came out
