@@ -32,6 +32,8 @@ _lib.register(
     [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, I, P],
 )
 _lib.register("fold_fwd_run", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
+_lib.register("fold_fwd_sm100_supported", [I, I])
+_lib.register("fold_fwd_run_sm100", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P])
 
 KERNELS = {"auto": 0, "mma": 1, "sm100": 2}
 
@@ -147,12 +149,16 @@ def prepare_backward(
     return launch
 
 
-def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, max_seqlen=None):
+def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, max_seqlen=None, kernel="auto"):
     """O and LSE (nats) of self-attention through the library's own forward.
 
     Dense: `(B, S, H, D)` tensors, lse `(B, H, S)`. Varlen: `(total, H, D)`,
     lse `(H, total)`. Stands in for the third-party forward the reference
-    calls (src/fold_attention/interface.py:42-44,70-81)."""
+    calls (src/fold_attention/interface.py:42-44,70-81). `kernel`: "mma" (warp-level,
+    every head dim, both 16-bit types), "sm100" (tcgen05; head_dim 128, bf16) or
+    "auto"."""
+    if kernel not in ("auto", "mma", "sm100"):
+        raise ValueError('kernel is one of ("auto", "mma", "sm100")')
     varlen = cu_seqlens is not None
     D = q.shape[-1]
     sm = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
@@ -175,6 +181,18 @@ def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, m
         for t in (q, k, v, o):
             st += [t.stride(0), t.stride(1), t.stride(2)]
     strides = (ctypes.c_int64 * 12)(*st)
+    can = bool(_lib.lib.fold_fwd_sm100_supported(D, int(q.dtype == torch.float16)))
+    if kernel == "sm100" and not can:
+        raise NotImplementedError("the tcgen05 forward takes head_dim 128, bf16")
+    if can and kernel != "mma":
+        status = torch.zeros(1, device=q.device, dtype=torch.int32)
+        _lib.call(
+            "fold_fwd_run_sm100", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+            ctypes.addressof(strides), _lib.ptr(cu_seqlens), B, H, k.shape[-2], S, total, D,
+            int(bool(causal)), sm, status.data_ptr(), _lib.stream(q.device),
+        )
+        attention_forward.last_status = status   # non-zero after a device-side wait ran out
+        return o, lse
     _lib.call(
         "fold_fwd_run", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
         ctypes.addressof(strides), _lib.ptr(cu_seqlens), B, H, k.shape[-2], S, total, D,
