@@ -224,7 +224,8 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
         c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, chunk=4096, device=device)
     else:
         lens = [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
-        c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, depth=16.0, v8=True, chunk=8192, device=device, kernel=kernel)
+        c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, depth=16.0, v8=True, device=device, kernel=kernel,
+                        chunk=8192 if kernel == "mma" else None)
     gd = torch.Generator(device=device).manual_seed(seed + 1)
     pages = c.page_table.shape[1]
     perm = torch.randperm(B * pages, device=device, generator=gd).int().view(B, pages)
@@ -258,7 +259,8 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
     vb = 2 * D if dense else D
     byts = keys * (D + 2 + D * refk + vb * live)
     name = (f"config4-shaped decode bf16 dense B{B} H32/8 D128 lens U[1024,32768] chunk4096" if dense else
-            f"config5-shaped decode v8 depth16 B{B} H64/8 D128 lens logU[4096,131072] chunk8192")
+            f"config5-shaped decode v8 depth16 B{B} H64/8 D128 lens logU[4096,131072] " +
+            ("chunk8192" if kernel == "mma" else "default split"))
     return dict(workload=name, kernel="/".join(sorted({l.kernel for l in c._launches.values()})),
                 us_per_step=us, keys=keys, live_fraction=live, refined_fraction=refk,
                 algorithmic_gbs=byts / us / 1e3, hbm_frac=byts / us / 1e3 / peaks()["hbm"])
