@@ -209,7 +209,7 @@ def cpu_reference_tflops(seconds_budget=12.0):
 
 
 def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
-    """Config-5-shaped decode at a reduced batch (extra keys, not the headline):
+    """Config 5's decode (extra keys, not the headline; B=256 is the config's own batch):
     v8, depth 16, GQA 64/8, D128, lengths log-uniform in [4096, 131072]; or with
     `dense` config 4's shape: bf16 V, depth None, GQA 32/8, lengths uniform in
     [1024, 32768]."""
@@ -232,12 +232,19 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
     c.page_table.copy_(perm)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=device, dtype=torch.int32)
     T = sum(lens)
-    k = torch.randn(T, HKV, D, device=device, generator=gd)
-    hot = torch.rand(T, 1, 1, device=device, generator=gd) < 0.01
-    k = torch.where(hot, k * 8, k).bfloat16()
-    v = torch.randn(T, HKV, D, device=device, generator=gd)
-    out = torch.rand(T, HKV, D, device=device, generator=gd) < 0.001
-    v = torch.where(out, v * 20, v).bfloat16()
+    # request by request: the fp32 draws of a whole large batch would not fit beside the pool
+    k = torch.empty(T, HKV, D, device=device, dtype=torch.bfloat16)
+    v = torch.empty(T, HKV, D, device=device, dtype=torch.bfloat16)
+    at = 0
+    for n in lens:
+        kk = torch.randn(n, HKV, D, device=device, generator=gd)
+        hot = torch.rand(n, 1, 1, device=device, generator=gd) < 0.01
+        k[at:at + n] = torch.where(hot, kk * 8, kk)
+        vv = torch.randn(n, HKV, D, device=device, generator=gd)
+        out = torch.rand(n, HKV, D, device=device, generator=gd) < 0.001
+        v[at:at + n] = torch.where(out, vv * 20, vv)
+        at += n
+    del kk, vv, hot, out
     c.write_prompt(k, v, cu, lens)
     del k, v
     q = torch.randn(B, H, D, device=device, generator=gd).bfloat16()
@@ -363,7 +370,7 @@ def main():
             torch.cuda.empty_cache()
             line["extra"] = dict(gqa_32_8=dict(ms_per_step=ms_g, tflops=fl / ms_g / 1e9))
             for key, fn in (("varlen_config3", lambda: varlen_extra(device)),
-                            ("decode_config5", lambda: decode_extra(device)),
+                            ("decode_config5", lambda: decode_extra(device, steps=6, B=256)),
                             ("decode_config4", lambda: decode_extra(device, B=128, dense=True))):
                 try:
                     line["extra"][key] = fn()
