@@ -57,7 +57,7 @@ class Clocks:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
@@ -221,7 +221,8 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
     g = torch.Generator().manual_seed(seed)
     if dense:
         lens = torch.randint(1024, 32769, (B,), generator=g).tolist()
-        c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, chunk=4096, device=device)
+        c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, device=device, kernel=kernel,
+                        chunk=4096 if kernel == "mma" else None)
     else:
         lens = [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
         c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, depth=16.0, v8=True, device=device, kernel=kernel,
@@ -265,7 +266,8 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
     refk = c.counts[:, 1].sum().item() / keys
     vb = 2 * D if dense else D
     byts = keys * (D + 2 + D * refk + vb * live)
-    name = (f"config4-shaped decode bf16 dense B{B} H32/8 D128 lens U[1024,32768] chunk4096" if dense else
+    name = (f"config4-shaped decode bf16 dense B{B} H32/8 D128 lens U[1024,32768] " +
+            ("chunk4096" if kernel == "mma" else "default split") if dense else
             f"config5-shaped decode v8 depth16 B{B} H64/8 D128 lens logU[4096,131072] " +
             ("chunk8192" if kernel == "mma" else "default split"))
     return dict(workload=name, kernel="/".join(sorted({l.kernel for l in c._launches.values()})),

@@ -1,5 +1,7 @@
-// Quantised paged-KV decode on Blackwell tensor cores (tcgen05 + TMEM), for an
-// 8-bit V (two E4M3 planes), head dim 128, pages of a multiple of 128 keys.
+// Quantised paged-KV decode on Blackwell tensor cores (tcgen05 + TMEM), head dim 128,
+// pages of a multiple of 128 keys; described for an 8-bit V (two E4M3 planes). A bf16 V
+// runs the same schedule with a 256-byte row per key: 16 keys per kind::f16 MMA, the
+// weight as two bf16 terms (hi, lo), no second plane, 4-slot rings.
 //
 // The warp-level kernel in decode.cu spends 49 warp instructions per key and is
 // issue-bound at about a third of HBM bandwidth. Here a tile is 128 keys, the
@@ -54,8 +56,6 @@ namespace dsm100 {
 
 constexpr int TK = 128;          // keys per tile
 constexpr int HD = 128;
-constexpr int NA = 5;            // ring slots of K's plane A
-constexpr int NV = 5;            // ring slots of V's plane A and the key scales
 constexpr int QD = 8;            // tiles of helper masks in flight
 constexpr int NHELP = 4;
 constexpr int HD_KEYS = 4;       // keys whose rows a helper has in flight into its staging slots
@@ -68,39 +68,48 @@ constexpr long long WAIT_CYCLES = 1ll << 31;
 constexpr float BIG_TOP = 8.0f;  // a key whose weight could pass 2^8 is summed in fp32 by a helper
 constexpr int W_BIAS = 6;        // weights are stored times 2^6: under 2^14 on the tensor-core path
 
-// shared memory map (1024-aligned base)
+// shared memory map (1024-aligned base) and barrier numbers; an 8-bit V is two E4M3 planes of
+// 128 bytes per key (plane B fetched on demand), a 16-bit V one bf16 row of 256 bytes
 constexpr int SM_Q = 0;                               // [16 rows][128 B] int8, SW128
-constexpr int SM_KA = 2048;                           // NA x Ka [128 keys][128 B]
-constexpr int SM_VA = SM_KA + NA * 16384;             // NV x Va [128 keys][128 B]
-constexpr int SM_VB = SM_VA + NV * 16384;             // NB2 x Vb [128 keys][128 B], fetched by quarters
-constexpr int SM_KS = SM_VB + NB2 * 16384;            // NV x 128 bf16 scales
-constexpr int SM_W = SM_KS + NV * 256;                // 2 x [2 units][128 keys][16 B] E5M2
-constexpr int SM_W2 = SM_W + 2 * 4096;                // NB2 x the same, masked to the dense refine-V keys
-constexpr int SM_QM = SM_W2 + NB2 * 4096;             // QD x { refine-K, refine-V, helper } x 4 mask words
-constexpr int SM_QF = SM_QM + QD * 48;                // NBQ x 4 quarter flags
-constexpr int SM_EQZ = SM_QF + NBQ * 16;              // eq[8], z[8] of the row group
-constexpr int SM_HST = (SM_EQZ + 64 + 15) / 16 * 16;  // NHELP x HD_KEYS staging slots
-constexpr int SM_BAR = SM_HST + NHELP * HD_KEYS * HSLOT;
-// after the last MMA the rings are dead and hold the final reduction: 256 x 16 row sums,
-// 8 x 16 partial and 16 full column sums, per-warp counters; and the helpers' sums
-constexpr int SM_RED = SM_KA;
-constexpr int SM_CNT = SM_KA + (256 + 8 + 1) * 16 * 4;
-constexpr int SM_HOUT = SM_VA;                        // NHELP x { [8 rows][128 channels], [8] } floats
-constexpr int HOUT = (8 * 128 + 8) * 4;
-constexpr int SMEM_BYTES = SM_BAR + 512;
-
-enum {
-    B_AFULL = 0,                 // [NA] K's plane A has landed
-    B_LFULL = B_AFULL + NA,      // [NA] the tile's logit MMAs retired: its logits are in TMEM slot t % NA, its K slot is free
-    B_VFULL = B_LFULL + NA,      // [NV] V's plane A and the scales have landed
-    B_VEMPTY = B_VFULL + NV,     // [NV] the tile's value MMAs retired: its V slot and its weight buffer are free
-    B_WREADY = B_VEMPTY + NV,    // [2] 128 arrivals: the tile's weights are in shared memory
-    B_QFULL = B_WREADY + 2,      // [QD] 4 arrivals: the tile's masks are written
-    B_QFREE = B_QFULL + QD,      // [QD] its helper has read them
-    B_BFULL = B_QFREE + QD,      // [NBQ] 4 arrivals (+ bytes): the tile's quarters of plane B have landed
-    B_BFREE = B_BFULL + NBQ,     // [NB2] its plane-B MMAs retired
-    B_ALLDONE = B_BFREE + NB2,   // the last value MMAs retired
-    B_COUNT = B_ALLDONE + 1,
+constexpr int HOUT = (8 * 128 + 8) * 4;               // a helper's sums: [8 rows][128 channels], [8] floats
+template <bool V8>
+struct Lay {
+    static constexpr int NA = V8 ? 5 : 4;             // ring slots of K's plane A
+    static constexpr int NV = V8 ? 5 : 4;             // ring slots of V (plane A) and the key scales
+    static constexpr int VBYTES = V8 ? 16384 : 32768; // a V slot: [128 keys][128 B], or two 64-channel boxes of that
+    static constexpr int NB2E = V8 ? NB2 : 0;
+    static constexpr int SM_KA = 2048;                           // NA x Ka [128 keys][128 B]
+    static constexpr int SM_VA = SM_KA + NA * 16384;             // NV x V slots
+    static constexpr int SM_VB = SM_VA + NV * VBYTES;            // NB2 x Vb [128 keys][128 B], fetched by quarters
+    static constexpr int SM_KS = SM_VB + NB2E * 16384;           // NV x 128 bf16 scales
+    static constexpr int SM_W = SM_KS + NV * 256;                // 2 x [2 units][128 keys][16 B] weights
+    static constexpr int SM_W2 = SM_W + 2 * 4096;                // NB2 x the same, masked to the dense refine-V keys
+    static constexpr int SM_QM = SM_W2 + NB2E * 4096;            // QD x { refine-K, refine-V, helper } x 4 mask words
+    static constexpr int SM_QF = SM_QM + QD * 48;                // NBQ x 4 quarter flags
+    static constexpr int SM_EQZ = SM_QF + NBQ * 16;              // eq[8], z[8] of the row group
+    static constexpr int SM_HST = (SM_EQZ + 64 + 15) / 16 * 16;  // NHELP x HD_KEYS staging slots
+    static constexpr int SM_BAR = SM_HST + NHELP * HD_KEYS * HSLOT;
+    // after the last MMA the rings are dead and hold the final reduction: 256 x 16 row sums,
+    // 8 x 16 partial and 16 full column sums, per-warp counters; and the helpers' sums
+    static constexpr int SM_RED = SM_KA;
+    static constexpr int SM_CNT = SM_KA + (256 + 8 + 1) * 16 * 4;
+    static constexpr int SM_HOUT = SM_VA;
+    static constexpr int SMEM_BYTES = SM_BAR + 512;
+    static_assert(SMEM_BYTES <= 232448, "over the 227 KB a CTA may hold");
+    static_assert(NA * 16384 >= SM_CNT - SM_KA + 1024 && NV * VBYTES >= NHELP * HOUT, "the final reduction fits the dead rings");
+    enum {
+        B_AFULL = 0,                 // [NA] K's plane A has landed
+        B_LFULL = B_AFULL + NA,      // [NA] the tile's logit MMAs retired: its logits are in TMEM slot t % NA, its K slot is free
+        B_VFULL = B_LFULL + NA,      // [NV] V's plane A and the scales have landed
+        B_VEMPTY = B_VFULL + NV,     // [NV] the tile's value MMAs retired: its V slot and its weight buffer are free
+        B_WREADY = B_VEMPTY + NV,    // [2] 128 arrivals: the tile's weights are in shared memory
+        B_QFULL = B_WREADY + 2,      // [QD] 4 arrivals: the tile's masks are written
+        B_QFREE = B_QFULL + QD,      // [QD] its helper has read them
+        B_BFULL = B_QFREE + QD,      // [NBQ] 4 arrivals (+ bytes): the tile's quarters of plane B have landed
+        B_BFREE = B_BFULL + NBQ,     // [NB2] its plane-B MMAs retired
+        B_ALLDONE = B_BFREE + NB2,   // the last value MMAs retired
+        B_COUNT = B_ALLDONE + 1,
+    };
 };
 
 constexpr uint32_t T_L = 0, T_ACC = 96, T_ACC2 = 128;   // TMEM columns: NA logit buffers of 16, then the accumulators
@@ -204,6 +213,20 @@ __device__ __forceinline__ void mma4_f8(uint32_t d, uint64_t a, uint64_t b, uint
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a1, b1, %3, p1; }"
         ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc0), "n"(DA), "n"(DB) : "memory");
 }
+template <int DA, int DB>
+__device__ __forceinline__ void mma4_f16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc0) {
+    asm volatile(
+        "{ .reg .pred p0, p1; .reg .b64 a1, b1;\n"
+        "setp.ne.b32 p0, %4, 0; setp.eq.b32 p1, %4, %4;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p0;\n"
+        "add.u64 a1, %1, %5; add.u64 b1, %2, %6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, p1;\n"
+        "add.u64 a1, a1, %5; add.u64 b1, b1, %6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, p1;\n"
+        "add.u64 a1, a1, %5; add.u64 b1, b1, %6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, p1; }"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc0), "n"(DA), "n"(DB) : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
                  "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -256,9 +279,17 @@ __host__ __device__ constexpr uint32_t instr_desc(int c_fmt, int a_fmt, int b_fm
            (static_cast<uint32_t>(M >> 4) << 24);
 }
 
-template <bool TRUNC>
+template <bool TRUNC, bool V8>
 __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params p, const __grid_constant__ CUtensorMap vmap,
                                                                    const __grid_constant__ CUtensorMap vbmap) {
+    using L = Lay<V8>;
+    constexpr int NA = L::NA, NV = L::NV, VBYTES = L::VBYTES;
+    constexpr int SM_KA = L::SM_KA, SM_VA = L::SM_VA, SM_VB = L::SM_VB, SM_KS = L::SM_KS, SM_W = L::SM_W, SM_W2 = L::SM_W2,
+                  SM_QM = L::SM_QM, SM_QF = L::SM_QF, SM_EQZ = L::SM_EQZ, SM_HST = L::SM_HST, SM_BAR = L::SM_BAR,
+                  SM_RED = L::SM_RED, SM_CNT = L::SM_CNT, SM_HOUT = L::SM_HOUT;
+    constexpr int B_AFULL = L::B_AFULL, B_LFULL = L::B_LFULL, B_VFULL = L::B_VFULL, B_VEMPTY = L::B_VEMPTY,
+                  B_WREADY = L::B_WREADY, B_QFULL = L::B_QFULL, B_QFREE = L::B_QFREE, B_BFULL = L::B_BFULL,
+                  B_BFREE = L::B_BFREE, B_ALLDONE = L::B_ALLDONE, B_COUNT = L::B_COUNT;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     auto bar = [&](int i) { return base + SM_BAR + 8 * i; };
@@ -370,9 +401,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 const int s = t % NV;
                 if (t >= NV) mbar_wait(bar(B_VEMPTY + s), ((t / NV) - 1) & 1, abort_flag, p.status);
                 const int64_t r = tile_row(lo + t * tstep);
-                mbar_expect_tx(bar(B_VFULL + s), 16384 + 256);
+                mbar_expect_tx(bar(B_VFULL + s), VBYTES + 256);
                 bulk_load(base + SM_KS + s * 256, p.ek + r, 256, bar(B_VFULL + s));
-                tma_load_2d(base + SM_VA + s * 16384, &vmap, 0, static_cast<int>(r), bar(B_VFULL + s));
+                tma_load_2d(base + SM_VA + s * VBYTES, &vmap, 0, static_cast<int>(r), bar(B_VFULL + s));
+                if (!V8) tma_load_2d(base + SM_VA + s * VBYTES + 16384, &vmap, 64, static_cast<int>(r), bar(B_VFULL + s));
             }
         }
     } else if (warp == 1) {
@@ -396,7 +428,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
     } else if (warp == 3) {
         // ================= MMA issuer: values =================
         if (lane == 0) {
-            constexpr uint32_t ID_V = instr_desc(1, 0, 1, 1, 1, 32, 128);    // e4m3 x e5m2 -> f32, both MN-major
+            // an 8-bit V: e4m3 x e5m2 -> f32, N = 4 terms x 8 rows; a 16-bit V: bf16 x bf16 -> f32, N = 2 terms x 8 rows;
+            // both operands MN-major
+            constexpr uint32_t ID_V = V8 ? instr_desc(1, 0, 1, 1, 1, 32, 128) : instr_desc(1, 1, 1, 1, 1, 16, 128);
             const uint64_t dva = smem_desc(base + SM_VA, 16384, 1024, 2);
             const uint64_t dvb = smem_desc(base + SM_VB, 16384, 1024, 2);
             const uint64_t dw = smem_desc(base + SM_W, 128, 2048, 0);
@@ -407,7 +441,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             // value MMAs of t-2 and then, by parity, for the plane-B buffer of t-2; the commit for
             // t-4's buffer must be the older of the two or that parity test passes a phase early
             for (int j = 0; j < n_tiles + 2; ++j) {
-                if (j >= 2) {
+                if (V8 && j >= 2) {
                     const int t = j - 2, b2 = t % NB2;
                     mbar_wait(bar(B_BFULL + t % NBQ), (t / NBQ) & 1, abort_flag, p.status);
                     const volatile uint32_t* qfp = reinterpret_cast<const volatile uint32_t*>(smem + SM_QF + (t % NBQ) * 16);
@@ -429,8 +463,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                     mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status);
                     mbar_wait(bar(B_WREADY + (t & 1)), (t >> 1) & 1, abort_flag, p.status);
                     tc_fence_after();
-                    // 32 keys per K step: 4096 bytes of V, 512 bytes of weights
-                    mma4_f8<256, 32>(tmem + T_ACC, dva + s * 1024, dw + (t & 1) * 256, ID_V, t > 0 ? 1u : 0u);
+                    if (V8) {
+                        // 32 keys per K step: 4096 bytes of V, 512 bytes of weights
+                        mma4_f8<256, 32>(tmem + T_ACC, dva + s * (VBYTES >> 4), dw + (t & 1) * 256, ID_V, t > 0 ? 1u : 0u);
+                    } else {
+                        // 16 keys per K step: 2048 bytes of V in each 64-channel box, 256 bytes of weights
+                        mma4_f16<128, 16>(tmem + T_ACC, dva + s * (VBYTES >> 4), dw + (t & 1) * 256, ID_V, t > 0 ? 1u : 0u);
+                        mma4_f16<128, 16>(tmem + T_ACC, dva + s * (VBYTES >> 4) + 512, dw + (t & 1) * 256 + 64, ID_V, 1u);
+                    }
                     tc_commit(bar(B_VEMPTY + s));
                 }
             }
@@ -483,8 +523,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             }
             live = live && valid;
             const bool refk = live && top >= -rk;
-            const bool refv = live && top >= -rv;
-            const bool big = live && top >= BIG_TOP;
+            // a 16-bit V has no second plane, and bf16 weights no range to run out of
+            const bool refv = V8 && live && top >= -rv;
+            const bool big = V8 && live && top >= BIG_TOP;
             // a quarter (this warp's 32 keys) with enough refine-V keys fetches its plane B whole;
             // the last, partial tile does not (rows past the range are not V's to read)
             const bool dv = refv && !refk && !big;
@@ -497,7 +538,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             if (refk || refv) {
                 const int64_t row = tile_row(tb) + k;
                 if (refk) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kb + row * HD));
-                if (refv && !dense) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vb + row * HD));
+                if (V8 && refv && !dense) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vb + row * HD));
             }
             const unsigned mk = __ballot_sync(0xffffffffu, refk);
             const unsigned mv = __ballot_sync(0xffffffffu, refv);
@@ -511,20 +552,32 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 w[g] = (live && !helped) ? e : 0.f;
                 rN[g] += w[g];
             }
-            // four E5M2 terms per weight: bytes [term][row]. The chain runs in fp16, two rows
-            // at a time: an E5M2 number is the high byte of an fp16, the differences are exact
             uint32_t wb[8];
+            if (V8) {
+                // four E5M2 terms per weight: bytes [term][row]. The chain runs in fp16, two rows
+                // at a time: an E5M2 number is the high byte of an fp16, the differences are exact
 #pragma unroll
-            for (int g = 0; g < 8; g += 2) {
-                __half2 r = __floats2half2_rn(w[g] * static_cast<float>(1 << W_BIAS), w[g + 1] * static_cast<float>(1 << W_BIAS));
+                for (int g = 0; g < 8; g += 2) {
+                    __half2 r = __floats2half2_rn(w[g] * static_cast<float>(1 << W_BIAS), w[g + 1] * static_cast<float>(1 << W_BIAS));
 #pragma unroll
-                for (int term = 0; term < 4; ++term) {
-                    uint16_t pk;
-                    asm("cvt.rn.satfinite.e5m2x2.f16x2 %0, %1;" : "=h"(pk) : "r"(*reinterpret_cast<const uint32_t*>(&r)));
-                    const int word = term * 2 + (g >> 2), sh = (g & 3) * 8;   // byte term*8 + g (and g+1)
-                    if (g == 0 || g == 4) wb[word] = static_cast<uint32_t>(pk) << sh; else wb[word] |= static_cast<uint32_t>(pk) << sh;
-                    const uint32_t qb = __byte_perm(static_cast<uint32_t>(pk), 0u, 0x1404);
-                    r = __hmul2(__hsub2(r, *reinterpret_cast<const __half2*>(&qb)), __floats2half2_rn(8.0f, 8.0f));
+                    for (int term = 0; term < 4; ++term) {
+                        uint16_t pk;
+                        asm("cvt.rn.satfinite.e5m2x2.f16x2 %0, %1;" : "=h"(pk) : "r"(*reinterpret_cast<const uint32_t*>(&r)));
+                        const int word = term * 2 + (g >> 2), sh = (g & 3) * 8;   // byte term*8 + g (and g+1)
+                        if (g == 0 || g == 4) wb[word] = static_cast<uint32_t>(pk) << sh; else wb[word] |= static_cast<uint32_t>(pk) << sh;
+                        const uint32_t qb = __byte_perm(static_cast<uint32_t>(pk), 0u, 0x1404);
+                        r = __hmul2(__hsub2(r, *reinterpret_cast<const __half2*>(&qb)), __floats2half2_rn(8.0f, 8.0f));
+                    }
+                }
+            } else {
+                // two bf16 terms per weight, w = hi + lo with lo = bf16(w - hi): unit 0 the eight
+                // rows' hi, unit 1 their lo (decode/kernel.py:1181-1189)
+#pragma unroll
+                for (int g = 0; g < 8; g += 2) {
+                    const uint32_t hi = pack_bf16x2(w[g], w[g + 1]);
+                    const float r0 = w[g] - __uint_as_float(hi << 16), r1 = w[g + 1] - __uint_as_float(hi & 0xFFFF0000u);
+                    wb[g >> 1] = hi;
+                    wb[4 + (g >> 1)] = pack_bf16x2(r0, r1);
                 }
             }
             uint8_t* wdst = smem + SM_W + (t & 1) * 4096 + k * 16;
@@ -533,16 +586,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             if (!valid) {
                 // rows past the range hold whatever the pool holds (an E4M3 NaN times a zero
                 // weight is a NaN): clear them
-                uint4* vrow = reinterpret_cast<uint4*>(smem + SM_VA + s * 16384 + k * 128);
+                uint4* vrow = reinterpret_cast<uint4*>(smem + SM_VA + s * VBYTES + k * 128);
 #pragma unroll
                 for (int u = 0; u < 8; ++u) vrow[u] = make_uint4(0, 0, 0, 0);
+                if (!V8) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) vrow[1024 + u] = make_uint4(0, 0, 0, 0);   // the second 64-channel box
+                }
             }
             fence_async_smem();
             mbar_arrive(bar(B_WREADY + (t & 1)));
             // plane B of V for this quarter, and the weights it meets. The flags and their barrier
             // have more slots than the key threads can run ahead of the MMA issuer (they need its
             // logits); only the data buffers, two tiles deep, are waited for, and only when used
-            {
+            if (V8) {
                 const int b2 = t % NB2, bq = t % NBQ;
                 if (dense) {
                     if (lane == 0 && t >= NB2) mbar_wait(bar(B_BFREE + b2), ((t / NB2) - 1) & 1, abort_flag, p.status);
@@ -620,8 +677,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             for (int i = 0; i < 16; ++i) a0[i] = a1[i] = b0[i] = b1[i] = 0u;   // an empty range never wrote the accumulators
             if (n_tiles > 0) {
                 tmem_ld16(tmem + lane_addr + T_ACC, a0);
-                tmem_ld16(tmem + lane_addr + T_ACC + 16, a1);
-                if (use_b) {
+                if (V8) tmem_ld16(tmem + lane_addr + T_ACC + 16, a1);
+                if (V8 && use_b) {
                     tmem_ld16(tmem + lane_addr + T_ACC2, b0);
                     tmem_ld16(tmem + lane_addr + T_ACC2 + 16, b1);
                 }
@@ -633,11 +690,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
                 if (g < G) {
-                    float x = __uint_as_float(a0[g]) + __uint_as_float(a0[8 + g]) * 0.125f +
-                              __uint_as_float(a1[g]) * (1.0f / 64.0f) + __uint_as_float(a1[8 + g]) * (1.0f / 512.0f);
-                    x += 0.125f * (__uint_as_float(b0[g]) + __uint_as_float(b0[8 + g]) * 0.125f +
-                                   __uint_as_float(b1[g]) * (1.0f / 64.0f) + __uint_as_float(b1[8 + g]) * (1.0f / 512.0f));
-                    x *= 1.0f / static_cast<float>(1 << W_BIAS);
+                    float x;
+                    if (V8) {
+                        x = __uint_as_float(a0[g]) + __uint_as_float(a0[8 + g]) * 0.125f +
+                            __uint_as_float(a1[g]) * (1.0f / 64.0f) + __uint_as_float(a1[8 + g]) * (1.0f / 512.0f);
+                        x += 0.125f * (__uint_as_float(b0[g]) + __uint_as_float(b0[8 + g]) * 0.125f +
+                                       __uint_as_float(b1[g]) * (1.0f / 64.0f) + __uint_as_float(b1[8 + g]) * (1.0f / 512.0f));
+                        x *= 1.0f / static_cast<float>(1 << W_BIAS);
+                    } else {
+                        x = __uint_as_float(a0[g]) + __uint_as_float(a0[8 + g]);   // the hi and the lo terms' products
+                    }
 #pragma unroll
                     for (int h = 0; h < NHELP; ++h) x += hout[h * (HOUT / 4) + g * 128 + k];
                     x += sRed[(256 + 8) * 16 + 8 + g] * vm;
@@ -686,9 +748,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
         const uint32_t* qm = reinterpret_cast<const uint32_t*>(smem + SM_QM);
         uint8_t* stage = smem + SM_HST + h * HD_KEYS * HSLOT;
         const uint32_t stage_a = base + SM_HST + h * HD_KEYS * HSLOT;
+        // the plane this lane copies from, and its bytes per key: K's two planes, then V's two
+        // planes (8-bit) or the two halves of V's bf16 row
         const uint8_t* plane_l = part == 0 ? reinterpret_cast<const uint8_t*>(p.ka)
                                : part == 1 ? reinterpret_cast<const uint8_t*>(p.kb)
-                               : part == 2 ? p.va : p.vb;   // the plane this lane copies from
+                               : (V8 ? (part == 2 ? p.va : p.vb) : (part == 2 ? p.va : p.va + 128));
+        const int row_bytes_l = (!V8 && part >= 2) ? 256 : HD;
 
         // issue side: the tile whose marked keys are being handed out
         int it = h;                       // next tile to open
@@ -741,8 +806,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             const int slot_i = issued % HD_KEYS;
             const uint32_t dst = stage_a + slot_i * HSLOT;
             // lane l copies unit l & 7 of plane l >> 3; a plane the key does not need is zero-filled
-            const int need = part == 1 ? (isK ? 16 : 0) : (part == 3 ? (isV ? 16 : 0) : 16);
-            cp_async(dst + 128 * part + 16 * hg, plane_l + row * HD + 16 * hg, need);
+            const int need = part == 1 ? (isK ? 16 : 0) : ((V8 && part == 3) ? (isV ? 16 : 0) : 16);
+            cp_async(dst + 128 * part + 16 * hg, plane_l + row * row_bytes_l + 16 * hg, need);
             if (lane == 0) {
                 const uint16_t* e = p.ek + row;
                 cp_async4(dst + 512, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(e) & ~uintptr_t(3)));
@@ -793,11 +858,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             }
             const float wl = hg < G ? ex2f(sv) : 0.f;   // row hg's weight, in all four quarters' lanes
             hden += wl;
-            float fa[4], fb[4];
-            e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb + 256 + 4 * lane), fa);
-            e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb + 384 + 4 * lane), fb);
+            float fa[4];
+            if (V8) {
+                float fb[4];
+                e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb + 256 + 4 * lane), fa);
+                e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb + 384 + 4 * lane), fb);
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) fa[cc] = fmaf(fb[cc], 0.125f, fa[cc]);
+                for (int cc = 0; cc < 4; ++cc) fa[cc] = fmaf(fb[cc], 0.125f, fa[cc]);
+            } else {
+                const uint2 vv = *reinterpret_cast<const uint2*>(sb + 256 + 8 * lane);   // four bf16 channels
+                fa[0] = __uint_as_float(vv.x << 16); fa[1] = __uint_as_float(vv.x & 0xFFFF0000u);
+                fa[2] = __uint_as_float(vv.y << 16); fa[3] = __uint_as_float(vv.y & 0xFFFF0000u);
+            }
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
                 const float wg_ = __shfl_sync(0xffffffffu, wl, g);
@@ -847,19 +919,27 @@ EncodeFn encode_fn() {
     return fn;
 }
 
-// A plane of V in the pool as rows of 128 bytes; a box is `box_rows` rows, swizzled on
-// its way into shared memory. The call does not know the pool's size: the row count
-// only bounds the coordinates, and every tile asked for lies inside a page.
-bool make_v_map(CUtensorMap* m, const void* va, int box_rows) {
+// V in the pool as rows of `row_bytes` bytes (an E4M3 plane: 128; a bf16 row: 256); a box is 128
+// bytes of `box_rows` rows, swizzled on its way into shared memory. The call does not know the
+// pool's size: the row count only bounds the coordinates, and every tile asked for lies inside a page.
+bool make_v_map(CUtensorMap* m, const void* v, int row_bytes, int box_rows) {
     EncodeFn fn = encode_fn();
     if (!fn) return false;
+    const bool wide = row_bytes == 256;
     cuuint64_t dims[2] = {128, 1ull << 30};
-    cuuint64_t strides[1] = {128};
-    cuuint32_t box[2] = {128, static_cast<cuuint32_t>(box_rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+    cuuint32_t box[2] = {wide ? 64u : 128u, static_cast<cuuint32_t>(box_rows)};
     cuuint32_t estr[2] = {1, 1};
-    return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(va), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return fn(m, wide ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(v), dims,
+              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool TRUNC, bool V8>
+void launch(const dsm100::Params& p, const CUtensorMap& vmap, const CUtensorMap& vbmap, int ctas, cudaStream_t st) {
+    auto kern = dsm100::decode_sm100_kernel<TRUNC, V8>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dsm100::Lay<V8>::SMEM_BYTES);
+    kern<<<ctas, dsm100::NTHREADS, dsm100::Lay<V8>::SMEM_BYTES, st>>>(p, vmap, vbmap);
 }
 
 }  // namespace
@@ -870,7 +950,8 @@ extern "C" int fold_decode_combine(const float* o_part, const float* den_part, c
                                    float v_scale, void* stream);
 
 extern "C" int fold_decode_sm100_supported(int group, int head_dim, int page_size, int chunk_keys, int v8) {
-    return v8 && head_dim == 128 && group >= 1 && group <= 8 && page_size % 128 == 0 && chunk_keys % 128 == 0 &&
+    (void)v8;   // both an 8-bit and a bf16 V
+    return head_dim == 128 && group >= 1 && group <= 8 && page_size % 128 == 0 && chunk_keys % 128 == 0 &&
            encode_fn() != nullptr;
 }
 
@@ -884,11 +965,11 @@ extern "C" int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const f
                                      const float* refine_bands, float v_scale, float* o_part,
                                      float* den_part, int32_t* cnt_part, void* out, int out_dtype,
                                      float* den, int32_t* counts, int32_t* status, void* stream) {
-    FOLD_CHECK_ARG(qa && qb && eq && ka && kb && ek && va && vb && z && cut && page_table && seq_lens &&
+    FOLD_CHECK_ARG(qa && qb && eq && ka && kb && ek && va && z && cut && page_table && seq_lens &&
                        o_part && den_part && cnt_part && status && (!out || (den && counts)),
                    "fold_decode_run_sm100: null pointer");
     if (!fold_decode_sm100_supported(group, head_dim, page_size, chunk_keys, 1)) {
-        set_error("the tcgen05 decode takes an 8-bit V, head_dim 128, groups of 1..8 rows, pages and chunks of a multiple of 128 keys");
+        set_error("the tcgen05 decode takes head_dim 128, groups of 1..8 rows, pages and chunks of a multiple of 128 keys");
         return FOLD_ERR_UNSUPPORTED;
     }
     FOLD_CHECK_ARG(split >= 1 && out_dtype >= 0 && out_dtype <= 2, "fold_decode_run_sm100: bad split or out_dtype");
@@ -910,20 +991,18 @@ extern "C" int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const f
         p.band_e0 = p.band_e1 = p.rk1 = p.rk2 = p.rv1 = p.rv2 = 0.f;
     }
     p.status = status;
+    const bool v8 = vb != nullptr;   // a NULL second plane: V is one bf16 row per key
     CUtensorMap vmap, vbmap;
-    if (!make_v_map(&vmap, va, 128) || !make_v_map(&vbmap, vb, 32)) {
+    if (!make_v_map(&vmap, va, v8 ? 128 : 256, 128) || !make_v_map(&vbmap, v8 ? vb : va, v8 ? 128 : 256, 32)) {
         set_error("fold_decode_run_sm100: cuTensorMapEncodeTiled failed");
         return FOLD_ERR_LAUNCH;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int ctas = n_groups * split;
     if (truncate) {
-        auto kern = dsm100::decode_sm100_kernel<true>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dsm100::SMEM_BYTES);
-        kern<<<n_groups * split, dsm100::NTHREADS, dsm100::SMEM_BYTES, st>>>(p, vmap, vbmap);
+        if (v8) launch<true, true>(p, vmap, vbmap, ctas, st); else launch<true, false>(p, vmap, vbmap, ctas, st);
     } else {
-        auto kern = dsm100::decode_sm100_kernel<false>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dsm100::SMEM_BYTES);
-        kern<<<n_groups * split, dsm100::NTHREADS, dsm100::SMEM_BYTES, st>>>(p, vmap, vbmap);
+        if (v8) launch<false, true>(p, vmap, vbmap, ctas, st); else launch<false, false>(p, vmap, vbmap, ctas, st);
     }
     int rc = check_launch("fold_decode_run_sm100");
     if (rc) return rc;

@@ -64,8 +64,9 @@ def prepare_fold_decode(
     depth below `z` under which a key is dropped (`truncate`). Calling the
     launch returns `(out (NBH, G, D), den (NBH, G), counts (NBH, 2))`.
     `kernel` picks the split-KV kernel: "mma" (warp-level, every shape), "sm100"
-    (tcgen05; an 8-bit V, D = 128, pages and chunks of a multiple of 128 keys;
-    its weights are four E5M2 terms whatever `weight_terms` says) or "auto".
+    (tcgen05; D = 128, pages and chunks of a multiple of 128 keys; its weights are
+    four E5M2 terms on an 8-bit V and two bf16 terms on a bf16 V, whatever
+    `weight_terms` says) or "auto".
     With an `order`, its first `short_slots` slots stay on the warp-level kernel
     when the tcgen05 one takes the rest (requests too short for it to pay), and
     one combine follows both.
@@ -88,7 +89,7 @@ def prepare_fold_decode(
     can = bool(_lib.lib.fold_decode_sm100_supported(G, D, int(page_size), int(chunk_keys), int(bool(v8))))
     if kernel == "sm100" and not can:
         raise NotImplementedError(
-            "the tcgen05 decode takes an 8-bit V, head_dim 128, pages and chunks of a multiple of 128 keys")
+            "the tcgen05 decode takes head_dim 128, pages and chunks of a multiple of 128 keys")
     use_sm100 = can and kernel in ("auto", "sm100")
     dev = qa.device
     split = int(split)

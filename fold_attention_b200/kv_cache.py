@@ -48,10 +48,10 @@ class FoldKVCache:
     output depends on the request alone.
 
     `kernel` (not a reference argument) picks the split-KV kernel: "mma" is
-    the warp-level one, which takes every shape; "sm100" the tcgen05 one (an
-    8-bit V, head_dim 128, pages and chunks of a multiple of 128 keys), which
-    streams the first planes whole and is the faster the longer the contexts
-    are; "auto" takes "sm100" where it applies and the cache truncates, for
+    the warp-level one, which takes every shape; "sm100" the tcgen05 one
+    (head_dim 128, pages and chunks of a multiple of 128 keys), which
+    streams K's first plane and V whole and is the faster the longer the
+    contexts are; "auto" takes "sm100" where it applies, for
     the requests of 12288 keys or more (shorter requests keep too many keys
     inside the refine gates, and those leave its tensor-core path): the batch
     goes where most of its keys would. With `mix_kernels` set (and a `chunk`)
@@ -302,9 +302,7 @@ class FoldKVCache:
         refine = self._refine()
         kernel, short = self.kernel, 0
         if kernel == "auto":
-            if self.depth is None:
-                kernel = "mma"
-            elif self.chunk and self.mix_kernels:
+            if self.chunk and self.mix_kernels:
                 # the slot order is by length (_set_order): the short requests are its first slots
                 short = self.n_kv_heads * sum(1 for n in self.lens if n < self.SM100_MIN_KEYS)
             elif 2 * sum(n for n in self.lens if n >= self.SM100_MIN_KEYS) < sum(self.lens):

@@ -115,7 +115,8 @@ int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const i
  * and V's first planes stream whole through shared memory; V's second plane is
  * fetched by 32-key quarters where enough keys pass the refine-V gate; the
  * remaining refined keys, and keys whose weight passes 2^8, are summed in fp32
- * by helper warps in a fixed order. For an 8-bit V, head_dim 128, groups of
+ * by helper warps in a fixed order. A bf16 V (vb NULL) runs the same schedule
+ * with two bf16 weight terms and no second plane. For head_dim 128, groups of
  * 1..8 rows, page_size and chunk_keys multiples of 128
  * (fold_decode_sm100_supported, which also wants the driver's tensor-map
  * encoder). Arguments as fold_decode_run without weight_terms; `va` and `vb`

@@ -22,12 +22,13 @@ def _launch(c, z, *, depth, rk, rv, split, chunk, HKV, ps, kernel):
 
     return prepare_fold_decode(
         c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, c.cut, split=split,
-        truncate=depth is not None, refine_k=rk, refine_v=rv, v8=True, v2=c.vb, v_scale=c.v_scale,
+        truncate=depth is not None, refine_k=rk, refine_v=rv, v8=c.v8, v2=c.vb, v_scale=c.v_scale,
         vmean=c.vmean, page_table=c.page_table, page_size=ps, seq_lens=c.seq_lens,
         n_kv_heads=HKV, weight_terms=2, chunk_keys=chunk, kernel=kernel,
     )
 
 
+@pytest.mark.parametrize("v8", [True, False])
 @pytest.mark.parametrize("depth", [None, 16.0, 8.0])
 @pytest.mark.parametrize("ps,G,lens,split,chunk", [
     (256, 8, [1500, 700, 64, 2049], 1, 0),
@@ -36,11 +37,11 @@ def _launch(c, z, *, depth, rk, rv, split, chunk, HKV, ps, kernel):
     (256, 1, [513, 2000], 0, 512),
     (256, 2, [5000, 100], 0, 1024),
 ])
-def test_the_tcgen05_kernel_is_the_model(depth, ps, G, lens, split, chunk):
+def test_the_tcgen05_kernel_is_the_model(depth, ps, G, lens, split, chunk, v8):
     HKV, D = 2, 128
     B = len(lens)
     q, k, v, cu = _layer(B, HKV * G, HKV, D, lens, seed=2, vmu=0.5)
-    c = _cache(B, HKV * G, HKV, D, lens, ps=ps, v8=True, depth=depth)
+    c = _cache(B, HKV * G, HKV, D, lens, ps=ps, v8=v8, depth=depth)
     c.write_prompt(k, v, cu, lens)
     c.attend(q)
     z = (torch.ceil(c.z * 16) / 16).contiguous()
@@ -67,7 +68,7 @@ def test_the_tcgen05_kernel_is_the_model(depth, ps, G, lens, split, chunk):
                     c.qa[bh], c.qb[bh], c.eq[bh], ka, kb, ek, va, vb, c.v_scale, z[bh], depth,
                     rk, rv, lens[b], vmean=c.vmean[bh] if depth is not None else None)
                 assert counts[bh].tolist() == [nlive, nref], (rk, rv, b, h)
-                # weights are 12-bit (four E5M2 terms off an fp16): 2^-11 each, less in the sum
+                # weights are 12-bit (four E5M2 terms off an fp16; 16-bit, two bf16 terms, on a bf16 V)
                 assert _rel(out[bh], want) < 1e-3, (rk, rv, b, h, _rel(out[bh], want))
                 assert ((den[bh].double() - wden).abs() / wden).max().item() < 1e-3
 
