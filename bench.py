@@ -127,31 +127,62 @@ def time_backward(cfg, device, steps, warmup, seed, dist):
 def time_e2e(cfg, device, steps, state):
     """The same metric through the public launch with HOST buffers: every step
     copies q, k, v, o, dO and lse from pinned memory, runs the backward and
-    copies dq, dk, dv back."""
-    q, k, v, o, do, lse, run = state
+    copies dq, dk, dv back. Steps are pipelined the way a host that feeds the
+    GPU would run them: two sets of device buffers, the copies in and out on
+    their own streams, so step i+1's inputs travel while step i computes and
+    step i-1's gradients leave. Timed with events from before the first copy in
+    to after the last copy out."""
+    from fold_attention_b200.backward import prepare_backward
+
+    q, k, v, o, do, lse, run0 = state
     host_in = [t.detach().cpu().pin_memory() for t in (q, k, v, o, do, lse)]
-    dev_in = (q, k, v, o, do, lse)
-    outs = run()
-    host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
+    tr = lambda x: x.transpose(1, 2)  # noqa: E731
+    slots = []
+    for i in range(2):
+        dev = (q, k, v, o, do, lse) if i == 0 else tuple(torch.empty_like(t) for t in (q, k, v, o, do, lse))
+        run = run0 if i == 0 else prepare_backward(tr(dev[0]), tr(dev[1]), tr(dev[2]), tr(dev[3]), tr(dev[4]), dev[5], causal=True)
+        outs = run()
+        slots.append(dict(dev=dev, run=run, host_out=[torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs],
+                          in_ready=torch.cuda.Event(), comp_done=torch.cuda.Event(), out_done=torch.cuda.Event()))
     h2d = sum(t.numel() * t.element_size() for t in host_in)
-    d2h = sum(t.numel() * t.element_size() for t in host_out)
+    d2h = sum(t.numel() * t.element_size() for t in slots[0]["host_out"])
+    s_in, s_c, s_out = (torch.cuda.Stream(device) for _ in range(3))
 
-    def step():
-        for d, h in zip(dev_in, host_in):
-            d.copy_(h, non_blocking=True)
-        res = run()
-        for h, d in zip(host_out, res):
-            h.copy_(d, non_blocking=True)
+    def step(i):
+        sl = slots[i % 2]
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(sl["comp_done"])      # the step two back has read these inputs
+            for d, h in zip(sl["dev"], host_in):
+                d.copy_(h, non_blocking=True)
+            sl["in_ready"].record(s_in)
+        with torch.cuda.stream(s_c):
+            s_c.wait_event(sl["in_ready"])
+            s_c.wait_event(sl["out_done"])        # and its gradients have left
+            res = sl["run"]()
+            sl["comp_done"].record(s_c)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(sl["comp_done"])
+            for h, d in zip(sl["host_out"], res):
+                h.copy_(d, non_blocking=True)
+            sl["out_done"].record(s_out)
 
-    step()
+    torch.cuda.synchronize()
+    for sl in slots:
+        for name in ("in_ready", "comp_done", "out_done"):
+            sl[name].record()
+    for i in range(2):
+        step(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
+    e0.record(s_in)
+    for i in range(steps):
+        step(i)
+    s_out.wait_stream(s_c)
+    e1.record(s_out)
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / steps, h2d, d2h
+    ms = e0.elapsed_time(e1) / steps
+    del slots
+    return ms, h2d, d2h
 
 
 def varlen_extra(device, steps=3):
