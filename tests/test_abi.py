@@ -42,3 +42,23 @@ def test_python_signatures_cover_the_header():
     from fold_attention_b200 import _lib
 
     assert set(_declared()) <= set(_lib.exported_symbols())
+
+
+def test_the_product_never_reaches_for_the_oracle_or_scratch():
+    """The oracle is test infrastructure: nothing under the package may import, read
+    or run it (or a scratch folder), and the package has no CPU fallback to route
+    through; bench.py may use it only in its cpu_baseline / reference arm."""
+    pkg = os.path.join(ROOT, "fold_attention_b200")
+    for dirpath, _, files in os.walk(pkg):
+        if os.sep + "build" in dirpath:
+            continue
+        for f in files:
+            if not f.endswith((".py", ".cu", ".cuh", ".h")):
+                continue
+            text = open(os.path.join(dirpath, f)).read()
+            assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), (dirpath, f)
+            assert not re.search(r"[\"'/]_work\b", text), (dirpath, f)
+    bench = open(os.path.join(ROOT, "bench.py")).read()
+    uses = [m.start() for m in re.finditer(r"from oracle import", bench)]
+    assert len(uses) == 1 and "def cpu_reference_tflops" in bench[:uses[0]]
+    assert bench.rfind("def ", 0, uses[0]) == bench.find("def cpu_reference_tflops")
