@@ -1,20 +1,21 @@
 // Attention forward on Blackwell tensor cores (tcgen05 + TMEM), head dim 128, bf16:
-// O and the log-sum-exp the backward consumes. One CTA owns 128 query rows of one
-// head; a query row is one TMEM lane, so a row's maximum and sum need no shuffle.
+// O and the log-sum-exp the backward consumes. One CTA owns 256 query rows of one
+// head as two tiles of 128; a query row is one TMEM lane of its tile, so a row's
+// maximum and sum need no shuffle.
 //
 //   S  = Q K^T   tcgen05.mma kind::f16, M=128 queries, N=128 keys, 8 steps of 16 channels,
 //                both operands K-major from shared memory (TMA, 128-byte swizzle) -> TMEM fp32
-//   P  = exp2(S c log2e - m)  by the row's thread, written back to TMEM as packed bf16
+//   P  = exp2(S c log2e - m)  by the row's thread, written over S in TMEM as packed bf16
 //   O += P V     A = P from TMEM, B = V as stored (MN-major), 8 steps of 16 keys -> TMEM fp32
 //
-// S and P are double-buffered in TMEM, K and V in shared memory, so the scores of tile
-// j+1 are formed while the softmax of tile j runs and its P V product follows. The
-// running maximum only ever rises; O is rescaled in TMEM when a row's maximum rose
-// (skipped by warps in which no row's did), after the previous product has retired.
+// The two tiles share each K/V stage and take turns on the tensor core: while one tile's
+// rows are in their softmax, the other's scores or P V product run. The running maximum
+// only ever rises; O is rescaled in TMEM when a row's maximum rose (skipped by warps in
+// which no row's did), after the tile's previous product has retired.
 //
-// Warps: 0 TMA producer, 1 MMA issuer (owns all 512 TMEM columns), 4-7 softmax, the O
-// rescale and the epilogue. Every wait is bounded (about a second); on expiry a status
-// word is raised, nobody waits any more, TMEM is freed and the kernel returns.
+// Warps: 0 TMA producer, 1 MMA issuer (owns all 512 TMEM columns), 4-7 and 8-11 the two
+// tiles' softmax, O rescale and epilogue. Every wait is bounded (about a second); on expiry
+// a status word is raised, nobody waits any more, TMEM is freed and the kernel returns.
 // Replaces the third-party forward called at src/fold_attention/interface.py:42-44,
 // :70-81 and kv_cache.py:252-262 (the algorithm is the usual online softmax; the
 // schedule is this kernel's own).
@@ -27,13 +28,14 @@
 namespace fold {
 namespace fsm100 {
 
-constexpr int BM = 128, BN = 128;
-constexpr int NTHREADS = 256;
+constexpr int BM = 128, BN = 128;   // a query tile, a key tile
+constexpr int CTA_M = 2 * BM;       // a CTA owns two query tiles
+constexpr int NTHREADS = 384;
 constexpr long long WAIT_CYCLES = 1ll << 31;
 
 // shared memory map (1024-aligned base)
-constexpr int SM_Q = 0;                        // [2 boxes of 64 channels][128 rows][128 B]
-constexpr int SM_KV = 32768;                   // 2 stages x { K 32 KB, V 32 KB }
+constexpr int SM_Q = 0;                        // 2 tiles x [2 boxes of 64 channels][128 rows][128 B]
+constexpr int SM_KV = 65536;                   // 2 stages x { K 32 KB, V 32 KB }
 constexpr int STAGE = 65536;
 constexpr int SM_BAR = SM_KV + 2 * STAGE;
 constexpr int SMEM_BYTES = SM_BAR + 256 + 1024;   // + room to align the base
@@ -41,13 +43,16 @@ constexpr int SMEM_BYTES = SM_BAR + 256 + 1024;   // + room to align the base
 enum {
     B_Q = 0,
     B_KVFULL = 1,      // [2] the stage's K and V have landed
-    B_KVEMPTY = 3,     // [2] the tile's P V product retired: its stage, its S and its P buffer are free
-    B_SFULL = 5,       // [2] the tile's scores are in TMEM
-    B_PREADY = 7,      // [2] 128 arrivals: the tile's P is in TMEM and O is rescaled
-    B_COUNT = 9,
+    B_KVEMPTY = 3,     // [2] both query tiles' products with the stage retired
+    B_SFULL = 5,       // [2 query tiles] the tile's scores against this key tile are in TMEM
+    B_PREADY = 7,      // [2 query tiles] 128 arrivals: P is in TMEM and O is rescaled
+    B_ODONE = 9,       // [2 query tiles] the tile's P V product retired
+    B_COUNT = 11,
 };
 
-constexpr uint32_t T_S = 0, T_P = 256, T_O = 384;   // TMEM columns: S 2 x 128, P 2 x 64, O 128
+// TMEM columns: per query tile 128 of S (P is written over its first 64 as the row's thread
+// goes), then 128 of O per tile
+constexpr uint32_t T_S = 0, T_O = 256;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -167,20 +172,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 8 * B_COUNT + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // the longest (last) query tiles first: under a causal mask they hold the most key tiles
+    // the last query rows first: under a causal mask they meet the most key tiles
     const int mb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     int start = 0, len = p.S;
     if (p.cu) {
         start = p.cu[b];
         len = p.cu[b + 1] - start;
     }
-    const int m0 = mb * BM;
+    const int m0 = mb * CTA_M;
     if (m0 >= len) return;
     const int hkv = h / p.G;
     const int bb = p.cu ? 0 : b;
-    // key tiles this query tile meets
-    const int kv_end = p.causal ? min(len, m0 + BM) : len;
-    const int n_tiles = (kv_end + BN - 1) / BN;
+    // key tiles each of the two query tiles meets (the second tile may lie past the sequence)
+    int nt[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int mx = m0 + x * BM;
+        const int kv_end = mx >= len ? 0 : (p.causal ? min(len, mx + BM) : len);
+        nt[x] = (kv_end + BN - 1) / BN;
+    }
+    const int n_tiles = max(nt[0], nt[1]);
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -190,6 +201,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
             mbar_init(bar(B_KVEMPTY + i), 1);
             mbar_init(bar(B_SFULL + i), 1);
             mbar_init(bar(B_PREADY + i), 128);
+            mbar_init(bar(B_ODONE + i), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -206,16 +218,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
     if (warp == 0) {
         // ================= TMA producer =================
         if (lane == 0) {
-            mbar_expect_tx(bar(B_Q), 32768);
-            for (int x = 0; x < 2; ++x) tma_load_4d(base + SM_Q + x * 16384, &maps.q, 64 * x, start + m0, h, bb, bar(B_Q));
+            mbar_expect_tx(bar(B_Q), nt[1] > 0 ? 65536 : 32768);
+            for (int x = 0; x < 2; ++x) {
+                if (nt[x] == 0) continue;
+                for (int c = 0; c < 2; ++c)
+                    tma_load_4d(base + SM_Q + x * 32768 + c * 16384, &maps.q, 64 * c, start + m0 + x * BM, h, bb, bar(B_Q));
+            }
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j & 1;
                 if (j >= 2) mbar_wait(bar(B_KVEMPTY + s), ((j >> 1) - 1) & 1, abort_flag, p.status);
                 const uint32_t st = base + SM_KV + s * STAGE;
                 mbar_expect_tx(bar(B_KVFULL + s), 65536);
-                for (int x = 0; x < 2; ++x) {
-                    tma_load_4d(st + x * 16384, &maps.k, 64 * x, start + j * BN, hkv, bb, bar(B_KVFULL + s));
-                    tma_load_4d(st + 32768 + x * 16384, &maps.v, 64 * x, start + j * BN, hkv, bb, bar(B_KVFULL + s));
+                for (int c = 0; c < 2; ++c) {
+                    tma_load_4d(st + c * 16384, &maps.k, 64 * c, start + j * BN, hkv, bb, bar(B_KVFULL + s));
+                    tma_load_4d(st + 32768 + c * 16384, &maps.v, 64 * c, start + j * BN, hkv, bb, bar(B_KVFULL + s));
                 }
             }
         }
@@ -225,51 +241,59 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
             constexpr uint32_t ID_S = instr_desc(128, 128, 0, 0);    // Q (K-major) x K (K-major)
             constexpr uint32_t ID_PV = instr_desc(128, 128, 0, 1);   // P (TMEM) x V (MN-major)
             mbar_wait(bar(B_Q), 0, abort_flag, p.status);
-            auto issue_s = [&](int j) {
+            auto issue_s = [&](int x, int j) {
                 const int s = j & 1;
                 mbar_wait(bar(B_KVFULL + s), (j >> 1) & 1, abort_flag, p.status);
-                // S and P buffer s were tile j-2's: its product has retired (the producer waited
-                // for the same barrier before refilling the stage)
-                if (j >= 2) mbar_wait(bar(B_KVEMPTY + s), ((j >> 1) - 1) & 1, abort_flag, p.status);
                 tc_fence_after();
-                const uint32_t kt = base + SM_KV + s * STAGE;
+                const uint32_t kt = base + SM_KV + s * STAGE, qt = base + SM_Q + x * 32768;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {   // 16 channels per step; 4 steps per 64-channel box
                     const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-                    mma_ss(tmem + T_S + 128 * s, smem_desc(base + SM_Q + off, 16, 1024), smem_desc(kt + off, 16, 1024), ID_S, ks > 0);
+                    mma_ss(tmem + T_S + 128 * x, smem_desc(qt + off, 16, 1024), smem_desc(kt + off, 16, 1024), ID_S, ks > 0);
                 }
-                tc_commit(bar(B_SFULL + s));
+                tc_commit(bar(B_SFULL + x));
             };
-            if (n_tiles > 0) issue_s(0);
+            for (int x = 0; x < 2; ++x)
+                if (nt[x] > 0) issue_s(x, 0);
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j & 1;
-                if (j + 1 < n_tiles) issue_s(j + 1);
-                mbar_wait(bar(B_PREADY + s), (j >> 1) & 1, abort_flag, p.status);
-                tc_fence_after();
                 const uint32_t vt = base + SM_KV + s * STAGE + 32768;
+                for (int x = 0; x < 2; ++x) {
+                    if (j >= nt[x]) continue;
+                    mbar_wait(bar(B_PREADY + x), j & 1, abort_flag, p.status);
+                    tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 8 TMEM columns of P, 2048 bytes of V per box
-                    mma_ts(tmem + T_O, tmem + T_P + 64 * s + 8 * ks, smem_desc(vt + ks * 2048, 16384, 1024), ID_PV, (j > 0) || (ks > 0));
+                    for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 8 TMEM columns of P, 2048 bytes of V per box
+                        mma_ts(tmem + T_O + 128 * x, tmem + T_S + 128 * x + 8 * ks, smem_desc(vt + ks * 2048, 16384, 1024), ID_PV,
+                               (j > 0) || (ks > 0));
+                    tc_commit(bar(B_ODONE + x));
+                    // the next scores overwrite S (and the P just consumed): the tensor pipe runs a
+                    // thread's MMAs in the order it issued them
+                    if (j + 1 < nt[x]) issue_s(x, j + 1);
+                }
                 tc_commit(bar(B_KVEMPTY + s));
             }
         }
     } else if (warp >= 4) {
-        // ================= softmax: thread = query row = TMEM lane =================
+        // ================= softmax: two groups, one per query tile; thread = query row = TMEM lane =================
+        const int x = (warp - 4) >> 2;
         const int r = 32 * (warp & 3) + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const float c2 = p.scale * kLog2e;
-        const int qi = m0 + r;                 // the row's position in its sequence
+        const int mx = m0 + x * BM;
+        const int qi = mx + r;                 // the row's position in its sequence
+        const int my_tiles = nt[x];
         float m_run = -INFINITY, l_run = 0.f;  // running maximum (log2 domain) and sum
-        for (int j = 0; j < n_tiles; ++j) {
-            const int s = j & 1;
+        const uint32_t ts = tmem + lane_addr + T_S + 128 * x;
+        const uint32_t to = tmem + lane_addr + T_O + 128 * x;
+        for (int j = 0; j < my_tiles; ++j) {
             const int n0 = j * BN;
-            const bool need_mask = (p.causal && n0 + BN > m0) || (n0 + BN > len);
+            const bool need_mask = (p.causal && n0 + BN > mx) || (n0 + BN > len);
             const int kmax = min(len - 1, p.causal ? qi : len - 1) - n0;   // last key column this row may see
-            mbar_wait(bar(B_SFULL + s), (j >> 1) & 1, abort_flag, p.status);
+            mbar_wait(bar(B_SFULL + x), j & 1, abort_flag, p.status);
             tc_fence_after();
-            const uint32_t ts = tmem + lane_addr + T_S + 128 * s;
             // pass 1: the row's maximum over the tile
-            float mx = -INFINITY;
+            float mxv = -INFINITY;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t sv[32];
@@ -277,18 +301,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
                 tmem_wait_ld();
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                    float x = __uint_as_float(sv[e]);
-                    if (need_mask && 32 * c + e > kmax) x = -INFINITY;
-                    mx = fmaxf(mx, x);
+                    float v = __uint_as_float(sv[e]);
+                    if (need_mask && 32 * c + e > kmax) v = -INFINITY;
+                    mxv = fmaxf(mxv, v);
                 }
             }
-            const float m_new = fmaxf(m_run, mx * c2);
+            const float m_new = fmaxf(m_run, mxv * c2);
             // a row that sees no key yet keeps m = -inf; its weights are exp2(-inf) = 0
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = ex2f(m_run - m_use);   // 0 on the first tile that holds a key
-            // pass 2: weights into TMEM as packed bf16, and their sum
+            // pass 2: weights over the scores as packed bf16 (P chunk c lands on columns the row's
+            // thread has already read), and their sum
             float sum = 0.f;
-            const uint32_t tp = tmem + lane_addr + T_P + 64 * s;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t sv[32];
@@ -306,62 +330,61 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
                     sum += x0 + x1;
                     pp[e >> 1] = pack_bf16x2(x0, x1);
                 }
-                tmem_st16(tp + 16 * c, pp);
+                tmem_st16(ts + 16 * c, pp);
             }
             l_run = l_run * alpha + sum;
             m_run = m_new;
-            // O was last written by tile j-1's product: rescale it where a row's maximum rose
+            // O was last written by key tile j-1's product: rescale it where a row's maximum rose
             if (j > 0) {
-                mbar_wait(bar(B_KVEMPTY + (s ^ 1)), ((j - 1) >> 1) & 1, abort_flag, p.status);
+                mbar_wait(bar(B_ODONE + x), (j - 1) & 1, abort_flag, p.status);
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t ov[32];
-                        tmem_ld32(tmem + lane_addr + T_O + 32 * c, ov);
+                        tmem_ld32(to + 32 * c, ov);
                         tmem_wait_ld();
 #pragma unroll
                         for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
-                        tmem_st32(tmem + lane_addr + T_O + 32 * c, ov);
+                        tmem_st32(to + 32 * c, ov);
                     }
                 }
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(B_PREADY + s));
+            mbar_arrive(bar(B_PREADY + x));
         }
         // ---- epilogue: O / l -> bf16, LSE in nats ----
-        if (n_tiles > 0) {
-            const int last = n_tiles - 1;
-            mbar_wait(bar(B_KVEMPTY + (last & 1)), (last >> 1) & 1, abort_flag, p.status);
-        }
-        tc_fence_after();
-        // the warp's tcgen05.ld is collective: every lane reads, rows past the sequence store nothing
-        const bool row_ok = qi < len;
-        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-        uint16_t* orow = row_ptr<uint16_t>(p.o, b, start + (row_ok ? qi : 0), h);
+        if (my_tiles > 0) {
+            mbar_wait(bar(B_ODONE + x), (my_tiles - 1) & 1, abort_flag, p.status);
+            tc_fence_after();
+            // the warp's tcgen05.ld is collective: every lane reads, rows past the sequence store nothing
+            const bool row_ok = qi < len;
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            uint16_t* orow = row_ptr<uint16_t>(p.o, b, start + (row_ok ? qi : 0), h);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            uint32_t ov[32];
-            tmem_ld32(tmem + lane_addr + T_O + 32 * c, ov);
-            tmem_wait_ld();
-            if (row_ok) {
+            for (int c = 0; c < 4; ++c) {
+                uint32_t ov[32];
+                tmem_ld32(to + 32 * c, ov);
+                tmem_wait_ld();
+                if (row_ok) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    uint4 w;
-                    w.x = pack_bf16x2(__uint_as_float(ov[8 * u]) * inv, __uint_as_float(ov[8 * u + 1]) * inv);
-                    w.y = pack_bf16x2(__uint_as_float(ov[8 * u + 2]) * inv, __uint_as_float(ov[8 * u + 3]) * inv);
-                    w.z = pack_bf16x2(__uint_as_float(ov[8 * u + 4]) * inv, __uint_as_float(ov[8 * u + 5]) * inv);
-                    w.w = pack_bf16x2(__uint_as_float(ov[8 * u + 6]) * inv, __uint_as_float(ov[8 * u + 7]) * inv);
-                    *reinterpret_cast<uint4*>(orow + 32 * c + 8 * u) = w;
+                    for (int u = 0; u < 4; ++u) {
+                        uint4 w;
+                        w.x = pack_bf16x2(__uint_as_float(ov[8 * u]) * inv, __uint_as_float(ov[8 * u + 1]) * inv);
+                        w.y = pack_bf16x2(__uint_as_float(ov[8 * u + 2]) * inv, __uint_as_float(ov[8 * u + 3]) * inv);
+                        w.z = pack_bf16x2(__uint_as_float(ov[8 * u + 4]) * inv, __uint_as_float(ov[8 * u + 5]) * inv);
+                        w.w = pack_bf16x2(__uint_as_float(ov[8 * u + 6]) * inv, __uint_as_float(ov[8 * u + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + 32 * c + 8 * u) = w;
+                    }
                 }
             }
+            if (row_ok) {
+                const float lse = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+                p.lse[static_cast<int64_t>(b) * p.lse_sb + static_cast<int64_t>(h) * p.lse_sh + start + qi] = lse;
+            }
+            tc_fence_before();
         }
-        if (row_ok) {
-            const float lse = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
-            p.lse[static_cast<int64_t>(b) * p.lse_sb + static_cast<int64_t>(h) * p.lse_sh + start + qi] = lse;
-        }
-        tc_fence_before();
     }
     __syncthreads();
     if (warp == 1) {
@@ -454,7 +477,7 @@ extern "C" int fold_fwd_run_sm100(const void* q, const void* k, const void* v, v
     }
     auto kern = fsm100::fwd_sm100_kernel;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fsm100::SMEM_BYTES);
-    dim3 grid((max_seqlen + fsm100::BM - 1) / fsm100::BM, n_heads, batch);
+    dim3 grid((max_seqlen + fsm100::CTA_M - 1) / fsm100::CTA_M, n_heads, batch);
     kern<<<grid, fsm100::NTHREADS, fsm100::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p, maps);
     return check_launch("fold_fwd_run_sm100");
 }

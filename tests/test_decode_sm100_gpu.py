@@ -168,3 +168,26 @@ def test_a_batch_splits_between_the_kernels_by_request_length():
                        torch.tensor([0, 500, 4500], device="cuda", dtype=torch.int32), [500, 4000])
     short.attend(q[[1, 3]])
     assert next(iter(short._launches.values())).kernel == "mma"
+
+
+@pytest.mark.parametrize("v8", [False, True])
+def test_dense_gates_follow_each_requests_length_on_both_kernels(v8):
+    """depth=None with the default gates: the kernel moves each request to its own length band
+    (edges 5793 and 23170 keys); both kernels count the same refined keys and track the softmax."""
+    from test_decode_gpu import _attend_ref
+
+    lens = [3000, 7000, 25000]
+    B, H, HKV, D = len(lens), 8, 2, 128
+    q, k, v, cu = _layer(B, H, HKV, D, lens, seed=21)
+    want = torch.stack([_attend_ref(q, k, v, cu, b, HKV, H // HKV) for b in range(B)])
+    outs = {}
+    for kernel in ("mma", "sm100"):
+        c = _cache(B, H, HKV, D, lens, ps=256, v8=v8, kernel=kernel, seed=5)
+        assert c._banded()
+        c.write_prompt(k, v, cu, lens)
+        outs[kernel] = (c.attend(q), c.counts.clone())
+        assert next(iter(c._launches.values())).kernel == kernel
+        assert _rel(outs[kernel][0], want) < 4e-3, (kernel, _rel(outs[kernel][0], want))
+        assert int(c.counts[:, 0].sum()) == sum(lens) * HKV   # every key is live
+    assert torch.equal(outs["mma"][1], outs["sm100"][1])
+    assert _rel(outs["sm100"][0].float(), outs["mma"][0].float()) < 2e-3
