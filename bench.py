@@ -4,7 +4,7 @@ keys, the paged decode) on B200.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 One JSON line on stdout. A step is one backward (preprocess + main loop +
-postprocess) over BASELINE config 2: batch 4, seqlen 8192, 32 query / 32 KV
+postprocess) over the headline configuration (config 2): batch 4, seqlen 8192, 32 query / 32 KV
 heads, head_dim 128, bf16, causal; inputs iid N(0,1) with 1/sqrt(D) on q, O and
 LSE from the library's own forward, computed before the timed region. At
 N > 1 every rank runs that workload on its own shard (weak scaling; the path
@@ -218,7 +218,7 @@ def varlen_extra(device, steps=3):
                 ms_per_step=ms, tflops=fl / ms / 1e9)
 
 
-def cpu_reference_tflops(seconds_budget=12.0):
+def cpu_reference_tflops(seconds_limit=12.0):
     """The reference's CPU arithmetic for this path: FP32 gradients of causal
     softmax attention per request and head (its benchmarks/harness/training.py
     :124-164), here the oracle's restatement, on the host cores. A bounded
@@ -233,7 +233,7 @@ def cpu_reference_tflops(seconds_budget=12.0):
     while True:
         ob.reference_grads(q, k, v, do, dtype=torch.float32)
         n += 1
-        if time.time() - t0 > seconds_budget or n >= 8:
+        if time.time() - t0 > seconds_limit or n >= 8:
             break
     dt = (time.time() - t0) / n
     return flops(1, S, H, D) / dt / 1e12, f"B1 H4 S{S} D{D} causal FP32 autograd x{n}, scaled by FLOPs"

@@ -790,7 +790,7 @@ extern "C" int fold_decode_combine(const float* o_part, const float* den_part, c
 
 // ---- a decode entry point that allocates nothing ------------------------------------
 // Some hosts may not allocate device memory from the code that runs a decode
-// step: an inference server that hands a plugin a fixed memory budget up front
+// step: an inference server that hands a plugin a fixed amount of memory up front
 // and forbids cudaMalloc (or any allocating library call) inside its execution
 // callback, or a process whose device allocator belongs to another runtime.
 // For them the split partials live in this fixed array instead of in buffers

@@ -1,6 +1,6 @@
 """The decode through the library's built-in scratch, for hosts that may not
-allocate device memory while a step runs (a serving plugin with a fixed
-memory budget, a process whose device allocator belongs to another runtime).
+allocate device memory while a step runs (a serving plugin given a fixed
+amount of memory, a process whose device allocator belongs to another runtime).
 
 `decode_static` takes the same planes as `prepare_fold_decode`, but the split
 partials live in a fixed 4 MiB array inside libfold_b200 instead of in torch

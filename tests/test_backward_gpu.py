@@ -81,7 +81,7 @@ def test_forward_and_gradient_accuracy(H, HKV, D, dtype, kernel):
 def test_config1_dense_mha_d64_twice(kernel):
     if kernel != "mma":
         pytest.skip("config 1 is head_dim 64: the public API picks the mma.sync kernel")
-    """BASELINE config 1: B2 S512 H8/8 D64 causal, N(0,1) inputs; checked
+    """Config 1 of the benchmark: B2 S512 H8/8 D64 causal, N(0,1) inputs; checked
     against FP64 autograd, and two runs are the same bits."""
     fa, _, _ = _api()
     torch.manual_seed(0)
@@ -289,7 +289,7 @@ def test_a_shard_of_kv_heads_is_the_full_runs_bits():
 
 
 def test_config2_full_size_repeats_and_matches_a_slice():
-    """BASELINE config 2 (GQA variant) at full size: B4 S8192 H32/8 D128. Two runs
+    """Config 2 of the benchmark (GQA variant) at full size: B4 S8192 H32/8 D128. Two runs
     are the same bits; one (request, KV head) unit run alone is the full run's
     slice (size-independent property); that unit's gradients match FP32 autograd."""
     _, attention_forward, prepare_backward = _api()
@@ -318,7 +318,7 @@ def test_config2_full_size_repeats_and_matches_a_slice():
 
 
 def test_config3_packed_64k_tokens_invariance():
-    """BASELINE config 3: 64K tokens, lengths uniform in [256, 8192], GQA 32/8,
+    """Config 3 of the benchmark: 64K tokens, lengths uniform in [256, 8192], GQA 32/8,
     D128. A sequence's gradients are the same bits packed, alone, and in a
     reversed packing."""
     lens, total = [], 65536

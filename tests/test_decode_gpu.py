@@ -23,7 +23,7 @@ def _fa():
 
 
 def _layer(B, H, HKV, D, lens, seed=0, peaked=True, dtype=torch.bfloat16, vmu=0.0):
-    """Packed prompts with BASELINE's distributions: K, V, q ~ N(0,1), 1% of
+    """Packed prompts with the benchmark configs' distributions: K, V, q ~ N(0,1), 1% of
     key positions x8, 0.1% of V entries x20."""
     g = torch.Generator(device="cuda").manual_seed(seed)
     T = sum(lens)
