@@ -191,3 +191,49 @@ def test_dense_gates_follow_each_requests_length_on_both_kernels(v8):
         assert int(c.counts[:, 0].sum()) == sum(lens) * HKV   # every key is live
     assert torch.equal(outs["mma"][1], outs["sm100"][1])
     assert _rel(outs["sm100"][0].float(), outs["mma"][0].float()) < 2e-3
+
+
+@pytest.mark.parametrize("seed", list(range(10)))
+def test_seeded_random_shapes_match_the_model(seed):
+    """Group width, page size, lengths, split or chunk, depth, gates and V type drawn from a
+    seed: counts equal the model's, outputs within the weight format's error, twice the same."""
+    import random
+
+    rng = random.Random(1000 + seed)
+    HKV, D = rng.choice([1, 2, 3]), 128
+    G = rng.choice([1, 2, 3, 4, 5, 6, 7, 8])
+    ps = rng.choice([128, 256, 384, 512])
+    B = rng.choice([1, 2, 3, 5])
+    lens = [rng.choice([1, 17, 127, 128, 129, 640, 1000, 2304, 3001, 4500]) for _ in range(B)]
+    v8 = rng.random() < 0.6
+    depth = rng.choice([None, 6.0, 12.0, 16.0, 20.0])
+    if rng.random() < 0.5:
+        split, chunk = rng.choice([1, 2, 3, 5, 9]), 0
+    else:
+        split, chunk = 0, rng.choice([128, 384, 1024, 2048])
+    rk, rv = rng.choice([(10.0, 12.0), (12.0, 8.0), (4.0, 16.0), (0.0, 0.0), (1e9, 1e9)])
+    q, k, v, cu = _layer(B, HKV * G, HKV, D, lens, seed=seed, vmu=rng.choice([0.0, 0.5]))
+    c = _cache(B, HKV * G, HKV, D, lens, ps=ps, v8=v8, depth=depth, seed=seed)
+    c.write_prompt(k, v, cu, lens)
+    c.attend(q)
+    z = (torch.ceil(c.z * 16) / 16).contiguous()
+    sp = split if not chunk else -(-max(lens) // chunk)
+    run = _launch(c, z, depth=depth, rk=rk, rv=rv, split=sp, chunk=chunk, HKV=HKV, ps=ps, kernel="sm100")
+    out, den, counts = run()
+    torch.cuda.synchronize()
+    assert int(run.status) == 0
+    first = (out.clone(), den.clone(), counts.clone())
+    for _ in range(4):
+        out, den, counts = run()
+        torch.cuda.synchronize()
+        assert torch.equal(out, first[0]) and torch.equal(den, first[1]) and torch.equal(counts, first[2])
+    for b in range(B):
+        for h in range(HKV):
+            bh = b * HKV + h
+            ka, kb, ek, va, vb = _planes(c, b, h, lens[b])
+            want, wden, nlive, nref = od.decode_model(
+                c.qa[bh], c.qb[bh], c.eq[bh], ka, kb, ek, va, vb, c.v_scale, z[bh], depth,
+                rk, rv, lens[b], vmean=c.vmean[bh] if depth is not None else None)
+            assert counts[bh].tolist() == [nlive, nref], (b, h)
+            assert _rel(out[bh], want) < 1e-3, (b, h, _rel(out[bh], want))
+            assert ((den[bh].double() - wden).abs() / wden).max().item() < 1e-3

@@ -101,3 +101,29 @@ def test_the_two_forwards_agree_and_auto_picks_by_shape():
         fwd(q64, k64, v64, causal=True, kernel="sm100")
     with pytest.raises(ValueError, match="kernel is one of"):
         fwd(q, k, v, causal=True, kernel="wgmma")
+
+
+@pytest.mark.parametrize("seed", list(range(6)))
+def test_seeded_random_packings_match_fp32_attention(seed):
+    import random
+
+    fwd = _fwd()
+    rng = random.Random(50 + seed)
+    HKV = rng.choice([1, 2, 4])
+    H = HKV * rng.choice([1, 2, 4])
+    lens = [rng.choice([1, 5, 127, 128, 129, 255, 256, 257, 700, 1300]) for _ in range(rng.choice([1, 2, 4, 6]))]
+    causal = rng.random() < 0.7
+    T = sum(lens)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(T, H, 128, device="cuda", generator=g).bfloat16()
+    k = torch.randn(T, HKV, 128, device="cuda", generator=g).bfloat16()
+    v = torch.randn(T, HKV, 128, device="cuda", generator=g).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    o, lse = fwd(q, k, v, causal=causal, cu_seqlens=cu, max_seqlen=max(lens), kernel="sm100")
+    torch.cuda.synchronize()
+    assert int(fwd.last_status) == 0
+    for b, n in enumerate(lens):
+        a, e = int(cu[b]), int(cu[b + 1])
+        want_o, want_lse = _ref(q[None, a:e], k[None, a:e], v[None, a:e], causal)
+        assert _rel(o[a:e], want_o[0]) < TOL_O, (b, n)
+        assert (lse[:, a:e] - want_lse[0]).abs().max().item() < TOL_LSE * max(1.0, want_lse.abs().max().item())
