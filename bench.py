@@ -185,6 +185,37 @@ def time_e2e(cfg, device, steps, state):
     return ms, h2d, d2h
 
 
+def train_extra(device, steps=3):
+    """Forward + backward through the public operator (`fold_attn_func` under autograd) on the
+    shape the reference publishes its "train" row for: B2 S8192 H32/8 D128, causal."""
+    import fold_attention_b200 as fa
+
+    B, S, H, HKV, D = 2, 8192, 32, 8, 128
+    g = torch.Generator(device=device).manual_seed(7)
+    q = (torch.randn(B, S, H, D, device=device, generator=g) / D**0.5).bfloat16().requires_grad_()
+    k = torch.randn(B, S, HKV, D, device=device, generator=g).bfloat16().requires_grad_()
+    v = torch.randn(B, S, HKV, D, device=device, generator=g).bfloat16().requires_grad_()
+    do = torch.randn(B, S, H, D, device=device, generator=g).bfloat16()
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        fa.fold_attn_func(q, k, v, causal=True).backward(do)
+
+    for _ in range(2):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    fl = 3.5 * 2 * B * H * S * S * D / 2   # 2 forward + 5 backward GEMMs, causal half
+    return dict(workload="forward + backward, fold_attn_func, B2 S8192 H32/8 D128 causal", ms_per_step=ms,
+                tflops=fl / ms / 1e9)
+
+
 def varlen_extra(device, steps=3):
     """Config 3: packed causal backward, GQA 32/8, D128, 64K tokens in sequences
     of length uniform in [256, 8192] (last truncated), int32 cu_seqlens on device."""
@@ -403,6 +434,7 @@ def main():
             torch.cuda.empty_cache()
             line["extra"] = dict(gqa_32_8=dict(ms_per_step=ms_g, tflops=fl / ms_g / 1e9))
             for key, fn in (("varlen_config3", lambda: varlen_extra(device)),
+                            ("train_fwd_bwd", lambda: train_extra(device)),
                             ("decode_config5", lambda: decode_extra(device, steps=6, B=256)),
                             ("decode_config4", lambda: decode_extra(device, B=128, dense=True))):
                 try:
