@@ -346,3 +346,40 @@ def test_config3_packed_64k_tokens_invariance():
     rev = _bwd(cat(q), cat(k), cat(v), o2, cat(do), lse2, cu2, S)
     pos = sum(lens[j] for j in order[: order.index(i)])
     assert all(torch.equal(x[pos:pos + lens[i]], sl(y)) for x, y in zip(rev, packed))
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_a_prepared_backward_replays_from_a_cuda_graph(kernel):
+    """The three phases are stream-ordered launches over buffers the launch owns (the
+    accumulator is zeroed in-stream): captured once, the backward replays on new inputs."""
+    _need(kernel, 128, torch.bfloat16)
+    _, attention_forward, prepare_backward = _api()
+    torch.manual_seed(41)
+    B, S, H, HKV, D = 2, 700, 8, 2, 128
+    mk = lambda h: torch.randn(B, S, h, D, device="cuda").bfloat16()  # noqa: E731
+    q, k, v, do = mk(H), mk(HKV), mk(HKV), mk(H)
+    o, lse = attention_forward(q, k, v, causal=True)
+    tr = lambda x: x.transpose(1, 2)  # noqa: E731
+    run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True, kernel=kernel)
+    want = tuple(x.clone() for x in run())
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            outs = run()
+    torch.cuda.synchronize()
+    for x in outs:
+        x.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert _same(outs, want)
+    # new upstream gradient in the bound buffer: the replay follows it
+    do2 = mk(H)
+    do.copy_(do2)
+    g.replay()
+    torch.cuda.synchronize()
+    got = tuple(x.clone() for x in outs)
+    assert _same(got, tuple(x.clone() for x in run()))
+    assert not _same(got, want)
+    assert int(run.status) == 0

@@ -237,3 +237,33 @@ def test_seeded_random_shapes_match_the_model(seed):
             assert counts[bh].tolist() == [nlive, nref], (b, h)
             assert _rel(out[bh], want) < 1e-3, (b, h, _rel(out[bh], want))
             assert ((den[bh].double() - wden).abs() / wden).max().item() < 1e-3
+
+
+@pytest.mark.parametrize("kernel", ["mma", "sm100"])
+def test_an_attend_step_replays_from_a_cuda_graph(kernel):
+    """Q's planes, the mass reference, the decode and the combine are stream-ordered launches
+    with no host synchronisation between them: a step captured once replays on new queries."""
+    lens = [1500, 3000]
+    B, H, HKV, D = len(lens), 16, 2, 128
+    q, k, v, cu = _layer(B, H, HKV, D, lens, seed=31)
+    c = _cache(B, H, HKV, D, lens, ps=128, v8=True, depth=16.0, kernel=kernel)
+    c.write_prompt(k, v, cu, lens)
+    q_static = q.clone()
+    c.attend(q_static)                      # binds the launches and their buffers
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            out_static = c.attend(q_static)
+    torch.cuda.synchronize()
+    q2 = torch.randn_like(q)
+    want = c.attend(q2).clone()
+    q_static.copy_(q2)
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out_static, want)
+    q_static.copy_(q)
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out_static, c.attend(q))
