@@ -280,6 +280,12 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
     from fold_attention_b200 import FoldKVCache
 
     H, HKV, D = (32, 8, 128) if dense else (64, 8, 128)
+    # the pool is sized by the longest request for every request: halve the batch until the pool and
+    # the prompt tensors fit beside what is already on the device
+    free = torch.cuda.mem_get_info(device)[0]
+    top = 32768 if dense else 131072
+    while B > 8 and B * (top + 256) * HKV * (642 if dense else 514) * 1.30 + (6 << 30) > free:
+        B //= 2
     g = torch.Generator().manual_seed(seed)
     if dense:
         lens = torch.randint(1024, 32769, (B,), generator=g).tolist()
