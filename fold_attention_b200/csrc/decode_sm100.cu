@@ -48,6 +48,8 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "fold_b200.h"
 
@@ -836,48 +838,82 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             // keep the slots full as far as keys are to be had now; wait for one only when idle
             while (issued - taken < HD_KEYS && issue_one(false)) {}
             if (issued == taken && !issue_one(true)) break;
-            // the oldest key's rows: all copies but the younger ones have landed
-            if (issued - taken == HD_KEYS) asm volatile("cp.async.wait_group %0;" ::"n"(HD_KEYS - 1) : "memory");
+            // Two keys a pass when two are in flight: their dot products, shuffles and conversions do
+            // not depend on each other, which a lone warp's in-order issue needs to stay busy. The
+            // sums still take the keys in order.
+            const int avail = issued - taken;
+            // (measured: a gain on a bf16 V, where a tile holds about five such keys; a small loss on an
+            // 8-bit V, where most tiles hold one or two)
+            const bool two = !V8 && avail >= 2;
+            const int pending = avail - (two ? 2 : 1);   // younger copies that may still be in flight
+            if (pending >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+            else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
             else asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncwarp();
-            const uint8_t* sb = stage + (taken % HD_KEYS) * HSLOT;
-            const uint32_t note = *reinterpret_cast<const volatile uint32_t*>(sb + 516);
-            const int sw = note & 7;
-            const bool isK = (note & 8u) != 0u;
-            const uint32_t ekw = *reinterpret_cast<const uint32_t*>(sb + 512);
-            const float tk = eq_l * (bf16_bits_to_float(static_cast<uint16_t>((note & 16u) ? (ekw >> 16) : (ekw & 0xFFFFu))) * (1.0f / 256.0f));
-            // K's planes are stored with their 16-byte units swizzled by slot
-            const int u0 = ((2 * part) ^ sw) << 4, u1 = ((2 * part + 1) ^ sw) << 4;
-            const uint4 ka0 = *reinterpret_cast<const uint4*>(sb + u0), ka1 = *reinterpret_cast<const uint4*>(sb + u1);
-            const int c1 = dot8(ka0, ka1, qaw), c2 = dot8(ka0, ka1, qbw);
-            float sv = fmaf(static_cast<float>(c1 * 256 + c2), tk, -z_l);
-            if (isK) {
-                const uint4 kb0 = *reinterpret_cast<const uint4*>(sb + 128 + u0), kb1 = *reinterpret_cast<const uint4*>(sb + 128 + u1);
-                const int c3a = dot8(kb0, kb1, qaw), c3b = dot8(kb0, kb1, qbw);
-                sv = sv + (static_cast<float>(c3a) + static_cast<float>(c3b) * (1.0f / 256.0f)) * tk;
-            }
-            const float wl = hg < G ? ex2f(sv) : 0.f;   // row hg's weight, in all four quarters' lanes
-            hden += wl;
-            float fa[4];
-            if (V8) {
-                float fb[4];
-                e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb + 256 + 4 * lane), fa);
-                e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb + 384 + 4 * lane), fb);
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc) fa[cc] = fmaf(fb[cc], 0.125f, fa[cc]);
-            } else {
-                const uint2 vv = *reinterpret_cast<const uint2*>(sb + 256 + 8 * lane);   // four bf16 channels
-                fa[0] = __uint_as_float(vv.x << 16); fa[1] = __uint_as_float(vv.x & 0xFFFF0000u);
-                fa[2] = __uint_as_float(vv.y << 16); fa[3] = __uint_as_float(vv.y & 0xFFFF0000u);
-            }
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                const float wg_ = __shfl_sync(0xffffffffu, wl, g);
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc) acc[g][cc] = fmaf(wg_, fa[cc], acc[g][cc]);
-            }
-            __syncwarp();   // the slot is read out before the next copy may land in it
-            ++taken;
+            auto consume = [&](auto n_keys) {
+                constexpr int N = decltype(n_keys)::value;
+                const uint8_t* sb[2] = {stage + (taken % HD_KEYS) * HSLOT, stage + ((taken + N - 1) % HD_KEYS) * HSLOT};
+                uint32_t note[2];
+                float tk[2];
+                uint4 ka0[2], ka1[2];
+                int u0[2], u1[2];
+    #pragma unroll
+                for (int j = 0; j < N; ++j) {
+                    note[j] = *reinterpret_cast<const volatile uint32_t*>(sb[j] + 516);
+                    const uint32_t ekw = *reinterpret_cast<const uint32_t*>(sb[j] + 512);
+                    tk[j] = eq_l * (bf16_bits_to_float(static_cast<uint16_t>((note[j] & 16u) ? (ekw >> 16) : (ekw & 0xFFFFu))) * (1.0f / 256.0f));
+                    // K's planes are stored with their 16-byte units swizzled by slot
+                    const int sw = note[j] & 7;
+                    u0[j] = ((2 * part) ^ sw) << 4;
+                    u1[j] = ((2 * part + 1) ^ sw) << 4;
+                    ka0[j] = *reinterpret_cast<const uint4*>(sb[j] + u0[j]);
+                    ka1[j] = *reinterpret_cast<const uint4*>(sb[j] + u1[j]);
+                }
+                float sv[2];
+    #pragma unroll
+                for (int j = 0; j < N; ++j) {
+                    const int c1 = dot8(ka0[j], ka1[j], qaw), c2 = dot8(ka0[j], ka1[j], qbw);
+                    sv[j] = fmaf(static_cast<float>(c1 * 256 + c2), tk[j], -z_l);
+                }
+                if (((note[0] | note[N - 1]) & 8u) != 0u) {   // a key without plane B of K had zeros copied: its term is 0
+    #pragma unroll
+                    for (int j = 0; j < N; ++j) {
+                        const uint4 kb0 = *reinterpret_cast<const uint4*>(sb[j] + 128 + u0[j]), kb1 = *reinterpret_cast<const uint4*>(sb[j] + 128 + u1[j]);
+                        const int c3a = dot8(kb0, kb1, qaw), c3b = dot8(kb0, kb1, qbw);
+                        if (note[j] & 8u) sv[j] = sv[j] + (static_cast<float>(c3a) + static_cast<float>(c3b) * (1.0f / 256.0f)) * tk[j];
+                    }
+                }
+                float wl[2], fa[2][4];
+    #pragma unroll
+                for (int j = 0; j < N; ++j) {
+                    wl[j] = hg < G ? ex2f(sv[j]) : 0.f;   // row hg's weight, in all four quarters' lanes
+                    if (V8) {
+                        float fb[4];
+                        e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb[j] + 256 + 4 * lane), fa[j]);
+                        e4m3x4_to_float(*reinterpret_cast<const uint32_t*>(sb[j] + 384 + 4 * lane), fb);
+    #pragma unroll
+                        for (int cc = 0; cc < 4; ++cc) fa[j][cc] = fmaf(fb[cc], 0.125f, fa[j][cc]);
+                    } else {
+                        const uint2 vv = *reinterpret_cast<const uint2*>(sb[j] + 256 + 8 * lane);   // four bf16 channels
+                        fa[j][0] = __uint_as_float(vv.x << 16); fa[j][1] = __uint_as_float(vv.x & 0xFFFF0000u);
+                        fa[j][2] = __uint_as_float(vv.y << 16); fa[j][3] = __uint_as_float(vv.y & 0xFFFF0000u);
+                    }
+                }
+                hden += wl[0];
+                if (N == 2) hden += wl[1];
+    #pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float w0 = __shfl_sync(0xffffffffu, wl[0], g), w1 = N == 2 ? __shfl_sync(0xffffffffu, wl[1], g) : 0.f;
+    #pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        acc[g][cc] = fmaf(w0, fa[0][cc], acc[g][cc]);
+                        if (N == 2) acc[g][cc] = fmaf(w1, fa[1][cc], acc[g][cc]);
+                    }
+                }
+            };
+            if (two) consume(std::integral_constant<int, 2>{}); else consume(std::integral_constant<int, 1>{});
+            __syncwarp();   // the slots are read out before the next copies may land in them
+            taken += two ? 2 : 1;
         }
         // the sums go where V's ring was: wait until nothing reads or fills it any more
         if (n_tiles > 0) mbar_wait(bar(B_ALLDONE), 0, abort_flag, p.status);
