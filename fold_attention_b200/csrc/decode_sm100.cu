@@ -60,7 +60,6 @@ constexpr int TK = 128;          // keys per tile
 constexpr int HD = 128;
 constexpr int QD = 8;            // tiles of helper masks in flight
 constexpr int NHELP = 4;
-constexpr int HD_KEYS = 4;       // keys whose rows a helper has in flight into its staging slots
 constexpr int HSLOT = 528;       // a staging slot: Ka, Kb, Va, Vb rows of 128 bytes, the scale's word, the key's note
 constexpr int NBQ = 8;            // tiles of quarter flags (and their barrier) in flight: more than the key threads can lead by
 constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weights) in flight
@@ -80,6 +79,8 @@ struct Lay {
     static constexpr int NV = V8 ? 5 : 4;             // ring slots of V (plane A) and the key scales
     static constexpr int VBYTES = V8 ? 16384 : 32768; // a V slot: [128 keys][128 B], or two 64-channel boxes of that
     static constexpr int NB2E = V8 ? NB2 : 0;
+    static constexpr int HD_KEYS = V8 ? 4 : 8;        // keys whose rows a helper has in flight into its staging slots
+    static constexpr int HPASS = V8 ? 1 : 4;          // keys a helper takes in one pass, when that many are in flight
     static constexpr int SM_KA = 2048;                           // NA x Ka [128 keys][128 B]
     static constexpr int SM_VA = SM_KA + NA * 16384;             // NV x V slots
     static constexpr int SM_VB = SM_VA + NV * VBYTES;            // NB2 x Vb [128 keys][128 B], fetched by quarters
@@ -285,7 +286,7 @@ template <bool TRUNC, bool V8>
 __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params p, const __grid_constant__ CUtensorMap vmap,
                                                                    const __grid_constant__ CUtensorMap vbmap) {
     using L = Lay<V8>;
-    constexpr int NA = L::NA, NV = L::NV, VBYTES = L::VBYTES;
+    constexpr int NA = L::NA, NV = L::NV, VBYTES = L::VBYTES, HD_KEYS = L::HD_KEYS, HPASS = L::HPASS;
     constexpr int SM_KA = L::SM_KA, SM_VA = L::SM_VA, SM_VB = L::SM_VB, SM_KS = L::SM_KS, SM_W = L::SM_W, SM_W2 = L::SM_W2,
                   SM_QM = L::SM_QM, SM_QF = L::SM_QF, SM_EQZ = L::SM_EQZ, SM_HST = L::SM_HST, SM_BAR = L::SM_BAR,
                   SM_RED = L::SM_RED, SM_CNT = L::SM_CNT, SM_HOUT = L::SM_HOUT;
@@ -838,25 +839,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             // keep the slots full as far as keys are to be had now; wait for one only when idle
             while (issued - taken < HD_KEYS && issue_one(false)) {}
             if (issued == taken && !issue_one(true)) break;
-            // Two keys a pass when two are in flight: their dot products, shuffles and conversions do
-            // not depend on each other, which a lone warp's in-order issue needs to stay busy. The
-            // sums still take the keys in order.
+            // Several keys a pass when that many are in flight: their dot products, shuffles and
+            // conversions do not depend on each other, which a lone warp's in-order issue needs to
+            // stay busy. The sums still take the keys in order. (Measured: a gain on a bf16 V, where a
+            // tile holds about five such keys; a small loss on an 8-bit V, where most tiles hold one or
+            // two, so there a pass is one key.)
             const int avail = issued - taken;
-            // (measured: a gain on a bf16 V, where a tile holds about five such keys; a small loss on an
-            // 8-bit V, where most tiles hold one or two)
-            const bool two = !V8 && avail >= 2;
-            const int pending = avail - (two ? 2 : 1);   // younger copies that may still be in flight
-            if (pending >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
-            else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
-            else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            const int take = (HPASS >= 4 && avail >= 4) ? 4 : ((HPASS >= 2 && avail >= 2) ? 2 : 1);
+            {   // the younger copies may still be in flight
+                const int pending = avail - take;
+                if (pending >= 4) asm volatile("cp.async.wait_group 4;" ::: "memory");
+                else if (pending == 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
+                else if (pending == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+                else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+                else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
             __syncwarp();
             auto consume = [&](auto n_keys) {
                 constexpr int N = decltype(n_keys)::value;
-                const uint8_t* sb[2] = {stage + (taken % HD_KEYS) * HSLOT, stage + ((taken + N - 1) % HD_KEYS) * HSLOT};
-                uint32_t note[2];
-                float tk[2];
-                uint4 ka0[2], ka1[2];
-                int u0[2], u1[2];
+                const uint8_t* sb[N];
+    #pragma unroll
+                for (int j = 0; j < N; ++j) sb[j] = stage + ((taken + j) % HD_KEYS) * HSLOT;
+                uint32_t note[N];
+                float tk[N];
+                uint4 ka0[N], ka1[N];
+                int u0[N], u1[N];
     #pragma unroll
                 for (int j = 0; j < N; ++j) {
                     note[j] = *reinterpret_cast<const volatile uint32_t*>(sb[j] + 516);
@@ -869,13 +876,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                     ka0[j] = *reinterpret_cast<const uint4*>(sb[j] + u0[j]);
                     ka1[j] = *reinterpret_cast<const uint4*>(sb[j] + u1[j]);
                 }
-                float sv[2];
+                float sv[N];
     #pragma unroll
                 for (int j = 0; j < N; ++j) {
                     const int c1 = dot8(ka0[j], ka1[j], qaw), c2 = dot8(ka0[j], ka1[j], qbw);
                     sv[j] = fmaf(static_cast<float>(c1 * 256 + c2), tk[j], -z_l);
                 }
-                if (((note[0] | note[N - 1]) & 8u) != 0u) {   // a key without plane B of K had zeros copied: its term is 0
+                uint32_t any_note = 0u;
+    #pragma unroll
+                for (int j = 0; j < N; ++j) any_note |= note[j];
+                if ((any_note & 8u) != 0u) {   // a key without plane B of K had zeros copied: its term is 0
     #pragma unroll
                     for (int j = 0; j < N; ++j) {
                         const uint4 kb0 = *reinterpret_cast<const uint4*>(sb[j] + 128 + u0[j]), kb1 = *reinterpret_cast<const uint4*>(sb[j] + 128 + u1[j]);
@@ -883,7 +893,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                         if (note[j] & 8u) sv[j] = sv[j] + (static_cast<float>(c3a) + static_cast<float>(c3b) * (1.0f / 256.0f)) * tk[j];
                     }
                 }
-                float wl[2], fa[2][4];
+                float wl[N], fa[N][4];
     #pragma unroll
                 for (int j = 0; j < N; ++j) {
                     wl[j] = hg < G ? ex2f(sv[j]) : 0.f;   // row hg's weight, in all four quarters' lanes
@@ -899,21 +909,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                         fa[j][2] = __uint_as_float(vv.y << 16); fa[j][3] = __uint_as_float(vv.y & 0xFFFF0000u);
                     }
                 }
-                hden += wl[0];
-                if (N == 2) hden += wl[1];
+    #pragma unroll
+                for (int j = 0; j < N; ++j) hden += wl[j];
     #pragma unroll
                 for (int g = 0; g < 8; ++g) {
-                    const float w0 = __shfl_sync(0xffffffffu, wl[0], g), w1 = N == 2 ? __shfl_sync(0xffffffffu, wl[1], g) : 0.f;
+                    float wg_[N];
+    #pragma unroll
+                    for (int j = 0; j < N; ++j) wg_[j] = __shfl_sync(0xffffffffu, wl[j], g);
     #pragma unroll
                     for (int cc = 0; cc < 4; ++cc) {
-                        acc[g][cc] = fmaf(w0, fa[0][cc], acc[g][cc]);
-                        if (N == 2) acc[g][cc] = fmaf(w1, fa[1][cc], acc[g][cc]);
+    #pragma unroll
+                        for (int j = 0; j < N; ++j) acc[g][cc] = fmaf(wg_[j], fa[j][cc], acc[g][cc]);
                     }
                 }
             };
-            if (two) consume(std::integral_constant<int, 2>{}); else consume(std::integral_constant<int, 1>{});
+            if (take == 4) consume(std::integral_constant<int, (HPASS >= 4 ? 4 : 1)>{});
+            else if (take == 2) consume(std::integral_constant<int, (HPASS >= 2 ? 2 : 1)>{});
+            else consume(std::integral_constant<int, 1>{});
             __syncwarp();   // the slots are read out before the next copies may land in them
-            taken += two ? 2 : 1;
+            taken += take;
         }
         // the sums go where V's ring was: wait until nothing reads or fills it any more
         if (n_tiles > 0) mbar_wait(bar(B_ALLDONE), 0, abort_flag, p.status);
