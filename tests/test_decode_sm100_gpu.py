@@ -267,3 +267,97 @@ def test_an_attend_step_replays_from_a_cuda_graph(kernel):
     g.replay()
     torch.cuda.synchronize()
     assert torch.equal(out_static, c.attend(q))
+
+
+def test_config4_full_size_properties():
+    """Config 4 at its own size (dense bf16 V, B128, H32/8, D128, lengths U[1024, 32768], pages
+    shuffled): two serving steps through each kernel. The tcgen05 kernel repeats its bits, counts
+    the keys the warp-level kernel counts, agrees with it, and sampled requests match FP32
+    attention over everything written."""
+    from fold_attention_b200 import FoldKVCache
+
+    B, H, HKV, D = 128, 32, 8, 128
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(1024, 32769, (B,), generator=g).tolist()
+    gd = torch.Generator(device="cuda").manual_seed(6)
+    T = sum(lens)
+    k = torch.randn(T, HKV, D, device="cuda", generator=gd)
+    hot = torch.rand(T, 1, 1, device="cuda", generator=gd) < 0.01
+    k = torch.where(hot, k * 8, k).bfloat16()
+    v = torch.randn(T, HKV, D, device="cuda", generator=gd).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    steps = [tuple(torch.randn(B, h, D, device="cuda", generator=gd).bfloat16() for h in (H, HKV, HKV)) for _ in range(2)]
+    outs = {}
+    for kernel in ("sm100", "mma"):
+        c = FoldKVCache(B, H, HKV, D, max(lens) + 4, device="cuda", kernel=kernel)
+        c.page_table.copy_(torch.randperm(c.page_table.numel(), device="cuda", generator=torch.Generator(device="cuda").manual_seed(9)).int().view_as(c.page_table))
+        c.write_prompt(k, v, cu, lens)
+        res = [c.decode(q, kn, vn) for q, kn, vn in steps]
+        assert next(iter(c._launches.values())).kernel == kernel
+        outs[kernel] = (res, c.counts.clone())
+        if kernel == "sm100":
+            again = c.attend(steps[-1][0])      # the cache as it stands, the same query
+            assert torch.equal(again, res[-1])
+            assert int(next(iter(c._launches.values())).status) == 0
+            keep = c
+    assert torch.equal(outs["sm100"][1], outs["mma"][1])
+    for a, b in zip(outs["sm100"][0], outs["mma"][0]):
+        assert _rel(a.float(), b.float()) < 2e-3
+    G = H // HKV
+    q, kn, vn = steps[-1]
+    for b in (0, 17, 127):
+        a, e = int(cu[b]), int(cu[b + 1])
+        for h in (0, 7):
+            ks = torch.cat([k[a:e, h], steps[0][1][b, h][None], kn[b, h][None]]).float()
+            vs = torch.cat([v[a:e, h], steps[0][2][b, h][None], vn[b, h][None]]).float()
+            want = od.attend_fp32(q[b, h * G:(h + 1) * G].float(), ks, vs)
+            assert _rel(outs["sm100"][0][-1][b, h * G:(h + 1) * G], want) < 4e-3, (b, h)
+    assert keep.lens == [n + 2 for n in lens]
+
+
+def test_config5_shape_properties():
+    """Config 5's shape (v8, depth 16, H64/8, D128, lengths log-uniform in [4096, 131072], 1 % of
+    keys x 8, 0.1 % of V entries x 20) at 32 of its 256 requests (the full batch runs in bench.py):
+    the tcgen05 kernel repeats its bits, counts the warp-level kernel's live and refined keys,
+    agrees with it, and sampled requests stay inside the depth's error bound against FP32
+    attention."""
+    import math
+
+    from fold_attention_b200 import FoldKVCache
+
+    B, H, HKV, D = 32, 64, 8, 128
+    g = torch.Generator().manual_seed(5)
+    lens = [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
+    gd = torch.Generator(device="cuda").manual_seed(6)
+    T = sum(lens)
+    k = torch.randn(T, HKV, D, device="cuda", generator=gd)
+    hot = torch.rand(T, 1, 1, device="cuda", generator=gd) < 0.01
+    k = torch.where(hot, k * 8, k).bfloat16()
+    v = torch.randn(T, HKV, D, device="cuda", generator=gd)
+    big = torch.rand(T, HKV, D, device="cuda", generator=gd) < 0.001
+    v = torch.where(big, v * 20, v).bfloat16()
+    del hot, big
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    q, kn, vn = (torch.randn(B, h, D, device="cuda", generator=gd).bfloat16() for h in (H, HKV, HKV))
+    outs = {}
+    for kernel in ("sm100", "mma"):
+        c = FoldKVCache(B, H, HKV, D, max(lens) + 4, depth=16.0, v8=True, device="cuda", kernel=kernel)
+        c.page_table.copy_(torch.randperm(c.page_table.numel(), device="cuda", generator=torch.Generator(device="cuda").manual_seed(9)).int().view_as(c.page_table))
+        c.write_prompt(k, v, cu, lens)
+        out = c.decode(q, kn, vn)
+        assert next(iter(c._launches.values())).kernel == kernel
+        assert torch.equal(c.attend(q), out)
+        assert int(next(iter(c._launches.values())).status) == 0
+        outs[kernel] = (out, c.counts.clone())
+        del c
+    assert torch.equal(outs["sm100"][1], outs["mma"][1])
+    assert _rel(outs["sm100"][0].float(), outs["mma"][0].float()) < 2e-3
+    G = H // HKV
+    short = min(range(B), key=lambda b: lens[b])
+    for b in (short, 3):
+        a, e = int(cu[b]), int(cu[b + 1])
+        for h in (0, 5):
+            ks = torch.cat([k[a:e, h], kn[b, h][None]]).float()
+            vs = torch.cat([v[a:e, h], vn[b, h][None]]).float()
+            want = od.attend_fp32(q[b, h * G:(h + 1) * G].float(), ks, vs)
+            assert _rel(outs["sm100"][0][b, h * G:(h + 1) * G], want) < 2.0 ** (-16.0 / 3), (b, h)
