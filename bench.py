@@ -315,6 +315,9 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
         at += n
     del kk, vv, hot, out
     c.write_prompt(k, v, cu, lens)
+    # the two shortest and the longest request's prompts, kept to check the steps' output afterwards
+    order = sorted(range(B), key=lambda b: lens[b])
+    sample = {b: (k[int(cu[b]):int(cu[b + 1])].clone(), v[int(cu[b]):int(cu[b + 1])].clone()) for b in order[:2] + order[-1:]}
     del k, v
     q = torch.randn(B, H, D, device=device, generator=gd).bfloat16()
     kn = torch.randn(B, HKV, D, device=device, generator=gd).bfloat16()
@@ -325,10 +328,20 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
     torch.cuda.synchronize()
     e0.record()
     for _ in range(steps):
-        c.decode(q, kn, vn)
+        out = c.decode(q, kn, vn)
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) / steps * 1e3
+    # the last step against dense FP32 attention over everything written (rel-L2, worst sampled request)
+    G, err = H // HKV, 0.0
+    for b, (kp, vp) in sample.items():
+        ks = torch.cat([kp, kn[b][None].expand(2 + steps, -1, -1)]).float()
+        vs = torch.cat([vp, vn[b][None].expand(2 + steps, -1, -1)]).float()
+        qs = q[b].float().view(HKV, G, D)
+        w = torch.softmax(torch.einsum("hgd,shd->hgs", qs, ks) / D**0.5, -1)
+        want = torch.einsum("hgs,shd->hgd", w, vs).reshape(H, D)
+        err = max(err, ((out[b].float() - want).norm() / want.norm()).item())
+    del sample
     keys = sum(c.lens) * HKV
     live = c.counts[:, 0].sum().item() / keys
     refk = c.counts[:, 1].sum().item() / keys
@@ -339,7 +352,7 @@ def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
             f"config5-shaped decode v8 depth16 B{B} H64/8 D128 lens logU[4096,131072] " +
             ("chunk8192" if kernel == "mma" else "default split"))
     return dict(workload=name, kernel="/".join(sorted({l.kernel for l in c._launches.values()})),
-                us_per_step=us, keys=keys, live_fraction=live, refined_fraction=refk,
+                us_per_step=us, keys=keys, live_fraction=live, refined_fraction=refk, rel_l2_vs_fp32=err,
                 algorithmic_gbs=byts / us / 1e3, hbm_frac=byts / us / 1e3 / peaks()["hbm"])
 
 
