@@ -441,8 +441,8 @@ def main():
         clocks=ck,
         roofline=dict(bound="tensor", achieved=fl / main_max / 1e9, peak=pk["bf16"], unit="TFLOP/s",
                       frac=fl / main_max / 1e9 / pk["bf16"],
-                      # dram__bytes_read + write of one main-loop launch: 631.1 MB captured at batch 1
-                      # (profiles/bwd_main_sm100_config2.md), scaled by the batch (traffic is per request)
+                      # dram__bytes_read + write of one main-loop launch: 631.1 MB in an ncu capture at
+                      # batch 1, scaled by the batch (the traffic is per request)
                       traffic=631.1e6 * CFG["B"],
                       note=f"main-loop kernel, of {pk['which']} sustained bf16 GEMM; burst peak {pk['bf16_burst']}; "
                            "traffic in bytes per launch, scaled from a batch-1 ncu capture"),
