@@ -33,7 +33,7 @@ _lib.register(
 )
 _lib.register("fold_fwd_run", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
 _lib.register("fold_fwd_sm100_supported", [I, I])
-_lib.register("fold_fwd_run_sm100", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P])
+_lib.register("fold_fwd_run_sm100", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P])
 
 KERNELS = {"auto": 0, "mma": 1, "sm100": 2}
 
@@ -155,7 +155,7 @@ def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, m
     Dense: `(B, S, H, D)` tensors, lse `(B, H, S)`. Varlen: `(total, H, D)`,
     lse `(H, total)`. Stands in for the third-party forward the reference
     calls (src/fold_attention/interface.py:42-44,70-81). `kernel`: "mma" (warp-level,
-    every head dim, both 16-bit types), "sm100" (tcgen05; head_dim 128, bf16) or
+    every head dim), "sm100" (tcgen05; head_dim 128) or
     "auto"."""
     if kernel not in ("auto", "mma", "sm100"):
         raise ValueError('kernel is one of ("auto", "mma", "sm100")')
@@ -183,13 +183,13 @@ def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, m
     strides = (ctypes.c_int64 * 12)(*st)
     can = bool(_lib.lib.fold_fwd_sm100_supported(D, int(q.dtype == torch.float16)))
     if kernel == "sm100" and not can:
-        raise NotImplementedError("the tcgen05 forward takes head_dim 128, bf16")
+        raise NotImplementedError("the tcgen05 forward takes head_dim 128")
     if can and kernel != "mma":
         status = torch.zeros(1, device=q.device, dtype=torch.int32)
         _lib.call(
             "fold_fwd_run_sm100", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
             ctypes.addressof(strides), _lib.ptr(cu_seqlens), B, H, k.shape[-2], S, total, D,
-            int(bool(causal)), sm, status.data_ptr(), _lib.stream(q.device),
+            int(bool(causal)), int(q.dtype == torch.float16), sm, status.data_ptr(), _lib.stream(q.device),
         )
         attention_forward.last_status = status   # non-zero after a device-side wait ran out
         return o, lse

@@ -1,11 +1,11 @@
-// Attention forward on Blackwell tensor cores (tcgen05 + TMEM), head dim 128, bf16:
+// Attention forward on Blackwell tensor cores (tcgen05 + TMEM), head dim 128, bf16 or fp16:
 // O and the log-sum-exp the backward consumes. One CTA owns 256 query rows of one
 // head as two tiles of 128; a query row is one TMEM lane of its tile, so a row's
 // maximum and sum need no shuffle.
 //
 //   S  = Q K^T   tcgen05.mma kind::f16, M=128 queries, N=128 keys, 8 steps of 16 channels,
 //                both operands K-major from shared memory (TMA, 128-byte swizzle) -> TMEM fp32
-//   P  = exp2(S c log2e - m)  by the row's thread, written over S in TMEM as packed bf16
+//   P  = exp2(S c log2e - m)  by the row's thread, written over S in TMEM as packed 16-bit
 //   O += P V     A = P from TMEM, B = V as stored (MN-major), 8 steps of 16 keys -> TMEM fp32
 //
 // The two tiles share each K/V stage and take turns on the tensor core: while one tile's
@@ -142,9 +142,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
     d |= 2ull << 61;
     return d;
 }
-// instruction descriptor: bf16 x bf16 -> f32, M x N, operand majors (0 K, 1 MN)
-__host__ __device__ constexpr uint32_t instr_desc(int M, int N, int a_mn, int b_mn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn) << 15) |
+// instruction descriptor: 16-bit x 16-bit -> f32 (format 1 bf16, 0 fp16), M x N, operand majors (0 K, 1 MN)
+__host__ __device__ constexpr uint32_t instr_desc(int fmt, int M, int N, int a_mn, int b_mn) {
+    return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) | (static_cast<uint32_t>(a_mn) << 15) |
            (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
            (static_cast<uint32_t>(M >> 4) << 24);
 }
@@ -162,6 +162,7 @@ struct Maps {
     CUtensorMap q, k, v;   // (channel, row, head, batch), boxes (64, 128, 1, 1)
 };
 
+template <bool F16>
 __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, const __grid_constant__ Maps maps) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
@@ -238,8 +239,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            constexpr uint32_t ID_S = instr_desc(128, 128, 0, 0);    // Q (K-major) x K (K-major)
-            constexpr uint32_t ID_PV = instr_desc(128, 128, 0, 1);   // P (TMEM) x V (MN-major)
+            constexpr uint32_t ID_S = instr_desc(F16 ? 0 : 1, 128, 128, 0, 0);    // Q (K-major) x K (K-major)
+            constexpr uint32_t ID_PV = instr_desc(F16 ? 0 : 1, 128, 128, 0, 1);   // P (TMEM) x V (MN-major)
             mbar_wait(bar(B_Q), 0, abort_flag, p.status);
             auto issue_s = [&](int x, int j) {
                 const int s = j & 1;
@@ -328,7 +329,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
                         if (32 * c + e + 1 > kmax) x1 = 0.f;
                     }
                     sum += x0 + x1;
-                    pp[e >> 1] = pack_bf16x2(x0, x1);
+                    pp[e >> 1] = F16 ? pack_f16x2(x0, x1) : pack_bf16x2(x0, x1);
                 }
                 tmem_st16(ts + 16 * c, pp);
             }
@@ -360,6 +361,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
             tc_fence_after();
             // the warp's tcgen05.ld is collective: every lane reads, rows past the sequence store nothing
             const bool row_ok = qi < len;
+            auto pk2 = [](float a, float b2) { return F16 ? pack_f16x2(a, b2) : pack_bf16x2(a, b2); };
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
             uint16_t* orow = row_ptr<uint16_t>(p.o, b, start + (row_ok ? qi : 0), h);
 #pragma unroll
@@ -371,10 +373,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         uint4 w;
-                        w.x = pack_bf16x2(__uint_as_float(ov[8 * u]) * inv, __uint_as_float(ov[8 * u + 1]) * inv);
-                        w.y = pack_bf16x2(__uint_as_float(ov[8 * u + 2]) * inv, __uint_as_float(ov[8 * u + 3]) * inv);
-                        w.z = pack_bf16x2(__uint_as_float(ov[8 * u + 4]) * inv, __uint_as_float(ov[8 * u + 5]) * inv);
-                        w.w = pack_bf16x2(__uint_as_float(ov[8 * u + 6]) * inv, __uint_as_float(ov[8 * u + 7]) * inv);
+                        w.x = pk2(__uint_as_float(ov[8 * u]) * inv, __uint_as_float(ov[8 * u + 1]) * inv);
+                        w.y = pk2(__uint_as_float(ov[8 * u + 2]) * inv, __uint_as_float(ov[8 * u + 3]) * inv);
+                        w.z = pk2(__uint_as_float(ov[8 * u + 4]) * inv, __uint_as_float(ov[8 * u + 5]) * inv);
+                        w.w = pk2(__uint_as_float(ov[8 * u + 6]) * inv, __uint_as_float(ov[8 * u + 7]) * inv);
                         *reinterpret_cast<uint4*>(orow + 32 * c + 8 * u) = w;
                     }
                 }
@@ -418,7 +420,7 @@ EncodeFn encode_fn() {
 
 // (channel, row, head, batch) view of a (batch, row, head, channel)-strided bf16 tensor; a box is
 // 64 channels of 128 rows. Rows past the tensor read as zeros.
-bool make_map(CUtensorMap* m, const void* ptr, int64_t sb, int64_t sr, int64_t sh, int64_t rows, int heads, int batch) {
+bool make_map(CUtensorMap* m, const void* ptr, int64_t sb, int64_t sr, int64_t sh, int64_t rows, int heads, int batch, bool f16) {
     EncodeFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
@@ -426,7 +428,7 @@ bool make_map(CUtensorMap* m, const void* ptr, int64_t sb, int64_t sr, int64_t s
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(sr * 2), static_cast<cuuint64_t>(sh * 2), static_cast<cuuint64_t>(sb * 2)};
     cuuint32_t box[4] = {64, 128, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+    return fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -434,18 +436,19 @@ bool make_map(CUtensorMap* m, const void* ptr, int64_t sb, int64_t sr, int64_t s
 }  // namespace
 
 extern "C" int fold_fwd_sm100_supported(int head_dim, int is_f16) {
-    return head_dim == 128 && !is_f16 && encode_fn() != nullptr;
+    (void)is_f16;   // bf16 and fp16
+    return head_dim == 128 && encode_fn() != nullptr;
 }
 
 extern "C" int fold_fwd_run_sm100(const void* q, const void* k, const void* v, void* o, float* lse,
                                   const int64_t* strides, const int32_t* cu_seqlens, int batch, int n_heads,
-                                  int n_kv_heads, int max_seqlen, int total, int head_dim, int causal,
+                                  int n_kv_heads, int max_seqlen, int total, int head_dim, int causal, int is_f16,
                                   float softmax_scale, int32_t* status, void* stream) {
     FOLD_CHECK_ARG(q && k && v && o && lse && strides && status, "fold_fwd_run_sm100: null pointer");
     FOLD_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0, "the query heads must be a multiple of the KV heads");
     FOLD_CHECK_ARG(batch > 0 && max_seqlen > 0, "fold_fwd_run_sm100: empty call");
     if (!fold_fwd_sm100_supported(head_dim, 0)) {
-        set_error("the tcgen05 forward takes head_dim 128, bf16");
+        set_error("the tcgen05 forward takes head_dim 128");
         return FOLD_ERR_UNSUPPORTED;
     }
     const void* ptrs[4] = {q, k, v, o};
@@ -469,15 +472,22 @@ extern "C" int fold_fwd_run_sm100(const void* q, const void* k, const void* v, v
     const int64_t rows = cu_seqlens ? total : max_seqlen;
     const int mbatch = cu_seqlens ? 1 : batch;
     fsm100::Maps maps;
-    if (!make_map(&maps.q, q, strides[0], strides[1], strides[2], rows, n_heads, mbatch) ||
-        !make_map(&maps.k, k, strides[3], strides[4], strides[5], rows, n_kv_heads, mbatch) ||
-        !make_map(&maps.v, v, strides[6], strides[7], strides[8], rows, n_kv_heads, mbatch)) {
+    const bool f16 = is_f16 != 0;
+    if (!make_map(&maps.q, q, strides[0], strides[1], strides[2], rows, n_heads, mbatch, f16) ||
+        !make_map(&maps.k, k, strides[3], strides[4], strides[5], rows, n_kv_heads, mbatch, f16) ||
+        !make_map(&maps.v, v, strides[6], strides[7], strides[8], rows, n_kv_heads, mbatch, f16)) {
         set_error("fold_fwd_run_sm100: cuTensorMapEncodeTiled failed");
         return FOLD_ERR_LAUNCH;
     }
-    auto kern = fsm100::fwd_sm100_kernel;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fsm100::SMEM_BYTES);
     dim3 grid((max_seqlen + fsm100::CTA_M - 1) / fsm100::CTA_M, n_heads, batch);
-    kern<<<grid, fsm100::NTHREADS, fsm100::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p, maps);
+    if (f16) {
+        auto kern = fsm100::fwd_sm100_kernel<true>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fsm100::SMEM_BYTES);
+        kern<<<grid, fsm100::NTHREADS, fsm100::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p, maps);
+    } else {
+        auto kern = fsm100::fwd_sm100_kernel<false>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fsm100::SMEM_BYTES);
+        kern<<<grid, fsm100::NTHREADS, fsm100::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p, maps);
+    }
     return check_launch("fold_fwd_run_sm100");
 }

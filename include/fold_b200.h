@@ -226,14 +226,14 @@ int fold_fwd_run(const void* q, const void* k, const void* v, void* o, float* ls
                  int is_f16, float softmax_scale, void* stream);
 
 /* The same forward on tcgen05 tensor cores (TMA-fed Q K^T and P V with S, P and O in TMEM),
- * for head_dim 128 and bf16 (fold_fwd_sm100_supported). Arguments as fold_fwd_run without
- * is_f16, plus status: int32[1], set non-zero if a device-side wait ran out. Replaces the
- * same third-party forward as fold_fwd_run. */
+ * for head_dim 128, bf16 or fp16 (fold_fwd_sm100_supported). Arguments as fold_fwd_run, plus
+ * status: int32[1], set non-zero if a device-side wait ran out. Replaces the same third-party
+ * forward as fold_fwd_run. */
 int fold_fwd_sm100_supported(int head_dim, int is_f16);
 int fold_fwd_run_sm100(const void* q, const void* k, const void* v, void* o, float* lse,
                        const int64_t* strides /* host */, const int32_t* cu_seqlens, int batch,
                        int n_heads, int n_kv_heads, int max_seqlen, int total, int head_dim,
-                       int causal, float softmax_scale, int32_t* status, void* stream);
+                       int causal, int is_f16, float softmax_scale, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -92,15 +92,31 @@ def test_the_two_forwards_agree_and_auto_picks_by_shape():
     assert torch.equal(o_a, o_s) and torch.equal(lse_a, lse_s)
     assert _rel(o_s, o_m.float()) < 2e-3 and (lse_s - lse_m).abs().max().item() < 1e-5
     q16, k16, v16 = _qkv(1, 200, 4, 4, 128, 4, torch.float16)
-    o16, _ = fwd(q16, k16, v16, causal=True)                  # fp16: the warp-level kernel
-    assert o16.dtype == torch.float16
-    with pytest.raises(NotImplementedError, match="head_dim 128, bf16"):
-        fwd(q16, k16, v16, causal=True, kernel="sm100")
+    o16, lse16 = fwd(q16, k16, v16, causal=True)              # fp16, head_dim 128: tcgen05 as well
+    o16s, lse16s = fwd(q16, k16, v16, causal=True, kernel="sm100")
+    assert o16.dtype == torch.float16 and torch.equal(o16, o16s) and torch.equal(lse16, lse16s)
     q64, k64, v64 = _qkv(1, 200, 4, 4, 64, 5)
-    with pytest.raises(NotImplementedError, match="head_dim 128, bf16"):
+    o64, _ = fwd(q64, k64, v64, causal=True)                  # head_dim 64: the warp-level kernel
+    assert o64.shape == q64.shape
+    with pytest.raises(NotImplementedError, match="head_dim 128"):
         fwd(q64, k64, v64, causal=True, kernel="sm100")
     with pytest.raises(ValueError, match="kernel is one of"):
         fwd(q, k, v, causal=True, kernel="wgmma")
+
+
+@pytest.mark.parametrize("kernel", ["mma", "sm100"])
+@pytest.mark.parametrize("B,S,H,HKV,causal", [(2, 384, 4, 2, True), (1, 1000, 8, 2, False), (1, 129, 8, 1, True)])
+def test_fp16_forward_is_softmax_attention(kernel, B, S, H, HKV, causal):
+    fwd = _fwd()
+    q, k, v = _qkv(B, S, H, HKV, 128, 7 * S + H, torch.float16)
+    o, lse = fwd(q, k, v, causal=causal, kernel=kernel)
+    torch.cuda.synchronize()
+    if kernel == "sm100":
+        assert int(fwd.last_status) == 0
+    want_o, want_lse = _ref(q, k, v, causal)
+    assert o.dtype == torch.float16
+    assert _rel(o, want_o) < TOL_O
+    assert (lse - want_lse).abs().max().item() < TOL_LSE * max(1.0, want_lse.abs().max().item())
 
 
 @pytest.mark.parametrize("seed", list(range(6)))
