@@ -91,7 +91,7 @@ static int bwd_run_phases(const void* q, const void* k, const void* v, const voi
     bool sm100 = false;
     if (kernel == FOLD_BWD_KERNEL_SM100) {
         if (!bwd_sm100_supported(p)) {
-            set_error("the tcgen05 backward takes head_dim 128, bf16");
+            set_error("the tcgen05 backward takes head_dim 128");
             return FOLD_ERR_UNSUPPORTED;
         }
         sm100 = true;

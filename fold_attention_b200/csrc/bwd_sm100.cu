@@ -1,6 +1,6 @@
 // The deterministic attention backward on Blackwell tensor cores: tcgen05.mma
 // with TMEM accumulators, TMA-fed 128-byte-swizzled shared tiles, mbarrier
-// pipelines between specialised warps. Head dim 128, bf16, dense or packed.
+// pipelines between specialised warps. Head dim 128, bf16 or fp16, dense or packed.
 //
 // One CTA owns one block of 128 keys of one (request, KV head) and walks query
 // blocks of 64 rows, for each of the group's G query heads in turn. Per query
@@ -8,7 +8,7 @@
 //     S^T  = K Q^T            SS  M=128 keys,  N=64 queries, K=128      -> R_S[b]
 //     dP^T = V dO^T           SS                                          -> R_D[b]
 //     P~^T = exp2(S^T c - (L - s)), dS~^T = P~^T (dP^T - Delta)   (compute warps:
-//            P~^T back to TMEM as bf16 over S^T, dS~^T to shared, swizzled)
+//            P~^T back to TMEM as 16-bit over S^T, dS~^T to shared, swizzled)
 //     dV  += P~^T dO          TS  A from TMEM, M=128 keys, N=128, K=64
 //     dK  += dS~^T Q          SS  A = dS~^T (K-major), B = Q (MN-major)
 //     dQ~^T = K^T dS~^T       SS  A = K^T (MN-major), B = dS~^T (MN-major) -> R_D[b]
@@ -156,9 +156,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
     d |= 2ull << 61;   // SWIZZLE_128B
     return d;
 }
-// instruction descriptor: bf16 x bf16 -> f32, M x N, operand majors (0 K, 1 MN)
-__host__ __device__ constexpr uint32_t instr_desc(int M, int N, int a_mn, int b_mn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn) << 15) |
+// instruction descriptor: 16-bit x 16-bit -> f32 (format 1 bf16, 0 fp16), M x N, operand majors (0 K, 1 MN)
+__host__ __device__ constexpr uint32_t instr_desc(int fmt, int M, int N, int a_mn, int b_mn) {
+    return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) | (static_cast<uint32_t>(a_mn) << 15) |
            (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
            (static_cast<uint32_t>(M >> 4) << 24);
 }
@@ -167,6 +167,7 @@ struct Maps {
     CUtensorMap q, dout, k, v;   // (channel, row, head, batch), boxes (64, 64|128, 1, 1)
 };
 
+template <bool F16>
 __global__ void __launch_bounds__(NTHREADS, 1)
 bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
     extern __shared__ uint8_t smem_raw[];
@@ -249,10 +250,10 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            constexpr uint32_t ID_S = instr_desc(128, 64, 0, 0);    // K (K-major) x Q (K-major)
-            constexpr uint32_t ID_DV = instr_desc(128, 128, 0, 1);  // P^T (TMEM) x dO (MN-major)
-            constexpr uint32_t ID_DK = instr_desc(128, 128, 0, 1);  // dS^T (K-major) x Q (MN-major)
-            constexpr uint32_t ID_DQ = instr_desc(128, 64, 1, 1);   // K^T (MN-major) x dS^T (MN-major)
+            constexpr uint32_t ID_S = instr_desc(F16 ? 0 : 1, 128, 64, 0, 0);    // K (K-major) x Q (K-major)
+            constexpr uint32_t ID_DV = instr_desc(F16 ? 0 : 1, 128, 128, 0, 1);  // P^T (TMEM) x dO (MN-major)
+            constexpr uint32_t ID_DK = instr_desc(F16 ? 0 : 1, 128, 128, 0, 1);  // dS^T (K-major) x Q (MN-major)
+            constexpr uint32_t ID_DQ = instr_desc(F16 ? 0 : 1, 128, 64, 1, 1);   // K^T (MN-major) x dS^T (MN-major)
             mbar_wait(sh.bar(B_KV), 0, abort_flag, p.status);
             tc_fence_after();
             auto issue_sdp = [&](int i) {
@@ -309,7 +310,9 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         const int r = 32 * (warp & 3) + lane;   // key row = TMEM lane
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const float c2 = p.scale * kLog2e;
-        const float s_bias = static_cast<float>(s_exp);
+        // bf16 has fp32's range, so P~ and dS~ carry the grid's exponent; fp16 does not, and the
+        // exponent is applied to dQ's fp32 sums at the drain instead
+        const float s_bias = F16 ? 0.f : static_cast<float>(s_exp);
         const int kj = n0 + r;
         for (int i = bf; i < total; i += 2) {
             const int s = i % STAGES;
@@ -346,8 +349,8 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                         pv[e] = x;
                         ds[e] = x * (__uint_as_float(dv[j + e]) - sDl[q]);
                     }
-                    pp[j >> 1] = pack_bf16x2(pv[0], pv[1]);
-                    dd[j >> 1] = pack_bf16x2(ds[0], ds[1]);
+                    pp[j >> 1] = F16 ? pack_f16x2(pv[0], pv[1]) : pack_bf16x2(pv[0], pv[1]);
+                    dd[j >> 1] = F16 ? pack_f16x2(ds[0], ds[1]) : pack_bf16x2(ds[0], ds[1]);
                 }
                 tmem_st16(rs + 16 * c, pp);
                 // dS~^T row r: 16-byte chunk u (8 queries) at u ^ (r & 7)
@@ -365,6 +368,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
     } else if (warp >= 12) {
         // ================= dQ drain: TMEM -> int32 grid -> global atomics =================
         const int d = 32 * (warp & 3) + lane;   // channel = TMEM lane
+        const float dq_mul = F16 ? pow2f(s_exp) : 1.f;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         for (int i = 0; i < total; ++i) {
             const int bf = i & 1;
@@ -382,12 +386,12 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             int* acc = p.dq_acc + (static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM) * HD + d;
 #pragma unroll
             for (int q = 0; q < 32; ++q) {
-                const int a = __float2int_rn(__uint_as_float(v0[q]));
+                const int a = __float2int_rn(F16 ? __uint_as_float(v0[q]) * dq_mul : __uint_as_float(v0[q]));
                 if (a != 0) atomicAdd(acc + q * HD, a);
             }
 #pragma unroll
             for (int q = 0; q < 32; ++q) {
-                const int a = __float2int_rn(__uint_as_float(v1[q]));
+                const int a = __float2int_rn(F16 ? __uint_as_float(v1[q]) * dq_mul : __uint_as_float(v1[q]));
                 if (a != 0) atomicAdd(acc + (32 + q) * HD, a);
             }
         }
@@ -406,7 +410,8 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         const int r = 32 * (warp & 3) + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const bool is_dv = warp >= 8;
-        const float un = pow2f(-s_exp);
+        auto pk2 = [](float a, float b2) { return F16 ? pack_f16x2(a, b2) : pack_bf16x2(a, b2); };
+        const float un = F16 ? 1.f : pow2f(-s_exp);
         const float f = is_dv ? un : p.scale * un;
         const uint32_t src = tmem + lane_addr + (is_dv ? T_DV : T_DK);
         const bool ok = n0 + r < sq.len;
@@ -420,10 +425,10 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint4 w;
-                    w.x = pack_bf16x2(__uint_as_float(v[j]) * f, __uint_as_float(v[j + 1]) * f);
-                    w.y = pack_bf16x2(__uint_as_float(v[j + 2]) * f, __uint_as_float(v[j + 3]) * f);
-                    w.z = pack_bf16x2(__uint_as_float(v[j + 4]) * f, __uint_as_float(v[j + 5]) * f);
-                    w.w = pack_bf16x2(__uint_as_float(v[j + 6]) * f, __uint_as_float(v[j + 7]) * f);
+                    w.x = pk2(__uint_as_float(v[j]) * f, __uint_as_float(v[j + 1]) * f);
+                    w.y = pk2(__uint_as_float(v[j + 2]) * f, __uint_as_float(v[j + 3]) * f);
+                    w.z = pk2(__uint_as_float(v[j + 4]) * f, __uint_as_float(v[j + 5]) * f);
+                    w.w = pk2(__uint_as_float(v[j + 6]) * f, __uint_as_float(v[j + 7]) * f);
                     *reinterpret_cast<uint4*>(dst + 32 * c + j) = w;
                 }
             } else if (ok) {
@@ -462,7 +467,7 @@ EncodeFn encode_fn() {
 }
 
 // (channel, row, head, batch) view of a (batch, row, head, channel)-strided bf16 tensor
-bool make_map(CUtensorMap* m, const TensorView& t, int64_t rows, int heads, int batch, int box_rows) {
+bool make_map(CUtensorMap* m, const TensorView& t, int64_t rows, int heads, int batch, int box_rows, bool f16) {
     EncodeFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[4] = {static_cast<cuuint64_t>(sm100::HD), static_cast<cuuint64_t>(rows),
@@ -472,7 +477,7 @@ bool make_map(CUtensorMap* m, const TensorView& t, int64_t rows, int heads, int 
                              static_cast<cuuint64_t>(sb * 2)};
     cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, estr,
+    return fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -480,7 +485,7 @@ bool make_map(CUtensorMap* m, const TensorView& t, int64_t rows, int heads, int 
 }  // namespace
 
 bool bwd_sm100_supported(const BwdParams& p) {
-    return p.D == 128 && !p.f16 && encode_fn() != nullptr;
+    return p.D == 128 && encode_fn() != nullptr;
 }
 
 int launch_bwd_main_sm100(const BwdParams& p, cudaStream_t st) {
@@ -488,15 +493,22 @@ int launch_bwd_main_sm100(const BwdParams& p, cudaStream_t st) {
     const bool varlen = p.cu != nullptr;
     const int64_t rows = varlen ? p.total : p.S;
     const int batch = varlen ? 1 : p.B;
-    if (!make_map(&maps.q, p.q, rows, p.H, batch, sm100::BM) || !make_map(&maps.dout, p.dout, rows, p.H, batch, sm100::BM) ||
-        !make_map(&maps.k, p.k, rows, p.HKV, batch, sm100::BN) || !make_map(&maps.v, p.v, rows, p.HKV, batch, sm100::BN)) {
+    const bool f16 = p.f16;
+    if (!make_map(&maps.q, p.q, rows, p.H, batch, sm100::BM, f16) || !make_map(&maps.dout, p.dout, rows, p.H, batch, sm100::BM, f16) ||
+        !make_map(&maps.k, p.k, rows, p.HKV, batch, sm100::BN, f16) || !make_map(&maps.v, p.v, rows, p.HKV, batch, sm100::BN, f16)) {
         set_error("bwd_main_sm100: cuTensorMapEncodeTiled failed");
         return FOLD_ERR_LAUNCH;
     }
-    auto kern = sm100::bwd_main_sm100_kernel;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm100::SMEM_BYTES);
     dim3 grid((p.S + sm100::BN - 1) / sm100::BN, p.HKV, p.B);
-    kern<<<grid, sm100::NTHREADS, sm100::SMEM_BYTES, st>>>(p, maps);
+    if (f16) {
+        auto kern = sm100::bwd_main_sm100_kernel<true>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm100::SMEM_BYTES);
+        kern<<<grid, sm100::NTHREADS, sm100::SMEM_BYTES, st>>>(p, maps);
+    } else {
+        auto kern = sm100::bwd_main_sm100_kernel<false>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm100::SMEM_BYTES);
+        kern<<<grid, sm100::NTHREADS, sm100::SMEM_BYTES, st>>>(p, maps);
+    }
     return check_launch("bwd_main_sm100");
 }
 

@@ -19,9 +19,9 @@ KERNELS = ["mma", "sm100"]
 
 
 def _need(kernel, D, dtype=torch.bfloat16):
-    """The tcgen05 kernel serves head_dim 128 in bf16; everything runs on mma.sync."""
-    if kernel == "sm100" and (D != 128 or dtype != torch.bfloat16):
-        pytest.skip("the tcgen05 kernel takes head_dim 128, bf16")
+    """The tcgen05 kernel serves head_dim 128 (bf16 and fp16); everything runs on mma.sync."""
+    if kernel == "sm100" and D != 128:
+        pytest.skip("the tcgen05 kernel takes head_dim 128")
 
 
 def _api():
@@ -75,6 +75,28 @@ def test_forward_and_gradient_accuracy(H, HKV, D, dtype, kernel):
     ref = ob.reference_grads(q, k, v, do)
     for name, a, r in zip("qkv", ours, ref):
         assert ob.rel_l2(a, r) <= TOL, (name, ob.rel_l2(a, r))
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_fp16_packed_sequences_repeat_their_bits(kernel, causal):
+    """fp16 keeps the grid's exponent out of P and dS (fp16 has no room for it) and applies it to
+    dQ's fp32 sums; the gradients still match FP64 autograd and two runs are the same bits."""
+    lens = [300, 129, 1, 640, 77]
+    H, HKV, D = 8, 2, 128
+    q, k, v, do, cu = _packed(lens, H, HKV, D, seed=11, dtype=torch.float16)
+    S = max(lens)
+    o, lse = _fwd(q, k, v, cu, S, causal=causal)
+    a = _bwd(q, k, v, o, do, lse, cu, S, causal=causal, kernel=kernel)
+    b = _bwd(q, k, v, o, do, lse, cu, S, causal=causal, kernel=kernel)
+    assert _same(a, b)
+    assert all(x.dtype == torch.float16 for x in a)
+    for i in range(len(lens)):
+        s0, s1 = int(cu[i]), int(cu[i + 1])
+        ref = ob.reference_grads(q[s0:s1], k[s0:s1], v[s0:s1], do[s0:s1], causal=causal)
+        for name, x, r in zip("qkv", a, ref):
+            if r.double().norm().item() > 0:
+                assert ob.rel_l2(x[s0:s1], r) <= TOL, (i, name, ob.rel_l2(x[s0:s1], r))
 
 
 @pytest.mark.parametrize("kernel", KERNELS)
