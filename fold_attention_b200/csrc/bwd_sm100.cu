@@ -3,22 +3,30 @@
 // pipelines between specialised warps. Head dim 128, bf16 or fp16, dense or packed.
 //
 // One CTA owns one block of 128 keys of one (request, KV head) and walks query
-// blocks of 64 rows, for each of the group's G query heads in turn. Per query
-// block i (buffers b = i & 1 are double-buffered in TMEM):
-//     S^T  = K Q^T            SS  M=128 keys,  N=64 queries, K=128      -> R_S[b]
-//     dP^T = V dO^T           SS                                          -> R_D[b]
-//     P~^T = exp2(S^T c - (L - s)), dS~^T = P~^T (dP^T - Delta)   (compute warps:
-//            P~^T back to TMEM as 16-bit over S^T, dS~^T to shared, swizzled)
-//     dV  += P~^T dO          TS  A from TMEM, M=128 keys, N=128, K=64
+// tiles of 128 rows, for each of the group's G query heads in turn. Every MMA is
+// M=128, N=128, K=16 (the shape the tensor pipe runs at its full rate whatever
+// else the SM does; N=64 runs at half of it). Per query tile i:
+//     S^T  = K Q^T            SS  keys x queries                          -> T_S
+//     dP^T = V dO^T           SS                                          -> T_DP
+//     P~^T = exp2(S^T c - (L - s))      compute warps; 16-bit, over S^T in TMEM
+//     dS~^T = P~^T (dP^T - Delta)       compute warps; to shared, swizzled
+//     dV  += P~^T dO          TS  A from TMEM
+//     dQ~^T = K^T dS~^T       SS  A = K^T (MN-major), B = dS~^T (MN-major) -> T_DP
 //     dK  += dS~^T Q          SS  A = dS~^T (K-major), B = Q (MN-major)
-//     dQ~^T = K^T dS~^T       SS  A = K^T (MN-major), B = dS~^T (MN-major) -> R_D[b]
+// TMEM holds exactly S^T, dP^T/dQ~^T, dK and dV (4 x 128 columns), so nothing is
+// double-buffered; the one MMA thread keeps the pipe fed by interleaving two
+// tiles: dP(i) | dV(i) S(i+1) | dQ(i) dK(i) dP(i+1) | ..., so that the exponentials
+// of tile i+1 run under dQ(i), dK(i), dP(i+1) and its dS~ under dV(i+1). A thread's
+// MMAs execute in issue order, which is what lets S(i+1) overwrite P~(i) right
+// behind dV(i).
 // dK and dV stay in TMEM for the CTA's whole life, summed in one fixed order;
 // dQ~ leaves the GEMM on the request's integer grid (the softmax carries the
-// grid exponent s), is rounded to nearest-even int32 and added to the
-// accumulator with integer atomics, which commute exactly.
+// grid exponent s; for fp16 it is applied at the drain), is rounded to
+// nearest-even int32 and added to the accumulator with integer atomics, which
+// commute exactly.
 //
-// Warps: 0 TMA producer, 1 MMA issuer (owns the TMEM allocation), 4-7 and
-// 8-11 the two compute groups (one per TMEM buffer), 12-15 the dQ drain.
+// Warps: 0 TMA producer, 1 MMA issuer (owns the TMEM allocation), 2-5 and 6-9
+// the two compute groups (64 queries of the tile each), 10-13 the dQ drain.
 // Every mbarrier wait is bounded: on expiry the kernel raises a status word,
 // stops waiting everywhere, frees its TMEM and returns.
 // Reference arithmetic: src/fold_attention/backward/kernel.py:1191-1330.
@@ -31,38 +39,43 @@ namespace fold {
 namespace sm100 {
 
 constexpr int BN = 128;   // keys per CTA
-constexpr int BM = 64;    // queries per step
+constexpr int BM = 128;   // queries per tile
 constexpr int HD = 128;   // head dim
-constexpr int STAGES = 3;
-constexpr int NTHREADS = 512;
+constexpr int STAGES = 2;
+constexpr int NTHREADS = 448;
 constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 
 // shared memory map (bytes from a 1024-aligned base)
-constexpr int SM_K = 0;                         // [2 boxes][128 keys][64 ch] bf16, SW128
+constexpr int SM_K = 0;                         // [2 boxes][128 keys][64 ch] 16-bit, SW128
 constexpr int SM_V = 32768;
-constexpr int SM_STAGE = 65536;                 // per stage: Q 16 KB, dO 16 KB, L 256, Delta 256
-constexpr int STAGE_BYTES = 33792;
-constexpr int ST_Q = 0, ST_DO = 16384, ST_L = 32768, ST_DL = 33024;
-constexpr int SM_DS = SM_STAGE + STAGES * STAGE_BYTES;   // [2][128 keys][64 queries] bf16, SW128
-constexpr int SM_BAR = SM_DS + 2 * 16384;
+constexpr int SM_STAGE = 65536;                 // per stage: Q 32 KB, dO 32 KB, L 512, Delta 512
+constexpr int STAGE_BYTES = 66560;
+constexpr int ST_Q = 0, ST_DO = 32768, ST_L = 65536, ST_DL = 66048;
+constexpr int SM_DS = SM_STAGE + STAGES * STAGE_BYTES;   // [2 boxes][128 keys][64 queries] 16-bit, SW128
+constexpr int SM_BAR = SM_DS + 32768;
 constexpr int SM_TOTAL = SM_BAR + 256;
-constexpr int SMEM_BYTES = SM_TOTAL + 1024;     // slack to align the base
+constexpr int SMEM_BYTES = 232448;              // all an SM gives one CTA; the base may use what is left to align
+constexpr int ALIGN_SLACK = SMEM_BYTES - SM_TOTAL;
 
 // barrier indices
 enum {
     B_KV = 0,
-    B_QFULL = 1,                 // [STAGES]
-    B_QEMPTY = B_QFULL + STAGES, // [STAGES]
-    B_SDP = B_QEMPTY + STAGES,   // [2]  S^T, dP^T in TMEM
-    B_PDS = B_SDP + 2,           // [2]  P~^T in TMEM, dS~^T in shared
-    B_DQF = B_PDS + 2,           // [2]  dQ~^T in TMEM (and the step's MMAs retired)
-    B_DQE = B_DQF + 2,           // [2]  dQ~^T drained
-    B_GRP = B_DQE + 2,           // [2]  the step's dQ, dV, dK MMAs have all retired
-    B_COUNT = B_GRP + 2,
+    B_QFULL = 1,                 // [STAGES] Q and L of the stage have landed
+    B_QEMPTY = B_QFULL + STAGES, // [STAGES] dK has read Q
+    B_OFULL = B_QEMPTY + STAGES, // [STAGES] dO and Delta have landed
+    B_OEMPTY = B_OFULL + STAGES, // [STAGES] dV has read dO
+    B_S = B_OEMPTY + STAGES,     // S^T in TMEM
+    B_DP,                        // dP^T in TMEM (and dS~^T's shared buffer free: dQ, dK of the tile before retired)
+    B_P,                         // P~^T in TMEM (256 arrivals)
+    B_DS,                        // dS~^T in shared (256 arrivals)
+    B_DQF,                       // dQ~^T in TMEM
+    B_DQE,                       // dQ~^T read out (128 arrivals)
+    B_DONE,                      // every MMA retired
+    B_COUNT,
 };
 
 // TMEM columns
-constexpr uint32_t T_RS0 = 0, T_RS1 = 64, T_RD0 = 128, T_RD1 = 192, T_DK = 256, T_DV = 384;
+constexpr uint32_t T_S = 0, T_DP = 128, T_DK = 256, T_DV = 384;
 
 struct Shared {
     uint32_t base;
@@ -87,11 +100,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait. `abort` (shared) is raised by whoever runs out first; once it
 // is up nobody waits any more, so every role runs to its end.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try(bar, parity)) return;
     if (*abort_flag) return;
     const long long t0 = clock64();
     for (int i = 0;; ++i) {
         if (mbar_try(bar, parity)) return;
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);   // a waiting warp group must not take the issue slots of a working one
         if ((i & 63) == 63) {
             if (*abort_flag) return;
             if (clock64() - t0 > WAIT_CYCLES) break;
@@ -145,6 +161,19 @@ __device__ __forceinline__ float ex2f(float x) {
     return y;
 }
 
+// Round-to-nearest-even float -> int32 for |x| < 2^31 on the FMA pipe (cvt.rni shares the
+// transcendental pipe with the softmax's ex2 and was the drain's bottleneck). Adding 1.5 * 2^23
+// rounds a float of magnitude below 2^22 to an integer in its low mantissa bits; x is split as
+// hi * 2^16 + lo with both parts in that range, and lo = x - hi * 2^16 is exact.
+__device__ __forceinline__ int rint_to_int(float x) {
+    constexpr float M = 12582912.f;   // 1.5 * 2^23, bits 0x4B400000
+    const float t1 = fmaf(x, 1.52587890625e-05f, M);   // x * 2^-16, rounded to an integer
+    const float hi = t1 - M;
+    const float t2 = fmaf(hi, -65536.f, x) + M;
+    // ((i1 - K) << 16) + (i2 - K), and K << 16 is 0 mod 2^32
+    return static_cast<int>((__float_as_uint(t1) << 16) + __float_as_uint(t2) - 0x4B400000u);
+}
+
 // ---- descriptors ----------------------------------------------------------------
 // shared-memory matrix descriptor, 128-byte swizzle; offsets in bytes
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -164,7 +193,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int fmt, int M, int N, int a_m
 }
 
 struct Maps {
-    CUtensorMap q, dout, k, v;   // (channel, row, head, batch), boxes (64, 64|128, 1, 1)
+    CUtensorMap q, dout, k, v;   // (channel, row, head, batch), boxes (64, 128, 1, 1)
 };
 
 template <bool F16>
@@ -173,20 +202,22 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
     const uint32_t base = (raw + 1023u) & ~1023u;
+    if (base - raw > static_cast<uint32_t>(ALIGN_SLACK)) {   // the map below would not fit: refuse, loudly
+        if (threadIdx.x == 0) atomicExch(p.status, FOLD_ERR_LAUNCH);
+        return;
+    }
     uint8_t* smem = smem_raw + (base - raw);
     Shared sh{base};
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_BAR + 8 * B_COUNT);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 8 * B_COUNT + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nblocks = (p.S + BN - 1) / BN;
     const int nb = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
-    (void)nblocks;
     const SeqInfo sq = seq_info(p, b);
     const int n0 = nb * BN;
     if (n0 >= sq.len) return;
 
-    // query steps: all heads of the group, each from the first block that can see this key block
+    // query tiles: all heads of the group, each from the first tile that can see this key block
     const int nm = (sq.len + BM - 1) / BM;
     const int m_min = p.causal ? (n0 / BM) : 0;
     const int per_head = nm - m_min;
@@ -198,14 +229,16 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(sh.bar(B_QFULL + s), 1);
             mbar_init(sh.bar(B_QEMPTY + s), 1);
+            mbar_init(sh.bar(B_OFULL + s), 1);
+            mbar_init(sh.bar(B_OEMPTY + s), 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(sh.bar(B_SDP + i), 1);
-            mbar_init(sh.bar(B_PDS + i), 128);
-            mbar_init(sh.bar(B_DQF + i), 1);
-            mbar_init(sh.bar(B_DQE + i), 128);
-            mbar_init(sh.bar(B_GRP + i), 1);
-        }
+        mbar_init(sh.bar(B_S), 1);
+        mbar_init(sh.bar(B_DP), 1);
+        mbar_init(sh.bar(B_P), 256);
+        mbar_init(sh.bar(B_DS), 256);
+        mbar_init(sh.bar(B_DQF), 1);
+        mbar_init(sh.bar(B_DQE), 128);
+        mbar_init(sh.bar(B_DONE), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -234,79 +267,96 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 const int s = i % STAGES;
                 const int g = i / per_head, mb = m_min + i % per_head;
                 const int h = hkv * p.G + g;
-                if (i >= STAGES) mbar_wait(sh.bar(B_QEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
                 const uint32_t st = base + SM_STAGE + s * STAGE_BYTES;
-                mbar_expect_tx(sh.bar(B_QFULL + s), 2 * 16384 + 512);
                 const int row = sq.start + mb * BM;
-                for (int x = 0; x < 2; ++x) {
-                    tma_load_4d(st + ST_Q + x * 8192, &maps.q, 64 * x, row, h, bb, sh.bar(B_QFULL + s));
-                    tma_load_4d(st + ST_DO + x * 8192, &maps.dout, 64 * x, row, h, bb, sh.bar(B_QFULL + s));
-                }
                 const int64_t wrow = static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM;
-                bulk_load(st + ST_L, p.lse2 + wrow, 256, sh.bar(B_QFULL + s));
-                bulk_load(st + ST_DL, p.dpsum + wrow, 256, sh.bar(B_QFULL + s));
+                // Q and L first: S^T wants them a whole GEMM before dP^T wants dO
+                if (i >= STAGES) mbar_wait<100>(sh.bar(B_QEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
+                mbar_expect_tx(sh.bar(B_QFULL + s), 32768 + 512);
+                for (int x = 0; x < 2; ++x) tma_load_4d(st + ST_Q + x * 16384, &maps.q, 64 * x, row, h, bb, sh.bar(B_QFULL + s));
+                bulk_load(st + ST_L, p.lse2 + wrow, 512, sh.bar(B_QFULL + s));
+                if (i >= STAGES) mbar_wait<100>(sh.bar(B_OEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
+                mbar_expect_tx(sh.bar(B_OFULL + s), 32768 + 512);
+                for (int x = 0; x < 2; ++x) tma_load_4d(st + ST_DO + x * 16384, &maps.dout, 64 * x, row, h, bb, sh.bar(B_OFULL + s));
+                bulk_load(st + ST_DL, p.dpsum + wrow, 512, sh.bar(B_OFULL + s));
             }
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            constexpr uint32_t ID_S = instr_desc(F16 ? 0 : 1, 128, 64, 0, 0);    // K (K-major) x Q (K-major)
-            constexpr uint32_t ID_DV = instr_desc(F16 ? 0 : 1, 128, 128, 0, 1);  // P^T (TMEM) x dO (MN-major)
-            constexpr uint32_t ID_DK = instr_desc(F16 ? 0 : 1, 128, 128, 0, 1);  // dS^T (K-major) x Q (MN-major)
-            constexpr uint32_t ID_DQ = instr_desc(F16 ? 0 : 1, 128, 64, 1, 1);   // K^T (MN-major) x dS^T (MN-major)
+            constexpr uint32_t ID_KK = instr_desc(F16 ? 0 : 1, 128, 128, 0, 0);   // S^T, dP^T: both K-major
+            constexpr uint32_t ID_KM = instr_desc(F16 ? 0 : 1, 128, 128, 0, 1);   // dV, dK: B MN-major
+            constexpr uint32_t ID_MM = instr_desc(F16 ? 0 : 1, 128, 128, 1, 1);   // dQ~^T: both MN-major
+            // K-major operand, 16 channels per step: 4 steps per 64-channel box of 16 KB;
+            // MN-major operand, 16 rows per step: 2 KB on, the second 64 columns one box (16 KB) further
+            uint64_t dk_kk[8], dv_kk[8], dk_mn[8];
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t kk = (ks >> 2) * 16384 + (ks & 3) * 32;
+                dk_kk[ks] = smem_desc(base + SM_K + kk, 16, 1024);
+                dv_kk[ks] = smem_desc(base + SM_V + kk, 16, 1024);
+                dk_mn[ks] = smem_desc(base + SM_K + ks * 2048, 16384, 1024);
+            }
+            const uint64_t ds_kk0 = smem_desc(base + SM_DS, 16, 1024), ds_mn0 = smem_desc(base + SM_DS, 16384, 1024);
             mbar_wait(sh.bar(B_KV), 0, abort_flag, p.status);
             tc_fence_after();
-            auto issue_sdp = [&](int i) {
-                const int s = i % STAGES, bf = i & 1;
+            auto issue_s = [&](int i) {
+                const int s = i % STAGES;
                 mbar_wait(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);
-                if (i >= 2) mbar_wait(sh.bar(B_DQE + bf), ((i >> 1) - 1) & 1, abort_flag, p.status);
                 tc_fence_after();
-                const uint32_t st = base + SM_STAGE + s * STAGE_BYTES;
-                const uint32_t rs = tmem + (bf ? T_RS1 : T_RS0), rd = tmem + (bf ? T_RD1 : T_RD0);
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {   // 16 channels per step; 4 steps per 64-channel box
-                    const uint32_t ko = (ks >> 2) * 16384 + (ks & 3) * 32;
-                    const uint32_t qo = (ks >> 2) * 8192 + (ks & 3) * 32;
-                    mma_ss(rs, smem_desc(base + SM_K + ko, 16, 1024), smem_desc(st + ST_Q + qo, 16, 1024), ID_S, ks > 0);
-                }
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t ko = (ks >> 2) * 16384 + (ks & 3) * 32;
-                    const uint32_t qo = (ks >> 2) * 8192 + (ks & 3) * 32;
-                    mma_ss(rd, smem_desc(base + SM_V + ko, 16, 1024), smem_desc(st + ST_DO + qo, 16, 1024), ID_S, ks > 0);
-                }
-                tc_commit(sh.bar(B_SDP + bf));
-            };
-            if (total > 0) issue_sdp(0);
-            for (int i = 0; i < total; ++i) {
-                const int s = i % STAGES, bf = i & 1;
-                if (i + 1 < total) issue_sdp(i + 1);
-                mbar_wait(sh.bar(B_PDS + bf), (i >> 1) & 1, abort_flag, p.status);
-                tc_fence_after();
-                const uint32_t st = base + SM_STAGE + s * STAGE_BYTES;
-                const uint32_t ds = base + SM_DS + bf * 16384;
-                const uint32_t rs = tmem + (bf ? T_RS1 : T_RS0), rd = tmem + (bf ? T_RD1 : T_RD0);
-                // dQ~^T = K^T dS~^T first: 8 steps of 16 keys. Its drain then runs under
-                // dV and dK, so the buffer is free again when the next S^T/dP^T need it.
+                const uint64_t q0 = smem_desc(base + SM_STAGE + s * STAGE_BYTES + ST_Q, 16, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
-                    mma_ss(rd, smem_desc(base + SM_K + ks * 2048, 16384, 1024), smem_desc(ds + ks * 2048, 16384, 1024), ID_DQ, ks > 0);
-                tc_commit(sh.bar(B_DQF + bf));
-                // dV += P~^T dO : 4 steps of 16 queries; A = 8 TMEM columns per step
+                    mma_ss(tmem + T_S, dk_kk[ks], q0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), ID_KK, ks > 0);
+                tc_commit(sh.bar(B_S));
+            };
+            auto issue_dp = [&](int i) {
+                const int s = i % STAGES;
+                mbar_wait(sh.bar(B_OFULL + s), (i / STAGES) & 1, abort_flag, p.status);
+                if (i >= 1) mbar_wait(sh.bar(B_DQE), (i - 1) & 1, abort_flag, p.status);   // dQ~(i-1) has left the columns
+                tc_fence_after();
+                const uint64_t o0 = smem_desc(base + SM_STAGE + s * STAGE_BYTES + ST_DO, 16, 1024);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    mma_ts(tmem + T_DV, rs + 8 * ks, smem_desc(st + ST_DO + ks * 2048, 8192, 1024), ID_DV, (i > 0) || (ks > 0));
-                // dK += dS~^T Q
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    mma_ss(tmem + T_DK, smem_desc(ds + ks * 32, 16, 1024), smem_desc(st + ST_Q + ks * 2048, 8192, 1024), ID_DK, (i > 0) || (ks > 0));
-                tc_commit(sh.bar(B_QEMPTY + s));   // the stage's Q, dO are free once these retire
-                tc_commit(sh.bar(B_GRP + bf));
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_ss(tmem + T_DP, dv_kk[ks], o0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), ID_KK, ks > 0);
+                tc_commit(sh.bar(B_DP));
+            };
+            if (total > 0) {
+                issue_s(0);
+                issue_dp(0);
             }
+            for (int i = 0; i < total; ++i) {
+                const int s = i % STAGES;
+                const uint32_t st = base + SM_STAGE + s * STAGE_BYTES;
+                const uint64_t q_mn0 = smem_desc(st + ST_Q, 16384, 1024), o_mn0 = smem_desc(st + ST_DO, 16384, 1024);
+                // dV += P~^T dO : 8 steps of 16 queries; A = 8 TMEM columns per step, the second
+                // compute group's 64 queries start at column 64
+                mbar_wait(sh.bar(B_P), i & 1, abort_flag, p.status);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_ts(tmem + T_DV, tmem + T_S + (ks >> 2) * 64 + (ks & 3) * 8, o_mn0 + ((ks * 2048) >> 4), ID_KM, (i > 0) || (ks > 0));
+                tc_commit(sh.bar(B_OEMPTY + s));
+                if (i + 1 < total) issue_s(i + 1);   // over P~(i), behind dV(i)
+                // dQ~^T = K^T dS~^T : 8 steps of 16 keys
+                mbar_wait(sh.bar(B_DS), i & 1, abort_flag, p.status);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_ss(tmem + T_DP, dk_mn[ks], ds_mn0 + ((ks * 2048) >> 4), ID_MM, ks > 0);
+                tc_commit(sh.bar(B_DQF));
+                // dK += dS~^T Q : 8 steps of 16 queries
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_ss(tmem + T_DK, ds_kk0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), q_mn0 + ((ks * 2048) >> 4), ID_KM, (i > 0) || (ks > 0));
+                tc_commit(sh.bar(B_QEMPTY + s));
+                if (i + 1 < total) issue_dp(i + 1);
+            }
+            tc_commit(sh.bar(B_DONE));
         }
-    } else if (warp >= 4 && warp < 12) {
-        // ================= compute: P~^T and dS~^T for buffer bf =================
-        const int bf = (warp >= 8) ? 1 : 0;
+    } else if (warp >= 2 && warp < 10) {
+        // ================= compute: P~^T and dS~^T for 64 of the tile's queries =================
+        const int wg = (warp >= 6) ? 1 : 0;
         const int r = 32 * (warp & 3) + lane;   // key row = TMEM lane
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const float c2 = p.scale * kLog2e;
@@ -314,45 +364,68 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         // exponent is applied to dQ's fp32 sums at the drain instead
         const float s_bias = F16 ? 0.f : static_cast<float>(s_exp);
         const int kj = n0 + r;
-        for (int i = bf; i < total; i += 2) {
+        const uint32_t rs = tmem + lane_addr + T_S + 64 * wg;
+        const uint32_t rd = tmem + lane_addr + T_DP + 64 * wg;
+        uint8_t* sds = smem + SM_DS + wg * 16384 + r * 128;
+        for (int i = 0; i < total; ++i) {
             const int s = i % STAGES;
             const int mb = m_min + i % per_head;
-            const int m0 = mb * BM;
-            mbar_wait(sh.bar(B_SDP + bf), (i >> 1) & 1, abort_flag, p.status);
-            // dS~^T buffer bf was read by step i-2's dK and dQ MMAs
-            if (i >= 2) mbar_wait(sh.bar(B_GRP + bf), ((i >> 1) - 1) & 1, abort_flag, p.status);
-            tc_fence_after();
-            const float* sL = reinterpret_cast<const float*>(smem + SM_STAGE + s * STAGE_BYTES + ST_L);
-            const float* sDl = reinterpret_cast<const float*>(smem + SM_STAGE + s * STAGE_BYTES + ST_DL);
-            uint8_t* sds = smem + SM_DS + bf * 16384 + r * 128;
-            const uint32_t rs = tmem + lane_addr + (bf ? T_RS1 : T_RS0);
-            const uint32_t rd = tmem + lane_addr + (bf ? T_RD1 : T_RD0);
+            const int m0 = mb * BM + 64 * wg;   // the group's first query
+            const float* sL = reinterpret_cast<const float*>(smem + SM_STAGE + s * STAGE_BYTES + ST_L) + 64 * wg;
+            const float* sDl = reinterpret_cast<const float*>(smem + SM_STAGE + s * STAGE_BYTES + ST_DL) + 64 * wg;
             const bool need_mask = (p.causal && m0 < n0 + BN) || (n0 + BN > sq.len);
+            float x[64];
+            // ---- P~^T = exp2(S^T c - L), kept in registers for dS~ and written over S^T ----
+            mbar_wait<64>(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);   // L (long since there)
+            mbar_wait<64>(sh.bar(B_S), i & 1, abort_flag, p.status);
+            tc_fence_after();
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                uint32_t sv[32], dv[32];
+                uint32_t sv[32];
                 tmem_ld32(rs + 32 * c, sv);
-                tmem_ld32(rd + 32 * c, dv);
                 tmem_wait_ld();
-                uint32_t pp[16], dd[16];
+                uint32_t pp[16];
+                float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f);   // one 16-byte broadcast read per four queries
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
-                    float pv[2], ds[2];
+                    if ((j & 3) == 0) l4 = *reinterpret_cast<const float4*>(sL + 32 * c + j);
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int q = 32 * c + j + e;
-                        float x = ex2f(fmaf(__uint_as_float(sv[j + e]), c2, s_bias - sL[q]));
+                        const float lq = (j & 3) == 0 ? (e ? l4.y : l4.x) : (e ? l4.w : l4.z);
+                        float v = ex2f(fmaf(__uint_as_float(sv[j + e]), c2, s_bias - lq));
                         if (need_mask) {
                             const int qi = m0 + q;
-                            if (kj >= sq.len || (p.causal && kj > qi)) x = 0.f;
+                            if (kj >= sq.len || (p.causal && kj > qi)) v = 0.f;
                         }
-                        pv[e] = x;
-                        ds[e] = x * (__uint_as_float(dv[j + e]) - sDl[q]);
+                        x[q] = v;
                     }
-                    pp[j >> 1] = F16 ? pack_f16x2(pv[0], pv[1]) : pack_bf16x2(pv[0], pv[1]);
-                    dd[j >> 1] = F16 ? pack_f16x2(ds[0], ds[1]) : pack_bf16x2(ds[0], ds[1]);
+                    pp[j >> 1] = F16 ? pack_f16x2(x[32 * c + j], x[32 * c + j + 1]) : pack_bf16x2(x[32 * c + j], x[32 * c + j + 1]);
                 }
                 tmem_st16(rs + 16 * c, pp);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(sh.bar(B_P));
+            // ---- dS~^T = P~^T (dP^T - Delta) to shared ----
+            mbar_wait<64>(sh.bar(B_OFULL + s), (i / STAGES) & 1, abort_flag, p.status);   // Delta
+            mbar_wait<64>(sh.bar(B_DP), i & 1, abort_flag, p.status);
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t dv[32];
+                tmem_ld32(rd + 32 * c, dv);
+                tmem_wait_ld();
+                uint32_t dd[16];
+                float4 d4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const int q = 32 * c + j;
+                    if ((j & 3) == 0) d4 = *reinterpret_cast<const float4*>(sDl + q);
+                    const float d0 = x[q] * (__uint_as_float(dv[j]) - ((j & 3) == 0 ? d4.x : d4.z));
+                    const float d1 = x[q + 1] * (__uint_as_float(dv[j + 1]) - ((j & 3) == 0 ? d4.y : d4.w));
+                    dd[j >> 1] = F16 ? pack_f16x2(d0, d1) : pack_bf16x2(d0, d1);
+                }
                 // dS~^T row r: 16-byte chunk u (8 queries) at u ^ (r & 7)
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -360,56 +433,70 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                     *reinterpret_cast<uint4*>(sds + cu * 16) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
                 }
             }
-            tmem_wait_st();
             tc_fence_before();
             fence_async_smem();
-            mbar_arrive(sh.bar(B_PDS + bf));
+            mbar_arrive(sh.bar(B_DS));
         }
-    } else if (warp >= 12) {
+    } else if (warp >= 10) {
         // ================= dQ drain: TMEM -> int32 grid -> global atomics =================
         const int d = 32 * (warp & 3) + lane;   // channel = TMEM lane
         const float dq_mul = F16 ? pow2f(s_exp) : 1.f;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+        const uint32_t rd = tmem + lane_addr + T_DP;
+        auto add32 = [&](int* acc, uint32_t (&v)[32]) {
+            // Float -> int32 on the FMA pipe (see rint_to_int). The drain shares its scheduler with
+            // two compute warps, so instructions are what it pays in: when every element of the
+            // warp's chunk is below 2^22 (the usual case: the grid leaves 2^30 to a row's whole
+            // sum) one add and one subtract per element do; else the two-step split. Zeros are added
+            // too: a branch per element costs more than the few masked tiles save.
+            constexpr float M = 12582912.f;   // 1.5 * 2^23, bits 0x4B400000
+            float mx = 0.f;
+#pragma unroll
+            for (int q = 0; q < 32; ++q) {
+                if (F16) v[q] = __float_as_uint(__uint_as_float(v[q]) * dq_mul);
+                mx = fmaxf(mx, fabsf(__uint_as_float(v[q])));
+            }
+            if (!__any_sync(0xffffffffu, !(mx < 4194304.f))) {
+#pragma unroll
+                for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(__uint_as_float(v[q]) + M) - 0x4B400000u;
+            } else {
+#pragma unroll
+                for (int q = 0; q < 32; ++q) v[q] = static_cast<uint32_t>(rint_to_int(__uint_as_float(v[q])));
+            }
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+                asm volatile("red.global.add.s32 [%0], %1;" ::"l"(acc + q * HD), "r"(v[q]) : "memory");
+        };
         for (int i = 0; i < total; ++i) {
-            const int bf = i & 1;
             const int g = i / per_head, mb = m_min + i % per_head;
             const int h = hkv * p.G + g;
-            mbar_wait(sh.bar(B_DQF + bf), (i >> 1) & 1, abort_flag, p.status);
+            int* acc = p.dq_acc + (static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM) * HD + d;
+            mbar_wait<64>(sh.bar(B_DQF), i & 1, abort_flag, p.status);
             tc_fence_after();
-            const uint32_t rd = tmem + lane_addr + (bf ? T_RD1 : T_RD0);
-            uint32_t v0[32], v1[32];
+            uint32_t v0[32], v1[32], v2[32];
             tmem_ld32(rd, v0);
             tmem_ld32(rd + 32, v1);
+            tmem_ld32(rd + 64, v2);
+            tmem_wait_ld();
+            add32(acc, v0);
+            tmem_ld32(rd + 96, v0);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(sh.bar(B_DQE + bf));
-            int* acc = p.dq_acc + (static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM) * HD + d;
-#pragma unroll
-            for (int q = 0; q < 32; ++q) {
-                const int a = __float2int_rn(F16 ? __uint_as_float(v0[q]) * dq_mul : __uint_as_float(v0[q]));
-                if (a != 0) atomicAdd(acc + q * HD, a);
-            }
-#pragma unroll
-            for (int q = 0; q < 32; ++q) {
-                const int a = __float2int_rn(F16 ? __uint_as_float(v1[q]) * dq_mul : __uint_as_float(v1[q]));
-                if (a != 0) atomicAdd(acc + (32 + q) * HD, a);
-            }
+            mbar_arrive(sh.bar(B_DQE));   // the rest of the tile is in registers: the columns are free for dP^T of the next tile
+            add32(acc + 32 * HD, v1);
+            add32(acc + 64 * HD, v2);
+            add32(acc + 96 * HD, v0);
         }
     }
 
     // ================= epilogue: dK, dV out of TMEM =================
     __syncthreads();
-    if (warp >= 4 && warp < 12) {
-        // every MMA has retired once the last step's group barrier completes
-        const int total_steps = total;
-        if (total_steps > 0) {
-            const int last = total_steps - 1;
-            mbar_wait(sh.bar(B_GRP + (last & 1)), (last >> 1) & 1, abort_flag, p.status);
-        }
+    if (warp >= 2 && warp < 10) {
+        if (total > 0) mbar_wait(sh.bar(B_DONE), 0, abort_flag, p.status);   // every MMA has retired
         tc_fence_after();
         const int r = 32 * (warp & 3) + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
-        const bool is_dv = warp >= 8;
+        const bool is_dv = warp >= 6;
         auto pk2 = [](float a, float b2) { return F16 ? pack_f16x2(a, b2) : pack_bf16x2(a, b2); };
         const float un = F16 ? 1.f : pow2f(-s_exp);
         const float f = is_dv ? un : p.scale * un;
@@ -421,7 +508,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             uint32_t v[32];
             tmem_ld32(src + 32 * c, v);
             tmem_wait_ld();
-            if (ok && total_steps > 0) {
+            if (ok && total > 0) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint4 w;
