@@ -44,6 +44,15 @@ constexpr int HD = 128;   // head dim
 constexpr int STAGES = 2;
 constexpr int NTHREADS = 448;
 constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
+// nanoseconds a waiting thread sleeps between polls of its barrier: a polling warp takes issue
+// slots from the working warps of its scheduler
+#ifndef FOLD_SLEEP_WORKER
+#define FOLD_SLEEP_WORKER 64
+#endif
+#ifndef FOLD_SLEEP_ISSUER
+#define FOLD_SLEEP_ISSUER 0
+#endif
+constexpr int SLEEP_WORKER = FOLD_SLEEP_WORKER, SLEEP_PRODUCER = 100, SLEEP_ISSUER = FOLD_SLEEP_ISSUER;
 
 // shared memory map (bytes from a 1024-aligned base)
 constexpr int SM_K = 0;                         // [2 boxes][128 keys][64 ch] 16-bit, SW128
@@ -155,23 +164,19 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 32 floats of shared memory as eight 16-byte reads issued back to back (volatile: they stay where
+// they are written, ahead of the wait they are meant to overlap; under the MMAs' operand traffic a
+// shared load takes a couple of hundred cycles)
+__device__ __forceinline__ void lds32(uint32_t addr, float (&v)[32]) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(v[4 * u]), "=f"(v[4 * u + 1]), "=f"(v[4 * u + 2]), "=f"(v[4 * u + 3]) : "r"(addr + 16 * u));
+}
 __device__ __forceinline__ float ex2f(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-
-// Round-to-nearest-even float -> int32 for |x| < 2^31 on the FMA pipe (cvt.rni shares the
-// transcendental pipe with the softmax's ex2 and was the drain's bottleneck). Adding 1.5 * 2^23
-// rounds a float of magnitude below 2^22 to an integer in its low mantissa bits; x is split as
-// hi * 2^16 + lo with both parts in that range, and lo = x - hi * 2^16 is exact.
-__device__ __forceinline__ int rint_to_int(float x) {
-    constexpr float M = 12582912.f;   // 1.5 * 2^23, bits 0x4B400000
-    const float t1 = fmaf(x, 1.52587890625e-05f, M);   // x * 2^-16, rounded to an integer
-    const float hi = t1 - M;
-    const float t2 = fmaf(hi, -65536.f, x) + M;
-    // ((i1 - K) << 16) + (i2 - K), and K << 16 is 0 mod 2^32
-    return static_cast<int>((__float_as_uint(t1) << 16) + __float_as_uint(t2) - 0x4B400000u);
 }
 
 // ---- descriptors ----------------------------------------------------------------
@@ -271,11 +276,11 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 const int row = sq.start + mb * BM;
                 const int64_t wrow = static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM;
                 // Q and L first: S^T wants them a whole GEMM before dP^T wants dO
-                if (i >= STAGES) mbar_wait<100>(sh.bar(B_QEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
+                if (i >= STAGES) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_QEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
                 mbar_expect_tx(sh.bar(B_QFULL + s), 32768 + 512);
                 for (int x = 0; x < 2; ++x) tma_load_4d(st + ST_Q + x * 16384, &maps.q, 64 * x, row, h, bb, sh.bar(B_QFULL + s));
                 bulk_load(st + ST_L, p.lse2 + wrow, 512, sh.bar(B_QFULL + s));
-                if (i >= STAGES) mbar_wait<100>(sh.bar(B_OEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
+                if (i >= STAGES) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_OEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
                 mbar_expect_tx(sh.bar(B_OFULL + s), 32768 + 512);
                 for (int x = 0; x < 2; ++x) tma_load_4d(st + ST_DO + x * 16384, &maps.dout, 64 * x, row, h, bb, sh.bar(B_OFULL + s));
                 bulk_load(st + ST_DL, p.dpsum + wrow, 512, sh.bar(B_OFULL + s));
@@ -298,11 +303,11 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 dk_mn[ks] = smem_desc(base + SM_K + ks * 2048, 16384, 1024);
             }
             const uint64_t ds_kk0 = smem_desc(base + SM_DS, 16, 1024), ds_mn0 = smem_desc(base + SM_DS, 16384, 1024);
-            mbar_wait(sh.bar(B_KV), 0, abort_flag, p.status);
+            mbar_wait<SLEEP_ISSUER>(sh.bar(B_KV), 0, abort_flag, p.status);
             tc_fence_after();
             auto issue_s = [&](int i) {
                 const int s = i % STAGES;
-                mbar_wait(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);
+                mbar_wait<SLEEP_ISSUER>(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);
                 tc_fence_after();
                 const uint64_t q0 = smem_desc(base + SM_STAGE + s * STAGE_BYTES + ST_Q, 16, 1024);
 #pragma unroll
@@ -312,8 +317,8 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             };
             auto issue_dp = [&](int i) {
                 const int s = i % STAGES;
-                mbar_wait(sh.bar(B_OFULL + s), (i / STAGES) & 1, abort_flag, p.status);
-                if (i >= 1) mbar_wait(sh.bar(B_DQE), (i - 1) & 1, abort_flag, p.status);   // dQ~(i-1) has left the columns
+                mbar_wait<SLEEP_ISSUER>(sh.bar(B_OFULL + s), (i / STAGES) & 1, abort_flag, p.status);
+                if (i >= 1) mbar_wait<SLEEP_ISSUER>(sh.bar(B_DQE), (i - 1) & 1, abort_flag, p.status);   // dQ~(i-1) has left the columns
                 tc_fence_after();
                 const uint64_t o0 = smem_desc(base + SM_STAGE + s * STAGE_BYTES + ST_DO, 16, 1024);
 #pragma unroll
@@ -331,7 +336,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 const uint64_t q_mn0 = smem_desc(st + ST_Q, 16384, 1024), o_mn0 = smem_desc(st + ST_DO, 16384, 1024);
                 // dV += P~^T dO : 8 steps of 16 queries; A = 8 TMEM columns per step, the second
                 // compute group's 64 queries start at column 64
-                mbar_wait(sh.bar(B_P), i & 1, abort_flag, p.status);
+                mbar_wait<SLEEP_ISSUER>(sh.bar(B_P), i & 1, abort_flag, p.status);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
@@ -339,7 +344,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 tc_commit(sh.bar(B_OEMPTY + s));
                 if (i + 1 < total) issue_s(i + 1);   // over P~(i), behind dV(i)
                 // dQ~^T = K^T dS~^T : 8 steps of 16 keys
-                mbar_wait(sh.bar(B_DS), i & 1, abort_flag, p.status);
+                mbar_wait<SLEEP_ISSUER>(sh.bar(B_DS), i & 1, abort_flag, p.status);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
@@ -371,59 +376,57 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             const int s = i % STAGES;
             const int mb = m_min + i % per_head;
             const int m0 = mb * BM + 64 * wg;   // the group's first query
-            const float* sL = reinterpret_cast<const float*>(smem + SM_STAGE + s * STAGE_BYTES + ST_L) + 64 * wg;
-            const float* sDl = reinterpret_cast<const float*>(smem + SM_STAGE + s * STAGE_BYTES + ST_DL) + 64 * wg;
+            const uint32_t sL_addr = base + SM_STAGE + s * STAGE_BYTES + ST_L + 256 * wg;
+            const uint32_t sDl_addr = base + SM_STAGE + s * STAGE_BYTES + ST_DL + 256 * wg;
             const bool need_mask = (p.causal && m0 < n0 + BN) || (n0 + BN > sq.len);
             float x[64];
             // ---- P~^T = exp2(S^T c - L), kept in registers for dS~ and written over S^T ----
-            mbar_wait<64>(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);   // L (long since there)
-            mbar_wait<64>(sh.bar(B_S), i & 1, abort_flag, p.status);
+            mbar_wait<SLEEP_WORKER>(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);   // L (long since there)
+            float lv[32];
+            lds32(sL_addr, lv);   // the first 32 queries' L, in flight under the wait for S^T
+            mbar_wait<SLEEP_WORKER>(sh.bar(B_S), i & 1, abort_flag, p.status);
             tc_fence_after();
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t sv[32];
+                if (c == 1) lds32(sL_addr + 128, lv);
                 tmem_ld32(rs + 32 * c, sv);
                 tmem_wait_ld();
                 uint32_t pp[16];
-                float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f);   // one 16-byte broadcast read per four queries
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    if ((j & 3) == 0) l4 = *reinterpret_cast<const float4*>(sL + 32 * c + j);
+                for (int j = 0; j < 32; ++j) x[32 * c + j] = ex2f(fmaf(__uint_as_float(sv[j]), c2, s_bias - lv[j]));
+                if (need_mask) {   // the diagonal tile and the sequence's last key block only: kept out of the common path
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int q = 32 * c + j + e;
-                        const float lq = (j & 3) == 0 ? (e ? l4.y : l4.x) : (e ? l4.w : l4.z);
-                        float v = ex2f(fmaf(__uint_as_float(sv[j + e]), c2, s_bias - lq));
-                        if (need_mask) {
-                            const int qi = m0 + q;
-                            if (kj >= sq.len || (p.causal && kj > qi)) v = 0.f;
-                        }
-                        x[q] = v;
+                    for (int j = 0; j < 32; ++j) {
+                        const int qi = m0 + 32 * c + j;
+                        if (kj >= sq.len || (p.causal && kj > qi)) x[32 * c + j] = 0.f;
                     }
-                    pp[j >> 1] = F16 ? pack_f16x2(x[32 * c + j], x[32 * c + j + 1]) : pack_bf16x2(x[32 * c + j], x[32 * c + j + 1]);
                 }
+#pragma unroll
+                for (int j = 0; j < 32; j += 2)
+                    pp[j >> 1] = F16 ? pack_f16x2(x[32 * c + j], x[32 * c + j + 1]) : pack_bf16x2(x[32 * c + j], x[32 * c + j + 1]);
                 tmem_st16(rs + 16 * c, pp);
             }
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(sh.bar(B_P));
             // ---- dS~^T = P~^T (dP^T - Delta) to shared ----
-            mbar_wait<64>(sh.bar(B_OFULL + s), (i / STAGES) & 1, abort_flag, p.status);   // Delta
-            mbar_wait<64>(sh.bar(B_DP), i & 1, abort_flag, p.status);
+            mbar_wait<SLEEP_WORKER>(sh.bar(B_OFULL + s), (i / STAGES) & 1, abort_flag, p.status);   // Delta
+            lds32(sDl_addr, lv);
+            mbar_wait<SLEEP_WORKER>(sh.bar(B_DP), i & 1, abort_flag, p.status);
             tc_fence_after();
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t dv[32];
+                if (c == 1) lds32(sDl_addr + 128, lv);
                 tmem_ld32(rd + 32 * c, dv);
                 tmem_wait_ld();
                 uint32_t dd[16];
-                float4 d4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
                     const int q = 32 * c + j;
-                    if ((j & 3) == 0) d4 = *reinterpret_cast<const float4*>(sDl + q);
-                    const float d0 = x[q] * (__uint_as_float(dv[j]) - ((j & 3) == 0 ? d4.x : d4.z));
-                    const float d1 = x[q + 1] * (__uint_as_float(dv[j + 1]) - ((j & 3) == 0 ? d4.y : d4.w));
+                    const float d0 = x[q] * (__uint_as_float(dv[j]) - lv[j]);
+                    const float d1 = x[q + 1] * (__uint_as_float(dv[j + 1]) - lv[j + 1]);
                     dd[j >> 1] = F16 ? pack_f16x2(d0, d1) : pack_bf16x2(d0, d1);
                 }
                 // dS~^T row r: 16-byte chunk u (8 queries) at u ^ (r & 7)
@@ -444,11 +447,11 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const uint32_t rd = tmem + lane_addr + T_DP;
         auto add32 = [&](int* acc, uint32_t (&v)[32]) {
-            // Float -> int32 on the FMA pipe (see rint_to_int). The drain shares its scheduler with
-            // two compute warps, so instructions are what it pays in: when every element of the
-            // warp's chunk is below 2^22 (the usual case: the grid leaves 2^30 to a row's whole
-            // sum) one add and one subtract per element do; else the two-step split. Zeros are added
-            // too: a branch per element costs more than the few masked tiles save.
+            // Float -> int32, round to nearest even. Adding 1.5 * 2^23 rounds a float below 2^22 to an
+            // integer in its low mantissa bits: one add and one subtract per element when every
+            // element of the warp's chunk is in that range (the usual case: the grid leaves 2^30 to
+            // a row's whole sum), which keeps the conversion off the pipe the softmax's ex2 runs on.
+            // Zeros are added too: a branch per element costs more than the few masked tiles save.
             constexpr float M = 12582912.f;   // 1.5 * 2^23, bits 0x4B400000
             float mx = 0.f;
 #pragma unroll
@@ -459,9 +462,9 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             if (!__any_sync(0xffffffffu, !(mx < 4194304.f))) {
 #pragma unroll
                 for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(__uint_as_float(v[q]) + M) - 0x4B400000u;
-            } else {
+            } else {   // rare, and kept small: the conversion instruction (same rounding; it shares a pipe with ex2)
 #pragma unroll
-                for (int q = 0; q < 32; ++q) v[q] = static_cast<uint32_t>(rint_to_int(__uint_as_float(v[q])));
+                for (int q = 0; q < 32; ++q) v[q] = static_cast<uint32_t>(__float2int_rn(__uint_as_float(v[q])));
             }
 #pragma unroll
             for (int q = 0; q < 32; ++q)
@@ -471,7 +474,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             const int g = i / per_head, mb = m_min + i % per_head;
             const int h = hkv * p.G + g;
             int* acc = p.dq_acc + (static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM) * HD + d;
-            mbar_wait<64>(sh.bar(B_DQF), i & 1, abort_flag, p.status);
+            mbar_wait<SLEEP_WORKER>(sh.bar(B_DQF), i & 1, abort_flag, p.status);
             tc_fence_after();
             uint32_t v0[32], v1[32], v2[32];
             tmem_ld32(rd, v0);
