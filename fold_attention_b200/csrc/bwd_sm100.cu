@@ -394,7 +394,9 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 tmem_wait_ld();
                 uint32_t pp[16];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) x[32 * c + j] = ex2f(fmaf(__uint_as_float(sv[j]), c2, s_bias - lv[j]));
+                for (int j = 0; j < 32; ++j) x[32 * c + j] = fmaf(__uint_as_float(sv[j]), c2, s_bias - lv[j]);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[32 * c + j] = ex2f(x[32 * c + j]);   // 32 independent ex2 in a row
                 if (need_mask) {   // the diagonal tile and the sequence's last key block only: kept out of the common path
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -423,12 +425,9 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 tmem_wait_ld();
                 uint32_t dd[16];
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int q = 32 * c + j;
-                    const float d0 = x[q] * (__uint_as_float(dv[j]) - lv[j]);
-                    const float d1 = x[q + 1] * (__uint_as_float(dv[j + 1]) - lv[j + 1]);
-                    dd[j >> 1] = F16 ? pack_f16x2(d0, d1) : pack_bf16x2(d0, d1);
-                }
+                for (int j = 0; j < 32; ++j) lv[j] = x[32 * c + j] * (__uint_as_float(dv[j]) - lv[j]);
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) dd[j >> 1] = F16 ? pack_f16x2(lv[j], lv[j + 1]) : pack_bf16x2(lv[j], lv[j + 1]);
                 // dS~^T row r: 16-byte chunk u (8 queries) at u ^ (r & 7)
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
