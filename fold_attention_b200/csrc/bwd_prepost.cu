@@ -15,13 +15,13 @@ constexpr int PRE_ROWS = 64;
 constexpr int PRE_THREADS = 256;
 
 template <bool F16>
-__device__ __forceinline__ void load4(const void* p, float (&x)[4]) {
-    uint2 w = __ldg(reinterpret_cast<const uint2*>(p));
+__device__ __forceinline__ void unpack4(uint2 w, float (&x)[4]) {
     x[0] = half_bits_to_float<F16>(static_cast<uint16_t>(w.x & 0xFFFF));
     x[1] = half_bits_to_float<F16>(static_cast<uint16_t>(w.x >> 16));
     x[2] = half_bits_to_float<F16>(static_cast<uint16_t>(w.y & 0xFFFF));
     x[3] = half_bits_to_float<F16>(static_cast<uint16_t>(w.y >> 16));
 }
+__device__ __forceinline__ uint2 ldg8(const void* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
 
 template <bool F16>
 __global__ void __launch_bounds__(PRE_THREADS) bwd_preprocess_kernel(const BwdParams p) {
@@ -36,41 +36,64 @@ __global__ void __launch_bounds__(PRE_THREADS) bwd_preprocess_kernel(const BwdPa
     const bool kv_owner = (h % p.G) == 0;
     float mx_k = 0.f, mx_v = 0.f, mx_dn = 0.f, mx_dl = 0.f;
     const int64_t wbase = static_cast<int64_t>(h) * p.rows_p + sq.pstart;
-    for (int r = warp; r < PRE_ROWS; r += PRE_THREADS / 32) {
-        const int i = mb * PRE_ROWS + r;
-        float delta = 0.f, lse2 = INFINITY;
-        if (i < sq.len) {
-            float o[4] = {0, 0, 0, 0}, g[4] = {0, 0, 0, 0};
-            if (active) {
-                load4<F16>(row_ptr<const uint16_t>(p.o, b, sq.start + i, h) + lane * 4, o);
-                load4<F16>(row_ptr<const uint16_t>(p.dout, b, sq.start + i, h) + lane * 4, g);
-            }
-            float d = o[0] * g[0] + o[1] * g[1] + o[2] * g[2] + o[3] * g[3];
-            float n2 = g[0] * g[0] + g[1] * g[1] + g[2] * g[2] + g[3] * g[3];
-            d = warp_sum(d);
-            n2 = warp_sum(n2);
-            delta = d;
-            mx_dn = fmaxf(mx_dn, sqrtf(n2));
-            mx_dl = fmaxf(mx_dl, fabsf(d));
-            if (kv_owner && active) {
-                float kk[4], vv[4];
-                load4<F16>(row_ptr<const uint16_t>(p.k, b, sq.start + i, hkv) + lane * 4, kk);
-                load4<F16>(row_ptr<const uint16_t>(p.v, b, sq.start + i, hkv) + lane * 4, vv);
+    // Four rows per pass: all of their loads are issued before the first row's reductions, so a
+    // warp keeps 8-16 requests in flight instead of 2-4 (the kernel is one pass over O, dO, K, V).
+    constexpr int NW = PRE_THREADS / 32, RB = 4;
+    for (int r0 = warp; r0 < PRE_ROWS; r0 += RB * NW) {
+        uint2 ow[RB], gw[RB], kw[RB], vw[RB];
+        float lraw[RB];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    mx_k = fmaxf(mx_k, fabsf(kk[j]));
-                    mx_v = fmaxf(mx_v, fabsf(vv[j]));
+        for (int u = 0; u < RB; ++u) {
+            const int i = mb * PRE_ROWS + r0 + u * NW;
+            ow[u] = gw[u] = kw[u] = vw[u] = make_uint2(0u, 0u);
+            lraw[u] = 0.f;
+            if (i < sq.len) {
+                if (active) {
+                    ow[u] = ldg8(row_ptr<const uint16_t>(p.o, b, sq.start + i, h) + lane * 4);
+                    gw[u] = ldg8(row_ptr<const uint16_t>(p.dout, b, sq.start + i, h) + lane * 4);
+                    if (kv_owner) {
+                        kw[u] = ldg8(row_ptr<const uint16_t>(p.k, b, sq.start + i, hkv) + lane * 4);
+                        vw[u] = ldg8(row_ptr<const uint16_t>(p.v, b, sq.start + i, hkv) + lane * 4);
+                    }
                 }
+                lraw[u] = p.lse[b * p.lse_sb + h * p.lse_sh + sq.start + i];
             }
-            const float l = p.lse[b * p.lse_sb + h * p.lse_sh + sq.start + i];
-            lse2 = (l == -INFINITY) ? 0.f : l * kLog2e;
         }
-        if (lane == 0) {
-            p.dpsum[wbase + i] = delta;
-            p.lse2[wbase + i] = lse2;
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+            const int i = mb * PRE_ROWS + r0 + u * NW;
+            float delta = 0.f, lse2 = INFINITY;
+            if (i < sq.len) {
+                float o[4], g[4];
+                unpack4<F16>(ow[u], o);
+                unpack4<F16>(gw[u], g);
+                float d = o[0] * g[0] + o[1] * g[1] + o[2] * g[2] + o[3] * g[3];
+                float n2 = g[0] * g[0] + g[1] * g[1] + g[2] * g[2] + g[3] * g[3];
+                d = warp_sum(d);
+                n2 = warp_sum(n2);
+                delta = d;
+                mx_dn = fmaxf(mx_dn, sqrtf(n2));
+                mx_dl = fmaxf(mx_dl, fabsf(d));
+                if (kv_owner && active) {
+                    float kk[4], vv[4];
+                    unpack4<F16>(kw[u], kk);
+                    unpack4<F16>(vw[u], vv);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        mx_k = fmaxf(mx_k, fabsf(kk[j]));
+                        mx_v = fmaxf(mx_v, fabsf(vv[j]));
+                    }
+                }
+                const float l = lraw[u];
+                lse2 = (l == -INFINITY) ? 0.f : l * kLog2e;
+            }
+            if (lane == 0) {
+                p.dpsum[wbase + i] = delta;
+                p.lse2[wbase + i] = lse2;
+            }
+            int4* acc = reinterpret_cast<int4*>(p.dq_acc + (wbase + i) * D);
+            for (int c = lane; c < D / 4; c += 32) acc[c] = make_int4(0, 0, 0, 0);
         }
-        int4* acc = reinterpret_cast<int4*>(p.dq_acc + (wbase + i) * D);
-        for (int c = lane; c < D / 4; c += 32) acc[c] = make_int4(0, 0, 0, 0);
     }
     __shared__ float s_red[4][PRE_THREADS / 32];
     mx_k = warp_max(mx_k);
