@@ -22,11 +22,12 @@
 // dK and dV stay in TMEM for the CTA's whole life, summed in one fixed order;
 // dQ~ leaves the GEMM on the request's integer grid (the softmax carries the
 // grid exponent s; for fp16 it is applied at the drain), is rounded to
-// nearest-even int32 and added to the accumulator with integer atomics, which
+// nearest-even int32 and added to the accumulator with integer reductions, which
 // commute exactly.
 //
 // Warps: 0 TMA producer, 1 MMA issuer (owns the TMEM allocation), 2-5 and 6-9
-// the two compute groups (64 queries of the tile each), 10-13 the dQ drain.
+// the two compute groups (64 queries of the tile each), 10-13 the dQ drain
+// (TMEM -> int32 -> shared -> cp.reduce.async.bulk add into the accumulator).
 // Every mbarrier wait is bounded: on expiry the kernel raises a status word,
 // stops waiting everywhere, frees its TMEM and returns.
 // Reference arithmetic: src/fold_attention/backward/kernel.py:1191-1330.
@@ -57,11 +58,13 @@ constexpr int SLEEP_WORKER = FOLD_SLEEP_WORKER, SLEEP_PRODUCER = 100, SLEEP_ISSU
 // shared memory map (bytes from a 1024-aligned base)
 constexpr int SM_K = 0;                         // [2 boxes][128 keys][64 ch] 16-bit, SW128
 constexpr int SM_V = 32768;
-constexpr int SM_STAGE = 65536;                 // per stage: Q 32 KB, dO 32 KB, L 512, Delta 512
-constexpr int STAGE_BYTES = 66560;
-constexpr int ST_Q = 0, ST_DO = 32768, ST_L = 65536, ST_DL = 66048;
-constexpr int SM_DS = SM_STAGE + STAGES * STAGE_BYTES;   // [2 boxes][128 keys][64 queries] 16-bit, SW128
-constexpr int SM_BAR = SM_DS + 32768;
+constexpr int SM_Q = 65536;                     // [2 stages][2 boxes][128 queries][64 ch]
+constexpr int SM_DO = SM_Q + 2 * 32768;         // one buffer: dO(i+1) lands between dV(i) and dP(i+1)
+constexpr int SM_DS = SM_DO + 32768;            // [2 boxes][128 keys][64 queries] 16-bit, SW128
+constexpr int SM_STG = SM_DS + 32768;           // [2][32 queries][128 ch] int32: dQ~ on its way to the accumulator
+constexpr int SM_L = SM_STG + 2 * 16384;        // L [2 stages][128] f32, then Delta [2][128] f32
+constexpr int SM_DL = SM_L + 2 * 512;
+constexpr int SM_BAR = SM_DL + 2 * 512;
 constexpr int SM_TOTAL = SM_BAR + 256;
 constexpr int SMEM_BYTES = 232448;              // all an SM gives one CTA; the base may use what is left to align
 constexpr int ALIGN_SLACK = SMEM_BYTES - SM_TOTAL;
@@ -71,9 +74,9 @@ enum {
     B_KV = 0,
     B_QFULL = 1,                 // [STAGES] Q and L of the stage have landed
     B_QEMPTY = B_QFULL + STAGES, // [STAGES] dK has read Q
-    B_OFULL = B_QEMPTY + STAGES, // [STAGES] dO and Delta have landed
-    B_OEMPTY = B_OFULL + STAGES, // [STAGES] dV has read dO
-    B_S = B_OEMPTY + STAGES,     // S^T in TMEM
+    B_OFULL = B_QEMPTY + STAGES, // dO and Delta have landed
+    B_OEMPTY,                    // dV has read dO
+    B_S,                         // S^T in TMEM
     B_DP,                        // dP^T in TMEM (and dS~^T's shared buffer free: dQ, dK of the tile before retired)
     B_P,                         // P~^T in TMEM (256 arrivals)
     B_DS,                        // dS~^T in shared (256 arrivals)
@@ -234,9 +237,9 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(sh.bar(B_QFULL + s), 1);
             mbar_init(sh.bar(B_QEMPTY + s), 1);
-            mbar_init(sh.bar(B_OFULL + s), 1);
-            mbar_init(sh.bar(B_OEMPTY + s), 1);
         }
+        mbar_init(sh.bar(B_OFULL), 1);
+        mbar_init(sh.bar(B_OEMPTY), 1);
         mbar_init(sh.bar(B_S), 1);
         mbar_init(sh.bar(B_DP), 1);
         mbar_init(sh.bar(B_P), 256);
@@ -272,18 +275,20 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 const int s = i % STAGES;
                 const int g = i / per_head, mb = m_min + i % per_head;
                 const int h = hkv * p.G + g;
-                const uint32_t st = base + SM_STAGE + s * STAGE_BYTES;
                 const int row = sq.start + mb * BM;
                 const int64_t wrow = static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM;
-                // Q and L first: S^T wants them a whole GEMM before dP^T wants dO
+                // Q and L: two stages, free when dK of the tile two back has read Q
                 if (i >= STAGES) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_QEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
                 mbar_expect_tx(sh.bar(B_QFULL + s), 32768 + 512);
-                for (int x = 0; x < 2; ++x) tma_load_4d(st + ST_Q + x * 16384, &maps.q, 64 * x, row, h, bb, sh.bar(B_QFULL + s));
-                bulk_load(st + ST_L, p.lse2 + wrow, 512, sh.bar(B_QFULL + s));
-                if (i >= STAGES) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_OEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
-                mbar_expect_tx(sh.bar(B_OFULL + s), 32768 + 512);
-                for (int x = 0; x < 2; ++x) tma_load_4d(st + ST_DO + x * 16384, &maps.dout, 64 * x, row, h, bb, sh.bar(B_OFULL + s));
-                bulk_load(st + ST_DL, p.dpsum + wrow, 512, sh.bar(B_OFULL + s));
+                for (int x = 0; x < 2; ++x) tma_load_4d(base + SM_Q + s * 32768 + x * 16384, &maps.q, 64 * x, row, h, bb, sh.bar(B_QFULL + s));
+                bulk_load(base + SM_L + s * 512, p.lse2 + wrow, 512, sh.bar(B_QFULL + s));
+                // dO: one buffer, free when dV of the tile before has read it (three GEMMs ahead of
+                // the dP^T that wants the new one); Delta rides with it but alternates between two
+                // slots, because the compute warps may still be reading the last one
+                if (i >= 1) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_OEMPTY), (i - 1) & 1, abort_flag, p.status);
+                mbar_expect_tx(sh.bar(B_OFULL), 32768 + 512);
+                for (int x = 0; x < 2; ++x) tma_load_4d(base + SM_DO + x * 16384, &maps.dout, 64 * x, row, h, bb, sh.bar(B_OFULL));
+                bulk_load(base + SM_DL + s * 512, p.dpsum + wrow, 512, sh.bar(B_OFULL));
             }
         }
     } else if (warp == 1) {
@@ -309,18 +314,17 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 const int s = i % STAGES;
                 mbar_wait<SLEEP_ISSUER>(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);
                 tc_fence_after();
-                const uint64_t q0 = smem_desc(base + SM_STAGE + s * STAGE_BYTES + ST_Q, 16, 1024);
+                const uint64_t q0 = smem_desc(base + SM_Q + s * 32768, 16, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ss(tmem + T_S, dk_kk[ks], q0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), ID_KK, ks > 0);
                 tc_commit(sh.bar(B_S));
             };
             auto issue_dp = [&](int i) {
-                const int s = i % STAGES;
-                mbar_wait<SLEEP_ISSUER>(sh.bar(B_OFULL + s), (i / STAGES) & 1, abort_flag, p.status);
+                mbar_wait<SLEEP_ISSUER>(sh.bar(B_OFULL), i & 1, abort_flag, p.status);
                 if (i >= 1) mbar_wait<SLEEP_ISSUER>(sh.bar(B_DQE), (i - 1) & 1, abort_flag, p.status);   // dQ~(i-1) has left the columns
                 tc_fence_after();
-                const uint64_t o0 = smem_desc(base + SM_STAGE + s * STAGE_BYTES + ST_DO, 16, 1024);
+                const uint64_t o0 = smem_desc(base + SM_DO, 16, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ss(tmem + T_DP, dv_kk[ks], o0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), ID_KK, ks > 0);
@@ -332,8 +336,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             }
             for (int i = 0; i < total; ++i) {
                 const int s = i % STAGES;
-                const uint32_t st = base + SM_STAGE + s * STAGE_BYTES;
-                const uint64_t q_mn0 = smem_desc(st + ST_Q, 16384, 1024), o_mn0 = smem_desc(st + ST_DO, 16384, 1024);
+                const uint64_t q_mn0 = smem_desc(base + SM_Q + s * 32768, 16384, 1024), o_mn0 = smem_desc(base + SM_DO, 16384, 1024);
                 // dV += P~^T dO : 8 steps of 16 queries; A = 8 TMEM columns per step, the second
                 // compute group's 64 queries start at column 64
                 mbar_wait<SLEEP_ISSUER>(sh.bar(B_P), i & 1, abort_flag, p.status);
@@ -341,7 +344,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ts(tmem + T_DV, tmem + T_S + (ks >> 2) * 64 + (ks & 3) * 8, o_mn0 + ((ks * 2048) >> 4), ID_KM, (i > 0) || (ks > 0));
-                tc_commit(sh.bar(B_OEMPTY + s));
+                tc_commit(sh.bar(B_OEMPTY));
                 if (i + 1 < total) issue_s(i + 1);   // over P~(i), behind dV(i)
                 // dQ~^T = K^T dS~^T : 8 steps of 16 keys
                 mbar_wait<SLEEP_ISSUER>(sh.bar(B_DS), i & 1, abort_flag, p.status);
@@ -376,8 +379,8 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             const int s = i % STAGES;
             const int mb = m_min + i % per_head;
             const int m0 = mb * BM + 64 * wg;   // the group's first query
-            const uint32_t sL_addr = base + SM_STAGE + s * STAGE_BYTES + ST_L + 256 * wg;
-            const uint32_t sDl_addr = base + SM_STAGE + s * STAGE_BYTES + ST_DL + 256 * wg;
+            const uint32_t sL_addr = base + SM_L + s * 512 + 256 * wg;
+            const uint32_t sDl_addr = base + SM_DL + s * 512 + 256 * wg;
             const bool need_mask = (p.causal && m0 < n0 + BN) || (n0 + BN > sq.len);
             float x[64];
             // ---- P~^T = exp2(S^T c - L), kept in registers for dS~ and written over S^T ----
@@ -413,10 +416,10 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             tc_fence_before();
             mbar_arrive(sh.bar(B_P));
             // ---- dS~^T = P~^T (dP^T - Delta) to shared ----
-            mbar_wait<SLEEP_WORKER>(sh.bar(B_OFULL + s), (i / STAGES) & 1, abort_flag, p.status);   // Delta
-            lds32(sDl_addr, lv);
+            // dP^T done means dO, and Delta with it, landed (the MMA thread waited for them)
             mbar_wait<SLEEP_WORKER>(sh.bar(B_DP), i & 1, abort_flag, p.status);
             tc_fence_after();
+            lds32(sDl_addr, lv);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t dv[32];
@@ -440,17 +443,23 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             mbar_arrive(sh.bar(B_DS));
         }
     } else if (warp >= 10) {
-        // ================= dQ drain: TMEM -> int32 grid -> global atomics =================
+        // ================= dQ drain: TMEM -> int32 grid -> shared -> bulk add into the accumulator =================
+        // The tile's int32 values are staged 32 queries (16 KB) at a time in one of two shared
+        // buffers, in the accumulator's own row-major order, and one thread hands each block to the
+        // TMA engine as a reduction (integer add, so the order of arrival does not matter). The
+        // same bytes as 128 `red` instructions per thread, without their place in the instruction
+        // queue the compute warps' ex2 and shared loads go through.
         const int d = 32 * (warp & 3) + lane;   // channel = TMEM lane
         const float dq_mul = F16 ? pow2f(s_exp) : 1.f;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const uint32_t rd = tmem + lane_addr + T_DP;
-        auto add32 = [&](int* acc, uint32_t (&v)[32]) {
+        const bool leader = (warp == 10 && lane == 0);   // issues every bulk reduction: they form its groups
+        const uint32_t stg = base + SM_STG + 4 * d;
+        auto stage = [&](int buf, uint32_t (&v)[32], int* gdst) {
             // Float -> int32, round to nearest even. Adding 1.5 * 2^23 rounds a float below 2^22 to an
             // integer in its low mantissa bits: one add and one subtract per element when every
             // element of the warp's chunk is in that range (the usual case: the grid leaves 2^30 to
             // a row's whole sum), which keeps the conversion off the pipe the softmax's ex2 runs on.
-            // Zeros are added too: a branch per element costs more than the few masked tiles save.
             constexpr float M = 12582912.f;   // 1.5 * 2^23, bits 0x4B400000
             float mx = 0.f;
 #pragma unroll
@@ -465,14 +474,25 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
 #pragma unroll
                 for (int q = 0; q < 32; ++q) v[q] = static_cast<uint32_t>(__float2int_rn(__uint_as_float(v[q])));
             }
+            // the buffer's last block (two blocks ago) must have been read out
+            if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const uint32_t dst = stg + buf * 16384;
 #pragma unroll
-            for (int q = 0; q < 32; ++q)
-                asm volatile("red.global.add.s32 [%0], %1;" ::"l"(acc + q * HD), "r"(v[q]) : "memory");
+            for (int q = 0; q < 32; ++q)   // row q of the block: 128 channels, one per thread
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + q * 512), "r"(v[q]) : "memory");
+            fence_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (leader) {
+                asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.s32 [%0], [%1], %2;"
+                             ::"l"(gdst), "r"(base + SM_STG + buf * 16384), "r"(16384) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
         };
         for (int i = 0; i < total; ++i) {
             const int g = i / per_head, mb = m_min + i % per_head;
             const int h = hkv * p.G + g;
-            int* acc = p.dq_acc + (static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM) * HD + d;
+            int* acc = p.dq_acc + (static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM) * HD;   // [128 queries][128 ch]
             mbar_wait<SLEEP_WORKER>(sh.bar(B_DQF), i & 1, abort_flag, p.status);
             tc_fence_after();
             uint32_t v0[32], v1[32], v2[32];
@@ -480,15 +500,17 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             tmem_ld32(rd + 32, v1);
             tmem_ld32(rd + 64, v2);
             tmem_wait_ld();
-            add32(acc, v0);
+            stage(0, v0, acc);
             tmem_ld32(rd + 96, v0);
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(sh.bar(B_DQE));   // the rest of the tile is in registers: the columns are free for dP^T of the next tile
-            add32(acc + 32 * HD, v1);
-            add32(acc + 64 * HD, v2);
-            add32(acc + 96 * HD, v0);
+            stage(1, v1, acc + 32 * HD);
+            stage(0, v2, acc + 64 * HD);
+            stage(1, v0, acc + 96 * HD);
         }
+        // the engine must be done with shared memory, and the adds complete, before the CTA goes
+        if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     // ================= epilogue: dK, dV out of TMEM =================
