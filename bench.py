@@ -121,7 +121,8 @@ def time_backward(cfg, device, steps, warmup, seed, dist):
     t1 = time.time()
     total = ev[0][0].elapsed_time(ev[-1][3]) / steps
     main = sum(e[1].elapsed_time(e[2]) for e in ev) / steps
-    return total, main, 4, (q, k, v, o, do, lse, run), (t0, t1)
+    # per step: the statistics' memset, preprocess, its finalize pass, main loop, postprocess
+    return total, main, 5, (q, k, v, o, do, lse, run), (t0, t1)
 
 
 def time_e2e(cfg, device, steps, state):

@@ -27,7 +27,7 @@ struct BwdParams {
     // workspace
     int* dq_acc;    // int32 [H][rows_p][D], the fixed-point dQ / scale * 2^s
     float* dpsum;   // [H][rows_p]  Delta_i = sum_d dO O
-    float* lse2;    // [H][rows_p]  lse * log2(e) - s ; +inf on padded rows
+    float* lse2;    // [H][rows_p]  s - lse * log2(e) (fp16: -lse * log2(e)); -inf on padded rows
     int* stats;     // [B][HKV][N_STATS] float bits of the order-free maxima
     int* status;    // one word after the stats: raised if a device-side wait ran out
     int64_t rows_p; // padded rows per head

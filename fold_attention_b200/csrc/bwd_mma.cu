@@ -48,8 +48,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_main_mma_kernel(const BwdPara
     // bf16 has fp32's range, so the softmax carries the grid's exponent
     // (P~ = P 2^s) and dQ~ leaves the GEMM on the grid. fp16 would overflow:
     // there P stays unscaled and the partial is multiplied by 2^s (exact)
-    // before it is rounded.
-    const float s_bias = F16 ? 0.f : static_cast<float>(s_exp);
+    // before it is rounded. The exponent reaches the softmax inside the row
+    // statistic s - L that the preprocess leaves.
     const float dq_mul = F16 ? pow2f(s_exp) : 1.f;
     const float c2 = p.scale * kLog2e;
 
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_main_mma_kernel(const BwdPara
             load_tile_async<D, L::PITCH, NTHREADS>(sQ, row_ptr<const uint16_t>(p.q, b, sq.start + m0, h), p.q.sr, BM, qvalid, tid);
             load_tile_async<D, L::PITCH, NTHREADS>(sdO, row_ptr<const uint16_t>(p.dout, b, sq.start + m0, h), p.dout.sr, BM, qvalid, tid);
             cp_async_commit();
-            if (tid < 64) sL[tid] = p.lse2[wrow + m0 + tid] - s_bias;
+            if (tid < 64) sL[tid] = -p.lse2[wrow + m0 + tid];   // lse2 holds s - L: the same bits as L - s, negated
             else if (tid < 128) sDl[tid - 64] = p.dpsum[wrow + m0 + tid - 64];
             cp_async_wait<0>();
             __syncthreads();

@@ -155,6 +155,22 @@ __global__ void __launch_bounds__(256) bwd_postprocess_dq_kernel(const BwdParams
     }
 }
 
+// Second, tiny pass of the preprocess: once the maxima are in, the grid exponent s of each
+// (request, KV head) is known, and the row statistic the main loop adds inside its exponential
+// becomes s - lse * log2(e) (bf16; fp16 applies s at the dQ drain and keeps -lse * log2(e)): one
+// add per row here instead of one per score there. Padded rows hold -inf: their weights are 0.
+__global__ void __launch_bounds__(256) bwd_finalize_l_kernel(const BwdParams p) {
+    const int h = blockIdx.y, b = blockIdx.z;
+    const SeqInfo sq = seq_info(p, b);
+    const int len_r = (sq.len + ROW_PAD - 1) / ROW_PAD * ROW_PAD;
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= len_r) return;
+    const int s = dq_scale_exp(p.stats + (static_cast<int64_t>(b) * p.HKV + h / p.G) * N_STATS, root_d(p.D));
+    const float s_bias = p.f16 ? 0.f : static_cast<float>(s);
+    float* l = p.lse2 + static_cast<int64_t>(h) * p.rows_p + sq.pstart + i;
+    *l = s_bias - *l;
+}
+
 int launch_bwd_preprocess(const BwdParams& p, cudaStream_t st) {
     cudaMemsetAsync(p.stats, 0, sizeof(int) * (N_STATS * p.B * p.HKV + 1), st);
     const int s_r = (p.S + ROW_PAD - 1) / ROW_PAD * ROW_PAD;
@@ -163,6 +179,7 @@ int launch_bwd_preprocess(const BwdParams& p, cudaStream_t st) {
         bwd_preprocess_kernel<true><<<grid, PRE_THREADS, 0, st>>>(p);
     else
         bwd_preprocess_kernel<false><<<grid, PRE_THREADS, 0, st>>>(p);
+    bwd_finalize_l_kernel<<<dim3((s_r + 255) / 256, p.H, p.B), 256, 0, st>>>(p);
     return check_launch("bwd_preprocess");
 }
 

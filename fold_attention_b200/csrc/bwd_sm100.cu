@@ -368,9 +368,8 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         const int r = 32 * (warp & 3) + lane;   // key row = TMEM lane
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const float c2 = p.scale * kLog2e;
-        // bf16 has fp32's range, so P~ and dS~ carry the grid's exponent; fp16 does not, and the
-        // exponent is applied to dQ's fp32 sums at the drain instead
-        const float s_bias = F16 ? 0.f : static_cast<float>(s_exp);
+        // bf16 has fp32's range, so P~ and dS~ carry the grid's exponent (it comes in with the row
+        // statistic s - L); fp16 does not, and the exponent is applied to dQ's fp32 sums at the drain
         const int kj = n0 + r;
         const uint32_t rs = tmem + lane_addr + T_S + 64 * wg;
         const uint32_t rd = tmem + lane_addr + T_DP + 64 * wg;
@@ -397,7 +396,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 tmem_wait_ld();
                 uint32_t pp[16];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) x[32 * c + j] = fmaf(__uint_as_float(sv[j]), c2, s_bias - lv[j]);
+                for (int j = 0; j < 32; ++j) x[32 * c + j] = fmaf(__uint_as_float(sv[j]), c2, lv[j]);   // lv = s - L, from the preprocess
 #pragma unroll
                 for (int j = 0; j < 32; ++j) x[32 * c + j] = ex2f(x[32 * c + j]);   // 32 independent ex2 in a row
                 if (need_mask) {   // the diagonal tile and the sequence's last key block only: kept out of the common path
