@@ -47,6 +47,9 @@ constexpr int NTHREADS = 448;
 constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 // nanoseconds a waiting thread sleeps between polls of its barrier: a polling warp takes issue
 // slots from the working warps of its scheduler
+#ifndef FOLD_PACKED_MATH
+#define FOLD_PACKED_MATH 1
+#endif
 #ifndef FOLD_SLEEP_WORKER
 #define FOLD_SLEEP_WORKER 64
 #endif
@@ -175,6 +178,25 @@ __device__ __forceinline__ void lds32(uint32_t addr, float (&v)[32]) {
     for (int u = 0; u < 8; ++u)
         asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
                      : "=f"(v[4 * u]), "=f"(v[4 * u + 1]), "=f"(v[4 * u + 2]), "=f"(v[4 * u + 3]) : "r"(addr + 16 * u));
+}
+// Packed fp32 arithmetic (two IEEE operations per instruction, the results bit for bit those of
+// the scalar forms): the compute warps are short of issue slots and of nothing else.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, uint64_t b, float c0, float c1) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack2(a0, a1)), "l"(b), "l"(pack2(c0, c1)));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
+// (a - b) * c
+__device__ __forceinline__ void submul2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    uint64_t t, d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(t) : "l"(pack2(a0, a1)), "l"(pack2(b0, b1)));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(t), "l"(pack2(c0, c1)));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
 }
 __device__ __forceinline__ float ex2f(float x) {
     float y;
@@ -368,6 +390,8 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         const int r = 32 * (warp & 3) + lane;   // key row = TMEM lane
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const float c2 = p.scale * kLog2e;
+        const uint64_t c2x2 = pack2(c2, c2);
+        (void)c2x2;
         // bf16 has fp32's range, so P~ and dS~ carry the grid's exponent (it comes in with the row
         // statistic s - L); fp16 does not, and the exponent is applied to dQ's fp32 sums at the drain
         const int kj = n0 + r;
@@ -396,7 +420,12 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 tmem_wait_ld();
                 uint32_t pp[16];
 #pragma unroll
+#if FOLD_PACKED_MATH
+                for (int j = 0; j < 32; j += 2)   // lv = s - L, from the preprocess
+                    fma2(x[32 * c + j], x[32 * c + j + 1], __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]), c2x2, lv[j], lv[j + 1]);
+#else
                 for (int j = 0; j < 32; ++j) x[32 * c + j] = fmaf(__uint_as_float(sv[j]), c2, lv[j]);   // lv = s - L, from the preprocess
+#endif
 #pragma unroll
                 for (int j = 0; j < 32; ++j) x[32 * c + j] = ex2f(x[32 * c + j]);   // 32 independent ex2 in a row
                 if (need_mask) {   // the diagonal tile and the sequence's last key block only: kept out of the common path
@@ -427,7 +456,12 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 tmem_wait_ld();
                 uint32_t dd[16];
 #pragma unroll
+#if FOLD_PACKED_MATH
+                for (int j = 0; j < 32; j += 2)
+                    submul2(lv[j], lv[j + 1], __uint_as_float(dv[j]), __uint_as_float(dv[j + 1]), lv[j], lv[j + 1], x[32 * c + j], x[32 * c + j + 1]);
+#else
                 for (int j = 0; j < 32; ++j) lv[j] = x[32 * c + j] * (__uint_as_float(dv[j]) - lv[j]);
+#endif
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) dd[j >> 1] = F16 ? pack_f16x2(lv[j], lv[j + 1]) : pack_bf16x2(lv[j], lv[j + 1]);
                 // dS~^T row r: 16-byte chunk u (8 queries) at u ^ (r & 7)
