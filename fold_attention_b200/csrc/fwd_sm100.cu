@@ -127,6 +127,23 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Two fp32 FMAs per instruction and a three-input maximum (same results as the scalar forms): the
+// softmax warps are what this kernel waits for.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack2(a0, a1)), "l"(b), "l"(c));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2f(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -281,6 +298,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
         const int r = 32 * (warp & 3) + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const float c2 = p.scale * kLog2e;
+        const uint64_t c2x2 = pack2(c2, c2);
         const int mx = m0 + x * BM;
         const int qi = mx + r;                 // the row's position in its sequence
         const int my_tiles = nt[x];
@@ -300,12 +318,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
                 uint32_t sv[32];
                 tmem_ld32(ts + 32 * c, sv);
                 tmem_wait_ld();
+                if (need_mask) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    float v = __uint_as_float(sv[e]);
-                    if (need_mask && 32 * c + e > kmax) v = -INFINITY;
-                    mxv = fmaxf(mxv, v);
+                    for (int e = 0; e < 32; ++e)
+                        if (32 * c + e > kmax) sv[e] = 0xff800000u;   // -inf
                 }
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) mxv = max3f(mxv, __uint_as_float(sv[e]), __uint_as_float(sv[e + 1]));
             }
             const float m_new = fmaxf(m_run, mxv * c2);
             // a row that sees no key yet keeps m = -inf; its weights are exp2(-inf) = 0
@@ -314,6 +333,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
             // pass 2: weights over the scores as packed bf16 (P chunk c lands on columns the row's
             // thread has already read), and their sum
             float sum = 0.f;
+            const uint64_t nm2 = pack2(-m_use, -m_use);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t sv[32];
@@ -322,8 +342,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
                 uint32_t pp[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    float x0 = ex2f(fmaf(__uint_as_float(sv[e]), c2, -m_use));
-                    float x1 = ex2f(fmaf(__uint_as_float(sv[e + 1]), c2, -m_use));
+                    float x0, x1;
+                    fma2(x0, x1, __uint_as_float(sv[e]), __uint_as_float(sv[e + 1]), c2x2, nm2);
+                    x0 = ex2f(x0);
+                    x1 = ex2f(x1);
                     if (need_mask) {
                         if (32 * c + e > kmax) x0 = 0.f;
                         if (32 * c + e + 1 > kmax) x1 = 0.f;
