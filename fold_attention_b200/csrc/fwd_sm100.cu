@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
             const float alpha = ex2f(m_run - m_use);   // 0 on the first tile that holds a key
             // pass 2: weights over the scores as packed bf16 (P chunk c lands on columns the row's
             // thread has already read), and their sum
-            float sum = 0.f;
+            uint64_t sum2 = 0ull;   // two partial sums, added at the end of the tile
             const uint64_t nm2 = pack2(-m_use, -m_use);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -350,12 +350,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
                         if (32 * c + e > kmax) x0 = 0.f;
                         if (32 * c + e + 1 > kmax) x1 = 0.f;
                     }
-                    sum += x0 + x1;
+                    asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum2) : "l"(pack2(x0, x1)));   // even and odd columns apart
                     pp[e >> 1] = F16 ? pack_f16x2(x0, x1) : pack_bf16x2(x0, x1);
                 }
                 tmem_st16(ts + 16 * c, pp);
             }
-            l_run = l_run * alpha + sum;
+            float sum_e, sum_o;
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(sum_e), "=f"(sum_o) : "l"(sum2));
+            l_run = l_run * alpha + (sum_e + sum_o);
             m_run = m_new;
             // O was last written by key tile j-1's product: rescale it where a row's maximum rose
             if (j > 0) {
