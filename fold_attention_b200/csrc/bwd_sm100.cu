@@ -50,6 +50,9 @@ constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 #ifndef FOLD_PACKED_MATH
 #define FOLD_PACKED_MATH 1
 #endif
+#ifndef FOLD_DRAIN_PACKED
+#define FOLD_DRAIN_PACKED 1
+#endif
 #ifndef FOLD_SLEEP_WORKER
 #define FOLD_SLEEP_WORKER 64
 #endif
@@ -501,8 +504,20 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 mx = fmaxf(mx, fabsf(__uint_as_float(v[q])));
             }
             if (!__any_sync(0xffffffffu, !(mx < 4194304.f))) {
+#if FOLD_DRAIN_PACKED
+#pragma unroll
+                for (int q = 0; q < 32; q += 2) {
+                    uint64_t t;
+                    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(t) : "l"(pack2(__uint_as_float(v[q]), __uint_as_float(v[q + 1]))), "l"(pack2(M, M)));
+                    uint32_t lo, hi;
+                    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(t));
+                    v[q] = lo - 0x4B400000u;
+                    v[q + 1] = hi - 0x4B400000u;
+                }
+#else
 #pragma unroll
                 for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(__uint_as_float(v[q]) + M) - 0x4B400000u;
+#endif
             } else {   // rare, and kept small: the conversion instruction (same rounding; it shares a pipe with ex2)
 #pragma unroll
                 for (int q = 0; q < 32; ++q) v[q] = static_cast<uint32_t>(__float2int_rn(__uint_as_float(v[q])));
