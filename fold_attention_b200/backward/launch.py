@@ -31,6 +31,7 @@ _lib.register(
     "fold_bwd_run_phases",
     [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, I, P],
 )
+_lib.register("fold_bwd_counters", [P, I])
 _lib.register("fold_fwd_run", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
 _lib.register("fold_fwd_sm100_supported", [I, I])
 _lib.register("fold_fwd_run_sm100", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P])

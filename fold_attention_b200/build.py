@@ -4,6 +4,11 @@
 
 (run it by path: importing the package loads the library)
 
+Environment: FOLD_NVCC_FLAGS adds compiler flags (for instance
+`-DFOLD_BWD_COUNTERS`, which makes the backward's main loop count where each
+warp role's cycles go and `fold_bwd_counters` return them), FOLD_LIB_OUT names
+another output file (an instrumented build beside the product one).
+
 nvcc cross-compiles without a GPU. The library sits beside this file so it
 travels with the source tree; nothing is installed into site-packages.
 """
@@ -26,7 +31,10 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "--expt-relaxed-constexpr",
     "-Xcompiler", "-fPIC",
-]
+] + os.environ.get("FOLD_NVCC_FLAGS", "").split()
+if os.environ.get("FOLD_LIB_OUT"):
+    LIB = os.path.abspath(os.environ["FOLD_LIB_OUT"])
+    STAMP = LIB + ".stamp"
 
 
 def _sources():
@@ -96,11 +104,11 @@ def build(force=False, verbose=False):
     cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
            "-Xcompiler", "-fPIC", "-lcudart"]
     subprocess.check_call(cmd)
-    # drop objects of older source versions
+    # drop objects of older source versions (a side build keeps the product's objects)
     keep = set(objs)
     for f in os.listdir(objdir):
         p = os.path.join(objdir, f)
-        if p.endswith(".o") and p not in keep:
+        if p.endswith(".o") and p not in keep and not os.environ.get("FOLD_LIB_OUT"):
             os.remove(p)
     with open(STAMP, "w") as f:
         f.write(digest)

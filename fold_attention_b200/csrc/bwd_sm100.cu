@@ -25,9 +25,13 @@
 // nearest-even int32 and added to the accumulator with integer reductions, which
 // commute exactly.
 //
-// Warps: 0 TMA producer, 1 MMA issuer (owns the TMEM allocation), 2-5 and 6-9
-// the two compute groups (64 queries of the tile each), 10-13 the dQ drain
-// (TMEM -> int32 -> shared -> cp.reduce.async.bulk add into the accumulator).
+// Warps: 0 TMA producer, 1 MMA issuer (owns the TMEM allocation), then NWG
+// compute warpgroups (128 / NWG queries of the tile each; a thread is one key
+// row = one TMEM lane), then the dQ drain's four warps (TMEM -> int32 -> shared
+// -> cp.reduce.async.bulk add into the accumulator). The compute phases are
+// chains of TMEM load -> arithmetic -> store whose latency, not throughput,
+// sets their length, so four warpgroups of 32 queries (four compute warps per
+// scheduler) finish a tile's exponentials and dS~ sooner than two of 64.
 // Every mbarrier wait is bounded: on expiry the kernel raises a status word,
 // stops waiting everywhere, frees its TMEM and returns.
 // Reference arithmetic: src/fold_attention/backward/kernel.py:1191-1330.
@@ -43,7 +47,15 @@ constexpr int BN = 128;   // keys per CTA
 constexpr int BM = 128;   // queries per tile
 constexpr int HD = 128;   // head dim
 constexpr int STAGES = 2;
-constexpr int NTHREADS = 448;
+#ifndef FOLD_BWD_NWG
+#define FOLD_BWD_NWG 2
+#endif
+constexpr int NWG = FOLD_BWD_NWG;            // compute warpgroups
+constexpr int QPW = BM / NWG;                // queries per compute warpgroup
+constexpr int NCOMPUTE = 128 * NWG;          // compute threads
+constexpr int W_DRAIN = 2 + 4 * NWG;         // first warp of the dQ drain
+constexpr int NTHREADS = 32 * (W_DRAIN + 4);
+static_assert(NWG == 2 || NWG == 4, "two or four compute warpgroups");
 constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 // nanoseconds a waiting thread sleeps between polls of its barrier: a polling warp takes issue
 // slots from the working warps of its scheduler
@@ -58,6 +70,11 @@ constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 #endif
 #ifndef FOLD_SLEEP_ISSUER
 #define FOLD_SLEEP_ISSUER 0
+#endif
+// 1: the MMA thread polls the heads of its two chains (S -> dV and dP -> dQ, dK) and issues
+// whichever is ready, instead of one fixed order that lets a late drain hold back dV and S
+#ifndef FOLD_BWD_DYN_ISSUE
+#define FOLD_BWD_DYN_ISSUE 0
 #endif
 constexpr int SLEEP_WORKER = FOLD_SLEEP_WORKER, SLEEP_PRODUCER = 100, SLEEP_ISSUER = FOLD_SLEEP_ISSUER;
 
@@ -116,6 +133,13 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// one poll that never suspends the thread, for a thread that watches several barriers
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait. `abort` (shared) is raised by whoever runs out first; once it
 // is up nobody waits any more, so every role runs to its end.
 template <int SLEEP_NS = 0>
@@ -165,6 +189,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
                  "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -179,6 +210,12 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ void lds32(uint32_t addr, float (&v)[32]) {
 #pragma unroll
     for (int u = 0; u < 8; ++u)
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(v[4 * u]), "=f"(v[4 * u + 1]), "=f"(v[4 * u + 2]), "=f"(v[4 * u + 3]) : "r"(addr + 16 * u));
+}
+__device__ __forceinline__ void lds16(uint32_t addr, float (&v)[16]) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
         asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
                      : "=f"(v[4 * u]), "=f"(v[4 * u + 1]), "=f"(v[4 * u + 2]), "=f"(v[4 * u + 3]) : "r"(addr + 16 * u));
 }
@@ -229,6 +266,20 @@ struct Maps {
     CUtensorMap q, dout, k, v;   // (channel, row, head, batch), boxes (64, 128, 1, 1)
 };
 
+// ---- optional cycle counters (-DFOLD_BWD_COUNTERS): where each role's time goes -----------
+// Sums over every CTA of a launch, taken by one thread per role: slots are
+//  0 CTAs, 1 tiles, 2 CTA lifetime, 3 prologue (until K and V have landed), 4 epilogue,
+//  5 compute: wait for S^T, 6 exponential phase, 7 wait for dP^T, 8 dS~ phase,
+//  9 MMA thread: cycles with nothing ready to issue, 10 drain: wait for dQ~^T, 11 drain busy.
+#ifdef FOLD_BWD_COUNTERS
+__device__ unsigned long long g_counters[16];
+#define CNT_ADD(slot, v) atomicAdd(&g_counters[slot], static_cast<unsigned long long>(v))
+#define CNT_T(var) const long long var = clock64()
+#else
+#define CNT_ADD(slot, v) do { } while (0)
+#define CNT_T(var) do { } while (0)
+#endif
+
 template <bool F16>
 __global__ void __launch_bounds__(NTHREADS, 1)
 bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
@@ -249,6 +300,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
     const SeqInfo sq = seq_info(p, b);
     const int n0 = nb * BN;
     if (n0 >= sq.len) return;
+    CNT_T(cta_t0);
 
     // query tiles: all heads of the group, each from the first tile that can see this key block
     const int nm = (sq.len + BM - 1) / BM;
@@ -267,8 +319,8 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         mbar_init(sh.bar(B_OEMPTY), 1);
         mbar_init(sh.bar(B_S), 1);
         mbar_init(sh.bar(B_DP), 1);
-        mbar_init(sh.bar(B_P), 256);
-        mbar_init(sh.bar(B_DS), 256);
+        mbar_init(sh.bar(B_P), NCOMPUTE);
+        mbar_init(sh.bar(B_DS), NCOMPUTE);
         mbar_init(sh.bar(B_DQF), 1);
         mbar_init(sh.bar(B_DQE), 128);
         mbar_init(sh.bar(B_DONE), 1);
@@ -333,47 +385,41 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 dk_mn[ks] = smem_desc(base + SM_K + ks * 2048, 16384, 1024);
             }
             const uint64_t ds_kk0 = smem_desc(base + SM_DS, 16, 1024), ds_mn0 = smem_desc(base + SM_DS, 16384, 1024);
+            const uint64_t o_kk0 = smem_desc(base + SM_DO, 16, 1024), o_mn0 = smem_desc(base + SM_DO, 16384, 1024);
+            CNT_T(pro_t0);
             mbar_wait<SLEEP_ISSUER>(sh.bar(B_KV), 0, abort_flag, p.status);
             tc_fence_after();
-            auto issue_s = [&](int i) {
-                const int s = i % STAGES;
-                mbar_wait<SLEEP_ISSUER>(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);
-                tc_fence_after();
-                const uint64_t q0 = smem_desc(base + SM_Q + s * 32768, 16, 1024);
+#ifdef FOLD_BWD_COUNTERS
+            CNT_ADD(3, clock64() - pro_t0);
+            long long idle_clk = 0;
+#endif
+            // The five GEMMs of tile i, each eight K=16 steps, none of them waiting for anything:
+            // the barriers they depend on are taken by the issue loops below.
+            auto issue_s = [&](int i) {   // S^T = K Q^T -> T_S
+                const uint64_t q0 = smem_desc(base + SM_Q + (i % STAGES) * 32768, 16, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ss(tmem + T_S, dk_kk[ks], q0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), ID_KK, ks > 0);
                 tc_commit(sh.bar(B_S));
             };
-            auto issue_dp = [&](int i) {
-                mbar_wait<SLEEP_ISSUER>(sh.bar(B_OFULL), i & 1, abort_flag, p.status);
-                if (i >= 1) mbar_wait<SLEEP_ISSUER>(sh.bar(B_DQE), (i - 1) & 1, abort_flag, p.status);   // dQ~(i-1) has left the columns
-                tc_fence_after();
-                const uint64_t o0 = smem_desc(base + SM_DO, 16, 1024);
+            auto issue_dp = [&](int) {    // dP^T = V dO^T -> T_DP
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
-                    mma_ss(tmem + T_DP, dv_kk[ks], o0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), ID_KK, ks > 0);
+                    mma_ss(tmem + T_DP, dv_kk[ks], o_kk0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), ID_KK, ks > 0);
                 tc_commit(sh.bar(B_DP));
             };
-            if (total > 0) {
-                issue_s(0);
-                issue_dp(0);
-            }
-            for (int i = 0; i < total; ++i) {
-                const int s = i % STAGES;
-                const uint64_t q_mn0 = smem_desc(base + SM_Q + s * 32768, 16384, 1024), o_mn0 = smem_desc(base + SM_DO, 16384, 1024);
-                // dV += P~^T dO : 8 steps of 16 queries; A = 8 TMEM columns per step, the second
-                // compute group's 64 queries start at column 64
-                mbar_wait<SLEEP_ISSUER>(sh.bar(B_P), i & 1, abort_flag, p.status);
-                tc_fence_after();
+            auto issue_dv = [&](int i) {  // dV += P~^T dO: steps of 16 queries; A = 8 TMEM columns per step, at the
+                                          // head of the S^T columns of the warpgroup that owns those queries
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
-                    mma_ts(tmem + T_DV, tmem + T_S + (ks >> 2) * 64 + (ks & 3) * 8, o_mn0 + ((ks * 2048) >> 4), ID_KM, (i > 0) || (ks > 0));
+                    mma_ts(tmem + T_DV, tmem + T_S + (16 * ks / QPW) * QPW + (16 * ks % QPW) / 2, o_mn0 + ((ks * 2048) >> 4), ID_KM,
+                           (i > 0) || (ks > 0));
                 tc_commit(sh.bar(B_OEMPTY));
-                if (i + 1 < total) issue_s(i + 1);   // over P~(i), behind dV(i)
+            };
+            auto issue_dq_dk = [&](int i) {
+                const int s = i % STAGES;
+                const uint64_t q_mn0 = smem_desc(base + SM_Q + s * 32768, 16384, 1024);
                 // dQ~^T = K^T dS~^T : 8 steps of 16 keys
-                mbar_wait<SLEEP_ISSUER>(sh.bar(B_DS), i & 1, abort_flag, p.status);
-                tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ss(tmem + T_DP, dk_mn[ks], ds_mn0 + ((ks * 2048) >> 4), ID_MM, ks > 0);
@@ -383,13 +429,98 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ss(tmem + T_DK, ds_kk0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), q_mn0 + ((ks * 2048) >> 4), ID_KM, (i > 0) || (ks > 0));
                 tc_commit(sh.bar(B_QEMPTY + s));
-                if (i + 1 < total) issue_dp(i + 1);
+            };
+#if FOLD_BWD_DYN_ISSUE
+            // Two chains share the tensor pipe: A = S(0) dV(0) S(1) dV(1) ... (S(i+1) overwrites P~(i)
+            // right behind dV(i): a thread's MMAs execute in issue order) and B = dP(0) dQdK(0) dP(1) ...
+            // (dP(i+1) overwrites dQ~(i) once the drain has it). Each keeps its own order, so every
+            // accumulator sees the same sequence of MMAs whatever the interleaving; dV(i) also waits
+            // for dP(i) to have been issued, so that the commit behind dV(i) frees dO for both.
+            int a_s = 0, a_v = 0, b_p = 0, b_q = 0;
+            long long t_last = clock64();
+            int idle = 0;
+            while (a_v < total || b_q < total) {
+                bool prog = false;
+                if (a_s == a_v) {
+                    if (a_s < total && mbar_test(sh.bar(B_QFULL + a_s % STAGES), (a_s / STAGES) & 1)) {
+                        tc_fence_after();
+                        issue_s(a_s);
+                        ++a_s;
+                        prog = true;
+                    }
+                } else if (b_p > a_v && mbar_test(sh.bar(B_P), a_v & 1)) {
+                    tc_fence_after();
+                    issue_dv(a_v);
+                    ++a_v;
+                    prog = true;
+                }
+                if (b_p == b_q) {
+                    if (b_p < total && mbar_test(sh.bar(B_OFULL), b_p & 1) && (b_p == 0 || mbar_test(sh.bar(B_DQE), (b_p - 1) & 1))) {
+                        tc_fence_after();
+                        issue_dp(b_p);
+                        ++b_p;
+                        prog = true;
+                    }
+                } else if (mbar_test(sh.bar(B_DS), b_q & 1)) {
+                    tc_fence_after();
+                    issue_dq_dk(b_q);
+                    ++b_q;
+                    prog = true;
+                }
+                if (prog) {
+#ifdef FOLD_BWD_COUNTERS
+                    if (idle) idle_clk += clock64() - t_last;
+#endif
+                    idle = 0;
+                    t_last = clock64();
+                } else if ((++idle & 127) == 0) {
+                    if (*abort_flag) break;
+                    if (clock64() - t_last > WAIT_CYCLES) {
+                        *abort_flag = 1;
+                        atomicExch(p.status, FOLD_ERR_TIMEOUT);
+                        break;
+                    }
+                }
             }
+#else
+            if (total > 0) {
+                mbar_wait<SLEEP_ISSUER>(sh.bar(B_QFULL), 0, abort_flag, p.status);
+                tc_fence_after();
+                issue_s(0);
+                mbar_wait<SLEEP_ISSUER>(sh.bar(B_OFULL), 0, abort_flag, p.status);
+                tc_fence_after();
+                issue_dp(0);
+            }
+            for (int i = 0; i < total; ++i) {
+                mbar_wait<SLEEP_ISSUER>(sh.bar(B_P), i & 1, abort_flag, p.status);
+                tc_fence_after();
+                issue_dv(i);
+                if (i + 1 < total) {   // over P~(i), behind dV(i)
+                    mbar_wait<SLEEP_ISSUER>(sh.bar(B_QFULL + (i + 1) % STAGES), ((i + 1) / STAGES) & 1, abort_flag, p.status);
+                    tc_fence_after();
+                    issue_s(i + 1);
+                }
+                mbar_wait<SLEEP_ISSUER>(sh.bar(B_DS), i & 1, abort_flag, p.status);
+                tc_fence_after();
+                issue_dq_dk(i);
+                if (i + 1 < total) {
+                    mbar_wait<SLEEP_ISSUER>(sh.bar(B_OFULL), (i + 1) & 1, abort_flag, p.status);
+                    mbar_wait<SLEEP_ISSUER>(sh.bar(B_DQE), i & 1, abort_flag, p.status);   // dQ~(i) has left the columns
+                    tc_fence_after();
+                    issue_dp(i + 1);
+                }
+            }
+#endif
             tc_commit(sh.bar(B_DONE));
+#ifdef FOLD_BWD_COUNTERS
+            CNT_ADD(0, 1);
+            CNT_ADD(1, total);
+            CNT_ADD(9, idle_clk);
+#endif
         }
-    } else if (warp >= 2 && warp < 10) {
-        // ================= compute: P~^T and dS~^T for 64 of the tile's queries =================
-        const int wg = (warp >= 6) ? 1 : 0;
+    } else if (warp < W_DRAIN) {
+        // ================= compute: P~^T and dS~^T for QPW of the tile's queries =================
+        const int wg = (warp - 2) >> 2;
         const int r = 32 * (warp & 3) + lane;   // key row = TMEM lane
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const float c2 = p.scale * kLog2e;
@@ -398,27 +529,36 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         // bf16 has fp32's range, so P~ and dS~ carry the grid's exponent (it comes in with the row
         // statistic s - L); fp16 does not, and the exponent is applied to dQ's fp32 sums at the drain
         const int kj = n0 + r;
-        const uint32_t rs = tmem + lane_addr + T_S + 64 * wg;
-        const uint32_t rd = tmem + lane_addr + T_DP + 64 * wg;
-        uint8_t* sds = smem + SM_DS + wg * 16384 + r * 128;
+        const uint32_t rs = tmem + lane_addr + T_S + QPW * wg;
+        const uint32_t rd = tmem + lane_addr + T_DP + QPW * wg;
+        // dS~^T row r: 128 bytes = 64 queries per box, 16-byte chunk u (8 queries) at u ^ (r & 7)
+        uint8_t* sds = smem + SM_DS + ((QPW * wg) / 64) * 16384 + r * 128;
+        constexpr int CH0_MASK = (64 / QPW) - 1;        // warpgroups per 64-query box, minus one
+        const int ch0 = (wg & CH0_MASK) * (QPW / 8);    // the warpgroup's first chunk in its box
+#ifdef FOLD_BWD_COUNTERS
+        long long c_ws = 0, c_exp = 0, c_wd = 0, c_ds = 0;
+        const bool counting = (warp == 2 && lane == 0);
+#endif
         for (int i = 0; i < total; ++i) {
             const int s = i % STAGES;
             const int mb = m_min + i % per_head;
-            const int m0 = mb * BM + 64 * wg;   // the group's first query
-            const uint32_t sL_addr = base + SM_L + s * 512 + 256 * wg;
-            const uint32_t sDl_addr = base + SM_DL + s * 512 + 256 * wg;
+            const int m0 = mb * BM + QPW * wg;   // the group's first query
+            const uint32_t sL_addr = base + SM_L + s * 512 + 4 * QPW * wg;
+            const uint32_t sDl_addr = base + SM_DL + s * 512 + 4 * QPW * wg;
             const bool need_mask = (p.causal && m0 < n0 + BN) || (n0 + BN > sq.len);
-            float x[64];
+            float x[QPW];
             // ---- P~^T = exp2(S^T c - L), kept in registers for dS~ and written over S^T ----
+            CNT_T(t_a);
             mbar_wait<SLEEP_WORKER>(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);   // L (long since there)
             float lv[32];
             lds32(sL_addr, lv);   // the first 32 queries' L, in flight under the wait for S^T
             mbar_wait<SLEEP_WORKER>(sh.bar(B_S), i & 1, abort_flag, p.status);
             tc_fence_after();
+            CNT_T(t_b);
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < QPW / 32; ++c) {
                 uint32_t sv[32];
-                if (c == 1) lds32(sL_addr + 128, lv);
+                if (c > 0) lds32(sL_addr + 128 * c, lv);
                 tmem_ld32(rs + 32 * c, sv);
                 tmem_wait_ld();
                 uint32_t pp[16];
@@ -446,39 +586,57 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(sh.bar(B_P));
-            // ---- dS~^T = P~^T (dP^T - Delta) to shared ----
+            CNT_T(t_c);
+            // ---- dS~^T = P~^T (dP^T - Delta) to shared, 16 queries at a time ----
             // dP^T done means dO, and Delta with it, landed (the MMA thread waited for them)
             mbar_wait<SLEEP_WORKER>(sh.bar(B_DP), i & 1, abort_flag, p.status);
             tc_fence_after();
-            lds32(sDl_addr, lv);
+            CNT_T(t_d);
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t dv[32];
-                if (c == 1) lds32(sDl_addr + 128, lv);
-                tmem_ld32(rd + 32 * c, dv);
+            for (int hh = 0; hh < QPW / 16; ++hh) {
+                float dl[16];
+                uint32_t dv[16];
+                lds16(sDl_addr + 64 * hh, dl);
+                tmem_ld16(rd + 16 * hh, dv);
                 tmem_wait_ld();
-                uint32_t dd[16];
+                uint32_t dd[8];
 #pragma unroll
 #if FOLD_PACKED_MATH
-                for (int j = 0; j < 32; j += 2)
-                    submul2(lv[j], lv[j + 1], __uint_as_float(dv[j]), __uint_as_float(dv[j + 1]), lv[j], lv[j + 1], x[32 * c + j], x[32 * c + j + 1]);
+                for (int j = 0; j < 16; j += 2)
+                    submul2(dl[j], dl[j + 1], __uint_as_float(dv[j]), __uint_as_float(dv[j + 1]), dl[j], dl[j + 1], x[16 * hh + j], x[16 * hh + j + 1]);
 #else
-                for (int j = 0; j < 32; ++j) lv[j] = x[32 * c + j] * (__uint_as_float(dv[j]) - lv[j]);
+                for (int j = 0; j < 16; ++j) dl[j] = x[16 * hh + j] * (__uint_as_float(dv[j]) - dl[j]);
 #endif
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) dd[j >> 1] = F16 ? pack_f16x2(lv[j], lv[j + 1]) : pack_bf16x2(lv[j], lv[j + 1]);
-                // dS~^T row r: 16-byte chunk u (8 queries) at u ^ (r & 7)
+                for (int j = 0; j < 16; j += 2) dd[j >> 1] = F16 ? pack_f16x2(dl[j], dl[j + 1]) : pack_bf16x2(dl[j], dl[j + 1]);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int cu = (4 * c + u) ^ (r & 7);
+                for (int u = 0; u < 2; ++u) {
+                    const int cu = (ch0 + 2 * hh + u) ^ (r & 7);
                     *reinterpret_cast<uint4*>(sds + cu * 16) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
                 }
             }
             tc_fence_before();
             fence_async_smem();
             mbar_arrive(sh.bar(B_DS));
+#ifdef FOLD_BWD_COUNTERS
+            if (counting) {
+                const long long t_e = clock64();
+                c_ws += t_b - t_a;
+                c_exp += t_c - t_b;
+                c_wd += t_d - t_c;
+                c_ds += t_e - t_d;
+            }
+#endif
         }
-    } else if (warp >= 10) {
+#ifdef FOLD_BWD_COUNTERS
+        if (counting) {
+            CNT_ADD(5, c_ws);
+            CNT_ADD(6, c_exp);
+            CNT_ADD(7, c_wd);
+            CNT_ADD(8, c_ds);
+        }
+#endif
+    } else {
         // ================= dQ drain: TMEM -> int32 grid -> shared -> bulk add into the accumulator =================
         // The tile's int32 values are staged 32 queries (16 KB) at a time in one of two shared
         // buffers, in the accumulator's own row-major order, and one thread hands each block to the
@@ -489,7 +647,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         const float dq_mul = F16 ? pow2f(s_exp) : 1.f;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const uint32_t rd = tmem + lane_addr + T_DP;
-        const bool leader = (warp == 10 && lane == 0);   // issues every bulk reduction: they form its groups
+        const bool leader = (warp == W_DRAIN && lane == 0);   // issues every bulk reduction: they form its groups
         const uint32_t stg = base + SM_STG + 4 * d;
         auto stage = [&](int buf, uint32_t (&v)[32], int* gdst) {
             // Float -> int32, round to nearest even. Adding 1.5 * 2^23 rounds a float below 2^22 to an
@@ -537,46 +695,86 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
         };
+#ifdef FOLD_BWD_COUNTERS
+        long long c_wq = 0, c_busy = 0;
+#endif
         for (int i = 0; i < total; ++i) {
             const int g = i / per_head, mb = m_min + i % per_head;
             const int h = hkv * p.G + g;
             int* acc = p.dq_acc + (static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM) * HD;   // [128 queries][128 ch]
+            CNT_T(t_a);
             mbar_wait<SLEEP_WORKER>(sh.bar(B_DQF), i & 1, abort_flag, p.status);
             tc_fence_after();
-            uint32_t v0[32], v1[32], v2[32];
-            tmem_ld32(rd, v0);
-            tmem_ld32(rd + 32, v1);
-            tmem_ld32(rd + 64, v2);
-            tmem_wait_ld();
-            stage(0, v0, acc);
-            tmem_ld32(rd + 96, v0);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(sh.bar(B_DQE));   // the rest of the tile is in registers: the columns are free for dP^T of the next tile
-            stage(1, v1, acc + 32 * HD);
-            stage(0, v2, acc + 64 * HD);
-            stage(1, v0, acc + 96 * HD);
+            CNT_T(t_b);
+            if constexpr (NWG == 2) {
+                // three of the four 32-query blocks in registers: the columns are released after the first is staged
+                uint32_t v0[32], v1[32], v2[32];
+                tmem_ld32(rd, v0);
+                tmem_ld32(rd + 32, v1);
+                tmem_ld32(rd + 64, v2);
+                tmem_wait_ld();
+                stage(0, v0, acc);
+                tmem_ld32(rd + 96, v0);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(sh.bar(B_DQE));   // the rest of the tile is in registers: the columns are free for dP^T of the next tile
+                stage(1, v1, acc + 32 * HD);
+                stage(0, v2, acc + 64 * HD);
+                stage(1, v0, acc + 96 * HD);
+            } else {
+                // 22 warps leave a thread 88 registers: two blocks in registers at a time
+                uint32_t v0[32], v1[32];
+                tmem_ld32(rd, v0);
+                tmem_ld32(rd + 32, v1);
+                tmem_wait_ld();
+                stage(0, v0, acc);
+                tmem_ld32(rd + 64, v0);
+                tmem_wait_ld();
+                stage(1, v1, acc + 32 * HD);
+                tmem_ld32(rd + 96, v1);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(sh.bar(B_DQE));
+                stage(0, v0, acc + 64 * HD);
+                stage(1, v1, acc + 96 * HD);
+            }
+#ifdef FOLD_BWD_COUNTERS
+            c_wq += t_b - t_a;
+            c_busy += clock64() - t_b;
+#endif
         }
         // the engine must be done with shared memory, and the adds complete, before the CTA goes
         if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+#ifdef FOLD_BWD_COUNTERS
+        if (leader) {
+            CNT_ADD(10, c_wq);
+            CNT_ADD(11, c_busy);
+        }
+#endif
     }
 
     // ================= epilogue: dK, dV out of TMEM =================
     __syncthreads();
-    if (warp >= 2 && warp < 10) {
+    CNT_T(epi_t0);
+    if (warp >= 2 && warp < W_DRAIN) {
         if (total > 0) mbar_wait(sh.bar(B_DONE), 0, abort_flag, p.status);   // every MMA has retired
         tc_fence_after();
+        // the first half of the compute warpgroups takes dK, the second dV; with four, each takes
+        // 64 of the 128 channels
+        const int wg = (warp - 2) >> 2;
+        constexpr int PARTS = NWG / 2, CW = HD / PARTS;   // channels per warpgroup
+        const bool is_dv = wg >= PARTS;
+        const int c0 = (wg % PARTS) * CW;
         const int r = 32 * (warp & 3) + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
-        const bool is_dv = warp >= 6;
         auto pk2 = [](float a, float b2) { return F16 ? pack_f16x2(a, b2) : pack_bf16x2(a, b2); };
         const float un = F16 ? 1.f : pow2f(-s_exp);
         const float f = is_dv ? un : p.scale * un;
-        const uint32_t src = tmem + lane_addr + (is_dv ? T_DV : T_DK);
+        const uint32_t src = tmem + lane_addr + (is_dv ? T_DV : T_DK) + c0;
         const bool ok = n0 + r < sq.len;
-        uint16_t* dst = row_ptr<uint16_t>(is_dv ? p.dv : p.dk, b, sq.start + n0 + (ok ? r : 0), hkv);
+        uint16_t* dst = row_ptr<uint16_t>(is_dv ? p.dv : p.dk, b, sq.start + n0 + (ok ? r : 0), hkv) + c0;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < CW / 32; ++c) {
             uint32_t v[32];
             tmem_ld32(src + 32 * c, v);
             tmem_wait_ld();
@@ -601,6 +799,13 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
     }
+#ifdef FOLD_BWD_COUNTERS
+    if (tid == 0) {
+        const long long t_end = clock64();
+        CNT_ADD(2, t_end - cta_t0);
+        CNT_ADD(4, t_end - epi_t0);
+    }
+#endif
 }
 
 }  // namespace sm100
@@ -672,3 +877,22 @@ int launch_bwd_main_sm100(const BwdParams& p, cudaStream_t st) {
 }
 
 }  // namespace fold
+
+extern "C" int fold_bwd_counters(uint64_t* out16, int reset) {
+#ifdef FOLD_BWD_COUNTERS
+    FOLD_CHECK_ARG(out16, "fold_bwd_counters: null pointer");
+    unsigned long long h[16];
+    if (cudaMemcpyFromSymbol(h, fold::sm100::g_counters, sizeof(h)) != cudaSuccess) return fold::check_launch("fold_bwd_counters");
+    for (int i = 0; i < 16; ++i) out16[i] = h[i];
+    if (reset) {
+        memset(h, 0, sizeof(h));
+        if (cudaMemcpyToSymbol(fold::sm100::g_counters, h, sizeof(h)) != cudaSuccess) return fold::check_launch("fold_bwd_counters");
+    }
+    return FOLD_OK;
+#else
+    (void)out16;
+    (void)reset;
+    fold::set_error("fold_bwd_counters: the library was built without -DFOLD_BWD_COUNTERS");
+    return FOLD_ERR_UNSUPPORTED;
+#endif
+}

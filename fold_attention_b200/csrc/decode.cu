@@ -43,6 +43,7 @@ struct DecodeParams {
     int nbh, G, hkv, ppr, page_size, split, chunk_keys, truncate, banded;
     float rk, rv, band_e0, band_e1, rk1, rk2, rv1, rv2;
     int* status;
+    int bh_limit;   // > 0: the partial buffers hold this many row groups; an `order` entry outside is refused
 };
 
 // ---- small PTX wrappers -----------------------------------------------------
@@ -131,6 +132,10 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tq = lane & 3;
     const int slot = blockIdx.x / p.split, sp = blockIdx.x % p.split;
     const int bh = p.order ? p.order[slot] : slot;
+    if (p.bh_limit > 0 && (bh < 0 || bh >= p.bh_limit)) {   // would index past the partial buffers: touch nothing
+        if (tid == 0) atomicExch(p.status, FOLD_ERR_ARGUMENT);
+        return;
+    }
     const int breq = bh / p.hkv, hkv = bh % p.hkv;
     const int slen = p.seq_lens[breq];
     const int G = p.G, PS = p.page_size;
@@ -715,17 +720,17 @@ extern "C" int fold_mass_z(const int8_t* qa, const int8_t* qb, const float* eq, 
     return check_launch("fold_mass_z");
 }
 
-extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
-                               const int8_t* kb, const void* ek, const void* va, const void* vb,
-                               const float* vmean, const float* z, const float* cut,
-                               const int32_t* page_table, const int32_t* seq_lens,
-                               const int32_t* order, int n_groups, int group, int n_kv_heads,
-                               int head_dim, int pages_per_request, int page_size, int split,
-                               int chunk_keys, int truncate, int weight_terms, float refine_k,
-                               float refine_v, const float* refine_bands, float v_scale,
-                               float* o_part, float* den_part, int32_t* cnt_part, void* out,
-                               int out_dtype, float* den, int32_t* counts, int32_t* status,
-                               void* stream) {
+static int decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                      const int8_t* kb, const void* ek, const void* va, const void* vb,
+                      const float* vmean, const float* z, const float* cut,
+                      const int32_t* page_table, const int32_t* seq_lens,
+                      const int32_t* order, int n_groups, int group, int n_kv_heads,
+                      int head_dim, int pages_per_request, int page_size, int split,
+                      int chunk_keys, int truncate, int weight_terms, float refine_k,
+                      float refine_v, const float* refine_bands, float v_scale,
+                      float* o_part, float* den_part, int32_t* cnt_part, void* out,
+                      int out_dtype, float* den, int32_t* counts, int32_t* status,
+                      int bh_limit, void* stream) {
     FOLD_CHECK_ARG(qa && qb && eq && ka && kb && ek && va && z && cut && page_table && seq_lens &&
                        o_part && den_part && cnt_part && status && (!out || (den && counts)),
                    "fold_decode_run: null pointer");
@@ -755,6 +760,7 @@ extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* 
         p.band_e0 = p.band_e1 = p.rk1 = p.rk2 = p.rv1 = p.rv2 = 0.f;
     }
     p.status = status;
+    p.bh_limit = bh_limit;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool v8 = vb != nullptr;
     int rc;
@@ -769,6 +775,23 @@ extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* 
     else FOLD_COMBINE(2);
 #undef FOLD_COMBINE
     return check_launch("fold_decode_combine");
+}
+
+extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                               const int8_t* kb, const void* ek, const void* va, const void* vb,
+                               const float* vmean, const float* z, const float* cut,
+                               const int32_t* page_table, const int32_t* seq_lens,
+                               const int32_t* order, int n_groups, int group, int n_kv_heads,
+                               int head_dim, int pages_per_request, int page_size, int split,
+                               int chunk_keys, int truncate, int weight_terms, float refine_k,
+                               float refine_v, const float* refine_bands, float v_scale,
+                               float* o_part, float* den_part, int32_t* cnt_part, void* out,
+                               int out_dtype, float* den, int32_t* counts, int32_t* status,
+                               void* stream) {
+    return decode_run(qa, qb, eq, ka, kb, ek, va, vb, vmean, z, cut, page_table, seq_lens, order, n_groups,
+                      group, n_kv_heads, head_dim, pages_per_request, page_size, split, chunk_keys, truncate,
+                      weight_terms, refine_k, refine_v, refine_bands, v_scale, o_part, den_part, cnt_part, out,
+                      out_dtype, den, counts, status, /*bh_limit=*/0, stream);
 }
 
 // The combine alone, for decode kernels that fill the same partial buffers.
@@ -843,6 +866,9 @@ extern "C" int fold_decode_run_static(const int8_t* qa, const int8_t* qb, const 
                                       void* out, int out_dtype, float* den, int32_t* counts,
                                       int32_t* status, void* stream) {
     FOLD_CHECK_ARG(n_groups >= 1 && group >= 1 && split >= 1 && head_dim >= 1, "fold_decode_run_static: empty call");
+    // the partials stay inside the library, where the caller cannot combine them later
+    FOLD_CHECK_ARG(out && den && counts, "fold_decode_run_static: out, den and counts must be given (the partials "
+                                         "live in the library's own array: there is no uncombined form of this call)");
     const size_t need = fold_decode_static_scratch_needed(n_groups, group, head_dim, split);
     FOLD_CHECK_ARG(need <= FOLD_DECODE_STATIC_SCRATCH_BYTES,
                    "fold_decode_run_static: %d row groups x %d splits need %zu bytes of partials, the built-in "
@@ -860,8 +886,12 @@ extern "C" int fold_decode_run_static(const int8_t* qa, const int8_t* qb, const 
     // Nothing in the partials has to start at zero: every split a request
     // reaches writes its whole slot before the combine, launched behind it on
     // the same stream, reads exactly those slots.
-    return fold_decode_run(qa, qb, eq, ka, kb, ek, va, vb, vmean, z, cut, page_table, seq_lens, order,
-                           n_groups, group, n_kv_heads, head_dim, pages_per_request, page_size, split,
-                           chunk_keys, truncate, weight_terms, refine_k, refine_v, refine_bands, v_scale,
-                           o_part, den_part, cnt_part, out, out_dtype, den, counts, status, stream);
+    // The array is laid out for n_groups row groups, so `order` (if given) must map the n_groups
+    // slots onto row groups 0 .. n_groups-1. The host cannot read a device-side order without a
+    // synchronisation; the kernel checks each entry instead, and a CTA handed a row group outside
+    // the array raises `status` to FOLD_ERR_ARGUMENT and returns without touching memory.
+    return decode_run(qa, qb, eq, ka, kb, ek, va, vb, vmean, z, cut, page_table, seq_lens, order,
+                      n_groups, group, n_kv_heads, head_dim, pages_per_request, page_size, split,
+                      chunk_keys, truncate, weight_terms, refine_k, refine_v, refine_bands, v_scale,
+                      o_part, den_part, cnt_part, out, out_dtype, den, counts, status, /*bh_limit=*/n_groups, stream);
 }

@@ -6,8 +6,11 @@ amount of memory, a process whose device allocator belongs to another runtime).
 partials live in a fixed 4 MiB array inside libfold_b200 instead of in torch
 buffers, so the call itself allocates nothing: the caller passes the inputs
 and the outputs `out`, `den`, `counts`, `status`. Calls on one device share
-that array, so they must be stream-ordered; a call too large for it raises
-ValueError. The first call on a device resolves the array's address and
+that array, so they must be stream-ordered (calls on two streams or from two
+threads race on it); a call too large for it raises ValueError. `order`, if
+given, must be a permutation of all the call's row groups: the array has room
+for those and no others, and a slot that points elsewhere sets `status` to 1
+on the device instead of writing. The first call on a device resolves the array's address and
 should come before any stream capture starts.
 """
 

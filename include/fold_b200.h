@@ -148,12 +148,19 @@ int fold_decode_combine(const float* o_part, const float* den_part, const int32_
  * exit). The call allocates nothing: no cudaMalloc, cudaFree or allocating
  * library routine. A call whose partials would not fit (see
  * fold_decode_static_scratch_needed) is rejected with FOLD_ERR_ARGUMENT.
+ * Two differences from fold_decode_run, both because the array is laid out for
+ * exactly n_groups row groups and is out of the caller's reach: `out`, `den`
+ * and `counts` must be given (there is no partials-only form), and `order`
+ * must be NULL or a permutation of 0 .. n_groups-1 (no subset calls). The
+ * order lives on the device, so the kernel checks it: a slot mapped outside
+ * 0 .. n_groups-1 touches no memory and sets *status to FOLD_ERR_ARGUMENT.
  * The first call on each device looks the array's address up (with that
  * device current); make that first call before starting any stream capture.
  * Every call on a device shares the one array and leaves the last call's
- * partials in it: two calls that overlap on the GPU (different streams,
- * threads or processes' contexts excepted) race on it, so keep calls on one
- * device stream-ordered. Nothing in it needs clearing between calls. */
+ * partials in it, so two calls that overlap on the GPU race on it -- calls on
+ * different streams or from different host threads included. Keep every call
+ * on a device on one stream, or order them with events. (Another process has
+ * its own copy of the array.) Nothing in it needs clearing between calls. */
 #define FOLD_DECODE_STATIC_SCRATCH_BYTES (4u << 20)
 size_t fold_decode_static_scratch_needed(int n_groups, int group, int head_dim, int split);
 int fold_decode_run_static(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
@@ -216,6 +223,14 @@ int fold_bwd_run_phases(const void* q, const void* k, const void* v, const void*
                         int n_heads, int n_kv_heads, int max_seqlen, int total, int head_dim,
                         int causal, int is_f16, float softmax_scale, void* workspace,
                         size_t workspace_bytes, int kernel, int phases, void* stream);
+
+/* Cycle counters of the tcgen05 backward's main loop, summed over the launches since the
+ * last reset: out16 (host, 16 entries) receives CTAs, tiles, CTA lifetime, prologue, epilogue,
+ * the compute warps' wait for S^T / exponential phase / wait for dP^T / dS~ phase, the MMA
+ * thread's cycles with nothing to issue, the drain's wait and busy cycles (then zeros).
+ * Synchronises the device. Returns FOLD_ERR_UNSUPPORTED unless the library was built with
+ * -DFOLD_BWD_COUNTERS (the product build is not). No counterpart in the reference. */
+int fold_bwd_counters(uint64_t* out16 /* host */, int reset);
 
 /* Attention forward: O and the log-sum-exp (nats) the backward consumes.
  * Replaces the third-party forward called at src/fold_attention/interface.py:42-44,

@@ -70,3 +70,81 @@ def test_a_call_too_large_for_the_array_is_refused():
                       split=split, truncate=True, refine_k=10.0, refine_v=10.0, v2=c.vb, v_scale=c.v_scale,
                       vmean=c.vmean, page_table=c.page_table, page_size=c.page_size, seq_lens=c.seq_lens,
                       n_kv_heads=c.n_kv_heads, weight_terms=2)
+
+
+def _outputs(NBH, G, D):
+    out = torch.full((NBH, G, D), float("nan"), device="cuda")
+    den = torch.full((NBH, G), float("nan"), device="cuda")
+    counts = torch.full((NBH, 2), -1, device="cuda", dtype=torch.int32)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    return out, den, counts, status
+
+
+def test_a_permuted_order_gives_the_allocating_entry_points_bits():
+    """`order` maps grid slots to row groups (longest first, say). The built-in array is laid out
+    for exactly the call's row groups, so a permutation of all of them is what this entry takes."""
+    from fold_attention_b200.decode.launch import prepare_fold_decode
+    from fold_attention_b200.decode.static_scratch import decode_static
+
+    c, lens = _case(True, 16.0, seed=19)
+    NBH, G, D = c.qa.shape
+    g = torch.Generator(device="cuda").manual_seed(3)
+    order = torch.randperm(NBH, device="cuda", generator=g).int()
+    kw = dict(split=3, truncate=True, refine_k=10.0, refine_v=10.0, v2=c.vb, v_scale=c.v_scale, vmean=c.vmean,
+              page_table=c.page_table, page_size=c.page_size, seq_lens=c.seq_lens, n_kv_heads=c.n_kv_heads,
+              weight_terms=2, order=order)
+    want = [x.clone() for x in prepare_fold_decode(
+        c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, c.z, c.cut, v8=True, **kw)()]
+    for _ in range(2):
+        out, den, counts, status = _outputs(NBH, G, D)
+        decode_static(c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, c.z, c.cut, out, den, counts, status, **kw)
+        torch.cuda.synchronize()
+        assert int(status) == 0
+        assert torch.equal(out, want[0]) and torch.equal(den, want[1]) and torch.equal(counts, want[2])
+
+
+def test_an_order_that_leaves_the_array_is_refused_on_the_device():
+    """A slot mapped to a row group the array has no room for must not write anywhere: the CTA
+    raises the status word (FOLD_ERR_ARGUMENT = 1) and returns; the call itself returns normally."""
+    from fold_attention_b200.decode.static_scratch import decode_static
+
+    c, lens = _case(True, 16.0, seed=20)
+    NBH, G, D = c.qa.shape
+    order = torch.arange(NBH, device="cuda", dtype=torch.int32)
+    order[1] = NBH + 5
+    out, den, counts, status = _outputs(NBH, G, D)
+    decode_static(c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, c.z, c.cut, out, den, counts, status,
+                  split=3, truncate=True, refine_k=10.0, refine_v=10.0, v2=c.vb, v_scale=c.v_scale, vmean=c.vmean,
+                  page_table=c.page_table, page_size=c.page_size, seq_lens=c.seq_lens, n_kv_heads=c.n_kv_heads,
+                  weight_terms=2, order=order)
+    torch.cuda.synchronize()
+    assert int(status) == 1
+    # the next, well-formed call is unaffected
+    out, den, counts, status = _outputs(NBH, G, D)
+    decode_static(c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, c.z, c.cut, out, den, counts, status,
+                  split=3, truncate=True, refine_k=10.0, refine_v=10.0, v2=c.vb, v_scale=c.v_scale, vmean=c.vmean,
+                  page_table=c.page_table, page_size=c.page_size, seq_lens=c.seq_lens, n_kv_heads=c.n_kv_heads,
+                  weight_terms=2)
+    torch.cuda.synchronize()
+    assert int(status) == 0 and bool(torch.isfinite(out).all())
+
+
+def test_a_call_without_outputs_is_refused():
+    """The partials never leave the library, so a call that asks for partials only (out NULL, which
+    the allocating entry point allows) is an argument error here."""
+    import ctypes
+
+    from fold_attention_b200 import _lib
+    from fold_attention_b200.decode import static_scratch  # noqa: F401  (registers the signature)
+
+    c, lens = _case(False, None, seed=21)
+    NBH, G, D = c.qa.shape
+    _, den, counts, status = _outputs(NBH, G, D)
+    rc = _lib.lib.fold_decode_run_static(
+        c.qa.data_ptr(), c.qb.data_ptr(), c.eq.data_ptr(), c.ka.data_ptr(), c.kb.data_ptr(), c.ek.data_ptr(),
+        c.va.data_ptr(), None, None, c.z.data_ptr(), c.cut.data_ptr(), c.page_table.data_ptr(),
+        c.seq_lens.data_ptr(), None, NBH, G, c.n_kv_heads, D, c.page_table.shape[1], c.page_size, 2, 0, 0, 2,
+        ctypes.c_float(10.0), ctypes.c_float(10.0), None, ctypes.c_float(1.0), None, 0, den.data_ptr(),
+        counts.data_ptr(), status.data_ptr(), _lib.stream(c.qa.device))
+    assert rc == 1
+    assert b"out, den and counts must be given" in _lib.lib.fold_last_error()
