@@ -17,7 +17,7 @@ from dataclasses import dataclass
 import torch
 
 from .. import _lib
-from ..utils import Launch
+from ..utils import Launch, check_status
 from .plan import Plan, plan_dense, plan_varlen
 
 P, I, F, Z = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
@@ -32,6 +32,7 @@ _lib.register(
     [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, I, P],
 )
 _lib.register("fold_bwd_counters", [P, I])
+_lib.register("fold_wait_probe", [ctypes.c_longlong, P, P, P])
 _lib.register("fold_fwd_run", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
 _lib.register("fold_fwd_sm100_supported", [I, I])
 _lib.register("fold_fwd_run_sm100", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P])
@@ -193,6 +194,8 @@ def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, m
             int(bool(causal)), int(q.dtype == torch.float16), sm, status.data_ptr(), _lib.stream(q.device),
         )
         attention_forward.last_status = status   # non-zero after a device-side wait ran out
+        if attention_forward.check_status:
+            check_status(status, "attention_forward")
         return o, lse
     _lib.call(
         "fold_fwd_run", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
@@ -200,3 +203,9 @@ def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, m
         int(bool(causal)), int(q.dtype == torch.float16), sm, _lib.stream(q.device),
     )
     return o, lse
+
+
+# The tcgen05 forward's status word of the last call; with `check_status` set every call reads
+# it back (one host synchronisation per call) and raises FoldLibraryError when it is raised.
+attention_forward.last_status = None
+attention_forward.check_status = False

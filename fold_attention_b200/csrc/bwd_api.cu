@@ -100,6 +100,7 @@ static int bwd_run_phases(const void* q, const void* k, const void* v, const voi
     } else {
         FOLD_CHECK_ARG(kernel == FOLD_BWD_KERNEL_MMA, "fold_bwd_run: unknown kernel %d", kernel);
     }
+    p.dq_bias = (sm100 && bwd_sm100_biased()) ? 1 : 0;
     int rc = FOLD_OK;
     if (phases & FOLD_BWD_PHASE_PRE) rc = launch_bwd_preprocess(p, st);
     if (rc) return rc;

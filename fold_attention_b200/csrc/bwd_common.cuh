@@ -31,6 +31,7 @@ struct BwdParams {
     int* stats;     // [B][HKV][N_STATS] float bits of the order-free maxima
     int* status;    // one word after the stats: raised if a device-side wait ran out
     int64_t rows_p; // padded rows per head
+    int dq_bias;    // the main loop adds 0x4B400000 with every partial: the accumulator starts at minus their sum
     int S_r;        // dense: S rounded up to ROW_PAD
 };
 
@@ -71,6 +72,7 @@ int launch_bwd_postprocess(const BwdParams& p, int layout, cudaStream_t st);
 int launch_bwd_main_mma(const BwdParams& p, cudaStream_t st);
 int launch_bwd_main_sm100(const BwdParams& p, cudaStream_t st);
 bool bwd_sm100_supported(const BwdParams& p);
+bool bwd_sm100_biased();   // whether the tcgen05 main loop leaves its rounding constant in the partials
 
 // dq accumulator tile layouts
 enum { DQ_LAYOUT_ROW_MAJOR = 0, DQ_LAYOUT_SM100 = 1 };

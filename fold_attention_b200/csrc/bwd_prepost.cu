@@ -91,8 +91,16 @@ __global__ void __launch_bounds__(PRE_THREADS) bwd_preprocess_kernel(const BwdPa
                 p.dpsum[wbase + i] = delta;
                 p.lse2[wbase + i] = lse2;
             }
+            // Zero, or, when the main loop's partials each carry its rounding constant's bits, minus
+            // their sum over the key blocks that reach this row's tile (int32 wraps: the total is exact)
+            int init = 0;
+            if (p.dq_bias) {
+                const int tile = i / ROW_PAD, nkb = (sq.len + ROW_PAD - 1) / ROW_PAD;
+                const unsigned n_part = static_cast<unsigned>(p.causal ? min(tile + 1, nkb) : nkb);
+                init = static_cast<int>(0u - n_part * 0x4B400000u);
+            }
             int4* acc = reinterpret_cast<int4*>(p.dq_acc + (wbase + i) * D);
-            for (int c = lane; c < D / 4; c += 32) acc[c] = make_int4(0, 0, 0, 0);
+            for (int c = lane; c < D / 4; c += 32) acc[c] = make_int4(init, init, init, init);
         }
     }
     __shared__ float s_red[4][PRE_THREADS / 32];

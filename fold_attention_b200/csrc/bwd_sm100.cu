@@ -71,6 +71,19 @@ constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 #ifndef FOLD_SLEEP_ISSUER
 #define FOLD_SLEEP_ISSUER 0
 #endif
+// 1: dQ~ leaves the GEMM with queries on the TMEM lanes (dQ~ = dS~ K instead of its transpose), so a
+// drain thread holds 32 consecutive channels of one query: it stages them with eight 16-byte
+// stores into a 128-byte-swizzled block and the block is added to the accumulator by a tiled TMA
+// reduction. 0: channels on the lanes, 4-byte stores into a row-major block, untiled bulk reduction.
+#ifndef FOLD_BWD_DRAIN_T
+#define FOLD_BWD_DRAIN_T 1
+#endif
+// 1: the drain adds its rounding constant's bits to the accumulator along with the value and the
+// preprocess starts the accumulator at minus their sum (int32 wraps, so the total is exact):
+// one integer subtract per element less
+#ifndef FOLD_BWD_BIAS
+#define FOLD_BWD_BIAS 0
+#endif
 // 1: the MMA thread polls the heads of its two chains (S -> dV and dP -> dQ, dK) and issues
 // whichever is ready, instead of one fixed order that lets a late drain hold back dV and S
 #ifndef FOLD_BWD_DYN_ISSUE
@@ -143,7 +156,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // Bounded wait. `abort` (shared) is raised by whoever runs out first; once it
 // is up nobody waits any more, so every role runs to its end.
 template <int SLEEP_NS = 0>
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          long long limit = WAIT_CYCLES) {
     if (mbar_try(bar, parity)) return;
     if (*abort_flag) return;
     const long long t0 = clock64();
@@ -152,7 +166,7 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);   // a waiting warp group must not take the issue slots of a working one
         if ((i & 63) == 63) {
             if (*abort_flag) return;
-            if (clock64() - t0 > WAIT_CYCLES) break;
+            if (clock64() - t0 > limit) break;
         }
     }
     *abort_flag = 1;
@@ -264,20 +278,47 @@ __host__ __device__ constexpr uint32_t instr_desc(int fmt, int M, int N, int a_m
 
 struct Maps {
     CUtensorMap q, dout, k, v;   // (channel, row, head, batch), boxes (64, 128, 1, 1)
+    CUtensorMap dq;              // the int32 accumulator as (channel, head * padded row), boxes (32, 128)
 };
+
+// The bounded wait by itself: one warp waits on a barrier nobody will arrive at, for `limit`
+// cycles, through the same mbar_wait the main loop's roles use. The wait runs out, raises the
+// status word and the abort flag, and the kernel returns normally: what a host-side check of
+// the status word has to see, without a fault and without touching TMEM or the tensor pipe.
+__global__ void __launch_bounds__(32) wait_probe_kernel(long long limit, int* status, int* flag_out) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    const uint32_t b = static_cast<uint32_t>(__cvta_generic_to_shared(&bar));
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(b, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) mbar_wait<SLEEP_WORKER>(b, 0, &abort_flag, status, limit);
+    __syncwarp();
+    // every other role sees the flag and stops waiting at once
+    if (threadIdx.x == 1) mbar_wait<SLEEP_WORKER>(b, 0, &abort_flag, status, 1ll << 40);
+    __syncwarp();
+    if (threadIdx.x == 0 && flag_out) *flag_out = abort_flag;
+}
 
 // ---- optional cycle counters (-DFOLD_BWD_COUNTERS): where each role's time goes -----------
 // Sums over every CTA of a launch, taken by one thread per role: slots are
 //  0 CTAs, 1 tiles, 2 CTA lifetime, 3 prologue (until K and V have landed), 4 epilogue,
 //  5 compute: wait for S^T, 6 exponential phase, 7 wait for dP^T, 8 dS~ phase,
-//  9 MMA thread: cycles with nothing ready to issue, 10 drain: wait for dQ~^T, 11 drain busy.
+//  9 MMA thread: cycles with nothing ready to issue, 10 drain: wait for dQ~^T, 11 drain busy,
+// 12 drain: from dQ~^T ready to its columns released; the MMA thread's waits in the fixed issue
+// order: 13 for P~, 14 for Q, 15 for dS~, 16 for dO, 17 for the drain's release.
 #ifdef FOLD_BWD_COUNTERS
-__device__ unsigned long long g_counters[16];
+__device__ unsigned long long g_counters[24];
 #define CNT_ADD(slot, v) atomicAdd(&g_counters[slot], static_cast<unsigned long long>(v))
 #define CNT_T(var) const long long var = clock64()
+#define CNT_WAIT(acc, ...) do { const long long _t = clock64(); mbar_wait<SLEEP_ISSUER>(__VA_ARGS__); acc += clock64() - _t; } while (0)
 #else
 #define CNT_ADD(slot, v) do { } while (0)
 #define CNT_T(var) do { } while (0)
+#define CNT_WAIT(acc, ...) mbar_wait<SLEEP_ISSUER>(__VA_ARGS__)
 #endif
 
 template <bool F16>
@@ -393,6 +434,8 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             CNT_ADD(3, clock64() - pro_t0);
             long long idle_clk = 0;
 #endif
+            long long w_p = 0, w_q = 0, w_ds = 0, w_o = 0, w_dqe = 0;
+            (void)w_p; (void)w_q; (void)w_ds; (void)w_o; (void)w_dqe;
             // The five GEMMs of tile i, each eight K=16 steps, none of them waiting for anything:
             // the barriers they depend on are taken by the issue loops below.
             auto issue_s = [&](int i) {   // S^T = K Q^T -> T_S
@@ -419,10 +462,16 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             auto issue_dq_dk = [&](int i) {
                 const int s = i % STAGES;
                 const uint64_t q_mn0 = smem_desc(base + SM_Q + s * 32768, 16384, 1024);
-                // dQ~^T = K^T dS~^T : 8 steps of 16 keys
+                // 8 steps of 16 keys, both operands MN-major: dQ~ = dS~ K (queries on the lanes) or
+                // dQ~^T = K^T dS~^T (channels on the lanes); the same two shared tiles either way
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
+                for (int ks = 0; ks < 8; ++ks) {
+#if FOLD_BWD_DRAIN_T
+                    mma_ss(tmem + T_DP, ds_mn0 + ((ks * 2048) >> 4), dk_mn[ks], ID_MM, ks > 0);
+#else
                     mma_ss(tmem + T_DP, dk_mn[ks], ds_mn0 + ((ks * 2048) >> 4), ID_MM, ks > 0);
+#endif
+                }
                 tc_commit(sh.bar(B_DQF));
                 // dK += dS~^T Q : 8 steps of 16 queries
 #pragma unroll
@@ -492,20 +541,20 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 issue_dp(0);
             }
             for (int i = 0; i < total; ++i) {
-                mbar_wait<SLEEP_ISSUER>(sh.bar(B_P), i & 1, abort_flag, p.status);
+                CNT_WAIT(w_p, sh.bar(B_P), i & 1, abort_flag, p.status);
                 tc_fence_after();
                 issue_dv(i);
                 if (i + 1 < total) {   // over P~(i), behind dV(i)
-                    mbar_wait<SLEEP_ISSUER>(sh.bar(B_QFULL + (i + 1) % STAGES), ((i + 1) / STAGES) & 1, abort_flag, p.status);
+                    CNT_WAIT(w_q, sh.bar(B_QFULL + (i + 1) % STAGES), ((i + 1) / STAGES) & 1, abort_flag, p.status);
                     tc_fence_after();
                     issue_s(i + 1);
                 }
-                mbar_wait<SLEEP_ISSUER>(sh.bar(B_DS), i & 1, abort_flag, p.status);
+                CNT_WAIT(w_ds, sh.bar(B_DS), i & 1, abort_flag, p.status);
                 tc_fence_after();
                 issue_dq_dk(i);
                 if (i + 1 < total) {
-                    mbar_wait<SLEEP_ISSUER>(sh.bar(B_OFULL), (i + 1) & 1, abort_flag, p.status);
-                    mbar_wait<SLEEP_ISSUER>(sh.bar(B_DQE), i & 1, abort_flag, p.status);   // dQ~(i) has left the columns
+                    CNT_WAIT(w_o, sh.bar(B_OFULL), (i + 1) & 1, abort_flag, p.status);
+                    CNT_WAIT(w_dqe, sh.bar(B_DQE), i & 1, abort_flag, p.status);   // dQ~(i) has left the columns
                     tc_fence_after();
                     issue_dp(i + 1);
                 }
@@ -516,6 +565,11 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             CNT_ADD(0, 1);
             CNT_ADD(1, total);
             CNT_ADD(9, idle_clk);
+            CNT_ADD(13, w_p);
+            CNT_ADD(14, w_q);
+            CNT_ADD(15, w_ds);
+            CNT_ADD(16, w_o);
+            CNT_ADD(17, w_dqe);
 #endif
         }
     } else if (warp < W_DRAIN) {
@@ -637,50 +691,84 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         }
 #endif
     } else {
-        // ================= dQ drain: TMEM -> int32 grid -> shared -> bulk add into the accumulator =================
-        // The tile's int32 values are staged 32 queries (16 KB) at a time in one of two shared
-        // buffers, in the accumulator's own row-major order, and one thread hands each block to the
-        // TMA engine as a reduction (integer add, so the order of arrival does not matter). The
-        // same bytes as 128 `red` instructions per thread, without their place in the instruction
-        // queue the compute warps' ex2 and shared loads go through.
-        const int d = 32 * (warp & 3) + lane;   // channel = TMEM lane
+        // ================= dQ drain: TMEM -> int32 grid -> shared -> TMA add into the accumulator =================
+        // The tile's int32 values are staged 16 KB at a time in one of two shared buffers and one
+        // thread hands each block to the TMA engine as a reduction (integer add, so the order of
+        // arrival does not matter): the same bytes as 128 `red` instructions per thread, without
+        // their place in the instruction queue the compute warps' ex2 and shared loads go through.
+        // The next tile's dP^T cannot be issued until this tile's dQ~ has left its columns, so the
+        // time from B_DQF to B_DQE is on the kernel's critical path: blocks are converted with
+        // short dependency chains and stored with as few instructions as the layout allows.
+        const int ln = 32 * (warp & 3) + lane;   // TMEM lane: a query (FOLD_BWD_DRAIN_T) or a channel
         const float dq_mul = F16 ? pow2f(s_exp) : 1.f;
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const uint32_t rd = tmem + lane_addr + T_DP;
-        const bool leader = (warp == W_DRAIN && lane == 0);   // issues every bulk reduction: they form its groups
-        const uint32_t stg = base + SM_STG + 4 * d;
-        auto stage = [&](int buf, uint32_t (&v)[32], int* gdst) {
-            // Float -> int32, round to nearest even. Adding 1.5 * 2^23 rounds a float below 2^22 to an
-            // integer in its low mantissa bits: one add and one subtract per element when every
-            // element of the warp's chunk is in that range (the usual case: the grid leaves 2^30 to
-            // a row's whole sum), which keeps the conversion off the pipe the softmax's ex2 runs on.
+        const bool leader = (warp == W_DRAIN && lane == 0);   // issues every reduction: they form its groups
+        // Float -> int32, round to nearest even. Adding 1.5 * 2^23 rounds a float below 2^22 to an
+        // integer in its low mantissa bits: one add and one subtract per element when every
+        // element of the warp's block is in that range (the usual case: the grid leaves 2^30 to
+        // a row's whole sum), which keeps the conversion off the pipe the softmax's ex2 runs on.
+        // With FOLD_BWD_BIAS the subtract is left to the accumulator's starting value.
+        auto to_grid = [&](uint32_t (&v)[32]) {
             constexpr float M = 12582912.f;   // 1.5 * 2^23, bits 0x4B400000
-            float mx = 0.f;
+            constexpr uint32_t MB = 0x4B400000u, KEEP = FOLD_BWD_BIAS ? MB : 0u;
+            float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;   // four short chains, not one of 32
 #pragma unroll
-            for (int q = 0; q < 32; ++q) {
-                if (F16) v[q] = __float_as_uint(__uint_as_float(v[q]) * dq_mul);
-                mx = fmaxf(mx, fabsf(__uint_as_float(v[q])));
+            for (int q = 0; q < 32; q += 4) {
+                if (F16) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) v[q + u] = __float_as_uint(__uint_as_float(v[q + u]) * dq_mul);
+                }
+                m0 = fmaxf(m0, fabsf(__uint_as_float(v[q])));
+                m1 = fmaxf(m1, fabsf(__uint_as_float(v[q + 1])));
+                m2 = fmaxf(m2, fabsf(__uint_as_float(v[q + 2])));
+                m3 = fmaxf(m3, fabsf(__uint_as_float(v[q + 3])));
             }
+            const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
             if (!__any_sync(0xffffffffu, !(mx < 4194304.f))) {
-#if FOLD_DRAIN_PACKED
 #pragma unroll
                 for (int q = 0; q < 32; q += 2) {
                     uint64_t t;
                     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(t) : "l"(pack2(__uint_as_float(v[q]), __uint_as_float(v[q + 1]))), "l"(pack2(M, M)));
                     uint32_t lo, hi;
                     asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(t));
-                    v[q] = lo - 0x4B400000u;
-                    v[q + 1] = hi - 0x4B400000u;
+                    v[q] = lo - (MB - KEEP);
+                    v[q + 1] = hi - (MB - KEEP);
                 }
-#else
-#pragma unroll
-                for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(__uint_as_float(v[q]) + M) - 0x4B400000u;
-#endif
             } else {   // rare, and kept small: the conversion instruction (same rounding; it shares a pipe with ex2)
 #pragma unroll
-                for (int q = 0; q < 32; ++q) v[q] = static_cast<uint32_t>(__float2int_rn(__uint_as_float(v[q])));
+                for (int q = 0; q < 32; ++q) v[q] = static_cast<uint32_t>(__float2int_rn(__uint_as_float(v[q]))) + KEEP;
             }
+        };
+#if FOLD_BWD_DRAIN_T
+        // block c of a tile: channels 32c .. 32c+31 of all 128 queries, [query][32 ch] int32, 128 bytes
+        // per query with its 16-byte units XOR-swizzled by the query (SWIZZLE_128B, what the tensor
+        // map expects): a quarter warp's eight stores of one unit fall in eight different bank groups
+        const uint32_t stg = base + SM_STG + ln * 128;
+        const uint32_t sw = static_cast<uint32_t>(ln & 7);
+        auto stage = [&](int buf, uint32_t (&v)[32], int c, int row0) {
+            to_grid(v);
             // the buffer's last block (two blocks ago) must have been read out
+            if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const uint32_t dst = stg + buf * 16384;
+#pragma unroll
+            for (uint32_t u = 0; u < 8; ++u)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + ((u ^ sw) << 4)), "r"(v[4 * u]), "r"(v[4 * u + 1]),
+                             "r"(v[4 * u + 2]), "r"(v[4 * u + 3]) : "memory");
+            fence_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (leader) {
+                asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                             ::"l"(&maps.dq), "r"(32 * c), "r"(row0), "r"(base + SM_STG + buf * 16384) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        };
+#else
+        // block c of a tile: queries 32c .. 32c+31, all 128 channels, in the accumulator's own row-major order
+        const uint32_t stg = base + SM_STG + 4 * ln;
+        auto stage = [&](int buf, uint32_t (&v)[32], int c, int row0) {
+            to_grid(v);
             if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             asm volatile("bar.sync 1, 128;" ::: "memory");
             const uint32_t dst = stg + buf * 16384;
@@ -690,53 +778,62 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             fence_async_smem();
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (leader) {
+                int* gdst = p.dq_acc + (static_cast<int64_t>(row0) + 32 * c) * HD;
                 asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.s32 [%0], [%1], %2;"
                              ::"l"(gdst), "r"(base + SM_STG + buf * 16384), "r"(16384) : "memory");
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
         };
+#endif
 #ifdef FOLD_BWD_COUNTERS
-        long long c_wq = 0, c_busy = 0;
+        long long c_wq = 0, c_busy = 0, c_rel = 0;
 #endif
         for (int i = 0; i < total; ++i) {
             const int g = i / per_head, mb = m_min + i % per_head;
             const int h = hkv * p.G + g;
-            int* acc = p.dq_acc + (static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM) * HD;   // [128 queries][128 ch]
+            // the tile's first row in the accumulator [H * padded rows][128 ch]
+            const int row0 = static_cast<int>(static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM);
             CNT_T(t_a);
             mbar_wait<SLEEP_WORKER>(sh.bar(B_DQF), i & 1, abort_flag, p.status);
             tc_fence_after();
             CNT_T(t_b);
             if constexpr (NWG == 2) {
-                // three of the four 32-query blocks in registers: the columns are released after the first is staged
+                // three of the four blocks in registers: the columns are released after the first is staged
                 uint32_t v0[32], v1[32], v2[32];
                 tmem_ld32(rd, v0);
                 tmem_ld32(rd + 32, v1);
                 tmem_ld32(rd + 64, v2);
                 tmem_wait_ld();
-                stage(0, v0, acc);
+                stage(0, v0, 0, row0);
                 tmem_ld32(rd + 96, v0);
                 tmem_wait_ld();
                 tc_fence_before();
                 mbar_arrive(sh.bar(B_DQE));   // the rest of the tile is in registers: the columns are free for dP^T of the next tile
-                stage(1, v1, acc + 32 * HD);
-                stage(0, v2, acc + 64 * HD);
-                stage(1, v0, acc + 96 * HD);
+#ifdef FOLD_BWD_COUNTERS
+                c_rel += clock64() - t_b;
+#endif
+                stage(1, v1, 1, row0);
+                stage(0, v2, 2, row0);
+                stage(1, v0, 3, row0);
             } else {
-                // 22 warps leave a thread 88 registers: two blocks in registers at a time
+                // 22 warps leave a thread 80 registers: two blocks in registers at a time
                 uint32_t v0[32], v1[32];
                 tmem_ld32(rd, v0);
                 tmem_ld32(rd + 32, v1);
                 tmem_wait_ld();
-                stage(0, v0, acc);
+                stage(0, v0, 0, row0);
                 tmem_ld32(rd + 64, v0);
                 tmem_wait_ld();
-                stage(1, v1, acc + 32 * HD);
+                stage(1, v1, 1, row0);
                 tmem_ld32(rd + 96, v1);
                 tmem_wait_ld();
                 tc_fence_before();
                 mbar_arrive(sh.bar(B_DQE));
-                stage(0, v0, acc + 64 * HD);
-                stage(1, v1, acc + 96 * HD);
+#ifdef FOLD_BWD_COUNTERS
+                c_rel += clock64() - t_b;
+#endif
+                stage(0, v0, 2, row0);
+                stage(1, v1, 3, row0);
             }
 #ifdef FOLD_BWD_COUNTERS
             c_wq += t_b - t_a;
@@ -749,6 +846,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         if (leader) {
             CNT_ADD(10, c_wq);
             CNT_ADD(11, c_busy);
+            CNT_ADD(12, c_rel);
         }
 #endif
     }
@@ -846,7 +944,21 @@ bool make_map(CUtensorMap* m, const TensorView& t, int64_t rows, int heads, int 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// the int32 dQ accumulator [H * padded rows][128 ch] as (channel, row), boxes of 32 channels x 128 rows
+bool make_acc_map(CUtensorMap* m, const BwdParams& p) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(sm100::HD), static_cast<cuuint64_t>(p.H) * static_cast<cuuint64_t>(p.rows_p)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(sm100::HD) * 4};
+    cuuint32_t box[2] = {32, 128};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, p.dq_acc, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
+
+bool bwd_sm100_biased() { return FOLD_BWD_BIAS != 0; }
 
 bool bwd_sm100_supported(const BwdParams& p) {
     return p.D == 128 && encode_fn() != nullptr;
@@ -859,7 +971,8 @@ int launch_bwd_main_sm100(const BwdParams& p, cudaStream_t st) {
     const int batch = varlen ? 1 : p.B;
     const bool f16 = p.f16;
     if (!make_map(&maps.q, p.q, rows, p.H, batch, sm100::BM, f16) || !make_map(&maps.dout, p.dout, rows, p.H, batch, sm100::BM, f16) ||
-        !make_map(&maps.k, p.k, rows, p.HKV, batch, sm100::BN, f16) || !make_map(&maps.v, p.v, rows, p.HKV, batch, sm100::BN, f16)) {
+        !make_map(&maps.k, p.k, rows, p.HKV, batch, sm100::BN, f16) || !make_map(&maps.v, p.v, rows, p.HKV, batch, sm100::BN, f16) ||
+        !make_acc_map(&maps.dq, p)) {
         set_error("bwd_main_sm100: cuTensorMapEncodeTiled failed");
         return FOLD_ERR_LAUNCH;
     }
@@ -878,21 +991,28 @@ int launch_bwd_main_sm100(const BwdParams& p, cudaStream_t st) {
 
 }  // namespace fold
 
-extern "C" int fold_bwd_counters(uint64_t* out16, int reset) {
+extern "C" int fold_bwd_counters(uint64_t* out24, int reset) {
 #ifdef FOLD_BWD_COUNTERS
-    FOLD_CHECK_ARG(out16, "fold_bwd_counters: null pointer");
-    unsigned long long h[16];
+    FOLD_CHECK_ARG(out24, "fold_bwd_counters: null pointer");
+    unsigned long long h[24];
     if (cudaMemcpyFromSymbol(h, fold::sm100::g_counters, sizeof(h)) != cudaSuccess) return fold::check_launch("fold_bwd_counters");
-    for (int i = 0; i < 16; ++i) out16[i] = h[i];
+    for (int i = 0; i < 24; ++i) out24[i] = h[i];
     if (reset) {
         memset(h, 0, sizeof(h));
         if (cudaMemcpyToSymbol(fold::sm100::g_counters, h, sizeof(h)) != cudaSuccess) return fold::check_launch("fold_bwd_counters");
     }
     return FOLD_OK;
 #else
-    (void)out16;
+    (void)out24;
     (void)reset;
     fold::set_error("fold_bwd_counters: the library was built without -DFOLD_BWD_COUNTERS");
     return FOLD_ERR_UNSUPPORTED;
 #endif
+}
+
+extern "C" int fold_wait_probe(long long limit_cycles, int32_t* status, int32_t* flag_out, void* stream) {
+    FOLD_CHECK_ARG(status, "fold_wait_probe: null pointer");
+    FOLD_CHECK_ARG(limit_cycles > 0 && limit_cycles <= (1ll << 31), "fold_wait_probe: a limit of %lld cycles (1 .. 2^31)", limit_cycles);
+    fold::sm100::wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles, status, flag_out);
+    return fold::check_launch("fold_wait_probe");
 }

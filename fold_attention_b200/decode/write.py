@@ -64,6 +64,15 @@ def step(
     """One step's writes: Q's planes (`q` `(B*H, D)`), and/or one token per
     request appended at `lens` (`k`, `v` `(B, H_KV, D)`), `lens_out = lens + 1`."""
     x = q if q is not None else k
+    # one kernel reads all three as the same 16-bit type: anything else would be read as garbage
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if t is None:
+            continue
+        if t.dtype not in (torch.bfloat16, torch.float16) or t.dtype != x.dtype:
+            raise ValueError(f"q, k and v must be bf16 or fp16, and the same type ({name} is {t.dtype}, "
+                             f"{'q' if q is not None else 'k'} is {x.dtype})")
+        if t.device != lens.device:
+            raise ValueError(f"{name} is on {t.device}, the cache on {lens.device}")
     B = lens.shape[0]
     D = x.shape[-1]
     HKV = k.shape[1] if k is not None else vsum.shape[0] // B

@@ -156,6 +156,10 @@ class FoldKVCache:
         # after a step, look at every row's denominator and run the flagged rows again from a
         # reference moved to their log-sum-exp (one host sync per step; kv_cache.py:704-744)
         self.check_range = bool(check_range)
+        # not a reference argument: read the decode's device status word after every step (one host
+        # synchronisation) and raise FoldLibraryError if a kernel gave up a bounded wait. Steps
+        # under `check_range` synchronise anyway and always check.
+        self.check_status = False
         self._z_given = None
         if chunk is not None and (split is not None or chunk % BN):
             raise ValueError(f"chunk={chunk} is a multiple of {BN} and replaces split")
@@ -354,7 +358,10 @@ class FoldKVCache:
         out_dtype = q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.float32
         # a fresh tensor per step: the caller may hold every step's output
         out = torch.empty((self.n_groups, self.group, self.head_dim), device=q.device, dtype=out_dtype)
-        o, self.den, self.counts = self._launch(split, out_dtype).run(out=out)
+        launch = self._launch(split, out_dtype)
+        o, self.den, self.counts = launch.run(out=out)
+        if self.check_range or self.check_status:
+            launch.check()
         if self.check_range:
             bad = self._out_of_range(o, self.den)
             if bool(bad.any()):
@@ -388,6 +395,7 @@ class FoldKVCache:
             z = torch.where(bad, z + shift, z)
             self._z_given.copy_(z)
             o, den2, counts = launch.run(out=out)
+            launch.check()
             bad2 = self._out_of_range(o, den2)
             if not bool(bad2.any()):
                 return o, den2, counts

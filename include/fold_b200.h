@@ -225,12 +225,21 @@ int fold_bwd_run_phases(const void* q, const void* k, const void* v, const void*
                         size_t workspace_bytes, int kernel, int phases, void* stream);
 
 /* Cycle counters of the tcgen05 backward's main loop, summed over the launches since the
- * last reset: out16 (host, 16 entries) receives CTAs, tiles, CTA lifetime, prologue, epilogue,
+ * last reset: out24 (host, 24 entries) receives CTAs, tiles, CTA lifetime, prologue, epilogue,
  * the compute warps' wait for S^T / exponential phase / wait for dP^T / dS~ phase, the MMA
- * thread's cycles with nothing to issue, the drain's wait and busy cycles (then zeros).
- * Synchronises the device. Returns FOLD_ERR_UNSUPPORTED unless the library was built with
- * -DFOLD_BWD_COUNTERS (the product build is not). No counterpart in the reference. */
-int fold_bwd_counters(uint64_t* out16 /* host */, int reset);
+ * thread's cycles with nothing to issue, the drain's wait and busy cycles and its time from
+ * dQ~ ready to its columns released, the MMA thread's waits for P~, Q, dS~, dO and that release
+ * (then zeros). Synchronises the device. Returns FOLD_ERR_UNSUPPORTED unless the library was
+ * built with -DFOLD_BWD_COUNTERS (the product build is not). No counterpart in the reference. */
+int fold_bwd_counters(uint64_t* out24 /* host */, int reset);
+
+/* The kernels' bounded wait, alone: one warp waits `limit_cycles` SM cycles (1 .. 2^31) on a
+ * barrier nothing arrives at, through the same code path every role of the tcgen05 kernels
+ * waits with; when the wait runs out it stores FOLD_ERR_TIMEOUT to *status and raises the
+ * CTA's abort flag (copied to *flag_out if given), and the kernel returns normally. For tests of
+ * the host's handling of the status word; nothing faults. No counterpart in the reference (its
+ * device-side waits are unbounded). */
+int fold_wait_probe(long long limit_cycles, int32_t* status, int32_t* flag_out, void* stream);
 
 /* Attention forward: O and the log-sum-exp (nats) the backward consumes.
  * Replaces the third-party forward called at src/fold_attention/interface.py:42-44,

@@ -339,6 +339,91 @@ def test_config2_full_size_repeats_and_matches_a_slice():
     assert ob.rel_l2(tr(dq)[0, :, :1], ref[0]) <= TOL
 
 
+def test_config2_mha_full_size_repeats_and_matches_a_slice():
+    """Config 2's headline variant at full size: B4 S8192 H32/32 D128 (MHA). Two runs are the
+    same bits; one (request, head) unit run alone is the full run's slice; that unit's dQ, dK
+    and dV match FP32 autograd. (The whole tensor against an FP32 reference would take the CPU
+    minutes; the slice property carries the check to every unit.)"""
+    _, attention_forward, prepare_backward = _api()
+    torch.manual_seed(22)
+    B, S, H, D = 4, 8192, 32, 128
+    q = (torch.randn(B, S, H, D, device="cuda") / D**0.5).bfloat16()
+    do = torch.randn(B, S, H, D, device="cuda").bfloat16()
+    k, v = (torch.randn(B, S, H, D, device="cuda").bfloat16() for _ in range(2))
+    o, lse = attention_forward(q, k, v, causal=True)
+    tr = lambda x: x.transpose(1, 2)  # noqa: E731
+    run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True)
+    first = tuple(x.clone() for x in run())
+    assert _same(first, run())
+    assert int(run.status) == 0
+    for b, h in ((3, 17), (0, 0)):
+        qs, ks, vs, os_, dos = (x[b:b + 1, :, h:h + 1].contiguous() for x in (q, k, v, o, do))
+        ls = lse[b:b + 1, h:h + 1].contiguous()
+        part = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True)()
+        for x, y in zip(part, first):
+            assert torch.equal(x, y[b:b + 1, h:h + 1])
+    ref = ob.reference_grads(qs[0], ks[0], vs[0], dos[0], scale=1.0 / math.sqrt(D), dtype=torch.float32)
+    for name, x, r in zip("qkv", part, ref):
+        assert ob.rel_l2(tr(x)[0], r) <= TOL, name
+
+
+def test_varlen_autograd_matches_the_prepared_call_and_the_dense_call():
+    """`fold_attn_varlen_func` under autograd (src/fold_attention/interface.py:121-151): its output
+    is the library's forward, its gradients are the prepared call's bits on the same packing
+    (the reference's tests/test_backward.py:334-343), and a packing of equal lengths is the dense
+    `fold_attn_func` bit for bit (:318-332)."""
+    fa, attention_forward, prepare_backward = _api()
+    lens = [1024, 300, 512, 1]
+    H, HKV, D = 8, 2, 128
+    q, k, v, do, cu = _packed(lens, H, HKV, D, seed=5)
+    qa, ka, va = (x.clone().requires_grad_() for x in (q, k, v))
+    out = fa.fold_attn_varlen_func(qa, ka, va, cu, causal=True)
+    out.backward(do)
+    o, lse = _fwd(q, k, v, cu, max(lens))
+    assert torch.equal(out.detach(), o)
+    want = _bwd(q, k, v, o, do, lse, cu, max(lens))
+    assert all(torch.equal(x.grad, y) for x, y in zip((qa, ka, va), want))
+    # given maxima and key-side arguments change nothing; mismatched ones are refused
+    qb, kb, vb = (x.clone().requires_grad_() for x in (q, k, v))
+    fa.fold_attn_varlen_func(qb, kb, vb, cu, cu.clone(), max(lens), max(lens), None, True).backward(do)
+    assert all(torch.equal(x.grad, y.grad) for x, y in zip((qa, ka, va), (qb, kb, vb)))
+    with pytest.raises(ValueError, match="max_seqlen_k"):
+        fa.fold_attn_varlen_func(q, k, v, cu, max_seqlen_q=1024, max_seqlen_k=512)
+    # equal lengths: the packed call is the dense call
+    B, L = 3, 640
+    q, k, v, do, cu = _packed([L] * B, H, HKV, D, seed=6)
+    qa, ka, va = (x.clone().requires_grad_() for x in (q, k, v))
+    fa.fold_attn_varlen_func(qa, ka, va, cu, causal=True).backward(do)
+    dn = lambda x: x.view(B, L, *x.shape[1:])  # noqa: E731
+    qd, kd, vd = (dn(x).clone().requires_grad_() for x in (q, k, v))
+    outd = fa.fold_attn_func(qd, kd, vd, causal=True)
+    outd.backward(dn(do))
+    for x, y in zip((qa, ka, va), (qd, kd, vd)):
+        assert torch.equal(dn(x.grad), y.grad)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_dense_autograd_matches_the_forward_and_the_prepared_backward(causal):
+    """The dense public call (tests/test_backward.py:346-362 of the reference, with the library's
+    own forward where the reference has a third-party one)."""
+    fa, attention_forward, prepare_backward = _api()
+    B, S, H, HKV, D = 2, 256, 8, 2, 64
+    torch.manual_seed(7)
+    q = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, S, HKV, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn_like(k)
+    do = torch.randn_like(q)
+    qa, ka, va = (x.clone().requires_grad_() for x in (q, k, v))
+    got = fa.fold_attn_func(qa, ka, va, causal=causal)
+    got.backward(do)
+    ref, lse = attention_forward(q, k, v, causal=causal)
+    assert torch.equal(got.detach(), ref)
+    qh, kh, vh, oh, doh = (x.transpose(1, 2) for x in (q, k, v, ref, do))
+    want = prepare_backward(qh, kh, vh, oh, doh, lse, causal=causal)()
+    for x, y in zip((qa, ka, va), want):
+        assert x.grad is not None and torch.equal(x.grad, y.transpose(1, 2))
+
+
 def test_config3_packed_64k_tokens_invariance():
     """Config 3 of the benchmark: 64K tokens, lengths uniform in [256, 8192], GQA 32/8,
     D128. A sequence's gradients are the same bits packed, alone, and in a
