@@ -82,7 +82,7 @@ constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 // preprocess starts the accumulator at minus their sum (int32 wraps, so the total is exact):
 // one integer subtract per element less
 #ifndef FOLD_BWD_BIAS
-#define FOLD_BWD_BIAS 0
+#define FOLD_BWD_BIAS 1
 #endif
 // 1: the MMA thread polls the heads of its two chains (S -> dV and dP -> dQ, dK) and issues
 // whichever is ready, instead of one fixed order that lets a late drain hold back dV and S
