@@ -113,7 +113,7 @@ def time_backward(cfg, device, steps, warmup, seed, dist):
         ev[i][0].record()
         run.run_phase(1)
         ev[i][1].record()
-        run.run_phase(2)
+        run.run_phase(8 | 2)   # the work list, then the main loop
         ev[i][2].record()
         run.run_phase(4)
         ev[i][3].record()

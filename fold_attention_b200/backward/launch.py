@@ -18,18 +18,18 @@ import torch
 
 from .. import _lib
 from ..utils import Launch, check_status
-from .plan import Plan, plan_dense, plan_varlen
+from .plan import Plan, plan_dense, plan_varlen, tile_config
 
 P, I, F, Z = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
-_lib.register("fold_bwd_workspace_bytes", [I, I, I, I, I, I, I], Z)
-_lib.register("fold_bwd_workspace_layout", [I, I, I, I, I, I, I, P])
+_lib.register("fold_bwd_workspace_bytes", [I, I, I, I, I, I, I, I, I], Z)
+_lib.register("fold_bwd_workspace_layout", [I, I, I, I, I, I, I, I, I, P])
 _lib.register(
     "fold_bwd_run",
-    [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, P],
+    [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, I, I, P],
 )
 _lib.register(
     "fold_bwd_run_phases",
-    [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, I, P],
+    [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, Z, I, I, I, I, P],
 )
 _lib.register("fold_bwd_counters", [P, I])
 _lib.register("fold_wait_probe", [ctypes.c_longlong, P, P, P])
@@ -85,7 +85,9 @@ def prepare_backward(
     Dense: `(B, H, S, D)` views and `lse` `(B, H, S)`. Varlen: `(total, H, D)`
     packed by `cu_seqlens` `(B + 1,)` int32, and `lse` `(H, total)`. `lse` is
     in nats. `kernel` picks the main loop: "auto" (tcgen05 where it applies),
-    "mma" or "sm100".
+    "mma" or "sm100". `plan` cuts the work (`plan_dense` / `plan_varlen` by
+    default): the tcgen05 main loop takes any `Plan`, the mma.sync one only
+    whole groups over whole query ranges.
     """
     varlen = cu_seqlens is not None
     if varlen:
@@ -113,18 +115,25 @@ def prepare_backward(
         raise NotImplementedError("gradients are returned in the inputs' dtype")
     dev = q.device
     sm = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    if kernel not in KERNELS:
+        raise ValueError(f"kernel is one of {tuple(KERNELS)}")
+    G = H // H_KV
+    cfg = tile_config(D, kernel)
     if plan is None:
-        plan = plan_varlen(H, H_KV) if varlen else plan_dense(B, H, H_KV, S, D, bool(causal))
-    if plan.subgroup != H // H_KV or plan.record:
-        raise NotImplementedError("dK and dV are private to a CTA: the plan is the whole group")
+        plan = plan_varlen(H, H_KV, cfg) if varlen else plan_dense(B, H, H_KV, S, D, bool(causal), cfg)
+    if plan.subgroup < 1 or G % plan.subgroup or plan.record < 0:
+        raise ValueError(f"a plan of {plan.subgroup} heads per work item for groups of {G}")
+    if plan.folds(G) and cfg.tile_n != 128:
+        raise NotImplementedError(
+            "the mma.sync main loop keeps a key block's dK and dV in one CTA: its plan is the whole group over the whole range")
     lse = lse.contiguous()
     if lse.dtype != torch.float32:
         raise ValueError("lse must be fp32")
     dq, dk, dv = (torch.empty_like(x) for x in (q, k, v))
-    nbytes = _lib.lib.fold_bwd_workspace_bytes(B, H, H_KV, S, total, D, int(varlen))
+    nbytes = _lib.lib.fold_bwd_workspace_bytes(B, H, H_KV, S, total, D, int(varlen), plan.subgroup, plan.record)
     workspace = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-    lay = (ctypes.c_int64 * 6)()
-    _lib.call("fold_bwd_workspace_layout", B, H, H_KV, S, total, D, int(varlen), lay)
+    lay = (ctypes.c_int64 * 11)()
+    _lib.call("fold_bwd_workspace_layout", B, H, H_KV, S, total, D, int(varlen), plan.subgroup, plan.record, lay)
     tensors = (q, k, v, o, do, dq, dk, dv)
     strides = _strides(tensors, varlen)
     cu = cu_seqlens
@@ -133,6 +142,7 @@ def prepare_backward(
         dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ctypes.addressof(strides),
         _lib.ptr(cu), B, H, H_KV, S, total, D, int(bool(causal)),
         int(q.dtype == torch.float16), sm, workspace.data_ptr(), nbytes, KERNELS[kernel],
+        plan.subgroup, plan.record,
     )
 
     def run():
@@ -140,14 +150,26 @@ def prepare_backward(
         return dq, dk, dv
 
     def run_phase(phases):
-        """One or more of the backward's phases (1 preprocess, 2 main loop,
-        4 postprocess), for callers that time them apart."""
+        """One or more of the backward's phases (1 preprocess, 8 work list,
+        2 main loop, 4 postprocess; in that order), for callers that time them
+        apart or look at the work list between them."""
         _lib.call("fold_bwd_run_phases", *args, int(phases), _lib.stream(dev))
 
     held = (q, k, v, o, do, lse, dq, dk, dv, workspace, cu, strides)
     launch = BackwardLaunch(run, held, plan, workspace, tuple(lay))
     launch.run_phase = run_phase
     launch.status = workspace[lay[5]: lay[5] + 4].view(torch.int32)
+    # the work list as the device built it (n_items, 8): key block, KV head, request, first head,
+    # heads, first / one-past-last query block, cost in tiles; and, for a folding plan, the integer
+    # dK and dV accumulators [H_KV, padded rows, D]
+    launch.work = workspace[lay[9]: lay[9] + 32 * lay[10]].view(torch.int32).view(-1, 8)
+    launch.dk_acc = launch.dv_acc = None
+    if lay[8]:
+        rows_p = lay[4]
+        launch.dk_acc = workspace[lay[6]: lay[6] + 8 * H_KV * rows_p * D].view(torch.int64).view(H_KV, rows_p, D)
+        wide = lay[8] == 64
+        launch.dv_acc = workspace[lay[7]: lay[7] + (8 if wide else 4) * H_KV * rows_p * D].view(
+            torch.int64 if wide else torch.int32).view(H_KV, rows_p, D)
     return launch
 
 

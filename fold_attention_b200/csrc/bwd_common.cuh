@@ -32,6 +32,16 @@ struct BwdParams {
     int* status;    // one word after the stats: raised if a device-side wait ran out
     int64_t rows_p; // padded rows per head
     int dq_bias;    // the main loop adds 0x4B400000 with every partial: the accumulator starts at minus their sum
+    // how the tcgen05 main loop's work is cut (the other main loop takes whole groups and ranges)
+    int subgroup;   // query heads per work item; it divides G
+    int record;     // query blocks per work item, 0: every block that sees the key block
+    int fold;       // a key block's dK, dV are summed across work items, on integer grids
+    int dv_bits;    // dV's accumulator when folding: 32 (30-bit grid) or 64 (61-bit grid)
+    long long* dk_acc;   // int64 [HKV][rows_p][D], zero before the main loop (fold)
+    void* dv_acc;        // int32 or int64 [HKV][rows_p][D] (fold)
+    int* work;      // the work list: n_items x 8 ints, written in-stream ahead of the main loop
+    int n_items;
+    int* sched;     // [2]: the list's claim counter and the count of finished CTAs, zero between launches
     int S_r;        // dense: S rounded up to ROW_PAD
 };
 
@@ -69,8 +79,10 @@ inline int64_t padded_rows(int B, int S, int total, bool varlen) {
 // kernels
 int launch_bwd_preprocess(const BwdParams& p, cudaStream_t st);
 int launch_bwd_postprocess(const BwdParams& p, int layout, cudaStream_t st);
+// how many work items the tcgen05 main loop's list holds for a call (0 for the other main loop)
+int64_t bwd_sm100_work_items(int B, int H, int HKV, int S, int subgroup, int record);
 int launch_bwd_main_mma(const BwdParams& p, cudaStream_t st);
-int launch_bwd_main_sm100(const BwdParams& p, cudaStream_t st);
+int launch_bwd_main_sm100(const BwdParams& p, bool build_list, bool run_main, cudaStream_t st);
 bool bwd_sm100_supported(const BwdParams& p);
 bool bwd_sm100_biased();   // whether the tcgen05 main loop leaves its rounding constant in the partials
 

@@ -4,9 +4,11 @@
 //   Delta_i = sum_d dO_id O_id, lse * log2(e), a zeroed dQ accumulator, and the
 //   four order-free maxima the integer grid is derived from, published with
 //   atomicMax on float bits: max|K|, max|V|, max ||dO_i||, max |Delta_i| per
-//   (request, KV head). Reference: src/fold_attention/backward/preprocess.py:176-346.
-// Postprocess: dQ = round16( float(acc) * (softmax_scale * 2^-s) ).
-//   Reference: src/fold_attention/backward/postprocess.py:153-154,256-344.
+//   (request, KV head); when dK and dV are folded across CTAs, also max |dO_id|
+//   and max|Q|, which their grids need. Reference: src/fold_attention/backward/preprocess.py:176-346.
+// Postprocess: dQ = round16( float(acc) * (softmax_scale * 2^-s) ); and for folded
+//   dK, dV: dK = round16( float(acc) * (softmax_scale * 2^-s_dK) ), dV = round16( float(acc) * 2^-s_dV ).
+//   Reference: src/fold_attention/backward/postprocess.py:125-154,256-344.
 #include "bwd_common.cuh"
 
 namespace fold {
@@ -34,23 +36,24 @@ __global__ void __launch_bounds__(PRE_THREADS) bwd_preprocess_kernel(const BwdPa
     const bool active = lane * 4 < D;
     const int hkv = h / p.G;
     const bool kv_owner = (h % p.G) == 0;
-    float mx_k = 0.f, mx_v = 0.f, mx_dn = 0.f, mx_dl = 0.f;
+    float mx_k = 0.f, mx_v = 0.f, mx_dn = 0.f, mx_dl = 0.f, mx_doc = 0.f, mx_q = 0.f;
     const int64_t wbase = static_cast<int64_t>(h) * p.rows_p + sq.pstart;
     // Four rows per pass: all of their loads are issued before the first row's reductions, so a
     // warp keeps 8-16 requests in flight instead of 2-4 (the kernel is one pass over O, dO, K, V).
     constexpr int NW = PRE_THREADS / 32, RB = 4;
     for (int r0 = warp; r0 < PRE_ROWS; r0 += RB * NW) {
-        uint2 ow[RB], gw[RB], kw[RB], vw[RB];
+        uint2 ow[RB], gw[RB], kw[RB], vw[RB], qw[RB];
         float lraw[RB];
 #pragma unroll
         for (int u = 0; u < RB; ++u) {
             const int i = mb * PRE_ROWS + r0 + u * NW;
-            ow[u] = gw[u] = kw[u] = vw[u] = make_uint2(0u, 0u);
+            ow[u] = gw[u] = kw[u] = vw[u] = qw[u] = make_uint2(0u, 0u);
             lraw[u] = 0.f;
             if (i < sq.len) {
                 if (active) {
                     ow[u] = ldg8(row_ptr<const uint16_t>(p.o, b, sq.start + i, h) + lane * 4);
                     gw[u] = ldg8(row_ptr<const uint16_t>(p.dout, b, sq.start + i, h) + lane * 4);
+                    if (p.fold) qw[u] = ldg8(row_ptr<const uint16_t>(p.q, b, sq.start + i, h) + lane * 4);
                     if (kv_owner) {
                         kw[u] = ldg8(row_ptr<const uint16_t>(p.k, b, sq.start + i, hkv) + lane * 4);
                         vw[u] = ldg8(row_ptr<const uint16_t>(p.v, b, sq.start + i, hkv) + lane * 4);
@@ -74,6 +77,15 @@ __global__ void __launch_bounds__(PRE_THREADS) bwd_preprocess_kernel(const BwdPa
                 delta = d;
                 mx_dn = fmaxf(mx_dn, sqrtf(n2));
                 mx_dl = fmaxf(mx_dl, fabsf(d));
+                if (p.fold) {
+                    float qq[4];
+                    unpack4<F16>(qw[u], qq);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        mx_doc = fmaxf(mx_doc, fabsf(g[j]));
+                        mx_q = fmaxf(mx_q, fabsf(qq[j]));
+                    }
+                }
                 if (kv_owner && active) {
                     float kk[4], vv[4];
                     unpack4<F16>(kw[u], kk);
@@ -103,22 +115,27 @@ __global__ void __launch_bounds__(PRE_THREADS) bwd_preprocess_kernel(const BwdPa
             for (int c = lane; c < D / 4; c += 32) acc[c] = make_int4(init, init, init, init);
         }
     }
-    __shared__ float s_red[4][PRE_THREADS / 32];
+    __shared__ float s_red[6][PRE_THREADS / 32];
     mx_k = warp_max(mx_k);
     mx_v = warp_max(mx_v);
+    mx_doc = warp_max(mx_doc);
+    mx_q = warp_max(mx_q);
     if (lane == 0) {
         s_red[0][warp] = mx_k;
         s_red[1][warp] = mx_v;
         s_red[2][warp] = mx_dn;
         s_red[3][warp] = mx_dl;
+        s_red[4][warp] = mx_doc;
+        s_red[5][warp] = mx_q;
     }
     __syncthreads();
-    if (threadIdx.x < 4) {
+    if (threadIdx.x < (p.fold ? 6 : 4)) {
         float r = s_red[threadIdx.x][0];
         for (int w = 1; w < PRE_THREADS / 32; ++w) r = fmaxf(r, s_red[threadIdx.x][w]);
         // the max of non-negative floats is the max of their bits, and a max
         // lands the same in any order
-        const int slot = threadIdx.x == 0 ? ST_K : threadIdx.x == 1 ? ST_V : threadIdx.x == 2 ? ST_DO : ST_DELTA;
+        constexpr int slots[6] = {ST_K, ST_V, ST_DO, ST_DELTA, ST_DOC, ST_Q};
+        const int slot = slots[threadIdx.x];
         if (threadIdx.x >= 2 || kv_owner)
             atomicMax(reinterpret_cast<unsigned int*>(p.stats + (static_cast<int64_t>(b) * p.HKV + hkv) * N_STATS + slot),
                       __float_as_uint(r));
@@ -180,7 +197,12 @@ __global__ void __launch_bounds__(256) bwd_finalize_l_kernel(const BwdParams p) 
 }
 
 int launch_bwd_preprocess(const BwdParams& p, cudaStream_t st) {
-    cudaMemsetAsync(p.stats, 0, sizeof(int) * (N_STATS * p.B * p.HKV + 1), st);
+    // the maxima, the status word and the work list's two counters
+    cudaMemsetAsync(p.stats, 0, sizeof(int) * (N_STATS * p.B * p.HKV + 3), st);
+    if (p.fold) {
+        cudaMemsetAsync(p.dk_acc, 0, 8 * static_cast<size_t>(p.HKV) * p.rows_p * p.D, st);
+        cudaMemsetAsync(p.dv_acc, 0, (p.dv_bits / 8) * static_cast<size_t>(p.HKV) * p.rows_p * p.D, st);
+    }
     const int s_r = (p.S + ROW_PAD - 1) / ROW_PAD * ROW_PAD;
     dim3 grid(s_r / PRE_ROWS, p.H, p.B);
     if (p.f16)
@@ -191,12 +213,65 @@ int launch_bwd_preprocess(const BwdParams& p, cudaStream_t st) {
     return check_launch("bwd_preprocess");
 }
 
+// Folded dK and dV: the integer sums back to 16-bit. One fp32 multiply per element, as for dQ;
+// an int64 sum is rounded to fp32 first (nearest even), which is all the precision the 16-bit
+// result keeps.
+template <bool F16>
+__global__ void __launch_bounds__(256) bwd_postprocess_dkv_kernel(const BwdParams p) {
+    const int hkv = blockIdx.y, b = blockIdx.z;
+    const SeqInfo sq = seq_info(p, b);
+    const int D = p.D, cpr = D / 4;
+    const int rows_per_block = 256 / cpr > 0 ? 256 / cpr : 1;
+    const int r0 = blockIdx.x * 64;
+    if (r0 >= sq.len) return;
+    const int* st = p.stats + (static_cast<int64_t>(b) * p.HKV + hkv) * N_STATS;
+    const float rows = static_cast<float>(p.G) * static_cast<float>(sq.len);
+    const int s_k = dk_scale_exp(st, rows, root_d(D));
+    const int s_v = dv_scale_exp(st, rows, p.dv_bits == 32 ? DQ_BITS : DKV_BITS);
+    const float f_k = __fmul_rn(p.scale, pow2f(-s_k)), f_v = pow2f(-s_v);
+    const int64_t wbase = (static_cast<int64_t>(hkv) * p.rows_p + sq.pstart) * D;
+    auto pack4 = [](float x0, float x1, float x2, float x3) {
+        uint2 w;
+        w.x = F16 ? pack_f16x2(x0, x1) : pack_bf16x2(x0, x1);
+        w.y = F16 ? pack_f16x2(x2, x3) : pack_bf16x2(x2, x3);
+        return w;
+    };
+    for (int rr = threadIdx.x / cpr; rr < 64; rr += rows_per_block) {
+        const int i = r0 + rr;
+        const int c = threadIdx.x % cpr;
+        if (i >= sq.len || threadIdx.x >= rows_per_block * cpr) continue;
+        const int64_t at = wbase + static_cast<int64_t>(i) * D + c * 4;
+        const longlong2 k0 = *reinterpret_cast<const longlong2*>(p.dk_acc + at), k1 = *reinterpret_cast<const longlong2*>(p.dk_acc + at + 2);
+        *reinterpret_cast<uint2*>(row_ptr<uint16_t>(p.dk, b, sq.start + i, hkv) + c * 4) =
+            pack4(__fmul_rn(__ll2float_rn(k0.x), f_k), __fmul_rn(__ll2float_rn(k0.y), f_k), __fmul_rn(__ll2float_rn(k1.x), f_k),
+                  __fmul_rn(__ll2float_rn(k1.y), f_k));
+        float v0, v1, v2, v3;
+        if (p.dv_bits == 32) {
+            const int4 a = *reinterpret_cast<const int4*>(static_cast<const int*>(p.dv_acc) + at);
+            v0 = static_cast<float>(a.x); v1 = static_cast<float>(a.y); v2 = static_cast<float>(a.z); v3 = static_cast<float>(a.w);
+        } else {
+            const long long* va = static_cast<const long long*>(p.dv_acc) + at;
+            const longlong2 a0 = *reinterpret_cast<const longlong2*>(va), a1 = *reinterpret_cast<const longlong2*>(va + 2);
+            v0 = __ll2float_rn(a0.x); v1 = __ll2float_rn(a0.y); v2 = __ll2float_rn(a1.x); v3 = __ll2float_rn(a1.y);
+        }
+        *reinterpret_cast<uint2*>(row_ptr<uint16_t>(p.dv, b, sq.start + i, hkv) + c * 4) =
+            pack4(__fmul_rn(v0, f_v), __fmul_rn(v1, f_v), __fmul_rn(v2, f_v), __fmul_rn(v3, f_v));
+    }
+}
+
 int launch_bwd_postprocess(const BwdParams& p, int layout, cudaStream_t st) {
     dim3 grid((p.S + 63) / 64, p.H, p.B);
     if (p.f16)
         bwd_postprocess_dq_kernel<true><<<grid, 256, 0, st>>>(p, layout);
     else
         bwd_postprocess_dq_kernel<false><<<grid, 256, 0, st>>>(p, layout);
+    if (p.fold) {
+        dim3 gkv((p.S + 63) / 64, p.HKV, p.B);
+        if (p.f16)
+            bwd_postprocess_dkv_kernel<true><<<gkv, 256, 0, st>>>(p);
+        else
+            bwd_postprocess_dkv_kernel<false><<<gkv, 256, 0, st>>>(p);
+    }
     return check_launch("bwd_postprocess");
 }
 

@@ -37,6 +37,8 @@
 // Reference arithmetic: src/fold_attention/backward/kernel.py:1191-1330.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "bwd_common.cuh"
 
 namespace fold {
@@ -47,6 +49,7 @@ constexpr int BN = 128;   // keys per CTA
 constexpr int BM = 128;   // queries per tile
 constexpr int HD = 128;   // head dim
 constexpr int STAGES = 2;
+constexpr int ISLOTS = 2;   // work items the producer may run ahead of the slowest role
 #ifndef FOLD_BWD_NWG
 #define FOLD_BWD_NWG 2
 #endif
@@ -84,11 +87,6 @@ constexpr long long WAIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 #ifndef FOLD_BWD_BIAS
 #define FOLD_BWD_BIAS 1
 #endif
-// 1: the MMA thread polls the heads of its two chains (S -> dV and dP -> dQ, dK) and issues
-// whichever is ready, instead of one fixed order that lets a late drain hold back dV and S
-#ifndef FOLD_BWD_DYN_ISSUE
-#define FOLD_BWD_DYN_ISSUE 0
-#endif
 constexpr int SLEEP_WORKER = FOLD_SLEEP_WORKER, SLEEP_PRODUCER = 100, SLEEP_ISSUER = FOLD_SLEEP_ISSUER;
 
 // shared memory map (bytes from a 1024-aligned base)
@@ -118,8 +116,12 @@ enum {
     B_DS,                        // dS~^T in shared (256 arrivals)
     B_DQF,                       // dQ~^T in TMEM
     B_DQE,                       // dQ~^T read out (128 arrivals)
-    B_DONE,                      // every MMA retired
-    B_COUNT,
+    B_DONE,                      // every MMA of the item retired
+    B_KVFREE,                    // the item's last dQ~ (its last read of K) retired
+    B_ACCFREE,                   // the item's dK, dV have been read out of TMEM (NCOMPUTE arrivals)
+    B_IFULL,                     // [ISLOTS] the producer has published a work item
+    B_IEMPTY = B_IFULL + 2,      // [ISLOTS] every consumer has taken it
+    B_COUNT = B_IEMPTY + 2,
 };
 
 // TMEM columns
@@ -321,6 +323,39 @@ __device__ unsigned long long g_counters[24];
 #define CNT_WAIT(acc, ...) mbar_wait<SLEEP_ISSUER>(__VA_ARGS__)
 #endif
 
+// One work item: a key block of one (request, KV head), `nh` of the group's query heads from
+// `h0`, and the query blocks [m_first, m_first + per_head) that can see it.
+struct Item {
+    int nb, hkv, b, h0, nh, n0, m_first, per_head, total;
+    SeqInfo sq;
+};
+__device__ __forceinline__ Item load_item(const BwdParams& p, int idx) {
+    const int4* w = reinterpret_cast<const int4*>(p.work) + 2 * static_cast<int64_t>(idx);
+    const int4 a = __ldg(w), c = __ldg(w + 1);
+    Item it;
+    it.nb = a.x; it.hkv = a.y; it.b = a.z; it.h0 = a.w; it.nh = c.x;
+    it.sq = seq_info(p, it.b);
+    it.n0 = it.nb * BN;
+    const int nm = (it.sq.len + BM - 1) / BM;
+    const int m_min = p.causal ? (it.n0 / BM) : 0;
+    it.m_first = max(m_min, c.y);
+    it.per_head = (it.n0 < it.sq.len) ? max(min(nm, c.z) - it.m_first, 0) : 0;
+    it.total = it.per_head * it.nh;
+    return it;
+}
+
+// x * 2^e for any e in [-250, 250] without leaving fp32's exponent range half way
+__device__ __forceinline__ float scale_pow2(float x, int e) {
+    const int e1 = max(-120, min(120, e));
+    return x * pow2f(e1) * pow2f(e - e1);
+}
+
+// A persistent CTA: every role loops over the work items its producer thread claims from the
+// list (an atomic counter), longest first, so the grid ends on short items and a CTA's fixed
+// costs (TMEM allocation, barrier set-up, the wait for the first loads) are paid once. The
+// roles run asynchronously across item boundaries: while the drain finishes an item's last
+// tile and the compute warps write its dK and dV out, K and V of the next item are already
+// on their way. Barrier phases count tiles (or items) since the CTA started.
 template <bool F16>
 __global__ void __launch_bounds__(NTHREADS, 1)
 bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
@@ -335,23 +370,15 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
     Shared sh{base};
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_BAR + 8 * B_COUNT);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 8 * B_COUNT + 8);
+    volatile int* item_slot = reinterpret_cast<volatile int*>(smem + SM_BAR + 8 * B_COUNT + 16);   // [ISLOTS]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nb = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
-    const SeqInfo sq = seq_info(p, b);
-    const int n0 = nb * BN;
-    if (n0 >= sq.len) return;
     CNT_T(cta_t0);
-
-    // query tiles: all heads of the group, each from the first tile that can see this key block
-    const int nm = (sq.len + BM - 1) / BM;
-    const int m_min = p.causal ? (n0 / BM) : 0;
-    const int per_head = nm - m_min;
-    const int total = per_head * p.G;
 
     if (tid == 0) {
         *abort_flag = 0;
         mbar_init(sh.bar(B_KV), 1);
+        mbar_init(sh.bar(B_KVFREE), 1);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(sh.bar(B_QFULL + s), 1);
             mbar_init(sh.bar(B_QEMPTY + s), 1);
@@ -365,6 +392,11 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         mbar_init(sh.bar(B_DQF), 1);
         mbar_init(sh.bar(B_DQE), 128);
         mbar_init(sh.bar(B_DONE), 1);
+        mbar_init(sh.bar(B_ACCFREE), NCOMPUTE);
+        for (int s = 0; s < ISLOTS; ++s) {
+            mbar_init(sh.bar(B_IFULL + s), 1);
+            mbar_init(sh.bar(B_IEMPTY + s), 1 + NCOMPUTE + 128);   // the MMA thread, the compute warps, the drain
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -377,36 +409,65 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    const int s_exp = dq_scale_exp(p.stats + (static_cast<int64_t>(b) * p.HKV + hkv) * N_STATS, root_d(HD));
+    // The j-th item this CTA works on, as the producer published it (-1: the list is exhausted).
+    // Every consumer takes each slot once, in order.
+    auto next_item = [&](int j) -> int {
+        const int s = j % ISLOTS;
+        mbar_wait<SLEEP_WORKER>(sh.bar(B_IFULL + s), (j / ISLOTS) & 1, abort_flag, p.status);
+        const int idx = item_slot[s];
+        mbar_arrive(sh.bar(B_IEMPTY + s));
+        return (*abort_flag || static_cast<unsigned>(idx) >= static_cast<unsigned>(p.n_items)) ? -1 : idx;
+    };
 
     if (warp == 0) {
-        // ================= TMA producer =================
+        // ================= work claims and TMA loads =================
         if (lane == 0) {
-            const int brow = sq.start + n0;
-            const int bb = p.cu ? 0 : b;
-            mbar_expect_tx(sh.bar(B_KV), 2 * 32768);
-            for (int x = 0; x < 2; ++x) {
-                tma_load_4d(base + SM_K + x * 16384, &maps.k, 64 * x, brow, hkv, bb, sh.bar(B_KV));
-                tma_load_4d(base + SM_V + x * 16384, &maps.v, 64 * x, brow, hkv, bb, sh.bar(B_KV));
-            }
-            for (int i = 0; i < total; ++i) {
-                const int s = i % STAGES;
-                const int g = i / per_head, mb = m_min + i % per_head;
-                const int h = hkv * p.G + g;
-                const int row = sq.start + mb * BM;
-                const int64_t wrow = static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM;
-                // Q and L: two stages, free when dK of the tile two back has read Q
-                if (i >= STAGES) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_QEMPTY + s), ((i / STAGES) - 1) & 1, abort_flag, p.status);
-                mbar_expect_tx(sh.bar(B_QFULL + s), 32768 + 512);
-                for (int x = 0; x < 2; ++x) tma_load_4d(base + SM_Q + s * 32768 + x * 16384, &maps.q, 64 * x, row, h, bb, sh.bar(B_QFULL + s));
-                bulk_load(base + SM_L + s * 512, p.lse2 + wrow, 512, sh.bar(B_QFULL + s));
-                // dO: one buffer, free when dV of the tile before has read it (three GEMMs ahead of
-                // the dP^T that wants the new one); Delta rides with it but alternates between two
-                // slots, because the compute warps may still be reading the last one
-                if (i >= 1) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_OEMPTY), (i - 1) & 1, abort_flag, p.status);
-                mbar_expect_tx(sh.bar(B_OFULL), 32768 + 512);
-                for (int x = 0; x < 2; ++x) tma_load_4d(base + SM_DO + x * 16384, &maps.dout, 64 * x, row, h, bb, sh.bar(B_OFULL));
-                bulk_load(base + SM_DL + s * 512, p.dpsum + wrow, 512, sh.bar(B_OFULL));
+            int t = 0;   // tiles loaded so far
+            for (int j = 0;; ++j) {
+                // claim until an item has work (the list keeps a slot for every key block up to the
+                // longest sequence: the ones past a shorter request's end are empty) or the list ends
+                int idx;
+                Item it;
+                for (;;) {
+                    idx = atomicAdd(p.sched, 1);
+                    if (idx >= p.n_items) { idx = -1; break; }
+                    it = load_item(p, idx);
+                    if (it.total > 0) break;
+                }
+                const int sl = j % ISLOTS;
+                if (j >= ISLOTS) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_IEMPTY + sl), ((j / ISLOTS) - 1) & 1, abort_flag, p.status);
+                item_slot[sl] = idx;
+                __threadfence_block();
+                mbar_arrive(sh.bar(B_IFULL + sl));
+                if (idx < 0 || *abort_flag) break;
+                const int brow = it.sq.start + it.n0;
+                const int bb = p.cu ? 0 : it.b;
+                // K and V: one buffer each, free when the item before has issued its last dQ~
+                if (j >= 1) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_KVFREE), (j - 1) & 1, abort_flag, p.status);
+                mbar_expect_tx(sh.bar(B_KV), 2 * 32768);
+                for (int x = 0; x < 2; ++x) {
+                    tma_load_4d(base + SM_K + x * 16384, &maps.k, 64 * x, brow, it.hkv, bb, sh.bar(B_KV));
+                    tma_load_4d(base + SM_V + x * 16384, &maps.v, 64 * x, brow, it.hkv, bb, sh.bar(B_KV));
+                }
+                for (int i = 0; i < it.total; ++i, ++t) {
+                    const int s = t % STAGES;
+                    const int g = i / it.per_head, mb = it.m_first + i % it.per_head;
+                    const int h = it.hkv * p.G + it.h0 + g;
+                    const int row = it.sq.start + mb * BM;
+                    const int64_t wrow = static_cast<int64_t>(h) * p.rows_p + it.sq.pstart + mb * BM;
+                    // Q and L: two stages, free when dK of the tile two back has read Q
+                    if (t >= STAGES) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_QEMPTY + s), ((t / STAGES) - 1) & 1, abort_flag, p.status);
+                    mbar_expect_tx(sh.bar(B_QFULL + s), 32768 + 512);
+                    for (int x = 0; x < 2; ++x) tma_load_4d(base + SM_Q + s * 32768 + x * 16384, &maps.q, 64 * x, row, h, bb, sh.bar(B_QFULL + s));
+                    bulk_load(base + SM_L + s * 512, p.lse2 + wrow, 512, sh.bar(B_QFULL + s));
+                    // dO: one buffer, free when dV of the tile before has read it (three GEMMs ahead of
+                    // the dP^T that wants the new one); Delta rides with it but alternates between two
+                    // slots, because the compute warps may still be reading the last one
+                    if (t >= 1) mbar_wait<SLEEP_PRODUCER>(sh.bar(B_OEMPTY), (t - 1) & 1, abort_flag, p.status);
+                    mbar_expect_tx(sh.bar(B_OFULL), 32768 + 512);
+                    for (int x = 0; x < 2; ++x) tma_load_4d(base + SM_DO + x * 16384, &maps.dout, 64 * x, row, h, bb, sh.bar(B_OFULL));
+                    bulk_load(base + SM_DL + s * 512, p.dpsum + wrow, 512, sh.bar(B_OFULL));
+                }
             }
         }
     } else if (warp == 1) {
@@ -414,7 +475,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         if (lane == 0) {
             constexpr uint32_t ID_KK = instr_desc(F16 ? 0 : 1, 128, 128, 0, 0);   // S^T, dP^T: both K-major
             constexpr uint32_t ID_KM = instr_desc(F16 ? 0 : 1, 128, 128, 0, 1);   // dV, dK: B MN-major
-            constexpr uint32_t ID_MM = instr_desc(F16 ? 0 : 1, 128, 128, 1, 1);   // dQ~^T: both MN-major
+            constexpr uint32_t ID_MM = instr_desc(F16 ? 0 : 1, 128, 128, 1, 1);   // dQ~: both MN-major
             // K-major operand, 16 channels per step: 4 steps per 64-channel box of 16 KB;
             // MN-major operand, 16 rows per step: 2 KB on, the second 64 columns one box (16 KB) further
             uint64_t dk_kk[8], dv_kk[8], dk_mn[8];
@@ -427,40 +488,34 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             }
             const uint64_t ds_kk0 = smem_desc(base + SM_DS, 16, 1024), ds_mn0 = smem_desc(base + SM_DS, 16384, 1024);
             const uint64_t o_kk0 = smem_desc(base + SM_DO, 16, 1024), o_mn0 = smem_desc(base + SM_DO, 16384, 1024);
-            CNT_T(pro_t0);
-            mbar_wait<SLEEP_ISSUER>(sh.bar(B_KV), 0, abort_flag, p.status);
-            tc_fence_after();
-#ifdef FOLD_BWD_COUNTERS
-            CNT_ADD(3, clock64() - pro_t0);
-            long long idle_clk = 0;
-#endif
-            long long w_p = 0, w_q = 0, w_ds = 0, w_o = 0, w_dqe = 0;
-            (void)w_p; (void)w_q; (void)w_ds; (void)w_o; (void)w_dqe;
-            // The five GEMMs of tile i, each eight K=16 steps, none of them waiting for anything:
-            // the barriers they depend on are taken by the issue loops below.
-            auto issue_s = [&](int i) {   // S^T = K Q^T -> T_S
-                const uint64_t q0 = smem_desc(base + SM_Q + (i % STAGES) * 32768, 16, 1024);
+            long long w_kv = 0, w_p = 0, w_q = 0, w_ds = 0, w_o = 0, w_dqe = 0;
+            (void)w_kv; (void)w_p; (void)w_q; (void)w_ds; (void)w_o; (void)w_dqe;
+            // The five GEMMs of a tile, each eight K=16 steps; `t` is the tile's number since the
+            // CTA started (it picks the Q stage), `acc` whether dK / dV accumulate (not on an
+            // item's first tile). The barriers they depend on are taken by the loop below.
+            auto issue_s = [&](int t) {   // S^T = K Q^T -> T_S
+                const uint64_t q0 = smem_desc(base + SM_Q + (t % STAGES) * 32768, 16, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ss(tmem + T_S, dk_kk[ks], q0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), ID_KK, ks > 0);
                 tc_commit(sh.bar(B_S));
             };
-            auto issue_dp = [&](int) {    // dP^T = V dO^T -> T_DP
+            auto issue_dp = [&]() {       // dP^T = V dO^T -> T_DP
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ss(tmem + T_DP, dv_kk[ks], o_kk0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), ID_KK, ks > 0);
                 tc_commit(sh.bar(B_DP));
             };
-            auto issue_dv = [&](int i) {  // dV += P~^T dO: steps of 16 queries; A = 8 TMEM columns per step, at the
-                                          // head of the S^T columns of the warpgroup that owns those queries
+            auto issue_dv = [&](bool acc) {   // dV += P~^T dO: steps of 16 queries; A = 8 TMEM columns per step, at the
+                                              // head of the S^T columns of the warpgroup that owns those queries
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ts(tmem + T_DV, tmem + T_S + (16 * ks / QPW) * QPW + (16 * ks % QPW) / 2, o_mn0 + ((ks * 2048) >> 4), ID_KM,
-                           (i > 0) || (ks > 0));
+                           acc || (ks > 0));
                 tc_commit(sh.bar(B_OEMPTY));
             };
-            auto issue_dq_dk = [&](int i) {
-                const int s = i % STAGES;
+            auto issue_dq_dk = [&](int t, bool acc, bool last) {
+                const int s = t % STAGES;
                 const uint64_t q_mn0 = smem_desc(base + SM_Q + s * 32768, 16384, 1024);
                 // 8 steps of 16 keys, both operands MN-major: dQ~ = dS~ K (queries on the lanes) or
                 // dQ~^T = K^T dS~^T (channels on the lanes); the same two shared tiles either way
@@ -473,116 +528,67 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
 #endif
                 }
                 tc_commit(sh.bar(B_DQF));
+                if (last) tc_commit(sh.bar(B_KVFREE));   // the item's last read of K (V's was its last dP^T): the next item's may land
                 // dK += dS~^T Q : 8 steps of 16 queries
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
-                    mma_ss(tmem + T_DK, ds_kk0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), q_mn0 + ((ks * 2048) >> 4), ID_KM, (i > 0) || (ks > 0));
+                    mma_ss(tmem + T_DK, ds_kk0 + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), q_mn0 + ((ks * 2048) >> 4), ID_KM, acc || (ks > 0));
                 tc_commit(sh.bar(B_QEMPTY + s));
             };
-#if FOLD_BWD_DYN_ISSUE
-            // Two chains share the tensor pipe: A = S(0) dV(0) S(1) dV(1) ... (S(i+1) overwrites P~(i)
-            // right behind dV(i): a thread's MMAs execute in issue order) and B = dP(0) dQdK(0) dP(1) ...
-            // (dP(i+1) overwrites dQ~(i) once the drain has it). Each keeps its own order, so every
-            // accumulator sees the same sequence of MMAs whatever the interleaving; dV(i) also waits
-            // for dP(i) to have been issued, so that the commit behind dV(i) frees dO for both.
-            int a_s = 0, a_v = 0, b_p = 0, b_q = 0;
-            long long t_last = clock64();
-            int idle = 0;
-            while (a_v < total || b_q < total) {
-                bool prog = false;
-                if (a_s == a_v) {
-                    if (a_s < total && mbar_test(sh.bar(B_QFULL + a_s % STAGES), (a_s / STAGES) & 1)) {
+            int t = 0;   // tiles issued so far
+            for (int j = 0;; ++j) {
+                const int idx = next_item(j);
+                if (idx < 0) break;
+                const Item it = load_item(p, idx);
+                CNT_WAIT(w_kv, sh.bar(B_KV), j & 1, abort_flag, p.status);
+                // the order of a tile's GEMMs, two tiles interleaved: dP(i) | dV(i) S(i+1) | dQ(i) dK(i) dP(i+1)
+                CNT_WAIT(w_q, sh.bar(B_QFULL + t % STAGES), (t / STAGES) & 1, abort_flag, p.status);
+                tc_fence_after();
+                issue_s(t);
+                CNT_WAIT(w_o, sh.bar(B_OFULL), t & 1, abort_flag, p.status);
+                if (t >= 1) CNT_WAIT(w_dqe, sh.bar(B_DQE), (t - 1) & 1, abort_flag, p.status);   // the last dQ~ has left the columns
+                tc_fence_after();
+                issue_dp();
+                for (int i = 0; i < it.total; ++i, ++t) {
+                    CNT_WAIT(w_p, sh.bar(B_P), t & 1, abort_flag, p.status);
+                    // an item's first dV and dK overwrite the accumulators: the item before must have read its own out
+                    if (i == 0 && j >= 1) mbar_wait<SLEEP_ISSUER>(sh.bar(B_ACCFREE), (j - 1) & 1, abort_flag, p.status);
+                    tc_fence_after();
+                    issue_dv(i > 0);
+                    if (i + 1 < it.total) {   // over P~(i), behind dV(i)
+                        CNT_WAIT(w_q, sh.bar(B_QFULL + (t + 1) % STAGES), ((t + 1) / STAGES) & 1, abort_flag, p.status);
                         tc_fence_after();
-                        issue_s(a_s);
-                        ++a_s;
-                        prog = true;
+                        issue_s(t + 1);
                     }
-                } else if (b_p > a_v && mbar_test(sh.bar(B_P), a_v & 1)) {
+                    CNT_WAIT(w_ds, sh.bar(B_DS), t & 1, abort_flag, p.status);
                     tc_fence_after();
-                    issue_dv(a_v);
-                    ++a_v;
-                    prog = true;
-                }
-                if (b_p == b_q) {
-                    if (b_p < total && mbar_test(sh.bar(B_OFULL), b_p & 1) && (b_p == 0 || mbar_test(sh.bar(B_DQE), (b_p - 1) & 1))) {
+                    issue_dq_dk(t, i > 0, i + 1 == it.total);
+                    if (i + 1 < it.total) {
+                        CNT_WAIT(w_o, sh.bar(B_OFULL), (t + 1) & 1, abort_flag, p.status);
+                        CNT_WAIT(w_dqe, sh.bar(B_DQE), t & 1, abort_flag, p.status);   // dQ~(i) has left the columns
                         tc_fence_after();
-                        issue_dp(b_p);
-                        ++b_p;
-                        prog = true;
-                    }
-                } else if (mbar_test(sh.bar(B_DS), b_q & 1)) {
-                    tc_fence_after();
-                    issue_dq_dk(b_q);
-                    ++b_q;
-                    prog = true;
-                }
-                if (prog) {
-#ifdef FOLD_BWD_COUNTERS
-                    if (idle) idle_clk += clock64() - t_last;
-#endif
-                    idle = 0;
-                    t_last = clock64();
-                } else if ((++idle & 127) == 0) {
-                    if (*abort_flag) break;
-                    if (clock64() - t_last > WAIT_CYCLES) {
-                        *abort_flag = 1;
-                        atomicExch(p.status, FOLD_ERR_TIMEOUT);
-                        break;
+                        issue_dp();
                     }
                 }
+                tc_commit(sh.bar(B_DONE));   // every MMA of the item has retired: dK and dV are final
+                CNT_ADD(1, it.total);
             }
-#else
-            if (total > 0) {
-                mbar_wait<SLEEP_ISSUER>(sh.bar(B_QFULL), 0, abort_flag, p.status);
-                tc_fence_after();
-                issue_s(0);
-                mbar_wait<SLEEP_ISSUER>(sh.bar(B_OFULL), 0, abort_flag, p.status);
-                tc_fence_after();
-                issue_dp(0);
-            }
-            for (int i = 0; i < total; ++i) {
-                CNT_WAIT(w_p, sh.bar(B_P), i & 1, abort_flag, p.status);
-                tc_fence_after();
-                issue_dv(i);
-                if (i + 1 < total) {   // over P~(i), behind dV(i)
-                    CNT_WAIT(w_q, sh.bar(B_QFULL + (i + 1) % STAGES), ((i + 1) / STAGES) & 1, abort_flag, p.status);
-                    tc_fence_after();
-                    issue_s(i + 1);
-                }
-                CNT_WAIT(w_ds, sh.bar(B_DS), i & 1, abort_flag, p.status);
-                tc_fence_after();
-                issue_dq_dk(i);
-                if (i + 1 < total) {
-                    CNT_WAIT(w_o, sh.bar(B_OFULL), (i + 1) & 1, abort_flag, p.status);
-                    CNT_WAIT(w_dqe, sh.bar(B_DQE), i & 1, abort_flag, p.status);   // dQ~(i) has left the columns
-                    tc_fence_after();
-                    issue_dp(i + 1);
-                }
-            }
-#endif
-            tc_commit(sh.bar(B_DONE));
-#ifdef FOLD_BWD_COUNTERS
             CNT_ADD(0, 1);
-            CNT_ADD(1, total);
-            CNT_ADD(9, idle_clk);
+            CNT_ADD(3, w_kv);
             CNT_ADD(13, w_p);
             CNT_ADD(14, w_q);
             CNT_ADD(15, w_ds);
             CNT_ADD(16, w_o);
             CNT_ADD(17, w_dqe);
-#endif
         }
     } else if (warp < W_DRAIN) {
-        // ================= compute: P~^T and dS~^T for QPW of the tile's queries =================
+        // ================= compute: P~^T and dS~^T for QPW of the tile's queries; then the item's dK, dV =================
         const int wg = (warp - 2) >> 2;
         const int r = 32 * (warp & 3) + lane;   // key row = TMEM lane
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const float c2 = p.scale * kLog2e;
         const uint64_t c2x2 = pack2(c2, c2);
         (void)c2x2;
-        // bf16 has fp32's range, so P~ and dS~ carry the grid's exponent (it comes in with the row
-        // statistic s - L); fp16 does not, and the exponent is applied to dQ's fp32 sums at the drain
-        const int kj = n0 + r;
         const uint32_t rs = tmem + lane_addr + T_S + QPW * wg;
         const uint32_t rd = tmem + lane_addr + T_DP + QPW * wg;
         // dS~^T row r: 128 bytes = 64 queries per box, 16-byte chunk u (8 queries) at u ^ (r & 7)
@@ -590,96 +596,184 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         constexpr int CH0_MASK = (64 / QPW) - 1;        // warpgroups per 64-query box, minus one
         const int ch0 = (wg & CH0_MASK) * (QPW / 8);    // the warpgroup's first chunk in its box
 #ifdef FOLD_BWD_COUNTERS
-        long long c_ws = 0, c_exp = 0, c_wd = 0, c_ds = 0;
+        long long c_ws = 0, c_exp = 0, c_wd = 0, c_ds = 0, c_epi = 0;
         const bool counting = (warp == 2 && lane == 0);
 #endif
-        for (int i = 0; i < total; ++i) {
-            const int s = i % STAGES;
-            const int mb = m_min + i % per_head;
-            const int m0 = mb * BM + QPW * wg;   // the group's first query
-            const uint32_t sL_addr = base + SM_L + s * 512 + 4 * QPW * wg;
-            const uint32_t sDl_addr = base + SM_DL + s * 512 + 4 * QPW * wg;
-            const bool need_mask = (p.causal && m0 < n0 + BN) || (n0 + BN > sq.len);
-            float x[QPW];
-            // ---- P~^T = exp2(S^T c - L), kept in registers for dS~ and written over S^T ----
-            CNT_T(t_a);
-            mbar_wait<SLEEP_WORKER>(sh.bar(B_QFULL + s), (i / STAGES) & 1, abort_flag, p.status);   // L (long since there)
-            float lv[32];
-            lds32(sL_addr, lv);   // the first 32 queries' L, in flight under the wait for S^T
-            mbar_wait<SLEEP_WORKER>(sh.bar(B_S), i & 1, abort_flag, p.status);
-            tc_fence_after();
-            CNT_T(t_b);
+        int t = 0;
+        for (int j = 0;; ++j) {
+            const int idx = next_item(j);
+            if (idx < 0) break;
+            const Item it = load_item(p, idx);
+            const int kj = it.n0 + r;
+            for (int i = 0; i < it.total; ++i, ++t) {
+                const int s = t % STAGES;
+                const int mb = it.m_first + i % it.per_head;
+                const int m0 = mb * BM + QPW * wg;   // the group's first query
+                const uint32_t sL_addr = base + SM_L + s * 512 + 4 * QPW * wg;
+                const uint32_t sDl_addr = base + SM_DL + s * 512 + 4 * QPW * wg;
+                const bool need_mask = (p.causal && m0 < it.n0 + BN) || (it.n0 + BN > it.sq.len);
+                float x[QPW];
+                // ---- P~^T = exp2(S^T c - L), kept in registers for dS~ and written over S^T ----
+                // bf16 has fp32's range, so P~ and dS~ carry the grid's exponent (it comes in with the row
+                // statistic s - L); fp16 does not, and the exponent is applied to dQ's fp32 sums at the drain
+                CNT_T(t_a);
+                mbar_wait<SLEEP_WORKER>(sh.bar(B_QFULL + s), (t / STAGES) & 1, abort_flag, p.status);   // L (long since there)
+                float lv[32];
+                lds32(sL_addr, lv);   // the first 32 queries' L, in flight under the wait for S^T
+                mbar_wait<SLEEP_WORKER>(sh.bar(B_S), t & 1, abort_flag, p.status);
+                tc_fence_after();
+                CNT_T(t_b);
 #pragma unroll
-            for (int c = 0; c < QPW / 32; ++c) {
-                uint32_t sv[32];
-                if (c > 0) lds32(sL_addr + 128 * c, lv);
-                tmem_ld32(rs + 32 * c, sv);
-                tmem_wait_ld();
-                uint32_t pp[16];
+                for (int c = 0; c < QPW / 32; ++c) {
+                    uint32_t sv[32];
+                    if (c > 0) lds32(sL_addr + 128 * c, lv);
+                    tmem_ld32(rs + 32 * c, sv);
+                    tmem_wait_ld();
+                    uint32_t pp[16];
 #pragma unroll
 #if FOLD_PACKED_MATH
-                for (int j = 0; j < 32; j += 2)   // lv = s - L, from the preprocess
-                    fma2(x[32 * c + j], x[32 * c + j + 1], __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]), c2x2, lv[j], lv[j + 1]);
+                    for (int q = 0; q < 32; q += 2)   // lv = s - L, from the preprocess
+                        fma2(x[32 * c + q], x[32 * c + q + 1], __uint_as_float(sv[q]), __uint_as_float(sv[q + 1]), c2x2, lv[q], lv[q + 1]);
 #else
-                for (int j = 0; j < 32; ++j) x[32 * c + j] = fmaf(__uint_as_float(sv[j]), c2, lv[j]);   // lv = s - L, from the preprocess
+                    for (int q = 0; q < 32; ++q) x[32 * c + q] = fmaf(__uint_as_float(sv[q]), c2, lv[q]);
 #endif
 #pragma unroll
-                for (int j = 0; j < 32; ++j) x[32 * c + j] = ex2f(x[32 * c + j]);   // 32 independent ex2 in a row
-                if (need_mask) {   // the diagonal tile and the sequence's last key block only: kept out of the common path
+                    for (int q = 0; q < 32; ++q) x[32 * c + q] = ex2f(x[32 * c + q]);   // 32 independent ex2 in a row
+                    if (need_mask) {   // the diagonal tile and the sequence's last key block only: kept out of the common path
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int qi = m0 + 32 * c + j;
-                        if (kj >= sq.len || (p.causal && kj > qi)) x[32 * c + j] = 0.f;
+                        for (int q = 0; q < 32; ++q) {
+                            const int qi = m0 + 32 * c + q;
+                            if (kj >= it.sq.len || (p.causal && kj > qi)) x[32 * c + q] = 0.f;
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 32; q += 2)
+                        pp[q >> 1] = F16 ? pack_f16x2(x[32 * c + q], x[32 * c + q + 1]) : pack_bf16x2(x[32 * c + q], x[32 * c + q + 1]);
+                    tmem_st16(rs + 16 * c, pp);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(sh.bar(B_P));
+                CNT_T(t_c);
+                // ---- dS~^T = P~^T (dP^T - Delta) to shared, 16 queries at a time ----
+                // dP^T done means dO, and Delta with it, landed (the MMA thread waited for them)
+                mbar_wait<SLEEP_WORKER>(sh.bar(B_DP), t & 1, abort_flag, p.status);
+                tc_fence_after();
+                CNT_T(t_d);
+#pragma unroll
+                for (int hh = 0; hh < QPW / 16; ++hh) {
+                    float dl[16];
+                    uint32_t dv[16];
+                    lds16(sDl_addr + 64 * hh, dl);
+                    tmem_ld16(rd + 16 * hh, dv);
+                    tmem_wait_ld();
+                    uint32_t dd[8];
+#pragma unroll
+#if FOLD_PACKED_MATH
+                    for (int q = 0; q < 16; q += 2)
+                        submul2(dl[q], dl[q + 1], __uint_as_float(dv[q]), __uint_as_float(dv[q + 1]), dl[q], dl[q + 1], x[16 * hh + q], x[16 * hh + q + 1]);
+#else
+                    for (int q = 0; q < 16; ++q) dl[q] = x[16 * hh + q] * (__uint_as_float(dv[q]) - dl[q]);
+#endif
+#pragma unroll
+                    for (int q = 0; q < 16; q += 2) dd[q >> 1] = F16 ? pack_f16x2(dl[q], dl[q + 1]) : pack_bf16x2(dl[q], dl[q + 1]);
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int cu = (ch0 + 2 * hh + u) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(sds + cu * 16) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
                     }
                 }
-#pragma unroll
-                for (int j = 0; j < 32; j += 2)
-                    pp[j >> 1] = F16 ? pack_f16x2(x[32 * c + j], x[32 * c + j + 1]) : pack_bf16x2(x[32 * c + j], x[32 * c + j + 1]);
-                tmem_st16(rs + 16 * c, pp);
-            }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(sh.bar(B_P));
-            CNT_T(t_c);
-            // ---- dS~^T = P~^T (dP^T - Delta) to shared, 16 queries at a time ----
-            // dP^T done means dO, and Delta with it, landed (the MMA thread waited for them)
-            mbar_wait<SLEEP_WORKER>(sh.bar(B_DP), i & 1, abort_flag, p.status);
-            tc_fence_after();
-            CNT_T(t_d);
-#pragma unroll
-            for (int hh = 0; hh < QPW / 16; ++hh) {
-                float dl[16];
-                uint32_t dv[16];
-                lds16(sDl_addr + 64 * hh, dl);
-                tmem_ld16(rd + 16 * hh, dv);
-                tmem_wait_ld();
-                uint32_t dd[8];
-#pragma unroll
-#if FOLD_PACKED_MATH
-                for (int j = 0; j < 16; j += 2)
-                    submul2(dl[j], dl[j + 1], __uint_as_float(dv[j]), __uint_as_float(dv[j + 1]), dl[j], dl[j + 1], x[16 * hh + j], x[16 * hh + j + 1]);
-#else
-                for (int j = 0; j < 16; ++j) dl[j] = x[16 * hh + j] * (__uint_as_float(dv[j]) - dl[j]);
+                tc_fence_before();
+                fence_async_smem();
+                mbar_arrive(sh.bar(B_DS));
+#ifdef FOLD_BWD_COUNTERS
+                if (counting) {
+                    const long long t_e = clock64();
+                    c_ws += t_b - t_a;
+                    c_exp += t_c - t_b;
+                    c_wd += t_d - t_c;
+                    c_ds += t_e - t_d;
+                }
 #endif
+            }
+            // ---- the item's dK and dV out of TMEM ----
+            // The first half of the compute warpgroups takes dK, the second dV (with four, each takes
+            // 64 of the 128 channels). Private items (the whole group, the whole query range) write
+            // the 16-bit gradients; the others round their sums onto the (request, KV head)'s dK / dV
+            // integer grids and add them to the accumulators, where every item of the key block meets.
+            CNT_T(t_f);
+            mbar_wait<SLEEP_WORKER>(sh.bar(B_DONE), j & 1, abort_flag, p.status);
+            tc_fence_after();
+            {
+                constexpr int PARTS = NWG / 2, CW = HD / PARTS;   // channels per warpgroup
+                const bool is_dv = wg >= PARTS;
+                const int c0 = (wg % PARTS) * CW;
+                const int* st = p.stats + (static_cast<int64_t>(it.b) * p.HKV + it.hkv) * N_STATS;
+                const int s_exp = dq_scale_exp(st, root_d(HD));
+                const uint32_t src = tmem + lane_addr + (is_dv ? T_DV : T_DK) + c0;
+                const bool ok = it.n0 + r < it.sq.len;
+                if (!p.fold) {
+                    auto pk2 = [](float a, float b2) { return F16 ? pack_f16x2(a, b2) : pack_bf16x2(a, b2); };
+                    const float un = F16 ? 1.f : pow2f(-s_exp);
+                    const float f = is_dv ? un : p.scale * un;
+                    uint16_t* dst = row_ptr<uint16_t>(is_dv ? p.dv : p.dk, it.b, it.sq.start + it.n0 + (ok ? r : 0), it.hkv) + c0;
 #pragma unroll
-                for (int j = 0; j < 16; j += 2) dd[j >> 1] = F16 ? pack_f16x2(dl[j], dl[j + 1]) : pack_bf16x2(dl[j], dl[j + 1]);
+                    for (int c = 0; c < CW / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(src + 32 * c, v);
+                        tmem_wait_ld();
+                        if (c == CW / 32 - 1) {   // the last read of the accumulators: the next item may overwrite them
+                            tc_fence_before();
+                            mbar_arrive(sh.bar(B_ACCFREE));
+                        }
+                        if (ok) {
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int cu = (ch0 + 2 * hh + u) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(sds + cu * 16) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+                            for (int q = 0; q < 32; q += 8) {
+                                uint4 w;
+                                w.x = pk2(__uint_as_float(v[q]) * f, __uint_as_float(v[q + 1]) * f);
+                                w.y = pk2(__uint_as_float(v[q + 2]) * f, __uint_as_float(v[q + 3]) * f);
+                                w.z = pk2(__uint_as_float(v[q + 4]) * f, __uint_as_float(v[q + 5]) * f);
+                                w.w = pk2(__uint_as_float(v[q + 6]) * f, __uint_as_float(v[q + 7]) * f);
+                                *reinterpret_cast<uint4*>(dst + 32 * c + q) = w;
+                            }
+                        }
+                    }
+                } else {
+                    // dK~ and dV~ carry the dQ grid's exponent (bf16) or none (fp16); their own grids'
+                    // exponents come from the same maxima, so every item of the key block agrees
+                    const float rows = static_cast<float>(p.G) * static_cast<float>(it.sq.len);
+                    const int e = (is_dv ? dv_scale_exp(st, rows, p.dv_bits == 32 ? DQ_BITS : DKV_BITS) : dk_scale_exp(st, rows, root_d(HD))) -
+                                  (F16 ? 0 : s_exp);
+                    const int64_t off = (static_cast<int64_t>(it.hkv) * p.rows_p + it.sq.pstart + it.n0 + r) * HD + c0;
+                    const bool narrow = is_dv && p.dv_bits == 32;
+#pragma unroll
+                    for (int c = 0; c < CW / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(src + 32 * c, v);
+                        tmem_wait_ld();
+                        if (c == CW / 32 - 1) {
+                            tc_fence_before();
+                            mbar_arrive(sh.bar(B_ACCFREE));
+                        }
+                        if (ok) {
+                            if (narrow) {
+                                int* acc = static_cast<int*>(p.dv_acc) + off + 32 * c;
+#pragma unroll
+                                for (int q = 0; q < 32; ++q)
+                                    asm volatile("red.global.add.s32 [%0], %1;" ::"l"(acc + q), "r"(__float2int_rn(scale_pow2(__uint_as_float(v[q]), e))) : "memory");
+                            } else {
+                                unsigned long long* acc = static_cast<unsigned long long*>(is_dv ? p.dv_acc : static_cast<void*>(p.dk_acc)) + off + 32 * c;
+#pragma unroll
+                                for (int q = 0; q < 32; ++q)
+                                    asm volatile("red.global.add.u64 [%0], %1;" ::"l"(acc + q),
+                                                 "l"(static_cast<unsigned long long>(__float2ll_rn(scale_pow2(__uint_as_float(v[q]), e)))) : "memory");
+                            }
+                        }
+                    }
                 }
             }
-            tc_fence_before();
-            fence_async_smem();
-            mbar_arrive(sh.bar(B_DS));
 #ifdef FOLD_BWD_COUNTERS
-            if (counting) {
-                const long long t_e = clock64();
-                c_ws += t_b - t_a;
-                c_exp += t_c - t_b;
-                c_wd += t_d - t_c;
-                c_ds += t_e - t_d;
-            }
+            if (counting) c_epi += clock64() - t_f;
 #endif
         }
 #ifdef FOLD_BWD_COUNTERS
@@ -688,6 +782,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             CNT_ADD(6, c_exp);
             CNT_ADD(7, c_wd);
             CNT_ADD(8, c_ds);
+            CNT_ADD(4, c_epi);
         }
 #endif
     } else {
@@ -700,7 +795,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         // time from B_DQF to B_DQE is on the kernel's critical path: blocks are converted with
         // short dependency chains and stored with as few instructions as the layout allows.
         const int ln = 32 * (warp & 3) + lane;   // TMEM lane: a query (FOLD_BWD_DRAIN_T) or a channel
-        const float dq_mul = F16 ? pow2f(s_exp) : 1.f;
+        float dq_mul = 1.f;   // fp16: the grid's exponent, applied here (per item)
         const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
         const uint32_t rd = tmem + lane_addr + T_DP;
         const bool leader = (warp == W_DRAIN && lane == 0);   // issues every reduction: they form its groups
@@ -788,13 +883,19 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
 #ifdef FOLD_BWD_COUNTERS
         long long c_wq = 0, c_busy = 0, c_rel = 0;
 #endif
-        for (int i = 0; i < total; ++i) {
-            const int g = i / per_head, mb = m_min + i % per_head;
-            const int h = hkv * p.G + g;
+        int t = 0;
+        for (int j = 0;; ++j) {
+          const int idx = next_item(j);
+          if (idx < 0) break;
+          const Item it = load_item(p, idx);
+          if (F16) dq_mul = pow2f(dq_scale_exp(p.stats + (static_cast<int64_t>(it.b) * p.HKV + it.hkv) * N_STATS, root_d(HD)));
+          for (int i = 0; i < it.total; ++i, ++t) {
+            const int g = i / it.per_head, mb = it.m_first + i % it.per_head;
+            const int h = it.hkv * p.G + it.h0 + g;
             // the tile's first row in the accumulator [H * padded rows][128 ch]
-            const int row0 = static_cast<int>(static_cast<int64_t>(h) * p.rows_p + sq.pstart + mb * BM);
+            const int row0 = static_cast<int>(static_cast<int64_t>(h) * p.rows_p + it.sq.pstart + mb * BM);
             CNT_T(t_a);
-            mbar_wait<SLEEP_WORKER>(sh.bar(B_DQF), i & 1, abort_flag, p.status);
+            mbar_wait<SLEEP_WORKER>(sh.bar(B_DQF), t & 1, abort_flag, p.status);
             tc_fence_after();
             CNT_T(t_b);
             if constexpr (NWG == 2) {
@@ -839,6 +940,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             c_wq += t_b - t_a;
             c_busy += clock64() - t_b;
 #endif
+          }
         }
         // the engine must be done with shared memory, and the adds complete, before the CTA goes
         if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -851,59 +953,77 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
 #endif
     }
 
-    // ================= epilogue: dK, dV out of TMEM =================
-    __syncthreads();
-    CNT_T(epi_t0);
-    if (warp >= 2 && warp < W_DRAIN) {
-        if (total > 0) mbar_wait(sh.bar(B_DONE), 0, abort_flag, p.status);   // every MMA has retired
-        tc_fence_after();
-        // the first half of the compute warpgroups takes dK, the second dV; with four, each takes
-        // 64 of the 128 channels
-        const int wg = (warp - 2) >> 2;
-        constexpr int PARTS = NWG / 2, CW = HD / PARTS;   // channels per warpgroup
-        const bool is_dv = wg >= PARTS;
-        const int c0 = (wg % PARTS) * CW;
-        const int r = 32 * (warp & 3) + lane;
-        const uint32_t lane_addr = static_cast<uint32_t>(32 * (warp & 3)) << 16;
-        auto pk2 = [](float a, float b2) { return F16 ? pack_f16x2(a, b2) : pack_bf16x2(a, b2); };
-        const float un = F16 ? 1.f : pow2f(-s_exp);
-        const float f = is_dv ? un : p.scale * un;
-        const uint32_t src = tmem + lane_addr + (is_dv ? T_DV : T_DK) + c0;
-        const bool ok = n0 + r < sq.len;
-        uint16_t* dst = row_ptr<uint16_t>(is_dv ? p.dv : p.dk, b, sq.start + n0 + (ok ? r : 0), hkv) + c0;
-#pragma unroll
-        for (int c = 0; c < CW / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld32(src + 32 * c, v);
-            tmem_wait_ld();
-            if (ok && total > 0) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    uint4 w;
-                    w.x = pk2(__uint_as_float(v[j]) * f, __uint_as_float(v[j + 1]) * f);
-                    w.y = pk2(__uint_as_float(v[j + 2]) * f, __uint_as_float(v[j + 3]) * f);
-                    w.z = pk2(__uint_as_float(v[j + 4]) * f, __uint_as_float(v[j + 5]) * f);
-                    w.w = pk2(__uint_as_float(v[j + 6]) * f, __uint_as_float(v[j + 7]) * f);
-                    *reinterpret_cast<uint4*>(dst + 32 * c + j) = w;
-                }
-            } else if (ok) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) *reinterpret_cast<uint4*>(dst + 32 * c + j) = make_uint4(0, 0, 0, 0);
-            }
-        }
-        tc_fence_before();
-    }
+    // every role has left its loop: no MMA, load or reduction of this CTA is in flight
+    tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
     }
-#ifdef FOLD_BWD_COUNTERS
     if (tid == 0) {
-        const long long t_end = clock64();
-        CNT_ADD(2, t_end - cta_t0);
-        CNT_ADD(4, t_end - epi_t0);
+        CNT_ADD(2, clock64() - cta_t0);
+        // the last CTA to finish puts both counters back, so the next launch (or a graph replay) starts from zero
+        __threadfence();
+        if (atomicAdd(p.sched + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+            p.sched[0] = 0;
+            p.sched[1] = 0;
+            __threadfence();
+        }
     }
-#endif
+}
+
+// ---- the work list ---------------------------------------------------------------------
+// One entry per (request, KV head, subgroup of query heads, key block, record of query blocks):
+// eight ints (key block, KV head, request, first head of the subgroup, heads, first and
+// one-past-last query block, cost in tiles). Entries are grouped in sections of `sec`
+// (request, KV head, subgroup) triples -- the CTAs running at any time then share few heads' Q,
+// dO and dQ, which stay in L2 -- and sorted by cost, longest first, inside each section, so
+// that the persistent CTAs end every section, and the launch, on short items. Built on the
+// device from cu_seqlens, in-stream: no host synchronisation, and a captured graph replays it.
+constexpr int WL_BINS = 1024;
+__global__ void __launch_bounds__(256) bwd_work_list_kernel(const BwdParams p, int n_trip, int nsub, int nb_max, int nrec, int sec) {
+    __shared__ int hist[WL_BINS];
+    __shared__ int offs[WL_BINS];
+    const int t0 = blockIdx.x * sec, t1 = min(t0 + sec, n_trip);
+    const int per = nb_max * nrec;
+    const int count = (t1 - t0) * per;
+    int* out = const_cast<int*>(p.work) + static_cast<int64_t>(t0) * per * 8;
+    for (int i = threadIdx.x; i < WL_BINS; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    auto describe = [&](int li, int (&w)[8]) {
+        const int trip = t0 + li / per, rem = li % per;
+        const int nb = rem / nrec, rec = rem % nrec;
+        const int b = trip / (p.HKV * nsub), hkv = (trip / nsub) % p.HKV, sub = trip % nsub;
+        const SeqInfo sq = seq_info(p, b);
+        const int nm = (sq.len + BM - 1) / BM;
+        const int m_lo = p.record > 0 ? rec * p.record : 0;
+        const int m_hi = p.record > 0 ? (rec + 1) * p.record : nm;
+        const int first = max(p.causal ? nb : 0, m_lo);
+        const int blocks = (nb * BN < sq.len) ? max(min(nm, m_hi) - first, 0) : 0;
+        w[0] = nb; w[1] = hkv; w[2] = b; w[3] = sub * p.subgroup; w[4] = p.subgroup;
+        w[5] = m_lo; w[6] = m_hi; w[7] = blocks * p.subgroup;
+    };
+    for (int li = threadIdx.x; li < count; li += blockDim.x) {
+        int w[8];
+        describe(li, w);
+        atomicAdd(&hist[min(w[7], WL_BINS - 1)], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int c = WL_BINS - 1; c >= 0; --c) {
+            offs[c] = at;
+            at += hist[c];
+        }
+    }
+    __syncthreads();
+    for (int li = threadIdx.x; li < count; li += blockDim.x) {
+        int w[8];
+        describe(li, w);
+        const int pos = atomicAdd(&offs[min(w[7], WL_BINS - 1)], 1);   // the order among equal costs is free: no bit depends on it
+        int4* o = reinterpret_cast<int4*>(out + static_cast<int64_t>(pos) * 8);
+        o[0] = make_int4(w[0], w[1], w[2], w[3]);
+        o[1] = make_int4(w[4], w[5], w[6], w[7]);
+    }
 }
 
 }  // namespace sm100
@@ -960,11 +1080,31 @@ bool make_acc_map(CUtensorMap* m, const BwdParams& p) {
 
 bool bwd_sm100_biased() { return FOLD_BWD_BIAS != 0; }
 
+namespace {
+struct ListShape {
+    int nsub, nb_max, nrec;
+    int64_t n_trip, n_items;
+};
+ListShape list_shape(int B, int H, int HKV, int S, int subgroup, int record) {
+    ListShape l;
+    l.nsub = (H / HKV) / subgroup;
+    l.nb_max = (S + sm100::BN - 1) / sm100::BN;
+    l.nrec = record > 0 ? (l.nb_max + record - 1) / record : 1;
+    l.n_trip = static_cast<int64_t>(B) * HKV * l.nsub;
+    l.n_items = l.n_trip * l.nb_max * l.nrec;
+    return l;
+}
+}  // namespace
+
+int64_t bwd_sm100_work_items(int B, int H, int HKV, int S, int subgroup, int record) {
+    return list_shape(B, H, HKV, S, subgroup, record).n_items;
+}
+
 bool bwd_sm100_supported(const BwdParams& p) {
     return p.D == 128 && encode_fn() != nullptr;
 }
 
-int launch_bwd_main_sm100(const BwdParams& p, cudaStream_t st) {
+int launch_bwd_main_sm100(const BwdParams& p, bool build_list, bool run_main, cudaStream_t st) {
     sm100::Maps maps;
     const bool varlen = p.cu != nullptr;
     const int64_t rows = varlen ? p.total : p.S;
@@ -976,7 +1116,26 @@ int launch_bwd_main_sm100(const BwdParams& p, cudaStream_t st) {
         set_error("bwd_main_sm100: cuTensorMapEncodeTiled failed");
         return FOLD_ERR_LAUNCH;
     }
-    dim3 grid((p.S + sm100::BN - 1) / sm100::BN, p.HKV, p.B);
+    // The work list, then one persistent CTA per SM claiming from it. Sections: as many (request,
+    // KV head, subgroup) triples as keep their Q, dO (16-bit) and dQ accumulator (int32) within a
+    // share of L2 that leaves room for K, V and the other sections' tails.
+    const ListShape l = list_shape(p.B, p.H, p.HKV, p.S, p.subgroup, p.record);
+    if (l.n_items != p.n_items || l.n_items > (1ll << 30)) {
+        set_error("bwd_main_sm100: a work list of %lld items, %d laid out", static_cast<long long>(l.n_items), p.n_items);
+        return FOLD_ERR_ARGUMENT;
+    }
+    constexpr int64_t kSectionBytes = 48ll << 20;
+    const int64_t trip_bytes = static_cast<int64_t>(p.S) * sm100::HD * (2 + 2 + 4) * p.subgroup;
+    const int sec = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(kSectionBytes / std::max<int64_t>(trip_bytes, 1), 64)));
+    const int n_sections = static_cast<int>((l.n_trip + sec - 1) / sec);
+    if (build_list) sm100::bwd_work_list_kernel<<<n_sections, 256, 0, st>>>(p, static_cast<int>(l.n_trip), l.nsub, l.nb_max, l.nrec, sec);
+    if (!run_main) return check_launch("bwd_work_list");
+    static int sms[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    const int grid = static_cast<int>(std::min<int64_t>(std::max(sms[dev], 1), l.n_items));
     if (f16) {
         auto kern = sm100::bwd_main_sm100_kernel<true>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm100::SMEM_BYTES);

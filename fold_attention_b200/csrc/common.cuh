@@ -81,6 +81,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // stats[b, h_kv, i] are float bits, zero before the call.
 enum { ST_K = 0, ST_V = 1, ST_DO = 2, ST_DELTA = 3, ST_DOC = 4, ST_Q = 5, N_STATS = 8 };
 constexpr int DQ_BITS = 30;
+constexpr int DKV_BITS = 61;   // dK's grid, and dV's when a group's column mass G * S can pass 16384
 
 // 2^(bits - ceil(log2(bound * (1 + 2^-6)))), clamped to [2^-100, 2^100]; a
 // zero bound takes 2^100. Every step is one rounded fp32 instruction or an
@@ -122,6 +123,20 @@ __device__ __forceinline__ int dq_scale_exp(const int* stats, float cd) {
     float dl = __int_as_float(stats[ST_DELTA]);
     float s = __fadd_rn(__fmul_rn(dn, __fmul_rn(v, cd)), dl);
     return pow2_scale_exp(__fmul_rn(s, k), DQ_BITS);
+}
+// dK's and dV's grid exponents for one (request, KV head), used when a key block's dK / dV are
+// summed across CTAs (src/fold_attention/backward/grid.py:86-100). `rows` = G * sequence length
+// bounds the column mass sum_{h,i} P_hij; dV's bound is rows * max |dO_id|, dK's
+// rows * (||dO||max * C_D * |V|max + |Delta|max) * |Q|max.
+__device__ __forceinline__ int dv_scale_exp(const int* stats, float rows, int bits) {
+    return pow2_scale_exp(__fmul_rn(rows, __int_as_float(stats[ST_DOC])), bits);
+}
+__device__ __forceinline__ int dk_scale_exp(const int* stats, float rows, float cd) {
+    float v = __int_as_float(stats[ST_V]);
+    float dn = __int_as_float(stats[ST_DO]);
+    float dl = __int_as_float(stats[ST_DELTA]);
+    float s = __fadd_rn(__fmul_rn(dn, __fmul_rn(v, cd)), dl);
+    return pow2_scale_exp(__fmul_rn(rows, __fmul_rn(s, __int_as_float(stats[ST_Q]))), DKV_BITS);
 }
 __device__ __forceinline__ float pow2f(int e) { return __int_as_float((e + 127) << 23); }
 #endif

@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define FOLD_B200_ABI_VERSION 1
+#define FOLD_B200_ABI_VERSION 2
 
 #define FOLD_OK 0
 #define FOLD_ERR_ARGUMENT 1
@@ -186,43 +186,62 @@ int fold_decode_run_static(const int8_t* qa, const int8_t* qb, const float* eq, 
  * batch stride 0 and cu_seqlens (batch+1) int32 on the device. lse is fp32 in
  * nats, (B, H, S) dense or (H, total) packed. */
 
-/* Bytes of scratch fold_bwd_run needs (the int32 dQ accumulator, Delta,
- * lse*log2e and the per-(request, KV head) maxima).
+/* How a call's work is cut for the tcgen05 main loop: `subgroup` query heads (a divisor of the
+ * group; 0 = the whole group) and `record` query blocks of 128 rows (0 = every block that sees the
+ * key block) per work item. With the whole group and the whole range a key block's dK and dV stay
+ * inside one CTA; otherwise its work items round their sums onto the (request, KV head)'s dK / dV
+ * integer grids and add them into int64 (dV: int32 while group * max_seqlen <= 16384)
+ * accumulators in the workspace, which the postprocess converts. Integer adds commute, so the
+ * gradients are the same bits in any execution order either way; they do depend on the plan.
+ * Replaces: src/fold_attention/backward/plan.py:58-118 (Plan), launch.py:172-213. The mma.sync
+ * main loop takes only (0, 0). */
+
+/* Bytes of scratch fold_bwd_run needs (the int32 dQ accumulator, Delta, lse*log2e, the
+ * per-(request, KV head) maxima, the work list and, for a folding plan, the dK / dV accumulators);
+ * 0 for an impossible plan.
  * Replaces the allocations of src/fold_attention/backward/launch.py:186-216. */
 size_t fold_bwd_workspace_bytes(int batch, int n_heads, int n_kv_heads, int max_seqlen, int total,
-                                int head_dim, int varlen);
+                                int head_dim, int varlen, int subgroup, int record);
 
-/* Byte offsets of the workspace's parts (dq_acc, dpsum, lse2, stats), the
- * padded row count per head, and the byte offset of the int32 status word
- * (non-zero after a call in which a device-side wait ran out), for callers
- * that inspect the accumulators. out6: host, six entries. */
+/* Byte offsets of the workspace's parts, for callers that inspect the accumulators. out11: host,
+ * eleven entries: [0..3] dq_acc, dpsum, lse2, stats; [4] padded rows per head; [5] the int32
+ * status word (non-zero after a call in which a device-side wait ran out); [6], [7] the dK and dV
+ * accumulators; [8] dV's accumulator width in bits (0: the plan does not fold); [9] the work list
+ * (eight int32 per item: key block, KV head, request, first head, heads, first and one-past-last
+ * query block, cost in tiles), [10] its length. */
 int fold_bwd_workspace_layout(int batch, int n_heads, int n_kv_heads, int max_seqlen, int total,
-                              int head_dim, int varlen, int64_t* out6);
+                              int head_dim, int varlen, int subgroup, int record, int64_t* out11);
 
-/* dQ, dK, dV of causal or full self-attention: preprocess, main loop and
+/* dQ, dK, dV of causal or full self-attention: preprocess, work list, main loop and
  * postprocess on `stream`, no host synchronisation.
  * Replaces: src/fold_attention/backward/launch.py:75-117 (prepare_backward) and
- * the run() closure :410-435; kernels backward/preprocess.py, kernel.py,
+ * the run() closure :410-435; kernels backward/preprocess.py, kernel.py, scheduler.py,
  * postprocess.py. strides: q, k, v, o, dout, dq, dk, dv (24 entries). */
 int fold_bwd_run(const void* q, const void* k, const void* v, const void* o, const void* dout,
                  const float* lse, void* dq, void* dk, void* dv, const int64_t* strides /* host */,
                  const int32_t* cu_seqlens, int batch, int n_heads, int n_kv_heads, int max_seqlen,
                  int total, int head_dim, int causal, int is_f16, float softmax_scale,
-                 void* workspace, size_t workspace_bytes, int kernel, void* stream);
+                 void* workspace, size_t workspace_bytes, int kernel, int subgroup, int record,
+                 void* stream);
 
 /* fold_bwd_run one phase at a time (a bit mask), so a caller can put events
  * between the preprocess, the main loop and the postprocess. The phases of
- * one backward must run in order on one stream with the same arguments.
- * No counterpart in the reference: its launch closure runs all three. */
+ * one backward must run in order on one stream with the same arguments
+ * (PRE, LIST, MAIN, POST; LIST writes the tcgen05 main loop's work list into the
+ * workspace, where it stays valid until the shapes or cu_seqlens change, and does
+ * nothing for the other main loop).
+ * No counterpart in the reference: its launch closure runs all of them. */
 #define FOLD_BWD_PHASE_PRE 1
 #define FOLD_BWD_PHASE_MAIN 2
 #define FOLD_BWD_PHASE_POST 4
+#define FOLD_BWD_PHASE_LIST 8
 int fold_bwd_run_phases(const void* q, const void* k, const void* v, const void* o,
                         const void* dout, const float* lse, void* dq, void* dk, void* dv,
                         const int64_t* strides /* host */, const int32_t* cu_seqlens, int batch,
                         int n_heads, int n_kv_heads, int max_seqlen, int total, int head_dim,
                         int causal, int is_f16, float softmax_scale, void* workspace,
-                        size_t workspace_bytes, int kernel, int phases, void* stream);
+                        size_t workspace_bytes, int kernel, int subgroup, int record, int phases,
+                        void* stream);
 
 /* Cycle counters of the tcgen05 backward's main loop, summed over the launches since the
  * last reset: out24 (host, 24 entries) receives CTAs, tiles, CTA lifetime, prologue, epilogue,

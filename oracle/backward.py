@@ -4,7 +4,7 @@ backward. Test infrastructure only.
 `reference_grads` is the FP64 autograd statement the reference's tests hold
 (tests/test_backward.py:79-92; the FP32 twin is
 benchmarks/harness/training.py:124-164). The grid functions restate
-src/fold_attention/backward/grid.py:41-83, which exists only as device code in
+src/fold_attention/backward/grid.py:41-100, which exists only as device code in
 the reference: pure functions of four maxima, evaluated one rounded fp32
 operation at a time, so they are exact; parity with the reference's integer
 accumulator *bits* is unpinned (those depend on tensor-core summation order).
@@ -44,6 +44,23 @@ def dq_scale_exp(max_k, max_v, max_do_norm, max_delta, D: int) -> int:
     t = F32(F32(max_do_norm) * F32(F32(max_v) * F32(root_d(D))))
     s = F32(t + F32(max_delta))
     return pow2_scale_exp(F32(s * F32(max_k)), DQ_BITS)
+
+
+DKV_BITS = 61
+
+
+def dv_scale_exp(max_doc, rows, bits: int) -> int:
+    """dV's grid exponent when a key block's dV is summed across CTAs (grid.py:86-90):
+    bound = rows * max |dO_id|, rows = G * sequence length bounding the column mass."""
+    return pow2_scale_exp(F32(F32(rows) * F32(max_doc)), bits)
+
+
+def dk_scale_exp(max_v, max_do_norm, max_delta, max_q, rows, D: int) -> int:
+    """dK's grid exponent on its 61-bit grid (grid.py:93-100):
+    bound = rows * (||dO||max * C_D * |V|max + |Delta|max) * |Q|max."""
+    t = F32(F32(max_do_norm) * F32(F32(max_v) * F32(root_d(D))))
+    s = F32(t + F32(max_delta))
+    return pow2_scale_exp(F32(F32(rows) * F32(s * F32(max_q))), DKV_BITS)
 
 
 def stats(q, k, v, o, do, G):

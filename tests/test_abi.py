@@ -28,12 +28,17 @@ def test_every_declared_symbol_is_exported():
 def test_bad_arguments_return_a_status_and_a_message():
     from fold_attention_b200 import _lib
 
-    rc = _lib.lib.fold_bwd_workspace_layout(1, 1, 1, 1, 1, 64, 0, None)
+    rc = _lib.lib.fold_bwd_workspace_layout(1, 1, 1, 1, 1, 64, 0, 0, 0, None)
     assert rc == 1
     assert b"null pointer" in _lib.lib.fold_last_error()
     # sizes are computed on the host: no GPU needed
-    n = _lib.lib.fold_bwd_workspace_bytes(4, 32, 32, 8192, 4 * 8192, 128, 0)
+    n = _lib.lib.fold_bwd_workspace_bytes(4, 32, 32, 8192, 4 * 8192, 128, 0, 0, 0)
     assert n >= 4 * 32 * 8192 * 128 * 4
+    # a folding plan (MQA cut four heads at a time) adds the int64 dK and dV accumulators and a longer list
+    private = _lib.lib.fold_bwd_workspace_bytes(2, 32, 1, 8192, 2 * 8192, 128, 0, 0, 0)
+    folded = _lib.lib.fold_bwd_workspace_bytes(2, 32, 1, 8192, 2 * 8192, 128, 0, 4, 0)
+    assert folded >= private + 2 * 8 * 2 * 8192 * 128
+    assert _lib.lib.fold_bwd_workspace_bytes(2, 32, 1, 8192, 2 * 8192, 128, 0, 5, 0) == 0   # 5 does not divide 32
 
 
 def test_python_signatures_cover_the_header():

@@ -226,7 +226,7 @@ def test_grid_exponent_accumulator_and_postprocess(kernel):
     run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True, kernel=kernel)
     dq, dk, dv = run()
     torch.cuda.synchronize()
-    off_acc, off_dp, off_l2, off_st, rows_p, _ = run.layout
+    off_acc, off_dp, off_l2, off_st, rows_p = run.layout[:5]
     ws = run.workspace
     stats = ws[off_st: off_st + B * HKV * 8 * 4].view(torch.float32).view(B, HKV, 8).cpu()
     acc = ws[off_acc: off_acc + H * rows_p * D * 4].view(torch.int32).view(H, rows_p, D)
@@ -296,14 +296,16 @@ def test_a_shard_of_kv_heads_is_the_full_runs_bits():
     k, v = (torch.randn(B, S, HKV, D, device="cuda").bfloat16() for _ in range(2))
     o, lse = attention_forward(q, k, v, causal=True)
     tr = lambda x: x.transpose(1, 2)
-    full = tuple(tr(x).clone() for x in prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True)())
+    whole = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True)
+    plan = whole.plan          # every rank runs the full call's plan on its slice
+    full = tuple(tr(x).clone() for x in whole())
     world = 3
     for rank in range(world):
         for b, (lo, hi) in parallel.backward_units(B, HKV, world, rank).items():
             qs, os_, dos = (x[b:b + 1, :, lo * G:hi * G].contiguous() for x in (q, o, do))
             ks, vs = (x[b:b + 1, :, lo:hi].contiguous() for x in (k, v))
             ls = lse[b:b + 1, lo * G:hi * G].contiguous()
-            part = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True)()
+            part = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True, plan=plan)()
             dq, dk, dv = (tr(x) for x in part)
             assert torch.equal(dq, full[0][b:b + 1, :, lo * G:hi * G])
             assert torch.equal(dk, full[1][b:b + 1, :, lo:hi])
@@ -331,7 +333,8 @@ def test_config2_full_size_repeats_and_matches_a_slice():
     qs, os_, dos = (x[b:b + 1, :, hk * G:(hk + 1) * G].contiguous() for x in (q, o, do))
     ks, vs = (x[b:b + 1, :, hk:hk + 1].contiguous() for x in (k, v))
     ls = lse[b:b + 1, hk * G:(hk + 1) * G].contiguous()
-    dq, dk, dv = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True)()
+    # the unit alone would plan for one small call: hold the full run's plan, as any comparison across batch sizes must
+    dq, dk, dv = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True, plan=run.plan)()
     assert torch.equal(dq, first[0][b:b + 1, hk * G:(hk + 1) * G])
     assert torch.equal(dk, first[1][b:b + 1, hk:hk + 1])
     assert torch.equal(dv, first[2][b:b + 1, hk:hk + 1])
@@ -359,7 +362,7 @@ def test_config2_mha_full_size_repeats_and_matches_a_slice():
     for b, h in ((3, 17), (0, 0)):
         qs, ks, vs, os_, dos = (x[b:b + 1, :, h:h + 1].contiguous() for x in (q, k, v, o, do))
         ls = lse[b:b + 1, h:h + 1].contiguous()
-        part = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True)()
+        part = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True, plan=run.plan)()
         for x, y in zip(part, first):
             assert torch.equal(x, y[b:b + 1, h:h + 1])
     ref = ob.reference_grads(qs[0], ks[0], vs[0], dos[0], scale=1.0 / math.sqrt(D), dtype=torch.float32)
