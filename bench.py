@@ -3,19 +3,30 @@ keys, the paged decode) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-One JSON line on stdout. A step is one backward (preprocess + main loop +
-postprocess) over the headline configuration (config 2): batch 4, seqlen 8192, 32 query / 32 KV
-heads, head_dim 128, bf16, causal; inputs iid N(0,1) with 1/sqrt(D) on q, O and
-LSE from the library's own forward, computed before the timed region. At
-N > 1 every rank runs that workload on its own shard (weak scaling; the path
-shards over batch x KV head with no collective on the data path).
+One JSON line on stdout. A step is one backward (preprocess, work list, main
+loop, postprocess) over the headline configuration (config 2): batch 4, seqlen
+8192, 32 query / 32 KV heads, head_dim 128, bf16, causal; inputs iid N(0,1)
+with 1/sqrt(D) on q, O and LSE from the library's own forward, computed before
+the timed region. At N > 1 every rank runs that workload on its own shard (weak
+scaling; the path shards over batch x KV head with no collective on the data
+path), and the extra keys add the same work sharded: config 2's (request, KV
+head) units split over the ranks, and config 5's 256 requests partitioned by
+length.
+
+Timing: `value` is the mean of K steps inside one region bracketed by barriers
+and synchronisation (the contract of this file); `extra.timing` repeats the
+measurement the way the reference's harness does (CUDA-graph replays, 21 rounds
+after dropped warm-ups, median: benchmarks/harness/timing.py:117-170) and over
+a region of at least two seconds, each with the SM clock sampled while it ran.
 """
 
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -29,6 +40,7 @@ import torch  # noqa: E402
 CFG = dict(B=4, S=8192, H=32, HKV=32, D=128)
 WORKLOAD = "config2 causal det. backward B{B} S8192 H32/32 D128 bf16"
 METRIC = "det. causal bwd TFLOP/s"
+KERNELS_PER_STEP = 5   # preprocess, its finalize pass, work list, main loop, dQ postprocess
 
 
 def flops(B, S, H, D):
@@ -43,6 +55,16 @@ def peaks():
         return dict(bf16=d["bf16_tflops_sustained"], bf16_burst=d["bf16_tflops"], hbm=d["hbm_gbs"],
                     which="measured")
     return dict(bf16=1400.0, bf16_burst=1590.0, hbm=6650.0, which="fallback")
+
+
+def profiled(name, key, default):
+    """A number kept in a tracked ncu summary (`profiles/<name>`), written there as `key = value`."""
+    try:
+        text = open(os.path.join(ROOT, "profiles", name)).read()
+        m = re.search(rf"^\s*{re.escape(key)}\s*=\s*([0-9.eE+-]+)", text, flags=re.M)
+        return float(m.group(1)) if m else default
+    except OSError:
+        return default
 
 
 class Clocks:
@@ -67,12 +89,8 @@ class Clocks:
         for line in self.proc.stdout:
             self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
 
-    def stop(self, t0, t1):
-        if self.proc is None:
-            return None
-        time.sleep(0.15)
-        self.proc.terminate()
-        rows = [r for ts, r in self.rows if t0 - 0.05 <= ts <= t1 + 0.15] or [r for _, r in self.rows[-3:]]
+    def window(self, t0, t1):
+        rows = [r for ts, r in self.rows if t0 - 0.02 <= ts <= t1 + 0.05] or [r for _, r in self.rows[-3:]]
         if not rows:
             return None
         mhz = sorted(int(r[0]) for r in rows if r[0].isdigit())
@@ -81,6 +99,13 @@ class Clocks:
         return dict(sm_mhz=mhz[len(mhz) // 2] if mhz else None,
                     sm_max_mhz=int(rows[0][1]) if rows[0][1].isdigit() else None,
                     reasons=reasons, samples=len(rows))
+
+    def stop(self, t0=None, t1=None):
+        if self.proc is None:
+            return None
+        time.sleep(0.1)
+        self.proc.terminate()
+        return self.window(t0, t1) if t0 is not None else None
 
 
 def make_inputs(cfg, device, seed):
@@ -93,14 +118,23 @@ def make_inputs(cfg, device, seed):
     return q, k, v, do
 
 
-def time_backward(cfg, device, steps, warmup, seed, dist):
-    """(ms per step, main-kernel ms per launch, launches per step, run)."""
+def tr(x):
+    return x.transpose(1, 2)
+
+
+def prepare(cfg, device, seed, plan=None):
     from fold_attention_b200.backward import attention_forward, prepare_backward
 
     q, k, v, do = make_inputs(cfg, device, seed)
     o, lse = attention_forward(q, k, v, causal=True)
-    tr = lambda x: x.transpose(1, 2)  # noqa: E731
-    run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True)
+    run = prepare_backward(tr(q), tr(k), tr(v), tr(o), tr(do), lse, causal=True, plan=plan)
+    return (q, k, v, o, do, lse, run)
+
+
+def time_backward(state, steps, warmup, dist):
+    """(ms per step, main-kernel ms per launch, host window): K steps in one region, the three
+    phases of each between events on the launching stream."""
+    run = state[-1]
     for _ in range(warmup):
         run()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
@@ -119,10 +153,90 @@ def time_backward(cfg, device, steps, warmup, seed, dist):
         ev[i][3].record()
     torch.cuda.synchronize()
     t1 = time.time()
+    if dist is not None:
+        dist.barrier()
     total = ev[0][0].elapsed_time(ev[-1][3]) / steps
     main = sum(e[1].elapsed_time(e[2]) for e in ev) / steps
-    # per step: the statistics' memset, preprocess, its finalize pass, main loop, postprocess
-    return total, main, 5, (q, k, v, o, do, lse, run), (t0, t1)
+    return total, main, (t0, t1)
+
+
+def time_protocols(state, device, clocks, ms_hint):
+    """The same step the way the reference's harness times a kernel, and over a long region.
+
+    graph: the whole step captured once in a CUDA graph; 3 dropped warm-up replays, then 21
+    replays each between its own events; median. long: back-to-back steps for at least two
+    seconds of device time (where the SM clock settles under the power limit). Each carries the
+    SM clock sampled while it ran and TFLOP/s per GHz, so burst and sustained read off one line."""
+    run = state[-1]
+    fl = flops(CFG["B"], CFG["S"], CFG["H"], CFG["D"])
+    out = {}
+    side = torch.cuda.Stream(device)
+    g = torch.cuda.CUDAGraph()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            run()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        g.replay()
+    rounds = 21
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(rounds)]
+    torch.cuda.synchronize()
+    t0 = time.time()
+    for a, b in ev:
+        a.record()
+        g.replay()
+        b.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = sorted(a.elapsed_time(b) for a, b in ev)
+    med = ms[rounds // 2]
+    ck = clocks.window(t0, t1) or {}
+    out["graph_median"] = dict(ms_per_step=med, tflops=fl / med / 1e9, rounds=rounds, dropped=3, min_ms=ms[0], max_ms=ms[-1],
+                               sm_mhz=ck.get("sm_mhz"), tflops_per_ghz=(fl / med / 1e9) / (ck["sm_mhz"] / 1e3) if ck.get("sm_mhz") else None)
+    n = max(8, int(math.ceil(2200.0 / max(ms_hint, 1e-3))))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    e0.record()
+    for _ in range(n):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    msl = e0.elapsed_time(e1) / n
+    ck = clocks.window(t0 + 0.5, t1) or {}
+    out["long_region"] = dict(ms_per_step=msl, tflops=fl / msl / 1e9, steps=n, seconds=e0.elapsed_time(e1) / 1e3,
+                              sm_mhz=ck.get("sm_mhz"), reasons=ck.get("reasons"),
+                              tflops_per_ghz=(fl / msl / 1e9) / (ck["sm_mhz"] / 1e3) if ck.get("sm_mhz") else None)
+    del g
+    return out
+
+
+def headline_check(state, device):
+    """One (request, head) unit of the timed workload against FP32 autograd attention in plain
+    torch on the GPU (outside every timed region): rel-L2 of dQ, dK, dV."""
+    q, k, v, o, do, lse, run = state
+    dq, dk, dv = run()
+    b, h = CFG["B"] - 1, 17 % CFG["H"]
+    hk = h * CFG["HKV"] // CFG["H"]
+    S, D = CFG["S"], CFG["D"]
+    qs = q[b, :, h].float().requires_grad_()
+    ks = k[b, :, hk].float().requires_grad_()
+    vs = v[b, :, hk].float().requires_grad_()
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        s = (qs @ ks.T) / D**0.5
+        s = s.masked_fill(torch.ones(S, S, device=device, dtype=torch.bool).triu(1), float("-inf"))
+        (s.softmax(-1) @ vs).backward(do[b, :, h].float())
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    rel = lambda a, r: ((a.double() - r.double()).norm() / r.double().norm()).item()  # noqa: E731
+    out = dict(unit=[b, h], reference="torch fp32 autograd on the GPU", status=int(run.status), dq=rel(dq[b, h], qs.grad))
+    if CFG["H"] == CFG["HKV"]:   # an MHA unit's dK, dV are that head's alone
+        out.update(dk=rel(dk[b, hk], ks.grad), dv=rel(dv[b, hk], vs.grad))
+    return out
 
 
 def time_e2e(cfg, device, steps, state):
@@ -137,7 +251,6 @@ def time_e2e(cfg, device, steps, state):
 
     q, k, v, o, do, lse, run0 = state
     host_in = [t.detach().cpu().pin_memory() for t in (q, k, v, o, do, lse)]
-    tr = lambda x: x.transpose(1, 2)  # noqa: E731
     slots = []
     for i in range(2):
         dev = (q, k, v, o, do, lse) if i == 0 else tuple(torch.empty_like(t) for t in (q, k, v, o, do, lse))
@@ -184,6 +297,51 @@ def time_e2e(cfg, device, steps, state):
     ms = e0.elapsed_time(e1) / steps
     del slots
     return ms, h2d, d2h
+
+
+def copy_bandwidth(device, dist):
+    """Pinned host <-> device copy bandwidth of this rank with every rank copying at once (what the
+    end-to-end leg leans on): GB/s in and out, 1 GiB each way."""
+    n = 1 << 30
+    host = torch.empty(n, dtype=torch.uint8).pin_memory()
+    dev = torch.empty(n, dtype=torch.uint8, device=device)
+    dev.copy_(host, non_blocking=True)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    res = []
+    for src, dst in ((host, dev), (dev, host)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            dst.copy_(src, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        res.append(3 * n / e0.elapsed_time(e1) / 1e6)
+    return res
+
+
+def bwd_shape_extra(device, B, H, HKV, steps=4, plan=None, seed=99):
+    """Another shape of the same backward (GQA, MQA, small batch): whole step, with the plan it ran."""
+    cfg = dict(CFG, B=B, H=H, HKV=HKV)
+    state = prepare(cfg, device, seed, plan)
+    run = state[-1]
+    for _ in range(3):
+        run()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    fl = flops(B, cfg["S"], H, cfg["D"])
+    out = dict(workload=f"B{B} S8192 H{H}/{HKV} D128 causal", ms_per_step=ms, tflops=fl / ms / 1e9,
+               plan=[run.plan.subgroup, run.plan.record], folds=run.dk_acc is not None, status=int(run.status))
+    del state
+    torch.cuda.empty_cache()
+    return out
 
 
 def train_extra(device, steps=3):
@@ -247,7 +405,7 @@ def varlen_extra(device, steps=3):
     ms = e0.elapsed_time(e1) / steps
     fl = 5.0 * H * D * sum(n * n for n in lens)
     return dict(workload=f"config3 packed causal backward H32/8 D128 {len(lens)} sequences, {total} tokens",
-                ms_per_step=ms, tflops=fl / ms / 1e9)
+                ms_per_step=ms, tflops=fl / ms / 1e9, status=int(run.status))
 
 
 def cpu_reference_tflops(seconds_limit=12.0):
@@ -271,90 +429,266 @@ def cpu_reference_tflops(seconds_limit=12.0):
     return flops(1, S, H, D) / dt / 1e12, f"B1 H4 S{S} D{D} causal FP32 autograd x{n}, scaled by FLOPs"
 
 
-def decode_extra(device, steps=8, B=32, dense=False, kernel="auto", seed=5):
-    """Config 5's decode (extra keys, not the headline; B=256 is the config's own batch):
-    v8, depth 16, GQA 64/8, D128, lengths log-uniform in [4096, 131072]; or with
-    `dense` config 4's shape: bf16 V, depth None, GQA 32/8, lengths uniform in
-    [1024, 32768]."""
-    import math
+# ---- the decode extras ---------------------------------------------------------------------
 
+def decode_lengths(kind, B, seed=5):
+    """The config's request lengths: config 5 log-uniform in [4096, 131072], config 4 uniform in
+    [1024, 32768]; one seeded draw, so every rank of a sharded run sees the same batch."""
+    g = torch.Generator().manual_seed(seed)
+    if kind == "config4":
+        return torch.randint(1024, 32769, (B,), generator=g).tolist()
+    return [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
+
+
+def request_kv(n, HKV, D, device, seed, tail=False):
+    """One request's prompt K, V from its own seed (a rank can draw any request alone): N(0,1),
+    1 % of key positions x 8, 0.1 % of V entries x 20. `tail`: a heavy-tailed key distribution in
+    place of the x 8 keys (2 % of positions far above the rest: few live keys at depth 16, as on
+    the model captures the reference publishes its decode rows for)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    kk = torch.randn(n, HKV, D, device=device, generator=g)
+    if tail:
+        boost = torch.rand(n, 1, 1, device=device, generator=g)
+        kk = kk * torch.where(boost < 0.02, 8.0, 0.15)
+    else:
+        hot = torch.rand(n, 1, 1, device=device, generator=g) < 0.01
+        kk = torch.where(hot, kk * 8, kk)
+    vv = torch.randn(n, HKV, D, device=device, generator=g)
+    out = torch.rand(n, HKV, D, device=device, generator=g) < 0.001
+    return kk.bfloat16(), torch.where(out, vv * 20, vv).bfloat16()
+
+
+def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail=False, with_e2e=True, B=None, seed=5):
+    """A decode config end to end: cache write, then `steps` serving steps (one token appended per
+    request per step, then attention), timed as one region; us/step is the mean over the steps.
+
+    config5: v8, depth 16, GQA 64/8, D128, 256 requests; config4: bf16 V, depth None, GQA 32/8,
+    128 requests. `ids` picks a subset of the batch's requests (a rank's shard). Returns the step
+    time, the kernel's own counts, the roofline on algorithmic bytes, the clocks while it ran, the
+    error of sampled requests against dense FP32 attention, and `e2e`: the same steps through
+    `fold_attn_with_kvcache` with q, k, v in pinned host memory and the output copied back."""
+    import fold_attention_b200 as fa
     from fold_attention_b200 import FoldKVCache
 
+    dense = kind == "config4"
     H, HKV, D = (32, 8, 128) if dense else (64, 8, 128)
-    # the pool is sized by the longest request for every request: halve the batch until the pool and
-    # the prompt tensors fit beside what is already on the device
-    free = torch.cuda.mem_get_info(device)[0]
-    top = 32768 if dense else 131072
-    while B > 8 and B * (top + 256) * HKV * (642 if dense else 514) * 1.30 + (6 << 30) > free:
-        B //= 2
-    g = torch.Generator().manual_seed(seed)
+    full = B or (128 if dense else 256)
+    lens_all = decode_lengths(kind, full, seed)
+    ids = list(range(full)) if ids is None else list(ids)
+    lens = [lens_all[i] for i in ids]
+    Bn = len(lens)
+    kw = dict(device=device, kernel=kernel)
     if dense:
-        lens = torch.randint(1024, 32769, (B,), generator=g).tolist()
-        c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, device=device, kernel=kernel,
-                        chunk=4096 if kernel == "mma" else None)
+        c = FoldKVCache(Bn, H, HKV, D, max(lens) + 2 * steps + 16, chunk=4096 if kernel == "mma" else None, **kw)
     else:
-        lens = [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
-        c = FoldKVCache(B, H, HKV, D, max(lens) + steps + 2, depth=16.0, v8=True, device=device, kernel=kernel,
-                        chunk=8192 if kernel == "mma" else None)
+        # a fixed V scale, as every shard of a sharded layer must use (2^-3 covers |v| <= 56 at 448 / 8)
+        c = FoldKVCache(Bn, H, HKV, D, max(lens) + 2 * steps + 16, depth=16.0, v8=True, v_scale=2.0 ** -3,
+                        chunk=8192 if kernel == "mma" else None, **kw)
     gd = torch.Generator(device=device).manual_seed(seed + 1)
     pages = c.page_table.shape[1]
-    perm = torch.randperm(B * pages, device=device, generator=gd).int().view(B, pages)
-    c.page_table.copy_(perm)
+    c.page_table.copy_(torch.randperm(Bn * pages, device=device, generator=gd).int().view(Bn, pages))
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=device, dtype=torch.int32)
     T = sum(lens)
-    # request by request: the fp32 draws of a whole large batch would not fit beside the pool
     k = torch.empty(T, HKV, D, device=device, dtype=torch.bfloat16)
     v = torch.empty(T, HKV, D, device=device, dtype=torch.bfloat16)
     at = 0
-    for n in lens:
-        kk = torch.randn(n, HKV, D, device=device, generator=gd)
-        hot = torch.rand(n, 1, 1, device=device, generator=gd) < 0.01
-        k[at:at + n] = torch.where(hot, kk * 8, kk)
-        vv = torch.randn(n, HKV, D, device=device, generator=gd)
-        out = torch.rand(n, HKV, D, device=device, generator=gd) < 0.001
-        v[at:at + n] = torch.where(out, vv * 20, vv)
+    for i, n in zip(ids, lens):   # request by request: the fp32 draws of a whole batch would not fit beside the pool
+        k[at:at + n], v[at:at + n] = request_kv(n, HKV, D, device, 1000 * seed + i, tail)
         at += n
-    del kk, vv, hot, out
-    c.write_prompt(k, v, cu, lens)
-    # the two shortest and the longest request's prompts, kept to check the steps' output afterwards
-    order = sorted(range(B), key=lambda b: lens[b])
-    sample = {b: (k[int(cu[b]):int(cu[b + 1])].clone(), v[int(cu[b]):int(cu[b + 1])].clone()) for b in order[:2] + order[-1:]}
-    del k, v
-    q = torch.randn(B, H, D, device=device, generator=gd).bfloat16()
-    kn = torch.randn(B, HKV, D, device=device, generator=gd).bfloat16()
-    vn = torch.randn(B, HKV, D, device=device, generator=gd).bfloat16()
-    for _ in range(2):
-        c.decode(q, kn, vn)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c.write_prompt(k, v, cu, lens)
     torch.cuda.synchronize()
+    e0.record()
+    c.write_prompt(k, v, cu, lens)
+    e1.record()
+    torch.cuda.synchronize()
+    write_us = e0.elapsed_time(e1) * 1e3
+    order = sorted(range(Bn), key=lambda b: lens[b])
+    picks = sorted({order[0], order[1 % Bn], order[Bn // 8], order[Bn // 4], order[Bn // 2], order[(3 * Bn) // 4], order[-2 % Bn],
+                    order[-1]})
+    sample = {b: (k[int(cu[b]):int(cu[b + 1])].clone(), v[int(cu[b]):int(cu[b + 1])].clone()) for b in picks}
+    del k, v
+    torch.cuda.empty_cache()
+    q = torch.randn(Bn, H, D, device=device, generator=gd).bfloat16()
+    kn = torch.randn(Bn, HKV, D, device=device, generator=gd).bfloat16()
+    vn = torch.randn(Bn, HKV, D, device=device, generator=gd).bfloat16()
+    for _ in range(3):
+        c.decode(q, kn, vn)
+    clocks = Clocks(device.index or 0)
+    torch.cuda.synchronize()
+    t0 = time.time()
     e0.record()
     for _ in range(steps):
         out = c.decode(q, kn, vn)
     e1.record()
     torch.cuda.synchronize()
+    t1 = time.time()
+    ck = clocks.stop(t0, t1)
     us = e0.elapsed_time(e1) / steps * 1e3
-    # the last step against dense FP32 attention over everything written (rel-L2, worst sampled request)
-    G, err = H // HKV, 0.0
+    done = 3 + steps
+    # the last step against dense FP32 attention over everything written (rel-L2 per sampled request)
+    G, errs = H // HKV, []
     for b, (kp, vp) in sample.items():
-        ks = torch.cat([kp, kn[b][None].expand(2 + steps, -1, -1)]).float()
-        vs = torch.cat([vp, vn[b][None].expand(2 + steps, -1, -1)]).float()
+        ks = torch.cat([kp, kn[b][None].expand(done, -1, -1)]).float()
+        vs = torch.cat([vp, vn[b][None].expand(done, -1, -1)]).float()
         qs = q[b].float().view(HKV, G, D)
         w = torch.softmax(torch.einsum("hgd,shd->hgs", qs, ks) / D**0.5, -1)
         want = torch.einsum("hgs,shd->hgd", w, vs).reshape(H, D)
-        err = max(err, ((out[b].float() - want).norm() / want.norm()).item())
-    del sample
+        errs.append(((out[b].float() - want).norm() / want.norm()).item())
     keys = sum(c.lens) * HKV
     live = c.counts[:, 0].sum().item() / keys
     refk = c.counts[:, 1].sum().item() / keys
     vb = 2 * D if dense else D
     byts = keys * (D + 2 + D * refk + vb * live)
-    name = (f"config4-shaped decode bf16 dense B{B} H32/8 D128 lens U[1024,32768] " +
-            ("chunk4096" if kernel == "mma" else "default split") if dense else
-            f"config5-shaped decode v8 depth16 B{B} H64/8 D128 lens logU[4096,131072] " +
-            ("chunk8192" if kernel == "mma" else "default split"))
-    return dict(workload=name, kernel="/".join(sorted({l.kernel for l in c._launches.values()})),
-                us_per_step=us, keys=keys, live_fraction=live, refined_fraction=refk, rel_l2_vs_fp32=err,
-                algorithmic_gbs=byts / us / 1e3, hbm_frac=byts / us / 1e3 / peaks()["hbm"])
+    pk = peaks()
+    launch_kernels = sorted({l.kernel for l in c._launches.values()})
+    status = max(int(l.status) for l in c._launches.values())
+    ratio = profiled("decode_sm100_kernel_configs4_5.md", "dram_bytes_over_algorithmic_bytes", None)
+    res = dict(
+        workload=(f"config4 decode bf16 dense B{Bn} H32/8 D128 lens U[1024,32768]" if dense else
+                  f"config5 decode v8 depth16 B{Bn} H64/8 D128 lens logU[4096,131072]") + (" heavy-tailed keys" if tail else "")
+                 + f", {steps} steps, page 256 shuffled",
+        kernel="/".join(launch_kernels), us_per_step=us, steps=steps, keys=keys, live_fraction=live, refined_fraction=refk,
+        rel_l2_vs_fp32=max(errs), rel_l2_requests=len(errs), status=status, write_prompt_us=write_us, tokens_written=T,
+        roofline=dict(bound="hbm", achieved=byts / us / 1e3, peak=pk["hbm"], unit="GB/s", frac=byts / us / 1e3 / pk["hbm"],
+                      traffic=(ratio * byts if ratio else None),
+                      note=f"algorithmic bytes per step from the kernel's own counts, of {pk['which']} copy bandwidth; traffic = "
+                           "the ncu DRAM/algorithmic ratio of a small capture (profiles/) times the step's algorithmic bytes"),
+        clocks=ck, gpu_launches=4 * steps,   # append + Q planes, mass reference, decode, combine
+    )
+    res["algorithmic_gbs"], res["hbm_frac"] = res["roofline"]["achieved"], res["roofline"]["frac"]
+    if with_e2e:
+        hq, hk, hv = (t.cpu().pin_memory() for t in (q, kn, vn))
+        ho = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        dq_, dk_, dv_ = (torch.empty_like(t) for t in (q, kn, vn))
+        n2 = max(4, steps // 4)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n2):
+            dq_.copy_(hq, non_blocking=True)
+            dk_.copy_(hk, non_blocking=True)
+            dv_.copy_(hv, non_blocking=True)
+            ho.copy_(fa.fold_attn_with_kvcache(dq_, c, dk_, dv_), non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        res["e2e"] = dict(value=e0.elapsed_time(e1) / n2 * 1e3, unit="us/step",
+                          h2d_bytes_per_step=sum(t.numel() * t.element_size() for t in (hq, hk, hv)),
+                          d2h_bytes_per_step=ho.numel() * ho.element_size(), steps=n2)
+    del c, sample
+    torch.cuda.empty_cache()
+    return res
+
+
+def write_prompt_extra(device):
+    """The prompt writer on the shape the reference publishes a row for (235 us on H100, eager, with
+    host planning: 32 prompts of 2048 tokens, 4 KV heads, D128, 8-bit V)."""
+    from fold_attention_b200 import FoldKVCache
+
+    B, L, H, HKV, D = 32, 2048, 32, 4, 128
+    c = FoldKVCache(B, H, HKV, D, L + 8, depth=16.0, v8=True, page_size=128, device=device)
+    g = torch.Generator(device=device).manual_seed(12)
+    k = torch.randn(B * L, HKV, D, device=device, generator=g).bfloat16()
+    v = torch.randn(B * L, HKV, D, device=device, generator=g).bfloat16()
+    cu = torch.arange(B + 1, device=device, dtype=torch.int32) * L
+    lens = [L] * B
+    for _ in range(3):
+        c.write_prompt(k, v, cu, lens)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    n = 20
+    for _ in range(n):
+        c.write_prompt(k, v, cu, lens)
+    e1.record()
+    torch.cuda.synchronize()
+    wall = (time.time() - t0) / n * 1e6
+    us = e0.elapsed_time(e1) / n * 1e3
+    byts = B * L * HKV * (2 * D * 2 + 4 * D + 2)   # k, v read (bf16); four planes and a scale written
+    return dict(workload="write_prompt 8-bit V, 32 x 2048 tokens, 4 KV heads, D128", us_device=us, us_wall_with_host_planning=wall,
+                gbs=byts / us / 1e3, hbm_frac=byts / us / 1e3 / peaks()["hbm"])
+
+
+# ---- sharded extras (N > 1) ------------------------------------------------------------------
+
+def sharded_backward_extra(device, dist, world, rank, steps=4):
+    """Config 2's (request, KV head) units split over the ranks (`parallel.backward_units`): every
+    rank draws the same seeded workload and runs its own slice under the full call's plan; the step
+    time is the slowest rank's. One unit is then gathered to rank 0 and compared, bit for bit, with
+    that unit run alone there."""
+    from fold_attention_b200 import parallel
+    from fold_attention_b200.backward import attention_forward, prepare_backward
+    from fold_attention_b200.backward.plan import plan_dense
+
+    cfg = dict(CFG, HKV=8)      # the GQA variant: 32 units of four heads
+    B, S, H, HKV, D = (cfg[k] for k in ("B", "S", "H", "HKV", "D"))
+    G = H // HKV
+    plan = plan_dense(B, H, HKV, S, D, True)
+    units = parallel.backward_units(B, HKV, world, rank)
+    q, k, v, do = make_inputs(cfg, device, 4321)      # the same on every rank
+    runs = []
+    for b, (lo, hi) in units.items():
+        qs, dos = (x[b:b + 1, :, lo * G:hi * G].contiguous() for x in (q, do))
+        ks, vs = (x[b:b + 1, :, lo:hi].contiguous() for x in (k, v))
+        os_, ls = attention_forward(qs, ks, vs, causal=True)
+        runs.append((b, lo, hi, prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True, plan=plan)))
+    for _ in range(2):
+        for r in runs:
+            r[3]()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0.record()
+    for _ in range(steps):
+        for r in runs:
+            r[3]()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    # the unit (request B-1, KV head HKV-1) lives on the last rank: its dK travels to rank 0
+    b, h = B - 1, HKV - 1
+    got = torch.empty(1, 1, S, D, device=device, dtype=torch.bfloat16)
+    if rank == world - 1:
+        own = [r for r in runs if r[0] == b and r[1] <= h < r[2]][0]
+        got.copy_(own[3]()[1][:, h - own[1]:h - own[1] + 1])
+    dist.broadcast(got, src=world - 1)
+    same = None
+    if rank == 0:
+        qs, dos = (x[b:b + 1, :, h * G:(h + 1) * G].contiguous() for x in (q, do))
+        ks, vs = (x[b:b + 1, :, h:h + 1].contiguous() for x in (k, v))
+        os_, ls = attention_forward(qs, ks, vs, causal=True)
+        alone = prepare_backward(tr(qs), tr(ks), tr(vs), tr(os_), tr(dos), ls, causal=True, plan=plan)()
+        same = bool(torch.equal(alone[1], got))
+    ms = t.item()
+    return dict(workload=f"config2 GQA B4 S8192 H32/8: {B * HKV} (request, KV head) units over {world} ranks, strong scaling",
+                ms_per_step=ms, tflops=flops(B, S, H, D) / ms / 1e9, units_this_rank=sum(hi - lo for lo, hi in units.values()),
+                gathered_unit_equals_single_gpu_run=same)
+
+
+def sharded_decode_extra(device, dist, world, rank, steps=64):
+    """Config 5's 256 requests (one seeded batch), partitioned over the ranks by length
+    (`parallel.balance`); the step time is the slowest rank's."""
+    from fold_attention_b200 import parallel
+
+    lens = decode_lengths("config5", 256)
+    part = parallel.balance(lens, world)[rank]
+    try:
+        d = decode_extra(device, "config5", ids=part, steps=steps, with_e2e=False)
+        t = torch.tensor([d["us_per_step"], 0.0], device=device, dtype=torch.float64)
+        u = torch.tensor([d["keys"], d["roofline"]["achieved"] * d["us_per_step"]], device=device, dtype=torch.float64)
+    except Exception as e:   # a rank that cannot hold its shard must not hang the others
+        d = dict(error=repr(e))
+        t = torch.tensor([float("inf"), 1.0], device=device, dtype=torch.float64)
+        u = torch.zeros(2, device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.all_reduce(u, op=dist.ReduceOp.SUM)
+    if t[1].item() != 0.0:
+        return d if "error" in d else dict(error="a rank failed")
+    us = t[0].item()
+    return dict(workload=f"config5 decode, the same 256 requests over {world} ranks balanced by length, {steps} steps",
+                kernel=d["kernel"], us_per_step=us, keys=int(u[0].item()), algorithmic_gbs=u[1].item() / us,
+                hbm_frac_per_gpu=u[1].item() / us / world / peaks()["hbm"], requests_this_rank=len(part))
 
 
 def run_reference(args):
@@ -382,15 +716,16 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
-    ap.add_argument("--no-extra", action="store_true", help="skip the decode extra keys")
+    ap.add_argument("--no-extra", action="store_true", help="skip the extra keys")
     ap.add_argument("--batch", type=int, default=CFG["B"],
                     help="batch of the backward workload (config 2 is 4; 1 gives the small case ncu captures)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--decode-only", action="store_true",
-                    help="run only the config-5-shaped decode (extra keys) and print its dict")
-    ap.add_argument("--decode-batch", type=int, default=32)
+    ap.add_argument("--decode-only", action="store_true", help="run only one decode extra and print its dict")
+    ap.add_argument("--decode-batch", type=int, default=None)
+    ap.add_argument("--decode-steps", type=int, default=64)
     ap.add_argument("--decode-kernel", default="auto", choices=("auto", "mma", "sm100"))
     ap.add_argument("--decode-dense", action="store_true", help="config 4's shape instead of config 5's")
+    ap.add_argument("--decode-tail", action="store_true", help="heavy-tailed keys: few live keys at depth 16")
     args = ap.parse_args()
     CFG["B"] = args.batch
     if args.impl == "reference":
@@ -399,8 +734,9 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.decode_only:
         torch.cuda.set_device(0)
-        print(json.dumps(decode_extra(torch.device("cuda", 0), steps=max(2, args.steps), B=args.decode_batch,
-                                      dense=args.decode_dense, kernel=args.decode_kernel)), flush=True)
+        print(json.dumps(decode_extra(torch.device("cuda", 0), "config4" if args.decode_dense else "config5",
+                                      steps=max(2, args.decode_steps), B=args.decode_batch, kernel=args.decode_kernel,
+                                      tail=args.decode_tail, with_e2e=False)), flush=True)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -414,13 +750,17 @@ def main():
 
         dist.init_process_group("nccl", device_id=device)
     clocks = Clocks(local)
-    ms, main_ms, launches, state, (t0, t1) = time_backward(CFG, device, args.steps, args.warmup, 1234 + rank, dist)
-    ck = clocks.stop(t0, t1)
+    state = prepare(CFG, device, 1234 + rank)
+    ms, main_ms, (t0, t1) = time_backward(state, args.steps, args.warmup, dist)
+    ck = clocks.window(t0, t1)
     fl = flops(CFG["B"], CFG["S"], CFG["H"], CFG["D"])
     t = torch.tensor([ms, main_ms], device=device, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max, main_max = t.tolist()
+    timing = time_protocols(state, device, clocks, ms) if (rank == 0 and not args.no_extra) else None
+    check = headline_check(state, device) if rank == 0 else None
+    clocks.stop()
     if args.no_e2e:
         e2e_ms, h2d, d2h = float("nan"), 0, 0
     else:
@@ -429,63 +769,65 @@ def main():
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_max = t.item()
+    plan = state[-1].plan
     del state
     torch.cuda.empty_cache()
     pk = peaks()
+    achieved = fl / main_max / 1e9
+    traffic1 = profiled("bwd_main_sm100_config2.md", "dram_bytes_per_launch_batch1", None)
     line = dict(
         metric=METRIC, value=world * fl / ms_max / 1e9, unit="TFLOP/s", n_gpus=world, steps=args.steps,
         warmup=args.warmup, ms_per_step=ms_max, higher_is_better=True, scaling="weak", vs_baseline=None,
         dtype="bf16", data="synthetic",
         config=dict(workload=WORKLOAD.format(B=CFG["B"]), l2="inputs (1.3 GB) larger than L2", shard="batch x KV head, one workload per rank"),
         e2e=dict(value=world * fl / e2e_max / 1e9, unit="TFLOP/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
-        gpu_launches=launches * args.steps,
+        gpu_launches=KERNELS_PER_STEP * args.steps,
         clocks=ck,
-        roofline=dict(bound="tensor", achieved=fl / main_max / 1e9, peak=pk["bf16"], unit="TFLOP/s",
-                      frac=fl / main_max / 1e9 / pk["bf16"],
-                      # dram__bytes_read + write of one main-loop launch: 631.1 MB in an ncu capture at
-                      # batch 1, scaled by the batch (the traffic is per request)
-                      traffic=631.1e6 * CFG["B"],
-                      note=f"main-loop kernel, of {pk['which']} sustained bf16 GEMM; burst peak {pk['bf16_burst']}; "
-                           "traffic in bytes per launch, scaled from a batch-1 ncu capture"),
+        roofline=dict(bound="tensor", achieved=achieved, peak=pk["bf16_burst"], unit="TFLOP/s",
+                      frac=achieved / pk["bf16_burst"], frac_of_sustained=achieved / pk["bf16"],
+                      frac_of_nominal_2250=achieved / 2250.0,
+                      # dram__bytes_read + write of one main-loop launch in the batch-1 ncu capture kept in
+                      # profiles/, times the batch (the traffic is per request)
+                      traffic=(traffic1 * CFG["B"] if traffic1 else None),
+                      note=f"main-loop kernel (work list included); peak = {pk['which']} burst bf16 GEMM (the timed region is "
+                           f"short: the clock has not settled under the power limit), sustained {pk['bf16']}; traffic in bytes "
+                           "per launch = the batch-1 ncu capture in profiles/ times the batch"),
     )
+    extra = dict(plan=[plan.subgroup, plan.record], headline_check=check)
+    if timing:
+        extra["timing"] = timing
     if rank == 0 and world == 1 and not args.no_e2e:
         val, sample = cpu_reference_tflops()
         line["cpu_baseline"] = dict(value=val, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port", sample=sample)
-        if not args.no_extra:
-            gqa = dict(CFG, HKV=8)
-            ms_g, main_g, _, st_g, _ = time_backward(gqa, device, max(2, args.steps // 2), 3, 99, None)
-            del st_g
+    if rank == 0 and world == 1 and not args.no_extra:
+        for key, fn in (("gqa_32_8", lambda: bwd_shape_extra(device, 4, 32, 8)),
+                        ("mqa_b2_32_1", lambda: bwd_shape_extra(device, 2, 32, 1)),
+                        ("small_batch_b1_32_8", lambda: bwd_shape_extra(device, 1, 32, 8)),
+                        ("varlen_config3", lambda: varlen_extra(device)),
+                        ("train_fwd_bwd", lambda: train_extra(device)),
+                        ("write_prompt", lambda: write_prompt_extra(device)),
+                        ("decode_config5", lambda: decode_extra(device, "config5")),
+                        ("decode_config4", lambda: decode_extra(device, "config4")),
+                        ("decode_config5_few_live_keys", lambda: decode_extra(device, "config5", B=64, tail=True, with_e2e=False))):
+            try:
+                extra[key] = fn()
+            except Exception as e:  # the headline stands on its own
+                extra[key] = dict(error=repr(e))
             torch.cuda.empty_cache()
-            line["extra"] = dict(gqa_32_8=dict(ms_per_step=ms_g, tflops=fl / ms_g / 1e9))
-            for key, fn in (("varlen_config3", lambda: varlen_extra(device)),
-                            ("train_fwd_bwd", lambda: train_extra(device)),
-                            ("decode_config5", lambda: decode_extra(device, steps=6, B=256)),
-                            ("decode_config4", lambda: decode_extra(device, B=128, dense=True))):
-                try:
-                    line["extra"][key] = fn()
-                except Exception as e:  # the headline stands on its own
-                    line["extra"][key] = dict(error=repr(e))
-                torch.cuda.empty_cache()
     if world > 1 and not args.no_extra:
-        # the decode path sharded over requests: config 5's shape, 32 requests per rank (8 ranks hold
-        # its 256), every rank its own lengths; the step time is the slowest rank's
-        try:
-            d = decode_extra(device, seed=5 + 2 * rank)
-            t = torch.tensor([d["us_per_step"], 0.0], device=device, dtype=torch.float64)
-            u = torch.tensor([d["keys"], d["algorithmic_gbs"] * d["us_per_step"]], device=device, dtype=torch.float64)
-        except Exception as e:
-            d = dict(error=repr(e))
-            t = torch.tensor([float("inf"), 1.0], device=device, dtype=torch.float64)
-            u = torch.zeros(2, device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.all_reduce(u, op=dist.ReduceOp.SUM)
-        if t[1].item() == 0.0:
-            us = t[0].item()
-            line["extra"] = dict(decode_config5=dict(
-                workload=d["workload"].replace("B32", f"B{32 * world} (32 per rank)"), kernel=d["kernel"], us_per_step=us,
-                keys=int(u[0].item()), algorithmic_gbs=u[1].item() / us, hbm_frac_per_gpu=u[1].item() / us / world / pk["hbm"]))
-        else:
-            line["extra"] = dict(decode_config5=d if "error" in d else dict(error="a rank failed"))
+        for key, fn in (("sharded_backward", lambda: sharded_backward_extra(device, dist, world, rank)),
+                        ("decode_config5", lambda: sharded_decode_extra(device, dist, world, rank))):
+            try:
+                extra[key] = fn()
+            except Exception as e:
+                extra[key] = dict(error=repr(e))
+            torch.cuda.empty_cache()
+        bw = torch.tensor(copy_bandwidth(device, dist), device=device, dtype=torch.float64)
+        allbw = [torch.zeros_like(bw) for _ in range(world)]
+        dist.all_gather(allbw, bw)
+        extra["pinned_copy_gbs_per_rank"] = dict(h2d=[round(x[0].item(), 1) for x in allbw], d2h=[round(x[1].item(), 1) for x in allbw],
+                                                 note="every rank copying 1 GiB each way at once")
+    line["extra"] = extra
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -280,6 +280,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int fmt, int M, int N, int a_m
 
 struct Maps {
     CUtensorMap q, dout, k, v;   // (channel, row, head, batch), boxes (64, 128, 1, 1)
+    CUtensorMap dk, dv;          // the same view of the outputs, for the private exit's tile stores
     CUtensorMap dq;              // the int32 accumulator as (channel, head * padded row), boxes (32, 128)
 };
 
@@ -342,6 +343,21 @@ __device__ __forceinline__ Item load_item(const BwdParams& p, int idx) {
     it.per_head = (it.n0 < it.sq.len) ? max(min(nm, c.z) - it.m_first, 0) : 0;
     it.total = it.per_head * it.nh;
     return it;
+}
+
+// Whether any of the `count` threads meeting at named barrier `id` wants to stop. The threads of
+// a role leave their item loop together or not at all: they share named barriers inside it, and a
+// thread that left alone (it saw the abort flag a moment before its neighbours did) would leave the
+// others waiting at one for ever.
+__device__ __forceinline__ bool any_stops(bool stop, int id, int count) {
+    uint32_t r;
+    asm volatile("{ .reg .pred p, q; setp.ne.b32 p, %1, 0; barrier.cta.red.or.pred q, %2, %3, p; selp.u32 %0, 1, 0, q; }"
+                 : "=r"(r) : "r"(static_cast<uint32_t>(stop)), "r"(id), "r"(count) : "memory");
+    return r != 0;
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
 // x * 2^e for any e in [-250, 250] without leaving fp32's exponent range half way
@@ -602,7 +618,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         int t = 0;
         for (int j = 0;; ++j) {
             const int idx = next_item(j);
-            if (idx < 0) break;
+            if (any_stops(idx < 0, 6, NCOMPUTE)) break;
             const Item it = load_item(p, idx);
             const int kj = it.n0 + r;
             for (int i = 0; i < it.total; ++i, ++t) {
@@ -712,8 +728,51 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
                 const int s_exp = dq_scale_exp(st, root_d(HD));
                 const uint32_t src = tmem + lane_addr + (is_dv ? T_DV : T_DK) + c0;
                 const bool ok = it.n0 + r < it.sq.len;
-                if (!p.fold) {
-                    auto pk2 = [](float a, float b2) { return F16 ? pack_f16x2(a, b2) : pack_bf16x2(a, b2); };
+                auto pk2 = [](float a, float b2) { return F16 ? pack_f16x2(a, b2) : pack_bf16x2(a, b2); };
+                if (NWG == 2 && !p.fold && it.n0 + BN <= it.sq.len) {
+                    // A whole key block: the 16-bit tile goes through shared memory in the swizzled layout of
+                    // the loads, 64 channels (16 KB) at a time, and one thread per warpgroup stores each half
+                    // with TMA: 32 KB in two instructions instead of 2048 scattered 16-byte stores. Each
+                    // warpgroup stages in its own half of dS~'s buffer -- the half it alone writes in the dS~
+                    // phase, free now that every MMA that read it has retired -- so dK and dV leave side by
+                    // side and neither group waits for the other. (A sequence's last, partial block keeps
+                    // the per-thread stores below: a tile store would write past the sequence's end in a
+                    // packed tensor.)
+                    const float un = F16 ? 1.f : pow2f(-s_exp);
+                    const float f = is_dv ? un : p.scale * un;
+                    const uint32_t buf = base + SM_DS + wg * 16384;
+                    const int brow = it.sq.start + it.n0, bb = p.cu ? 0 : it.b;
+#pragma unroll
+                    for (int box = 0; box < 2; ++box) {
+#pragma unroll
+                        for (int cc = 0; cc < 2; ++cc) {
+                            uint32_t v[32], pk[16];
+                            tmem_ld32(src + 64 * box + 32 * cc, v);
+                            tmem_wait_ld();
+                            if (box == 1 && cc == 1) {   // the last read of the accumulators: the next item may overwrite them
+                                tc_fence_before();
+                                mbar_arrive(sh.bar(B_ACCFREE));
+                            }
+#pragma unroll
+                            for (int q = 0; q < 32; q += 2) pk[q >> 1] = pk2(__uint_as_float(v[q]) * f, __uint_as_float(v[q + 1]) * f);
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const uint32_t a = buf + r * 128 + (static_cast<uint32_t>((cc * 4 + u) ^ (r & 7)) << 4);
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pk[4 * u]), "r"(pk[4 * u + 1]),
+                                             "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3]) : "memory");
+                            }
+                        }
+                        fence_async_smem();
+                        if (is_dv) asm volatile("bar.sync 3, 128;" ::: "memory"); else asm volatile("bar.sync 2, 128;" ::: "memory");
+                        if ((warp & 3) == 2 && lane == 0) {   // warps 2 and 6: each group's first warp
+                            tma_store_4d(is_dv ? &maps.dv : &maps.dk, buf, 64 * box, brow, it.hkv, bb);
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        }
+                        // the half has been read out: the group may stage the next one (or, after the second, its dS~)
+                        if (is_dv) asm volatile("bar.sync 3, 128;" ::: "memory"); else asm volatile("bar.sync 2, 128;" ::: "memory");
+                    }
+                } else if (!p.fold) {
                     const float un = F16 ? 1.f : pow2f(-s_exp);
                     const float f = is_dv ? un : p.scale * un;
                     uint16_t* dst = row_ptr<uint16_t>(is_dv ? p.dv : p.dk, it.b, it.sq.start + it.n0 + (ok ? r : 0), it.hkv) + c0;
@@ -776,6 +835,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
             if (counting) c_epi += clock64() - t_f;
 #endif
         }
+        if ((warp & 3) == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the tile stores have landed
 #ifdef FOLD_BWD_COUNTERS
         if (counting) {
             CNT_ADD(5, c_ws);
@@ -886,7 +946,7 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
         int t = 0;
         for (int j = 0;; ++j) {
           const int idx = next_item(j);
-          if (idx < 0) break;
+          if (any_stops(idx < 0, 7, 128)) break;
           const Item it = load_item(p, idx);
           if (F16) dq_mul = pow2f(dq_scale_exp(p.stats + (static_cast<int64_t>(it.b) * p.HKV + it.hkv) * N_STATS, root_d(HD)));
           for (int i = 0; i < it.total; ++i, ++t) {
@@ -977,13 +1037,19 @@ bwd_main_sm100_kernel(const BwdParams p, const __grid_constant__ Maps maps) {
 // one-past-last query block, cost in tiles). Entries are grouped in sections of `sec`
 // (request, KV head, subgroup) triples -- the CTAs running at any time then share few heads' Q,
 // dO and dQ, which stay in L2 -- and sorted by cost, longest first, inside each section, so
-// that the persistent CTAs end every section, and the launch, on short items. Built on the
+// that the persistent CTAs end every section, and the launch, on short items. The last sections
+// are merged into one that holds about a wave of the longest items (one per SM), so the launch's
+// last long items start while there is still a wave of work behind them. Built on the
 // device from cu_seqlens, in-stream: no host synchronisation, and a captured graph replays it.
 constexpr int WL_BINS = 1024;
-__global__ void __launch_bounds__(256) bwd_work_list_kernel(const BwdParams p, int n_trip, int nsub, int nb_max, int nrec, int sec) {
+__global__ void __launch_bounds__(256) bwd_work_list_kernel(const BwdParams p, int n_trip, int nsub, int nb_max, int nrec, int sec,
+                                                            int tail_trip) {
     __shared__ int hist[WL_BINS];
     __shared__ int offs[WL_BINS];
-    const int t0 = blockIdx.x * sec, t1 = min(t0 + sec, n_trip);
+    // the last block sorts the merged tail (the last `tail_trip` triples as one section)
+    const bool tail = blockIdx.x == gridDim.x - 1;
+    const int body = n_trip - tail_trip;
+    const int t0 = tail ? body : blockIdx.x * sec, t1 = tail ? n_trip : min(t0 + sec, body);
     const int per = nb_max * nrec;
     const int count = (t1 - t0) * per;
     int* out = const_cast<int*>(p.work) + static_cast<int64_t>(t0) * per * 8;
@@ -1112,6 +1178,7 @@ int launch_bwd_main_sm100(const BwdParams& p, bool build_list, bool run_main, cu
     const bool f16 = p.f16;
     if (!make_map(&maps.q, p.q, rows, p.H, batch, sm100::BM, f16) || !make_map(&maps.dout, p.dout, rows, p.H, batch, sm100::BM, f16) ||
         !make_map(&maps.k, p.k, rows, p.HKV, batch, sm100::BN, f16) || !make_map(&maps.v, p.v, rows, p.HKV, batch, sm100::BN, f16) ||
+        !make_map(&maps.dk, p.dk, rows, p.HKV, batch, sm100::BN, f16) || !make_map(&maps.dv, p.dv, rows, p.HKV, batch, sm100::BN, f16) ||
         !make_acc_map(&maps.dq, p)) {
         set_error("bwd_main_sm100: cuTensorMapEncodeTiled failed");
         return FOLD_ERR_LAUNCH;
@@ -1127,14 +1194,19 @@ int launch_bwd_main_sm100(const BwdParams& p, bool build_list, bool run_main, cu
     constexpr int64_t kSectionBytes = 48ll << 20;
     const int64_t trip_bytes = static_cast<int64_t>(p.S) * sm100::HD * (2 + 2 + 4) * p.subgroup;
     const int sec = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(kSectionBytes / std::max<int64_t>(trip_bytes, 1), 64)));
-    const int n_sections = static_cast<int>((l.n_trip + sec - 1) / sec);
-    if (build_list) sm100::bwd_work_list_kernel<<<n_sections, 256, 0, st>>>(p, static_cast<int>(l.n_trip), l.nsub, l.nb_max, l.nrec, sec);
-    if (!run_main) return check_launch("bwd_work_list");
     static int sms[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    // the merged tail: a triple holds about nb (nb + 1) / 2 blocks per head under a causal mask and its
+    // longest item nb, so a wave of longest items is 2 * SMs / (nb + 1) triples; within twice the budget
+    const int64_t wave = (2ll * sms[dev] + l.nb_max) / (l.nb_max + 1);
+    const int tail_trip = static_cast<int>(std::min<int64_t>(l.n_trip, std::max<int64_t>(sec, std::min<int64_t>(wave, 2 * kSectionBytes / std::max<int64_t>(trip_bytes, 1)))));
+    const int n_sections = static_cast<int>((l.n_trip - tail_trip + sec - 1) / sec) + 1;
+    if (build_list)
+        sm100::bwd_work_list_kernel<<<n_sections, 256, 0, st>>>(p, static_cast<int>(l.n_trip), l.nsub, l.nb_max, l.nrec, sec, tail_trip);
+    if (!run_main) return check_launch("bwd_work_list");
     const int grid = static_cast<int>(std::min<int64_t>(std::max(sms[dev], 1), l.n_items));
     if (f16) {
         auto kern = sm100::bwd_main_sm100_kernel<true>;

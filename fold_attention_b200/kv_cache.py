@@ -24,6 +24,11 @@ from .decode.heuristics import (
     weight_terms_for,
 )
 from .decode.launch import mass_z, prepare_fold_decode
+from .utils import Launch
+
+
+class ReplayStep(Launch):
+    """`prepare_replay_step`'s result: calling it runs the step again."""
 
 BN = 64  # keys per decode tile: a fixed `chunk` is a multiple of it
 
@@ -60,7 +65,10 @@ class FoldKVCache:
     short requests' launch cannot fill the GPU by itself), so it is off.
 
     The decode tail (`tail` >= 0, a rank-r K->V model of dropped mass on a
-    bf16 V) is not built: `tail` must resolve to None. `check_range` reads each
+    bf16 V) is not built: with `tail="auto"` a bf16 V at a finite depth runs
+    WITHOUT the reference's default tail (dropped mass re-enters at V's mean
+    instead; a warning says so once), and an explicit `tail` >= 0 raises.
+    `check_range` reads each
     step's denominators on the host and reruns the rows whose reference sat
     outside `[0.5, 2^60]` (`2^100` on a bf16 V) of their mass.
     """
@@ -143,7 +151,14 @@ class FoldKVCache:
         if tail == "auto":
             tail = tail_rank_for(D, self.group, self.v8) if depth is not None else -1
             if tail >= 0:
-                tail = None  # the K-predicted tail is not built: dropped mass re-enters at V's mean
+                # the K-predicted tail is not built: dropped mass re-enters at V's mean. This differs from
+                # the reference's default for a bf16 V at a finite depth, so say it rather than only document it
+                import warnings
+
+                warnings.warn(
+                    f"FoldKVCache(depth={depth}, v8=False): the reference's default rank-{tail} decode tail is not built; "
+                    "dropped mass re-enters at V's mean (pass tail=None to silence this)", RuntimeWarning, stacklevel=2)
+                tail = None
         self.tail_rank = -1 if tail is None else int(tail)
         if self.tail_rank >= 0:
             if depth is None:
@@ -239,6 +254,128 @@ class FoldKVCache:
         self._step(q, k, v)
         self.lens = [x + 1 for x in self.lens]
         return self._run(q, split)
+
+    # ---- replay and tuning helpers (src/fold_attention/kv_cache.py:441-570) ----
+
+    def prepare_replay_decode(self, split=None, out_dtype=torch.float32):
+        """A repeatable decode-only launch over the last step's front state
+        (Q planes, lengths, a copy of its reference), for timing: its outputs
+        and partial buffers are its own, so replaying it leaves the layer's
+        state untouched. `out_dtype` is the output it writes, so a benchmark
+        times the launch it scores. Returns the launch (`(out, den, counts)`)."""
+        split = self._resolve_split(split)
+        refine = self._refine()
+        truncate = self.depth is not None
+        kernel = self.kernel
+        if kernel == "auto" and 2 * sum(n for n in self.lens if n >= self.SM100_MIN_KEYS) < sum(self.lens):
+            kernel = "mma"
+        return prepare_fold_decode(
+            self.qa, self.qb, self.eq, self.ka, self.kb, self.ek, self.va, self.z.clone(), self.cut,
+            split=split, truncate=truncate, refine_k=refine[0], refine_v=refine[1], v8=self.v8, v2=self.vb,
+            v_scale=self.v_scale, vmean=self.vmean.clone() if truncate else None, page_table=self.page_table,
+            page_size=self.page_size, seq_lens=self.seq_lens.clone(), n_kv_heads=self.n_kv_heads, reference="given",
+            weight_terms=self.weight_terms, order=self.order.clone(), out_dtype=out_dtype,
+            refine_bands=refine_bands_for(self.v8, head_dim=self.head_dim, group=self.group) if self._banded() else (),
+            chunk_keys=self.chunk or 0, kernel=kernel,
+        )
+
+    def prepare_replay_step(self, q, k=None, v=None, split=None, at=None):
+        """A repeatable full step on private buffers, for timing under CUDA
+        graphs. The returned launch writes Q's planes and, with `k` and `v`,
+        the token at `at` (the current lengths by default) WITHOUT advancing
+        the lengths, estimates the reference and runs the decode. Its lengths,
+        reference and running V sums are its own; only the token's cache slot
+        and the Q planes are rewritten, with the same values every time."""
+        if (k is None) != (v is None):
+            raise ValueError("k and v are both given or both left out")
+        qf = q.reshape(-1, self.head_dim)
+        at = (self.seq_lens if at is None else at).clone()
+        appends = k is not None
+        if appends and int(at.max()) >= self.max_len:
+            raise ValueError(f"a replay position is at max_len={self.max_len}")
+        lens_out = torch.empty_like(at)
+        vsum = self.vsum.clone() if appends else self.vsum
+        vmean = self.vmean.clone() if appends else self.vmean
+        vsum0, vmean0 = (vsum.clone(), vmean.clone()) if appends else (None, None)
+        z = self.z.clone()
+        seen = lens_out if appends else at          # the lengths the decode reads
+        split = self._resolve_split(split)
+        refine = self._refine(int(at.max()) + int(appends))
+        truncate = self.depth is not None
+        out_dtype = q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.float32
+        kernel = self.kernel
+        if kernel == "auto" and 2 * sum(n for n in self.lens if n >= self.SM100_MIN_KEYS) < sum(self.lens):
+            kernel = "mma"
+        decode = prepare_fold_decode(
+            self.qa, self.qb, self.eq, self.ka, self.kb, self.ek, self.va, z, self.cut,
+            split=split, truncate=truncate, refine_k=refine[0], refine_v=refine[1], v8=self.v8, v2=self.vb,
+            v_scale=self.v_scale, vmean=vmean if truncate else None, page_table=self.page_table,
+            page_size=self.page_size, seq_lens=seen, n_kv_heads=self.n_kv_heads, reference="given",
+            weight_terms=self.weight_terms, order=self.order.clone(), out_dtype=out_dtype,
+            refine_bands=refine_bands_for(self.v8, head_dim=self.head_dim, group=self.group) if self._banded() else (),
+            chunk_keys=self.chunk or 0, kernel=kernel,
+        )
+        shape = (self.batch, self.n_heads, self.head_dim)
+
+        def replay():
+            if appends:   # the running sums start from the same state every replay
+                vsum.copy_(vsum0)
+                vmean.copy_(vmean0)
+            write.step(
+                qf, k, v, self.qa.view(-1, self.head_dim), self.qb.view(-1, self.head_dim), self.eq.view(-1), self.ek,
+                self.page_table, self.page_size, at, self.ka, self.kb, self.va, self.vb, self.v_scale, vsum, vmean, lens_out,
+            )
+            mass_z(self.qa, self.qb, self.eq, self.ka, self.ek, self.page_table, self.page_size, seen, self.n_kv_heads, z)
+            o, den, counts = decode.run()
+            return o.view(shape), den, counts
+
+        launch = ReplayStep(replay, (qf, k, v, at, lens_out, vsum, vmean, vsum0, vmean0, z, decode))
+        launch.status = decode.status
+        launch.decode = decode
+        return launch
+
+    def tune_split(self, candidates=(4, 6, 8, 10, 12, 14, 16, 20, 24, 32), rounds=7, reps=10):
+        """Time the decode at each split in `candidates` and at the default
+        one, on the cache as it stands, and keep the fastest as `split`.
+        Each candidate is replayed from a CUDA graph (the host's enqueue is
+        not what is timed), in rotating order across `rounds` so a drifting
+        clock cancels; the replays write only buffers of their own. Returns
+        `{split: us}`."""
+        if self.chunk is not None:
+            raise ValueError("a fixed chunk sets the split: there is nothing to tune")
+        tiles = -(-(sum(self.lens) // self.batch) // BN)
+        auto = self._auto_split()
+        cands = sorted({auto} | {int(c) for c in candidates if -(-tiles // int(c)) >= 4})
+        graphs, runs = {}, {}
+        for sp in cands:
+            run = self.prepare_replay_decode(sp)
+            runs[sp] = run      # a graph keeps device addresses, not the tensors that own them
+            for _ in range(2):
+                run()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    run()
+            graphs[sp] = g
+        torch.cuda.synchronize()
+        times = {sp: [] for sp in cands}
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        for r in range(rounds):
+            order = cands[r % len(cands):] + cands[: r % len(cands)]
+            for sp in order:
+                graphs[sp].replay()
+                ev[0].record()
+                for _ in range(reps):
+                    graphs[sp].replay()
+                ev[1].record()
+                ev[1].synchronize()
+                times[sp].append(ev[0].elapsed_time(ev[1]) * 1e3 / reps)
+        med = {sp: sorted(t)[len(t) // 2] for sp, t in times.items()}
+        self.split = min(med, key=lambda sp: med[sp])
+        self._launches.clear()
+        return med
 
     # ---- internals -------------------------------------------------------
 
