@@ -543,7 +543,7 @@ def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail
     pk = peaks()
     launch_kernels = sorted({l.kernel for l in c._launches.values()})
     status = max(int(l.status) for l in c._launches.values())
-    ratio = profiled("decode_sm100_kernel_configs4_5.md", "dram_bytes_over_algorithmic_bytes", None)
+    ratio = profiled("decode_sm100_kernel_configs4_5.md", "dram_bytes_over_algorithmic_bytes_" + ("bf16" if dense else "v8"), None)
     res = dict(
         workload=(f"config4 decode bf16 dense B{Bn} H32/8 D128 lens U[1024,32768]" if dense else
                   f"config5 decode v8 depth16 B{Bn} H64/8 D128 lens logU[4096,131072]") + (" heavy-tailed keys" if tail else "")
@@ -759,7 +759,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max, main_max = t.tolist()
     timing = time_protocols(state, device, clocks, ms) if (rank == 0 and not args.no_extra) else None
-    check = headline_check(state, device) if rank == 0 else None
+    check = headline_check(state, device) if (rank == 0 and not args.no_extra) else None
     clocks.stop()
     if args.no_e2e:
         e2e_ms, h2d, d2h = float("nan"), 0, 0

@@ -56,9 +56,20 @@
 namespace fold {
 namespace dsm100 {
 
+#ifndef FOLD_DEC_RING
+#define FOLD_DEC_RING 5
+#endif
+#ifndef FOLD_DEC_HDK
+#define FOLD_DEC_HDK 4
+#endif
 constexpr int TK = 128;          // keys per tile
 constexpr int HD = 128;
-constexpr int QD = 8;            // tiles of helper masks in flight
+#ifndef FOLD_DEC_QD
+#define FOLD_DEC_QD 32
+#endif
+// tiles of helper masks in flight: how far a helper may fall behind the key threads (its tiles come
+// every NHELP-th, with a bursty number of keys each) before they have to wait for it
+constexpr int QD = FOLD_DEC_QD;
 constexpr int NHELP = 4;
 constexpr int HSLOT = 528;       // a staging slot: Ka, Kb, Va, Vb rows of 128 bytes, the scale's word, the key's note
 constexpr int NBQ = 8;            // tiles of quarter flags (and their barrier) in flight: more than the key threads can lead by
@@ -75,11 +86,13 @@ constexpr int SM_Q = 0;                               // [16 rows][128 B] int8, 
 constexpr int HOUT = (8 * 128 + 8) * 4;               // a helper's sums: [8 rows][128 channels], [8] floats
 template <bool V8>
 struct Lay {
-    static constexpr int NA = V8 ? 5 : 4;             // ring slots of K's plane A
-    static constexpr int NV = V8 ? 5 : 4;             // ring slots of V (plane A) and the key scales
+    static constexpr int NA = V8 ? FOLD_DEC_RING : 4;   // ring slots of K's plane A
+    static constexpr int NV = V8 ? FOLD_DEC_RING : 4;   // ring slots of V (plane A) and the key scales
     static constexpr int VBYTES = V8 ? 16384 : 32768; // a V slot: [128 keys][128 B], or two 64-channel boxes of that
     static constexpr int NB2E = V8 ? NB2 : 0;
-    static constexpr int HD_KEYS = V8 ? 4 : 8;        // keys whose rows a helper has in flight into its staging slots
+    // keys whose rows a helper has in flight into its staging slots: four random 128-byte reads a key, each
+    // about a microsecond away, so the depth of this queue is what the helpers' rate comes to
+    static constexpr int HD_KEYS = V8 ? FOLD_DEC_HDK : 8;
     static constexpr int HPASS = V8 ? 1 : 4;          // keys a helper takes in one pass, when that many are in flight
     static constexpr int SM_KA = 2048;                           // NA x Ka [128 keys][128 B]
     static constexpr int SM_VA = SM_KA + NA * 16384;             // NV x V slots
@@ -97,7 +110,7 @@ struct Lay {
     static constexpr int SM_RED = SM_KA;
     static constexpr int SM_CNT = SM_KA + (256 + 8 + 1) * 16 * 4;
     static constexpr int SM_HOUT = SM_VA;
-    static constexpr int SMEM_BYTES = SM_BAR + 512;
+    static constexpr int SMEM_BYTES = SM_BAR + (QD > 8 ? 1024 : 512);
     static_assert(SMEM_BYTES <= 232448, "over the 227 KB a CTA may hold");
     static_assert(NA * 16384 >= SM_CNT - SM_KA + 1024 && NV * VBYTES >= NHELP * HOUT, "the final reduction fits the dead rings");
     enum {
@@ -848,11 +861,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             const int take = (HPASS >= 4 && avail >= 4) ? 4 : ((HPASS >= 2 && avail >= 2) ? 2 : 1);
             {   // the younger copies may still be in flight
                 const int pending = avail - take;
-                if (pending >= 4) asm volatile("cp.async.wait_group 4;" ::: "memory");
-                else if (pending == 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
-                else if (pending == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
-                else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
-                else asm volatile("cp.async.wait_group 0;" ::: "memory");
+                switch (pending < 15 ? pending : 15) {   // the instruction takes its count as an immediate
+#define FOLD_WAIT_CASE(n) case n: asm volatile("cp.async.wait_group " #n ";" ::: "memory"); break;
+                    FOLD_WAIT_CASE(0) FOLD_WAIT_CASE(1) FOLD_WAIT_CASE(2) FOLD_WAIT_CASE(3) FOLD_WAIT_CASE(4) FOLD_WAIT_CASE(5)
+                    FOLD_WAIT_CASE(6) FOLD_WAIT_CASE(7) FOLD_WAIT_CASE(8) FOLD_WAIT_CASE(9) FOLD_WAIT_CASE(10) FOLD_WAIT_CASE(11)
+                    FOLD_WAIT_CASE(12) FOLD_WAIT_CASE(13) FOLD_WAIT_CASE(14)
+                    default: asm volatile("cp.async.wait_group 15;" ::: "memory"); break;
+#undef FOLD_WAIT_CASE
+                }
             }
             __syncwarp();
             auto consume = [&](auto n_keys) {
@@ -1023,6 +1039,8 @@ extern "C" int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const f
         return FOLD_ERR_UNSUPPORTED;
     }
     FOLD_CHECK_ARG(split >= 1 && out_dtype >= 0 && out_dtype <= 2, "fold_decode_run_sm100: bad split or out_dtype");
+    FOLD_CHECK_ARG(chunk_keys >= 0, "chunk %d", chunk_keys);
+    FOLD_CHECK_ARG(n_groups >= 1 && n_kv_heads >= 1 && pages_per_request >= 1, "fold_decode_run_sm100: empty call");
     dsm100::Params p;
     p.qa = qa; p.qb = qb; p.eq = eq; p.ka = ka; p.kb = kb;
     p.ek = static_cast<const uint16_t*>(ek);

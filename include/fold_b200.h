@@ -120,7 +120,13 @@ int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const i
  * 1..8 rows, page_size and chunk_keys multiples of 128
  * (fold_decode_sm100_supported, which also wants the driver's tensor-map
  * encoder). Arguments as fold_decode_run without weight_terms; `va` and `vb`
- * 16-byte aligned. Replaces the same reference code as fold_decode_run. */
+ * 16-byte aligned. Replaces the same reference code as fold_decode_run.
+ * Two things the ABI cannot check, for both decode entries: every page_table
+ * entry a request's length reaches must be a page of this GPU's own pool (the
+ * entries carry no pool size, so a stale index is a wild read, not a zero tile;
+ * V's tensor map here spans the address space from `va`), and with chunk_keys > 0
+ * the caller provides split * chunk_keys >= the longest sequence: keys past the
+ * last split are not visited. The host layer (FoldKVCache) guarantees both. */
 int fold_decode_sm100_supported(int group, int head_dim, int page_size, int chunk_keys, int v8);
 int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
                           const int8_t* kb, const void* ek, const void* va, const void* vb,
