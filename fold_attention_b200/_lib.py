@@ -22,6 +22,7 @@ _SIGNATURES = {
     "fold_abi_version": [],
     "fold_cache_write_prompt": [P, P, I, P, I, I, P, I, I, I, I, P, P, P, P, P, P, P, P, F, F, P],
     "fold_step_append": [P, P, P, I, I, I, I, I, P, I, I, P, P, P, P, P, P, P, P, P, P, F, P, P, P],
+    "fold_tail_append": [P, I, I, I, I, P, I, I, P, I, P, P, P, P, P, P, P, I, P],
 }
 _RESTYPES = {"fold_last_error": ctypes.c_char_p}
 

@@ -371,9 +371,96 @@ __global__ void __launch_bounds__(NT) step_kernel(
     if (threadIdx.x == 0) lens_out[b] = pos + 1;
 }
 
+
+// ------------------------------------------------------ the tail's append ----
+// One CTA per (request, KV head), after the step that wrote the token: the
+// token's 64-key block gains its V and its projection y = (plane A . u) ek / 256
+// (the integer sum is exact in any order; the key's scale rounds it once), and
+// the block's row becomes vsum / n - (ysum / n) vr^T in V's bf16. A block's
+// first key restarts its sums, so a page reused from an earlier prompt carries
+// nothing over. Plane A and the scale are read back from the pool, where the
+// step left them (reference: src/fold_attention/decode/write.py:193-300).
+template <int D, bool F16>
+__global__ void __launch_bounds__(NT) tail_append_kernel(
+    const void* __restrict__ v, const int8_t* __restrict__ ka, const uint16_t* __restrict__ ek,
+    const int* __restrict__ page_table, int ppr, int page_size, const int* __restrict__ lens, int back,
+    int hkv, const int8_t* __restrict__ tu, const float* __restrict__ tvr, float* tvsum, float* tysum,
+    uint16_t* trows, int rank) {
+    constexpr int NU = D / 16 < 8 ? D / 16 : 8;
+    constexpr int SH = NU == 8 ? 0 : (NU == 4 ? 1 : 2);
+    __shared__ int sA[D];
+    __shared__ float sY[16];
+    const int kr = blockIdx.x, b = kr / hkv, h = kr % hkv, tid = threadIdx.x;
+    const int pos = lens[b] - back;
+    const int pg = __ldg(page_table + static_cast<int64_t>(b) * ppr + pos / page_size);
+    const int off = pos % page_size;
+    const int64_t prow = (static_cast<int64_t>(pg) * hkv + h) * page_size + off;
+    const int64_t blk = prow / 64;
+    const bool first = (off % 64) == 0;
+    const float nk = static_cast<float>(off % 64 + 1);
+    if (tid < D) sA[tid] = ka[prow * D + ((((tid >> 4) ^ ((off >> SH) & (NU - 1))) << 4) | (tid & 15))];
+    if (tid < 16) sY[tid] = 0.f;
+    __syncthreads();
+    if (rank > 0) {
+        const int warp = tid >> 5, lane = tid & 31;
+        const float ekf = __fmul_rn(bf16_bits_to_float(ek[prow]), 1.0f / 256.0f);
+        for (int j = warp; j < rank; j += NT / 32) {
+            const int8_t* up = tu + (static_cast<int64_t>(kr) * rank + j) * D;
+            int dot = 0;
+            for (int c = lane; c < D; c += 32) dot += sA[c] * static_cast<int>(up[c]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            if (lane == 0) {
+                const float yj = __fmul_rn(static_cast<float>(dot), ekf);
+                const float ys = __fadd_rn(first ? 0.f : tysum[blk * rank + j], yj);
+                tysum[blk * rank + j] = ys;
+                sY[j] = __fdiv_rn(ys, nk);
+            }
+        }
+        __syncthreads();
+    }
+    if (tid < D) {
+        const int64_t vi = static_cast<int64_t>(kr) * D + tid;
+        const float xv = F16 ? __half2float(static_cast<const __half*>(v)[vi])
+                             : __bfloat162float(static_cast<const __nv_bfloat16*>(v)[vi]);
+        const float sm = __fadd_rn(first ? 0.f : tvsum[blk * D + tid], xv);
+        float w = __fdiv_rn(sm, nk);
+        for (int j = 0; j < rank; ++j) w = __fsub_rn(w, __fmul_rn(sY[j], tvr[vi * rank + j]));
+        tvsum[blk * D + tid] = sm;
+        trows[blk * D + tid] = __bfloat16_as_ushort(__float2bfloat16_rn(w));
+    }
+}
+
 }  // namespace fold
 
 using namespace fold;
+
+// The tail's share of an append (no counterpart call in the reference, whose step
+// kernel does it in place): run after fold_step_append on the same stream. The token
+// sits at lens[b] - back: back = 1 when `lens` are the lengths the step already moved.
+extern "C" int fold_tail_append(const void* v, int is_f16, int batch, int n_kv_heads, int head_dim,
+                                const int32_t* page_table, int pages_per_request, int page_size,
+                                const int32_t* lens, int back, const int8_t* ka, const void* ek,
+                                const int8_t* tail_u, const float* tail_vr, float* tail_vsum,
+                                float* tail_ysum, void* tail_rows, int tail_rank, void* stream) {
+    FOLD_CHECK_ARG(head_dim == 64 || head_dim == 128, "head_dim %d: the cache writers take 64 or 128", head_dim);
+    FOLD_CHECK_ARG(tail_rank == 0 || tail_rank == 16, "tail rank %d: 0 (block rows alone) or 16", tail_rank);
+    FOLD_CHECK_ARG(v && page_table && lens && ka && ek && tail_vsum && tail_rows, "fold_tail_append: null pointer");
+    FOLD_CHECK_ARG(tail_rank == 0 || (tail_u && tail_vr && tail_ysum), "fold_tail_append: rank 16 needs u, vr and ysum");
+    FOLD_CHECK_ARG(page_size % 64 == 0, "page_size %d: the tail keeps one row per 64 keys of a page", page_size);
+    FOLD_CHECK_ARG(back == 0 || back == 1, "back %d", back);
+    if (batch <= 0) return FOLD_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint16_t* ekp = static_cast<const uint16_t*>(ek);
+    uint16_t* rows = static_cast<uint16_t*>(tail_rows);
+#define FOLD_TAIL(DD, FF)                                                                             \
+    tail_append_kernel<DD, FF><<<batch * n_kv_heads, NT, 0, st>>>(v, ka, ekp, page_table, pages_per_request, \
+        page_size, lens, back, n_kv_heads, tail_u, tail_vr, tail_vsum, tail_ysum, rows, tail_rank)
+    if (head_dim == 64) { if (is_f16) FOLD_TAIL(64, true); else FOLD_TAIL(64, false); }
+    else                { if (is_f16) FOLD_TAIL(128, true); else FOLD_TAIL(128, false); }
+#undef FOLD_TAIL
+    return check_launch("fold_tail_append");
+}
 
 extern "C" int fold_cache_write_prompt(const void* k, const void* v, int is_f16,
                                        const int32_t* chunk_meta, int n_chunks, int batch,

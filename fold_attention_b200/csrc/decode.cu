@@ -43,6 +43,9 @@ struct DecodeParams {
     int nbh, G, hkv, ppr, page_size, split, chunk_keys, truncate, banded;
     float rk, rv, band_e0, band_e1, rk1, rk2, rv1, rv2;
     int* status;
+    // the tail (bf16 V, truncating): one bf16 row per 64 pool rows, each row group's int8
+    // projection (16, D) and map back (D, 16); all null without a tail, u and vr null at rank 0
+    const uint16_t* tail_rows; const int8_t* tail_u; const float* tail_vr;
     int bh_limit;   // > 0: the partial buffers hold this many row groups; an `order` entry outside is refused
 };
 
@@ -115,15 +118,23 @@ struct DecSmem {
     static constexpr int SLOT = KA + KS;               // plane A tile + its scales
     static constexpr int VROW = V8 ? D : 2 * D;
     static constexpr int GKB = BNK * D, GVA = BNK * VROW, GVB = V8 ? BNK * D : 0;
-    static constexpr int GBUF = GKB + GVA + GVB;
+    static constexpr int GTL = V8 ? 0 : 2 * D;         // the tile's tail row (its 64-key block's)
+    static constexpr int OFF_TL = GKB + GVA + GVB;
+    static constexpr int GBUF = GKB + GVA + GVB + GTL;
     static constexpr int OFF_RING = 0, OFF_G = RING * SLOT, OFF_LIVE = OFF_G + 2 * GBUF;
     static constexpr int OFF_BAR = OFF_LIVE + 2 * BNK * 4, OFF_RED = OFF_BAR + 64;
     static constexpr int OFF_FAIL = OFF_RED + 1024;
     static constexpr int BYTES = OFF_FAIL + 16;
 };
 
-template <int D, bool V8, bool W2, bool TRUNC>
+// TR: the tail's rank (-1 none, 0 block rows alone, 16). With a tail a dropped key re-enters at
+// its 64-key block's row plus the part of its V its K predicts: y = (plane A . u) ek / 256 comes
+// out of the coarse logit's own matmul (u's rows are two more B operands), the dropped weights
+// meet it in one bf16 mma per 8 ranks, and the epilogue maps the rank sums back through vr.
+template <int D, bool V8, bool W2, bool TRUNC, int TR>
 __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams p) {
+    static_assert(TR < 0 || (TRUNC && !V8), "the tail re-enters truncated mass on a bf16 V");
+    static_assert(TR == -1 || TR == 0 || TR == 16, "tail ranks: none, 0, 16");
     using L = DecSmem<D, V8>;
     constexpr int NU = D / 16;          // 16-byte units per int8 row
     constexpr int KSTEPS = D / 32;      // k-steps of the int8 logit
@@ -213,6 +224,21 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                 qfb[ks][j] = ok ? *reinterpret_cast<const uint32_t*>(p.qb + qrow + c) : 0u;
             }
     }
+    // the tail's projection: rank rows gid and 8 + gid as B operands beside Q's
+    uint32_t ufa[TR > 0 ? KSTEPS : 1][2], ufb[TR > 0 ? KSTEPS : 1][2];
+    if constexpr (TR > 0) {
+        const int8_t* up = p.tail_u + static_cast<int64_t>(bh) * TR * D;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = 32 * ks + 16 * j + 4 * tq;
+                ufa[ks][j] = *reinterpret_cast<const uint32_t*>(up + gid * D + c);
+                ufb[ks][j] = *reinterpret_cast<const uint32_t*>(up + (8 + gid) * D + c);
+            }
+    }
+    float y_old[TR > 0 ? 8 : 1] = {}, yd[2][4] = {};
+    (void)ufa; (void)ufb; (void)y_old; (void)yd;
     // the two rows this lane's logit registers belong to
     float eqr[2], zr[2], cutr[2];
     bool rowok[2];
@@ -241,6 +267,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
     for (int t = 0; t <= n_tiles; ++t) {
         float s_new[4] = {0, 0, 0, 0}, tk_new[4] = {0, 0, 0, 0};
         int b_new[2] = {0, 0}, nrow_new = 0;
+        float y_new[TR > 0 ? 8 : 1] = {};
+        (void)y_new;
         if (t < n_tiles) {
             const int base = lo + t * tstep;
             const int nrow = min(BNK, hi - base);
@@ -250,6 +278,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
             if (!mbar_wait(bars[t % RING], (t / RING) & 1, p.status)) *sFail = 1;
             // ---- coarse logit: 16 keys x 8 rows, both Q planes ----
             int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+            int cy1[4] = {0, 0, 0, 0}, cy2[4] = {0, 0, 0, 0};
+            (void)cy1; (void)cy2;
             const int arow = 16 * warp + (lane & 7) + 8 * ((lane >> 3) & 1);
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -258,6 +288,10 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                 ldmatrix_x4(a, smem_u32(sKa + arow * D + u * 16));
                 mma_s8(c1, a, qfa[ks][0], qfa[ks][1]);
                 mma_s8(c2, a, qfb[ks][0], qfb[ks][1]);
+                if constexpr (TR > 0) {
+                    mma_s8(cy1, a, ufa[ks][0], ufa[ks][1]);
+                    mma_s8(cy2, a, ufb[ks][0], ufb[ks][1]);
+                }
             }
             int pk = TRUNC ? 0 : (1 | (1 << 3));
             float dg[2] = {-INFINITY, -INFINITY};
@@ -267,6 +301,12 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                 const float ekf = bf16_bits_to_float(sKs[ky]) * (1.0f / 256.0f);
                 const float tk = eqr[i & 1] * ekf;
                 tk_new[i] = tk;
+                if constexpr (TR > 0) {
+                    // key (i >> 1)'s projection on ranks 2 tq + (i & 1) and 8 + that: the exact
+                    // integer, rounded once by the key's scale; rows past the tile hold nothing
+                    y_new[i] = ky < nrow ? static_cast<float>(cy1[i]) * ekf : 0.f;
+                    y_new[4 + i] = ky < nrow ? static_cast<float>(cy2[i]) * ekf : 0.f;
+                }
                 float s1 = -INFINITY;
                 if (rowok[i & 1] && ky < nrow) {
                     s1 = fmaf(static_cast<float>(c1[i] * 256 + c2[i]), tk, -zr[i & 1]);
@@ -340,6 +380,14 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                                    (bits & 4) ? 16 : 0);
                     }
                 }
+                if constexpr (TR >= 0) {
+                    // the tile's block row: a tile is one 64-key block of a page
+                    if (tid < 2 * D / 16) {
+                        const int64_t blk = pool_row(base) / BNK;
+                        cp_async16(smem_u32(g + L::OFF_TL + tid * 16),
+                                   reinterpret_cast<const uint8_t*>(p.tail_rows) + blk * (2 * D) + tid * 16, 16);
+                    }
+                }
             }
         }
         cp_async_commit();
@@ -366,7 +414,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                     mma_s8(c3b, a, qfb[ks][0], qfb[ks][1]);
                 }
             }
-            float w[4];
+            float w[4], fd[4] = {0.f, 0.f, 0.f, 0.f};
+            (void)fd;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int ky = 16 * warp + gid + 8 * (i >> 1);
@@ -381,6 +430,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                     // its true weight; a cut key's weight joins the dropped mass
                     w[i] = live ? e : 0.f;
                     rM[i & 1] += live ? 0.f : e;
+                    fd[i] = live ? 0.f : e;
                 } else {
                     w[i] = e;
                 }
@@ -450,6 +500,45 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                 // unreachable: a dense tile is all live
             }
             (void)sVb;
+            if constexpr (TR >= 0) {
+                // this warp's 16 keys' dropped mass per row, then row gid's to the lanes that hold
+                // its accumulator columns
+                float t0 = fd[0] + fd[2], t1 = fd[1] + fd[3];
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    t0 += __shfl_xor_sync(0xffffffffu, t0, o);
+                    t1 += __shfl_xor_sync(0xffffffffu, t1, o);
+                }
+                if (__ballot_sync(0xffffffffu, t0 != 0.f || t1 != 0.f)) {
+                    const float v0 = __shfl_sync(0xffffffffu, t0, gid >> 1);
+                    const float v1 = __shfl_sync(0xffffffffu, t1, gid >> 1);
+                    const float m = (gid & 1) ? v1 : v0;
+                    const uint32_t* srow = reinterpret_cast<const uint32_t*>(g + L::OFF_TL);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const uint32_t wv = srow[4 * nt + tq];      // channels 8 nt + 2 tq, + 1
+                        acc[nt][0] = fmaf(m, __uint_as_float(wv << 16), acc[nt][0]);
+                        acc[nt][1] = fmaf(m, __uint_as_float(wv & 0xFFFF0000u), acc[nt][1]);
+                    }
+                    if constexpr (TR > 0) {
+                        uint32_t ad[4];
+                        ad[0] = movmatrix_t(pack_bf16x2(fd[0], fd[1]));
+                        ad[1] = 0u;
+                        ad[2] = movmatrix_t(pack_bf16x2(fd[2], fd[3]));
+                        ad[3] = 0u;
+#pragma unroll
+                        for (int n = 0; n < 2; ++n) {
+                            const uint32_t y0 = movmatrix_t(pack_bf16x2(y_old[4 * n], y_old[4 * n + 1]));
+                            const uint32_t y1 = movmatrix_t(pack_bf16x2(y_old[4 * n + 2], y_old[4 * n + 3]));
+                            mma_16816<false>(yd[n], ad, y0, y1);
+                        }
+                    }
+                }
+            }
+        }
+        if constexpr (TR > 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y_old[i] = y_new[i];
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -494,6 +583,15 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
             else ch = 8 * nt + 2 * tq + e;
             sO[(warp * 8 + gid) * D + ch] = acc[nt][e] + acc[nt][2 + e];
         }
+    float* sY = sO + 4 * 8 * D;          // [4 warps][8 rows][16 ranks], then [8 rows][16 ranks]
+    if constexpr (TR > 0) {
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) sY[(warp * 8 + gid) * 16 + 8 * n + 2 * tq + e] = yd[n][e];
+        __syncthreads();
+        sY[512 + tid] = (sY[tid] + sY[128 + tid]) + (sY[256 + tid] + sY[384 + tid]);
+    }
     __syncthreads();
     for (int i = tid; i < G * D; i += DEC_THREADS) {
         const int g = i / D, c = i % D;
@@ -504,7 +602,16 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
             m += sRed[w2 * 8 + g];
         }
         if (V8) x *= E4O;
-        if (TRUNC && p.vmean) x += m * p.vmean[static_cast<int64_t>(bh) * D + c];
+        if (TR < 0 && TRUNC && p.vmean) x += m * p.vmean[static_cast<int64_t>(bh) * D + c];
+        if constexpr (TR > 0) {
+            const float4* vr = reinterpret_cast<const float4*>(p.tail_vr + (static_cast<int64_t>(bh) * D + c) * TR);
+#pragma unroll
+            for (int q4 = 0; q4 < TR / 4; ++q4) {
+                const float4 r4 = __ldg(vr + q4);
+                const float* yr = sY + 512 + g * 16 + 4 * q4;
+                x += yr[0] * r4.x + yr[1] * r4.y + yr[2] * r4.z + yr[3] * r4.w;
+            }
+        }
         p.o_part[(pix * G + g) * D + c] = x;
     }
     if (tid < G) {
@@ -687,13 +794,19 @@ using namespace fold;
 
 namespace {
 
-template <int D, bool V8, bool W2, bool TRUNC>
+template <int D, bool V8, bool W2, bool TRUNC, int TR = -1>
 int launch_decode(const DecodeParams& p, cudaStream_t st) {
     using L = DecSmem<D, V8>;
-    auto kern = decode_kernel<D, V8, W2, TRUNC>;
+    auto kern = decode_kernel<D, V8, W2, TRUNC, TR>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES);
     kern<<<p.nbh * p.split, DEC_THREADS, L::BYTES, st>>>(p);
     return check_launch("fold_decode_run");
+}
+
+template <int D>
+int launch_decode_tail(const DecodeParams& p, int w2, cudaStream_t st) {
+    if (p.tail_u) return w2 ? launch_decode<D, false, true, true, 16>(p, st) : launch_decode<D, false, false, true, 16>(p, st);
+    return w2 ? launch_decode<D, false, true, true, 0>(p, st) : launch_decode<D, false, false, true, 0>(p, st);
 }
 
 template <int D, bool V8>
@@ -730,7 +843,16 @@ static int decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const
                       float refine_v, const float* refine_bands, float v_scale,
                       float* o_part, float* den_part, int32_t* cnt_part, void* out,
                       int out_dtype, float* den, int32_t* counts, int32_t* status,
-                      int bh_limit, void* stream) {
+                      int bh_limit, void* stream, const void* tail_rows = nullptr,
+                      const int8_t* tail_u = nullptr, const float* tail_vr = nullptr, int tail_rank = -1) {
+    if (tail_rank >= 0) {
+        FOLD_CHECK_ARG(tail_rank == 0 || tail_rank == 16, "tail rank %d: 0 (block rows alone) or 16", tail_rank);
+        FOLD_CHECK_ARG(tail_rows && (tail_rank == 0 ? (!tail_u && !tail_vr) : (tail_u && tail_vr)),
+                       "fold_decode_run_tail: rows always, u and vr at rank 16 only");
+        FOLD_CHECK_ARG(truncate && !vb, "the tail re-enters truncated mass on a bf16 V: truncate=1, no plane B of V");
+        FOLD_CHECK_ARG(!vmean, "a tail replaces V's mean: pass vmean = NULL");
+        FOLD_CHECK_ARG(page_size % 64 == 0, "page_size %d: the tail keeps one row per 64 keys of a page", page_size);
+    }
     FOLD_CHECK_ARG(qa && qb && eq && ka && kb && ek && va && z && cut && page_table && seq_lens &&
                        o_part && den_part && cnt_part && status && (!out || (den && counts)),
                    "fold_decode_run: null pointer");
@@ -761,10 +883,12 @@ static int decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const
     }
     p.status = status;
     p.bh_limit = bh_limit;
+    p.tail_rows = static_cast<const uint16_t*>(tail_rows); p.tail_u = tail_u; p.tail_vr = tail_vr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool v8 = vb != nullptr;
     int rc;
-    if (head_dim == 128) rc = v8 ? launch_decode_d<128, true>(p, weight_terms == 2, st) : launch_decode_d<128, false>(p, weight_terms == 2, st);
+    if (tail_rank >= 0) rc = head_dim == 128 ? launch_decode_tail<128>(p, weight_terms == 2, st) : launch_decode_tail<64>(p, weight_terms == 2, st);
+    else if (head_dim == 128) rc = v8 ? launch_decode_d<128, true>(p, weight_terms == 2, st) : launch_decode_d<128, false>(p, weight_terms == 2, st);
     else rc = v8 ? launch_decode_d<64, true>(p, weight_terms == 2, st) : launch_decode_d<64, false>(p, weight_terms == 2, st);
     if (rc) return rc;
     if (!out) return FOLD_OK;   // partials only: the caller combines
@@ -792,6 +916,27 @@ extern "C" int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* 
                       group, n_kv_heads, head_dim, pages_per_request, page_size, split, chunk_keys, truncate,
                       weight_terms, refine_k, refine_v, refine_bands, v_scale, o_part, den_part, cnt_part, out,
                       out_dtype, den, counts, status, /*bh_limit=*/0, stream);
+}
+
+// The same decode with a tail: dropped mass re-enters at each 64-key block's row
+// (`tail_rows`, bf16, one per 64 pool rows) and, at rank 16, through each row group's
+// projection `tail_u` (n_groups, 16, D) int8 and map back `tail_vr` (n_groups, D, 16).
+extern "C" int fold_decode_run_tail(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                                    const int8_t* kb, const void* ek, const void* va,
+                                    const void* tail_rows, const int8_t* tail_u, const float* tail_vr,
+                                    int tail_rank, const float* z, const float* cut,
+                                    const int32_t* page_table, const int32_t* seq_lens,
+                                    const int32_t* order, int n_groups, int group, int n_kv_heads,
+                                    int head_dim, int pages_per_request, int page_size, int split,
+                                    int chunk_keys, int weight_terms, float refine_k,
+                                    float* o_part, float* den_part, int32_t* cnt_part, void* out,
+                                    int out_dtype, float* den, int32_t* counts, int32_t* status,
+                                    void* stream) {
+    FOLD_CHECK_ARG(tail_rank >= 0, "fold_decode_run_tail: tail rank %d", tail_rank);
+    return decode_run(qa, qb, eq, ka, kb, ek, va, nullptr, nullptr, z, cut, page_table, seq_lens, order, n_groups,
+                      group, n_kv_heads, head_dim, pages_per_request, page_size, split, chunk_keys, /*truncate=*/1,
+                      weight_terms, refine_k, 0.f, nullptr, 1.0f, o_part, den_part, cnt_part, out,
+                      out_dtype, den, counts, status, /*bh_limit=*/0, stream, tail_rows, tail_u, tail_vr, tail_rank);
 }
 
 // The combine alone, for decode kernels that fill the same partial buffers.

@@ -28,6 +28,10 @@ _lib.register(
     "fold_decode_run_sm100",
     [P] * 14 + [I] * 9 + [F, F, P, F] + [P, P, P, P, I, P, P, P, P],
 )
+_lib.register(
+    "fold_decode_run_tail",
+    [P] * 10 + [I] + [P] * 5 + [I] * 9 + [F] + [P, P, P, P, I, P, P, P, P],
+)
 _lib.register("fold_decode_combine", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P])
 
 _OUT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
@@ -54,7 +58,7 @@ def prepare_fold_decode(
     split=1, truncate=False, refine_k=10.0, refine_v=10.0, v8=False, v2=None, v_scale=1.0,
     vmean=None, page_table, page_size, seq_lens, n_kv_heads, reference="given", weight_terms=1,
     order=None, out_dtype=torch.float32, refine_bands=(), chunk_keys=0, out=None, kernel="mma",
-    short_slots=0,
+    short_slots=0, tail=None,
 ):
     """Bind one decode over a paged cache and return its launch.
 
@@ -70,6 +74,11 @@ def prepare_fold_decode(
     With an `order`, its first `short_slots` slots stay on the warp-level kernel
     when the tcgen05 one takes the rest (requests too short for it to pay), and
     one combine follows both.
+    `tail` (a `tail.TailState`, or anything with `rows`, `u`, `vr` and `rank`)
+    replaces `vmean` as where dropped mass re-enters: each 64-key block's row
+    and, at rank 16, the part of a key's V its K predicts. It needs a
+    truncating decode on a bf16 V, pages of a multiple of 64 keys, and the
+    warp-level kernel (reference: decode/launch.py:380-500, `tail=`).
     """
     NBH, G, D = qa.shape
     if G > 8:
@@ -86,6 +95,25 @@ def prepare_fold_decode(
         raise ValueError(f"chunk={chunk_keys} is not a multiple of 64")
     if kernel not in KERNELS:
         raise ValueError(f"kernel is one of {KERNELS}")
+    if tail is not None:
+        if not truncate:
+            raise ValueError("the tail re-enters truncated mass: it needs truncate")
+        if v8:
+            raise ValueError("the decode tail needs a bf16 V cache")
+        if vmean is not None:
+            raise ValueError("a tail replaces vmean: pass one of them")
+        if page_size % 64:
+            raise ValueError(f"page_size={page_size}: the tail keeps one row per 64 keys, so a page must hold whole blocks")
+        if tail.rank not in (0, 16):
+            raise ValueError(f"tail rank {tail.rank}: 0 (block rows alone) or 16")
+        if tail.rows.dtype != torch.bfloat16 or tail.rows.shape != (ka.shape[0] // 64, D):
+            raise ValueError(f"the tail's rows are bf16 ({ka.shape[0] // 64}, {D}): one per 64 pool rows")
+        if tail.rank and (tail.u.shape != (NBH, 16, D) or tail.vr.shape != (NBH, D, 16)
+                          or tail.u.dtype != torch.int8 or tail.vr.dtype != torch.float32):
+            raise ValueError(f"the tail's u is int8 ({NBH}, 16, {D}) and vr fp32 ({NBH}, {D}, 16)")
+        if kernel == "sm100":
+            raise NotImplementedError("the tail runs on the warp-level kernel: kernel='mma' or 'auto'")
+        kernel = "mma"
     can = bool(_lib.lib.fold_decode_sm100_supported(G, D, int(page_size), int(chunk_keys), int(bool(v8))))
     if kernel == "sm100" and not can:
         raise NotImplementedError(
@@ -128,11 +156,23 @@ def prepare_fold_decode(
               den.data_ptr(), counts.data_ptr(), status.data_ptr(), _lib.stream(dev)]
         return a
 
+    def tail_args(o):
+        return [
+            qa.data_ptr(), qb.data_ptr(), eq.data_ptr(), ka.data_ptr(), kb.data_ptr(), ek.data_ptr(), v.data_ptr(),
+            tail.rows.data_ptr(), _lib.ptr(tail.u), _lib.ptr(tail.vr), tail.rank, z.data_ptr(), cut.data_ptr(),
+            page_table.data_ptr(), seq_lens.data_ptr(), _lib.ptr(order), NBH, G, int(n_kv_heads), D,
+            page_table.shape[1], int(page_size), split, int(chunk_keys), int(weight_terms), float(refine_k),
+            o_part.data_ptr(), den_part.data_ptr(), cnt_part.data_ptr(), o.data_ptr(), _OUT[o.dtype],
+            den.data_ptr(), counts.data_ptr(), status.data_ptr(), _lib.stream(dev),
+        ]
+
     def run(out=None):
         o = out_t if out is None else out
         if reference == "mass":
             mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z)
-        if use_sm100 and short_slots:
+        if tail is not None:
+            _lib.call("fold_decode_run_tail", *tail_args(o))
+        elif use_sm100 and short_slots:
             _lib.call("fold_decode_run_sm100", *args(short_slots, NBH - short_slots, True, None))
             _lib.call("fold_decode_run", *args(0, short_slots, False, None))
             _lib.call(
@@ -149,7 +189,7 @@ def prepare_fold_decode(
     launch = DecodeLaunch(
         run,
         (qa, qb, eq, ka, kb, ek, v, v2, vmean, z, cut, page_table, seq_lens, order, o_part,
-         den_part, cnt_part, out_t, den, counts, status, bands),
+         den_part, cnt_part, out_t, den, counts, status, bands, tail),
     )
     launch.z = z
     launch.status = status

@@ -88,3 +88,19 @@ def step(
         ka.data_ptr(), kb.data_ptr(), va.data_ptr(), _lib.ptr(vb), ek.data_ptr(), float(v_scale),
         vsum.data_ptr(), vmean.data_ptr(), _lib.stream(x.device),
     )
+
+
+def tail_append(v, tail, ka, ek, page_table, page_size, lens, back):
+    """The tail's share of an append, after `step` on the same stream: the token
+    of each request (at `lens - back`) joins its 64-key block's sums and row
+    (`tail` a `TailState`; reference: decode/write.py:193-300, `append_row`)."""
+    if v.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError(f"v must be bf16 or fp16 (it is {v.dtype})")
+    B, HKV, D = v.shape
+    v = v.contiguous()
+    _lib.call(
+        "fold_tail_append", v.data_ptr(), int(v.dtype == torch.float16), B, HKV, D, page_table.data_ptr(),
+        page_table.shape[1], int(page_size), lens.data_ptr(), int(back), ka.data_ptr(), ek.data_ptr(),
+        _lib.ptr(tail.u), _lib.ptr(tail.vr), tail.vsum.data_ptr(), _lib.ptr(tail.ysum), tail.rows.data_ptr(),
+        tail.rank, _lib.stream(v.device),
+    )

@@ -15,6 +15,7 @@ import math
 import torch
 
 from .backward.launch import attention_forward
+from .decode import tail as tail_fit
 from .decode import write
 from .decode.heuristics import (
     pick_split,
@@ -64,10 +65,13 @@ class FoldKVCache:
     the same step; on one B200 that measured slower up to 128 requests (the
     short requests' launch cannot fill the GPU by itself), so it is off.
 
-    The decode tail (`tail` >= 0, a rank-r K->V model of dropped mass on a
-    bf16 V) is not built: with `tail="auto"` a bf16 V at a finite depth runs
-    WITHOUT the reference's default tail (dropped mass re-enters at V's mean
-    instead; a warning says so once), and an explicit `tail` >= 0 raises.
+    `tail` is the decode tail's rank on a bf16 V at a finite depth: dropped
+    mass re-enters at each 64-key block's mean V (0) plus the part of a key's
+    V its K predicts through a rank-16 map fitted on the prompt (16); None for
+    V's mean alone, "auto" for the reference's policy (`tail_rank_for`: 16 for
+    these groups; no tail where the pages do not hold whole 64-key blocks).
+    The tail runs on the warp-level kernel, so a cache that has one does not
+    take "sm100" (pass `tail=None` to put a truncating bf16 V there).
     `check_range` reads each
     step's denominators on the host and reruns the rows whose reference sat
     outside `[0.5, 2^60]` (`2^100` on a bf16 V) of their mass.
@@ -150,22 +154,29 @@ class FoldKVCache:
         self.cut = torch.full_like(self.z, 1e4 if depth is None else float(depth))
         if tail == "auto":
             tail = tail_rank_for(D, self.group, self.v8) if depth is not None else -1
-            if tail >= 0:
-                # the K-predicted tail is not built: dropped mass re-enters at V's mean. This differs from
-                # the reference's default for a bf16 V at a finite depth, so say it rather than only document it
-                import warnings
-
-                warnings.warn(
-                    f"FoldKVCache(depth={depth}, v8=False): the reference's default rank-{tail} decode tail is not built; "
-                    "dropped mass re-enters at V's mean (pass tail=None to silence this)", RuntimeWarning, stacklevel=2)
-                tail = None
+            if page_size % tail_fit.TAIL_BLOCK or kernel == "sm100":
+                tail = -1
         self.tail_rank = -1 if tail is None else int(tail)
+        self.tail = None
         if self.tail_rank >= 0:
             if depth is None:
                 raise ValueError("the tail re-enters truncated mass, and depth=None truncates nothing")
             if self.v8:
                 raise ValueError("the decode tail needs a bf16 V cache; pass tail=None with v8")
-            raise NotImplementedError("the decode tail is not built: pass tail=None")
+            if page_size % tail_fit.TAIL_BLOCK:
+                raise ValueError(f"page_size={page_size}: the tail keeps one row per 64 keys, so a page must hold whole blocks")
+            if kernel == "sm100":
+                raise NotImplementedError("the tail runs on the warp-level kernel: kernel='mma' or 'auto'")
+            tail_fit.check_rank(self.tail_rank, D)
+            R, nblk = self.tail_rank, rows // tail_fit.TAIL_BLOCK
+            self.tail = tail_fit.TailState(
+                rows=torch.zeros((nblk, D), device=dev, dtype=torch.bfloat16),
+                vsum=torch.zeros((nblk, D), device=dev, dtype=torch.float32),
+                ysum=torch.zeros((nblk, R), device=dev, dtype=torch.float32) if R else None,
+                u=torch.zeros((self.n_groups, R, D), device=dev, dtype=torch.int8) if R else None,
+                vr=torch.zeros((self.n_groups, D, R), device=dev, dtype=torch.float32) if R else None,
+            )
+            self.kernel = "mma"
         self._refine_k_fixed = refine_k
         self._refine_v_fixed = refine_v
         # after a step, look at every row's denominator and run the flagged rows again from a
@@ -231,8 +242,36 @@ class FoldKVCache:
         )
         self.seq_lens.copy_(torch.tensor(lens, dtype=torch.int32), non_blocking=True)
         self.lens = list(lens)
+        if self.tail is not None:
+            self._fit_tail(v, lens)
         self._set_order()
         self._launches.clear()
+
+    def _fit_tail(self, v, lens):
+        """Each prompt's rank map and the block rows it fills, in the units and
+        pool slots the append then keeps current. A request is fitted from its
+        own keys alone (plane A and the scales as the prompt writer stored them,
+        read back and un-swizzled), so its tail does not depend on its batch
+        (reference: kv_cache.py:300-417, `_fit_tail`)."""
+        t, PS, HKV, D, TB = self.tail, self.page_size, self.n_kv_heads, self.head_dim, tail_fit.TAIL_BLOCK
+        dev = self.device
+        heads = torch.arange(HKV, device=dev)[:, None]
+        at = 0
+        for b, n in enumerate(lens):
+            pos = torch.arange(n, device=dev)
+            pg = self.page_table[b, pos // PS].long()
+            prow = (pg[None, :] * HKV + heads) * PS + (pos % PS)[None, :]          # (HKV, n)
+            kint = tail_fit.plane_rows(self.ka, prow, pos % PS, D)
+            u, vr, vsum, ysum, rows = tail_fit.fit_prompt(
+                kint, self.ek[prow], v[at:at + n].transpose(0, 1), t.rank)
+            blk = prow[:, ::TB] // TB                                              # (HKV, blocks)
+            t.vsum[blk] = vsum
+            t.rows[blk] = rows.to(t.rows.dtype)
+            if t.rank:
+                t.ysum[blk] = ysum
+                t.u[b * HKV:(b + 1) * HKV] = u
+                t.vr[b * HKV:(b + 1) * HKV] = vr
+            at += n
 
     def append(self, k, v):
         """Write one token per request, `(batch, H_KV, D)` each, at its length."""
@@ -272,7 +311,8 @@ class FoldKVCache:
         return prepare_fold_decode(
             self.qa, self.qb, self.eq, self.ka, self.kb, self.ek, self.va, self.z.clone(), self.cut,
             split=split, truncate=truncate, refine_k=refine[0], refine_v=refine[1], v8=self.v8, v2=self.vb,
-            v_scale=self.v_scale, vmean=self.vmean.clone() if truncate else None, page_table=self.page_table,
+            v_scale=self.v_scale, vmean=self.vmean.clone() if truncate and self.tail is None else None,
+            tail=self.tail, page_table=self.page_table,
             page_size=self.page_size, seq_lens=self.seq_lens.clone(), n_kv_heads=self.n_kv_heads, reference="given",
             weight_terms=self.weight_terms, order=self.order.clone(), out_dtype=out_dtype,
             refine_bands=refine_bands_for(self.v8, head_dim=self.head_dim, group=self.group) if self._banded() else (),
@@ -309,13 +349,22 @@ class FoldKVCache:
         decode = prepare_fold_decode(
             self.qa, self.qb, self.eq, self.ka, self.kb, self.ek, self.va, z, self.cut,
             split=split, truncate=truncate, refine_k=refine[0], refine_v=refine[1], v8=self.v8, v2=self.vb,
-            v_scale=self.v_scale, vmean=vmean if truncate else None, page_table=self.page_table,
+            v_scale=self.v_scale, vmean=vmean if truncate and self.tail is None else None, tail=self.tail,
+            page_table=self.page_table,
             page_size=self.page_size, seq_lens=seen, n_kv_heads=self.n_kv_heads, reference="given",
             weight_terms=self.weight_terms, order=self.order.clone(), out_dtype=out_dtype,
             refine_bands=refine_bands_for(self.v8, head_dim=self.head_dim, group=self.group) if self._banded() else (),
             chunk_keys=self.chunk or 0, kernel=kernel,
         )
         shape = (self.batch, self.n_heads, self.head_dim)
+        t, saved = self.tail, None
+        if appends and t is not None:
+            # the token's blocks, whose sums and rows every replay rewrites: keep what they hold now
+            PS, HKV = self.page_size, self.n_kv_heads
+            pg = self.page_table[torch.arange(self.batch, device=at.device), (at // PS).long()].long()
+            blk = ((pg[:, None] * HKV + torch.arange(HKV, device=at.device)[None, :]) * PS + (at % PS)[:, None].long()) // tail_fit.TAIL_BLOCK
+            blk = blk.reshape(-1)
+            saved = (blk, t.vsum[blk], t.rows[blk], t.ysum[blk] if t.rank else None)
 
         def replay():
             if appends:   # the running sums start from the same state every replay
@@ -325,8 +374,15 @@ class FoldKVCache:
                 qf, k, v, self.qa.view(-1, self.head_dim), self.qb.view(-1, self.head_dim), self.eq.view(-1), self.ek,
                 self.page_table, self.page_size, at, self.ka, self.kb, self.va, self.vb, self.v_scale, vsum, vmean, lens_out,
             )
+            if saved is not None:
+                write.tail_append(v, t, self.ka, self.ek, self.page_table, self.page_size, at, 0)
             mass_z(self.qa, self.qb, self.eq, self.ka, self.ek, self.page_table, self.page_size, seen, self.n_kv_heads, z)
             o, den, counts = decode.run()
+            if saved is not None:   # the token's blocks go back to what they held: the tail is the cache's own
+                t.vsum[saved[0]] = saved[1]
+                t.rows[saved[0]] = saved[2]
+                if t.rank:
+                    t.ysum[saved[0]] = saved[3]
             return o.view(shape), den, counts
 
         launch = ReplayStep(replay, (qf, k, v, at, lens_out, vsum, vmean, vsum0, vmean0, z, decode))
@@ -458,7 +514,8 @@ class FoldKVCache:
                 self._z_given if given else self.z, self.cut,
                 split=split, truncate=truncate, refine_k=refine[0], refine_v=refine[1],
                 v8=self.v8, v2=self.vb, v_scale=self.v_scale,
-                vmean=self.vmean if truncate else None, page_table=self.page_table,
+                vmean=self.vmean if truncate and self.tail is None else None, tail=self.tail,
+                page_table=self.page_table,
                 page_size=self.page_size, seq_lens=self.seq_lens, n_kv_heads=self.n_kv_heads,
                 reference="given", weight_terms=self.weight_terms, order=self.order,
                 out_dtype=out_dtype,
@@ -485,6 +542,8 @@ class FoldKVCache:
             self.eq.view(-1), self.ek, self.page_table, self.page_size, self.seq_lens,
             self.ka, self.kb, self.va, self.vb, self.v_scale, self.vsum, self.vmean, self.seq_lens,
         )
+        if k is not None and self.tail is not None:
+            write.tail_append(v, self.tail, self.ka, self.ek, self.page_table, self.page_size, self.seq_lens, 1)
         if q is not None:
             mass_z(self.qa, self.qb, self.eq, self.ka, self.ek, self.page_table, self.page_size,
                    self.seq_lens, self.n_kv_heads, self.z)

@@ -69,6 +69,24 @@ int fold_step_append(const void* q, const void* k, const void* v, int is_f16, in
                      void* va, void* vb, void* ek, float v_scale, float* vsum, float* vmean,
                      void* stream);
 
+/* The decode tail's share of an append: the appended token's 64-key block gains
+ * its V and its projection y = (plane A . u) ek / 256, and the block's row becomes
+ * vsum / n - (ysum / n) vr^T in bf16; a block's first key restarts its sums.
+ * Run it after fold_step_append on the same stream (plane A and the scale are
+ * read back from the pool). The token sits at lens[b] - back: back = 1 when
+ * `lens` are the lengths the step already moved, 0 when they are the positions.
+ * Replaces: the tail half of src/fold_attention/decode/write.py:193-300
+ * (append_row), which the reference runs inside its step kernel.
+ *   v (batch, n_kv_heads, head_dim) 16-bit; tail_u int8 (n_groups, 16, head_dim);
+ *   tail_vr fp32 (n_groups, head_dim, 16); tail_vsum fp32 (pool_rows/64, head_dim);
+ *   tail_ysum fp32 (pool_rows/64, 16); tail_rows bf16 (pool_rows/64, head_dim);
+ *   tail_rank 0 (u, vr, ysum NULL) or 16; page_size a multiple of 64 */
+int fold_tail_append(const void* v, int is_f16, int batch, int n_kv_heads, int head_dim,
+                     const int32_t* page_table, int pages_per_request, int page_size,
+                     const int32_t* lens, int back, const int8_t* ka, const void* ek,
+                     const int8_t* tail_u, const float* tail_vr, float* tail_vsum,
+                     float* tail_ysum, void* tail_rows, int tail_rank, void* stream);
+
 /* ---- Path B: decode ------------------------------------------------------- */
 
 /* The mass reference: each query row's log-sum-exp estimate Z (base 2) from
@@ -109,6 +127,26 @@ int fold_decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const i
                     float refine_k, float refine_v, const float* refine_bands /* host */,
                     float v_scale, float* o_part, float* den_part, int32_t* cnt_part, void* out,
                     int out_dtype, float* den, int32_t* counts, int32_t* status, void* stream);
+
+/* fold_decode_run with a tail, on a bf16 V at a finite depth: a dropped key's
+ * mass re-enters at its own 64-key block's row (tail_rows) and, at rank 16, at the
+ * part of its V that its K predicts: y = (plane A . u) ek / 256 comes out of the
+ * coarse logit's own matmul, and the epilogue maps the rows' rank sums back through
+ * vr. The denominator is the whole softmax's mass, as with vmean. Always truncating,
+ * no plane B of V, no vmean; page_size a multiple of 64; other arguments as
+ * fold_decode_run. Replaces: the tail paths of src/fold_attention/decode/kernel.py
+ * :905-1200 and decode/combine.py:38-75, fed by decode/cache.py:200-337.
+ *   tail_rows bf16 (pool_rows/64, head_dim); tail_u int8 (n_groups, 16, head_dim) and
+ *   tail_vr fp32 (n_groups, head_dim, 16), both NULL at tail_rank 0 */
+int fold_decode_run_tail(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                         const int8_t* kb, const void* ek, const void* va, const void* tail_rows,
+                         const int8_t* tail_u, const float* tail_vr, int tail_rank, const float* z,
+                         const float* cut, const int32_t* page_table, const int32_t* seq_lens,
+                         const int32_t* order, int n_groups, int group, int n_kv_heads, int head_dim,
+                         int pages_per_request, int page_size, int split, int chunk_keys,
+                         int weight_terms, float refine_k, float* o_part, float* den_part,
+                         int32_t* cnt_part, void* out, int out_dtype, float* den, int32_t* counts,
+                         int32_t* status, void* stream);
 
 /* The same decode on tcgen05 tensor cores (TMEM accumulators, the E4M3 V planes
  * read by the tensor core as stored; weights carried as four E5M2 terms). K's

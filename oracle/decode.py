@@ -81,11 +81,13 @@ def truncated_softmax(s, z, v, cut):
     return (p @ v) / p.sum(-1, keepdim=True), p
 
 
-def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, vmean=None):
+def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, vmean=None, reentry=None):
     """One row group's decode in float64 on the cache's own (unswizzled)
     planes: `ka`, `kb` (S, D) int8, `ek` (S,), `va` (S, D) float (bf16 values
     or plane A in scale units), `vb` plane B or None. `depth` None keeps every
-    key. Returns (out (G, D), den (G,), live count, refined count)."""
+    key. `reentry` (S, D), instead of `vmean`: where each key's mass re-enters if it is
+    dropped (the tail: its block's row plus its projection mapped back, `oracle.tail.reentry`).
+    Returns (out (G, D), den (G,), live count, refined count)."""
     ka, kb, va = ka[:n], kb[:n], va[:n].double()
     ek = ek[:n]
     G = qa.shape[0]
@@ -110,6 +112,8 @@ def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, v
     num = w @ vt
     if vmean is not None and depth is not None:
         num = num + m[:, None] * vmean.double()[None, :]
+    if reentry is not None and depth is not None:
+        num = num + torch.where(live[None], torch.zeros_like(e), e) @ reentry[:n].double().to(e.device)
     den = w.sum(-1) + m
     return num * v_scale / den[:, None], den, int(live.sum()), int(refk.sum())
 
