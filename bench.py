@@ -440,11 +440,13 @@ def decode_lengths(kind, B, seed=5):
     return [int(math.exp(x)) for x in (torch.rand(B, generator=g) * (math.log(131072) - math.log(4096)) + math.log(4096))]
 
 
-def request_kv(n, HKV, D, device, seed, tail=False):
+def request_kv(n, HKV, D, device, seed, tail=False, structured=False):
     """One request's prompt K, V from its own seed (a rank can draw any request alone): N(0,1),
     1 % of key positions x 8, 0.1 % of V entries x 20. `tail`: a heavy-tailed key distribution in
     place of the x 8 keys (2 % of positions far above the rest: few live keys at depth 16, as on
-    the model captures the reference publishes its decode rows for)."""
+    the model captures the reference publishes its decode rows for). `structured`: V drifts from
+    one 64-key block to the next and carries a rank-6 image of K, under N(0, 0.5) noise: the
+    structure a decode tail can use, and iid V cannot show."""
     g = torch.Generator(device=device).manual_seed(seed)
     kk = torch.randn(n, HKV, D, device=device, generator=g)
     if tail:
@@ -454,16 +456,25 @@ def request_kv(n, HKV, D, device, seed, tail=False):
         hot = torch.rand(n, 1, 1, device=device, generator=g) < 0.01
         kk = torch.where(hot, kk * 8, kk)
     vv = torch.randn(n, HKV, D, device=device, generator=g)
+    if structured:
+        nb = -(-n // 64)
+        drift = torch.randn(nb, HKV, D, device=device, generator=g).repeat_interleave(64, 0)[:n]
+        a = torch.randn(HKV, D, 6, device=device, generator=g) / D**0.5
+        b = torch.randn(HKV, 6, D, device=device, generator=g)
+        vv = 0.5 * vv + drift + torch.einsum("shd,hdr,hre->she", kk, a, b)
     out = torch.rand(n, HKV, D, device=device, generator=g) < 0.001
     return kk.bfloat16(), torch.where(out, vv * 20, vv).bfloat16()
 
 
-def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail=False, with_e2e=True, B=None, seed=5):
+def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail=False, with_e2e=True, B=None, seed=5,
+                 tail_rank="auto"):
     """A decode config end to end: cache write, then `steps` serving steps (one token appended per
     request per step, then attention), timed as one region; us/step is the mean over the steps.
 
     config5: v8, depth 16, GQA 64/8, D128, 256 requests; config4: bf16 V, depth None, GQA 32/8,
-    128 requests. `ids` picks a subset of the batch's requests (a rank's shard). Returns the step
+    128 requests; bf16depth: bf16 V at depth 12 with the decode tail `tail_rank` ("auto": rank 16;
+    0: block rows; None: V's mean), GQA 64/8, config 5's lengths, a structured V (`request_kv`).
+    `ids` picks a subset of the batch's requests (a rank's shard). Returns the step
     time, the kernel's own counts, the roofline on algorithmic bytes, the clocks while it ran, the
     error of sampled requests against dense FP32 attention, and `e2e`: the same steps through
     `fold_attn_with_kvcache` with q, k, v in pinned host memory and the output copied back."""
@@ -471,8 +482,9 @@ def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail
     from fold_attention_b200 import FoldKVCache
 
     dense = kind == "config4"
+    deep = kind == "bf16depth"
     H, HKV, D = (32, 8, 128) if dense else (64, 8, 128)
-    full = B or (128 if dense else 256)
+    full = B or (128 if dense else 64 if deep else 256)
     lens_all = decode_lengths(kind, full, seed)
     ids = list(range(full)) if ids is None else list(ids)
     lens = [lens_all[i] for i in ids]
@@ -480,6 +492,9 @@ def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail
     kw = dict(device=device, kernel=kernel)
     if dense:
         c = FoldKVCache(Bn, H, HKV, D, max(lens) + 2 * steps + 16, chunk=4096 if kernel == "mma" else None, **kw)
+    elif deep:
+        c = FoldKVCache(Bn, H, HKV, D, max(lens) + 2 * steps + 16, depth=12.0, tail=tail_rank,
+                        chunk=8192 if kernel == "mma" or tail_rank is not None else None, **kw)
     else:
         # a fixed V scale, as every shard of a sharded layer must use (2^-3 covers |v| <= 56 at 448 / 8)
         c = FoldKVCache(Bn, H, HKV, D, max(lens) + 2 * steps + 16, depth=16.0, v8=True, v_scale=2.0 ** -3,
@@ -493,7 +508,7 @@ def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail
     v = torch.empty(T, HKV, D, device=device, dtype=torch.bfloat16)
     at = 0
     for i, n in zip(ids, lens):   # request by request: the fp32 draws of a whole batch would not fit beside the pool
-        k[at:at + n], v[at:at + n] = request_kv(n, HKV, D, device, 1000 * seed + i, tail)
+        k[at:at + n], v[at:at + n] = request_kv(n, HKV, D, device, 1000 * seed + i, tail, structured=deep)
         at += n
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     c.write_prompt(k, v, cu, lens)
@@ -538,14 +553,15 @@ def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail
     keys = sum(c.lens) * HKV
     live = c.counts[:, 0].sum().item() / keys
     refk = c.counts[:, 1].sum().item() / keys
-    vb = 2 * D if dense else D
-    byts = keys * (D + 2 + D * refk + vb * live)
+    vb = 2 * D if dense or deep else D
+    byts = keys * (D + 2 + D * refk + vb * live + (2 * D / 64 if c.tail is not None else 0))
     pk = peaks()
     launch_kernels = sorted({l.kernel for l in c._launches.values()})
     status = max(int(l.status) for l in c._launches.values())
     ratio = profiled("decode_sm100_kernel_configs4_5.md", "dram_bytes_over_algorithmic_bytes_" + ("bf16" if dense else "v8"), None)
     res = dict(
         workload=(f"config4 decode bf16 dense B{Bn} H32/8 D128 lens U[1024,32768]" if dense else
+                  f"decode bf16 V depth12 tail rank {c.tail_rank} B{Bn} H64/8 D128 lens logU[4096,131072] structured V" if deep else
                   f"config5 decode v8 depth16 B{Bn} H64/8 D128 lens logU[4096,131072]") + (" heavy-tailed keys" if tail else "")
                  + f", {steps} steps, page 256 shuffled",
         kernel="/".join(launch_kernels), us_per_step=us, steps=steps, keys=keys, live_fraction=live, refined_fraction=refk,
@@ -554,7 +570,7 @@ def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail
                       traffic=(ratio * byts if ratio else None),
                       note=f"algorithmic bytes per step from the kernel's own counts, of {pk['which']} copy bandwidth; traffic = "
                            "the ncu DRAM/algorithmic ratio of a small capture (profiles/) times the step's algorithmic bytes"),
-        clocks=ck, gpu_launches=4 * steps,   # append + Q planes, mass reference, decode, combine
+        clocks=ck, gpu_launches=(5 if c.tail is not None else 4) * steps,   # append + Q planes (+ the tail's append), mass reference, decode, combine
     )
     res["algorithmic_gbs"], res["hbm_frac"] = res["roofline"]["achieved"], res["roofline"]["frac"]
     if with_e2e:
@@ -726,6 +742,8 @@ def main():
     ap.add_argument("--decode-kernel", default="auto", choices=("auto", "mma", "sm100"))
     ap.add_argument("--decode-dense", action="store_true", help="config 4's shape instead of config 5's")
     ap.add_argument("--decode-tail", action="store_true", help="heavy-tailed keys: few live keys at depth 16")
+    ap.add_argument("--decode-bf16-depth", default=None, choices=("auto", "rows", "mean"),
+                    help="the bf16-V depth-12 extra instead: with the rank-16 tail, the block rows alone, or V's mean")
     args = ap.parse_args()
     CFG["B"] = args.batch
     if args.impl == "reference":
@@ -734,9 +752,11 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.decode_only:
         torch.cuda.set_device(0)
-        print(json.dumps(decode_extra(torch.device("cuda", 0), "config4" if args.decode_dense else "config5",
+        kind = "bf16depth" if args.decode_bf16_depth else "config4" if args.decode_dense else "config5"
+        print(json.dumps(decode_extra(torch.device("cuda", 0), kind,
                                       steps=max(2, args.decode_steps), B=args.decode_batch, kernel=args.decode_kernel,
-                                      tail=args.decode_tail, with_e2e=False)), flush=True)
+                                      tail=args.decode_tail, with_e2e=False,
+                                      tail_rank={"auto": "auto", "rows": 0, "mean": None, None: "auto"}[args.decode_bf16_depth])), flush=True)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -808,7 +828,9 @@ def main():
                         ("write_prompt", lambda: write_prompt_extra(device)),
                         ("decode_config5", lambda: decode_extra(device, "config5")),
                         ("decode_config4", lambda: decode_extra(device, "config4")),
-                        ("decode_config5_few_live_keys", lambda: decode_extra(device, "config5", B=64, tail=True, with_e2e=False))):
+                        ("decode_config5_few_live_keys", lambda: decode_extra(device, "config5", B=64, tail=True, with_e2e=False)),
+                        ("decode_bf16_depth12_tail16", lambda: decode_extra(device, "bf16depth", with_e2e=False)),
+                        ("decode_bf16_depth12_vmean", lambda: decode_extra(device, "bf16depth", with_e2e=False, tail_rank=None, kernel="mma"))):
             try:
                 extra[key] = fn()
             except Exception as e:  # the headline stands on its own

@@ -12,9 +12,10 @@ rows current. bf16 V caches only.
 
 The model is the reference's (`cache.tail_basis` / `cache.tail_model` and
 `FoldKVCache._fit_tail`, src/fold_attention/decode/cache.py:270-337,
-kv_cache.py:300-417). The fit here works from the D x D moment matrices in
-float64 throughout: the fitted values' Gram matrix is `M^T (Kc^T Kc) M`, so no
-second pass over the keys is needed.
+kv_cache.py:300-417). The fit here works from the D x D moment matrices
+(`moments`, fp32 products over a request's own keys; `rank_map`, float64
+Cholesky and eigenvectors one matrix at a time): the fitted values' Gram
+matrix is `M^T (Kc^T Kc) M`, so no second pass over the keys is needed.
 """
 
 from __future__ import annotations
@@ -78,43 +79,57 @@ def _minus_block_mean(x):
     return x - mean.repeat_interleave(TAIL_BLOCK, 1)[:, : x.shape[1]]
 
 
-def fit_rank_map(kint, ek, vs, rank, lam=1e-3):
-    """The rank-`rank` K -> V maps of N row groups.
+def moments(kint, ek, vs):
+    """The block-centred moment matrices of N row groups over S keys:
+    `Kc^T Kc` and `Kc^T Vc` `(N, D, D)` float64, K the kernel's own view of it
+    (plane A times its scale, exact in fp32). The products run in fp32 over
+    the keys and are a request's own whatever its batch."""
+    kc = _minus_block_mean(kint * ek.float()[:, :, None])
+    vc = _minus_block_mean(vs.float())
+    kt = kc.transpose(1, 2)
+    return (kt @ kc).double(), (kt @ vc).double()
 
-    `kint` `(N, S, D)` plane A of K as floats (integers), `ek` `(N, S)` the
-    keys' scales, `vs` `(N, S, D)` the values. Ridge regression of the
-    block-centred values on the block-centred keys (plane A times its scale:
-    the kernel's own view of K), the ridge `lam` times the mean diagonal of
-    the keys' moment matrix; the map is cut to the `rank` leading eigenvectors
-    of its fitted values' Gram matrix. Returns `u` `(N, rank, D)` int8 (one
-    scale per rank, folded into `vr`) and `vr` `(N, D, rank)` f32 (with the
-    256 of the kernel's `ek / 256` folded in)."""
-    N, S, D = kint.shape
-    kc = _minus_block_mean(kint.double() * ek.double()[:, :, None])
-    vc = _minus_block_mean(vs.double())
-    kk = kc.transpose(1, 2) @ kc                                   # (N, D, D)
-    kv = kc.transpose(1, 2) @ vc
+
+def rank_map(kk, kv, rank, lam=1e-3):
+    """The rank-`rank` K -> V maps from moment matrices `(N, D, D)`: ridge
+    regression (the ridge `lam` times the mean diagonal of `kk`), cut to the
+    `rank` leading eigenvectors of the fitted values' Gram matrix
+    `M^T kk M`. Returns `u` `(N, rank, D)` int8 (one scale per rank, folded
+    into `vr`) and `vr` `(N, D, rank)` f32 (with the 256 of the kernels'
+    `ek / 256` folded in). The factorisations are batched calls, whose
+    per-matrix results do not depend on the other matrices; a batch of one
+    is padded to two, because a single matrix takes another routine
+    (reference: kv_cache.py:300-312)."""
+    N, D, _ = kk.shape
+    if N == 1:
+        u, vr = rank_map(kk.expand(2, D, D).contiguous(), kv.expand(2, D, D).contiguous(), rank, lam)
+        return u[:1].contiguous(), vr[:1].contiguous()
+    eye = torch.eye(D, device=kk.device, dtype=kk.dtype)
     ridge = lam * kk.diagonal(dim1=1, dim2=2).mean(-1)
-    eye = torch.eye(D, device=kint.device, dtype=kk.dtype)
     chol = torch.linalg.cholesky(kk + (ridge[:, None, None] + 1e-30) * eye)     # a one-key prompt has no moments
-    M = torch.cholesky_solve(kv, chol)                             # (N, D, D): v ~ k M
-    gram = M.transpose(1, 2) @ kk @ M                              # of the fitted values
-    gram = 0.5 * (gram + gram.transpose(1, 2))
-    _, vec = torch.linalg.eigh(gram)
-    basis = vec[:, :, -rank:].flip(-1)                             # leading direction first
-    proj = M @ basis                                               # (N, D, rank): y = k proj
-    step = proj.abs().amax(1).clamp_min(1e-30) / 127.0             # (N, rank)
+    M = torch.cholesky_solve(kv, chol)                                         # (N, D, D): v ~ k M
+    gram = M.transpose(1, 2) @ kk @ M
+    _, vec = torch.linalg.eigh(0.5 * (gram + gram.transpose(1, 2)))
+    basis = vec[:, :, -rank:].flip(-1)                                         # leading direction first
+    proj = M @ basis                                                           # (N, D, rank): y = k proj
+    step = proj.abs().amax(1).clamp_min(1e-30) / 127.0                         # (N, rank)
     u = torch.round(proj / step[:, None, :]).clamp(-127, 127)
     vr = basis * (step * KBR)[:, None, :]
     return u.transpose(1, 2).to(torch.int8).contiguous(), vr.float().contiguous()
+
+
+def fit_rank_map(kint, ek, vs, rank, lam=1e-3):
+    """`rank_map` of `moments`: `kint` `(N, S, D)` plane A of K as floats
+    (integers), `ek` `(N, S)` the keys' scales, `vs` `(N, S, D)` the values."""
+    return rank_map(*moments(kint, ek, vs), rank, lam)
 
 
 def project(kint, ek, u):
     """Every key's projection `(N, S, r)` f32 as the kernels compute it: the
     exact integer product of plane A with `u`, times the key's `ek / 256`,
     rounded once."""
-    dots = kint.double() @ u.double().transpose(1, 2)
-    return dots.float() * (ek.float() * (1.0 / KBR))[:, :, None]
+    dots = kint.float() @ u.float().transpose(1, 2)      # integers under 2^24: exact in fp32 in any order
+    return dots * (ek.float() * (1.0 / KBR))[:, :, None]
 
 
 def fit_prompt(kint, ek, v, rank, lam=1e-3, fit=None):

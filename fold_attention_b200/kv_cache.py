@@ -254,24 +254,38 @@ class FoldKVCache:
         read back and un-swizzled), so its tail does not depend on its batch
         (reference: kv_cache.py:300-417, `_fit_tail`)."""
         t, PS, HKV, D, TB = self.tail, self.page_size, self.n_kv_heads, self.head_dim, tail_fit.TAIL_BLOCK
-        dev = self.device
+        dev, R = self.device, self.tail.rank
         heads = torch.arange(HKV, device=dev)[:, None]
-        at = 0
-        for b, n in enumerate(lens):
+
+        def keys_of(b, n):
+            """Request b's pool rows (HKV, n), plane A in channel order and scales."""
             pos = torch.arange(n, device=dev)
             pg = self.page_table[b, pos // PS].long()
-            prow = (pg[None, :] * HKV + heads) * PS + (pos % PS)[None, :]          # (HKV, n)
-            kint = tail_fit.plane_rows(self.ka, prow, pos % PS, D)
-            u, vr, vsum, ysum, rows = tail_fit.fit_prompt(
-                kint, self.ek[prow], v[at:at + n].transpose(0, 1), t.rank)
+            prow = (pg[None, :] * HKV + heads) * PS + (pos % PS)[None, :]
+            return prow, tail_fit.plane_rows(self.ka, prow, pos % PS, D), self.ek[prow]
+
+        starts = [0]
+        for n in lens:
+            starts.append(starts[-1] + n)
+        if R:
+            # every row group's D x D problem in one batched solve and one batched eigendecomposition
+            mom = [tail_fit.moments(*keys_of(b, n)[1:], v[starts[b]:starts[b] + n].transpose(0, 1)) for b, n in enumerate(lens)]
+            u, vr = tail_fit.rank_map(torch.cat([m[0] for m in mom]), torch.cat([m[1] for m in mom]), R)
+            t.u.copy_(u)
+            t.vr.copy_(vr)
+        for b, n in enumerate(lens):
+            prow, kint, ek = keys_of(b, n)
+            vsum, cnt = tail_fit.block_sums(v[starts[b]:starts[b] + n].transpose(0, 1).float())
+            cnt = cnt[None, :, None].float()
             blk = prow[:, ::TB] // TB                                              # (HKV, blocks)
+            rows = vsum / cnt
+            if R:
+                g = slice(b * HKV, (b + 1) * HKV)
+                ysum, _ = tail_fit.block_sums(tail_fit.project(kint, ek, t.u[g]))
+                rows = rows - (ysum / cnt) @ t.vr[g].transpose(1, 2)
+                t.ysum[blk] = ysum
             t.vsum[blk] = vsum
             t.rows[blk] = rows.to(t.rows.dtype)
-            if t.rank:
-                t.ysum[blk] = ysum
-                t.u[b * HKV:(b + 1) * HKV] = u
-                t.vr[b * HKV:(b + 1) * HKV] = vr
-            at += n
 
     def append(self, k, v):
         """Write one token per request, `(batch, H_KV, D)` each, at its length."""
