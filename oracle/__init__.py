@@ -19,5 +19,10 @@ Pinning status
   `benchmarks/harness/training.py:124-164` and `tests/test_backward.py:79-92`.
 * `decode` restates the float64 models the reference's tests hold
   (`tests/test_decode.py:902-928` coarse logit, `:983-1011` mass estimate,
-  `:151-153` truncated softmax).
+  `:151-153` truncated softmax), pinned against those functions' own outputs
+  (`tests/golden/float_models.npz`).
+* `tail` restates the decode tail's fit (`src/fold_attention/decode/cache.py:260-337`) and the
+  append's block update (`decode/write.py:193-300`); pinned against the reference's `tail_model`
+  outputs (`tests/golden/tail_model.npz`) through the effective map, the re-entry points and
+  the block rows.
 """
