@@ -33,6 +33,8 @@ from dataclasses import dataclass
 SMS = 148           # B200
 TILE = 128          # query and key block of the tcgen05 main loop
 MIN_ITEM = 8        # tiles: below this an item's fixed costs (K, V loads, the dK / dV exit) dominate
+PRIVATE_SHARE = 0.6 # a whole-group item may be this much of one SM's share of the tiles (B1 H32/8 S8192: 0.57,
+                    # where Plan(4, 0) measured 1005 TFLOP/s against 900 for Plan(2, 0))
 
 
 @dataclass(frozen=True)
@@ -73,7 +75,8 @@ def plan_dense(B, H, H_KV, S, D, causal, cfg: TileConfig | None = None, sms: int
 
     The longest item (key block 0 under a causal mask: it sees every query
     block) should be at most half of one SM's fair share of the tiles, or the
-    launch ends waiting for it. Whole groups first; then smaller subgroups;
+    launch ends waiting for it; a whole group may take `PRIVATE_SHARE` of it,
+    because its dK / dV never leave the CTA. Whole groups first; then smaller subgroups;
     then, for a single head still too long (few heads, long sequences),
     records of the query range.
     """
@@ -85,6 +88,10 @@ def plan_dense(B, H, H_KV, S, D, causal, cfg: TileConfig | None = None, sms: int
     cap = tiles / sms / 2
     if cap < MIN_ITEM:
         return Plan(G, 0)        # a small call: nothing to balance, and folding has fixed costs of its own
+    if nb * G <= PRIVATE_SHARE * tiles / sms:
+        # whole groups still fit: the private exit (no integer fold, no dK / dV postprocess) is worth
+        # more than finer items as long as the longest-first list can hide the longest one
+        return Plan(G, 0)
     for sub in _divisors_desc(G):
         if nb * sub <= cap:
             return Plan(sub, 0)

@@ -10,7 +10,9 @@ def test_the_dense_plan_follows_the_request_shape():
     assert plan_dense(2, 32, 8, 8192, 128, True) == Plan(4, 0)
     # too few, too long whole-group items for 148 SMs: cut the group
     assert plan_dense(2, 32, 1, 8192, 128, True) == Plan(4, 0) and Plan(4, 0).folds(32)
-    assert plan_dense(1, 32, 8, 8192, 128, True) == Plan(2, 0)
+    # a whole group may be a larger share of an SM's tiles than a folding subgroup: its dK / dV stay private
+    assert plan_dense(1, 32, 8, 8192, 128, True) == Plan(4, 0) and not Plan(4, 0).folds(4)
+    assert plan_dense(1, 16, 4, 8192, 128, True) == Plan(1, 0) and Plan(1, 0).folds(4)
     # one long sequence, few heads: even single heads are too long, so the query range is cut too
     assert plan_dense(1, 4, 1, 8192, 128, True) == Plan(1, 28)
     assert plan_dense(1, 8, 2, 8192, 128, True) == Plan(1, 56)
