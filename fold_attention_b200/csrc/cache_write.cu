@@ -392,6 +392,7 @@ __global__ void __launch_bounds__(NT) tail_append_kernel(
     __shared__ float sY[16];
     const int kr = blockIdx.x, b = kr / hkv, h = kr % hkv, tid = threadIdx.x;
     const int pos = lens[b] - back;
+    if (pos < 0 || pos >= ppr * page_size) return;      // no appended token at this length: touch nothing
     const int pg = __ldg(page_table + static_cast<int64_t>(b) * ppr + pos / page_size);
     const int off = pos % page_size;
     const int64_t prow = (static_cast<int64_t>(pg) * hkv + h) * page_size + off;

@@ -41,6 +41,33 @@ def test_bad_arguments_return_a_status_and_a_message():
     assert _lib.lib.fold_bwd_workspace_bytes(2, 32, 1, 8192, 2 * 8192, 128, 0, 5, 0) == 0   # 5 does not divide 32
 
 
+def test_the_tail_entries_refuse_what_they_cannot_run():
+    """Argument checks come before any CUDA call, so they run without a GPU."""
+    import fold_attention_b200.decode.launch  # noqa: F401  (registers fold_decode_run_tail)
+    from fold_attention_b200 import _lib
+
+    one = ctypes.c_void_p(256)      # never dereferenced: every call below is refused first
+
+    def tail_decode(rank=16, u=one, vr=one, page_size=128, rows=one):
+        return _lib.lib.fold_decode_run_tail(one, one, one, one, one, one, one, rows, u, vr, rank, one, one, one, one, None,
+                                             2, 8, 2, 128, 4, page_size, 1, 0, 2, 8.0, one, one, one, one, 0, one, one, one, None)
+
+    assert tail_decode(rank=12) == 1 and b"tail rank 12" in _lib.lib.fold_last_error()
+    assert tail_decode(rank=-1) == 1
+    assert tail_decode(u=None) == 1 and b"rank 16 only" in _lib.lib.fold_last_error()
+    assert tail_decode(rank=0) == 1              # rank 0 takes no u and vr
+    assert tail_decode(page_size=32) == 1 and b"one row per 64 keys" in _lib.lib.fold_last_error()
+    assert tail_decode(rows=None) == 1
+
+    def tail_append(rank=16, page_size=128, back=1, ysum=one):
+        return _lib.lib.fold_tail_append(one, 0, 2, 2, 128, one, 4, page_size, one, back, one, one, one, one, one, ysum, one, rank, None)
+
+    assert tail_append(rank=8) == 1 and b"tail rank 8" in _lib.lib.fold_last_error()
+    assert tail_append(page_size=96) == 1
+    assert tail_append(back=2) == 1
+    assert tail_append(ysum=None) == 1 and b"rank 16 needs" in _lib.lib.fold_last_error()
+
+
 def test_python_signatures_cover_the_header():
     import fold_attention_b200  # noqa: F401  (registers every signature)
     import fold_attention_b200.decode.static_scratch  # noqa: F401
