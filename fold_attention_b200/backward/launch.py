@@ -107,6 +107,20 @@ def prepare_backward(
         raise NotImplementedError("the value head dim must equal the key head dim")
     if q.dtype not in (torch.bfloat16, torch.float16):
         raise ValueError("q, k and v must be bf16 or fp16")
+    # the kernels index every tensor by q's sizes: anything that does not match would be read or written past its end
+    lead = (total,) if varlen else (B,)
+    if k.dim() != q.dim() or tuple(k.shape[:1]) != lead or k.shape[-1] != D or v.shape != k.shape:
+        raise ValueError(f"k and v {tuple(k.shape)}, {tuple(v.shape)} do not match q {tuple(q.shape)}")
+    if o.shape != q.shape or do.shape != q.shape:
+        raise ValueError(f"o and do are q's shape {tuple(q.shape)} (got {tuple(o.shape)}, {tuple(do.shape)})")
+    if tuple(lse.shape) != ((H, total) if varlen else (B, H, S)):
+        raise ValueError(f"lse is {'(H, total)' if varlen else '(B, H, S)'} (got {tuple(lse.shape)})")
+    if any(t.dtype != q.dtype for t in (k, v, o, do)):
+        raise ValueError("q, k, v, o and do must be the same 16-bit type")
+    if any(t.device != q.device for t in (k, v, o, do, lse)) or any(t.stride(-1) != 1 for t in (q, k, v, o, do)):
+        raise ValueError("q, k, v, o, do and lse are on one device, each with a contiguous head dim")
+    if varlen and (cu_seqlens.dtype != torch.int32 or cu_seqlens.device != q.device):
+        raise ValueError("cu_seqlens is int32 on q's device")
     if H % H_KV:
         raise ValueError("the query heads must be a multiple of the KV heads")
     if D not in (64, 96, 128):
@@ -185,6 +199,19 @@ def attention_forward(q, k, v, *, causal, softmax_scale=None, cu_seqlens=None, m
         raise ValueError('kernel is one of ("auto", "mma", "sm100")')
     varlen = cu_seqlens is not None
     D = q.shape[-1]
+    # the kernels index k and v by q's batch, length and head dim: a mismatch would read past them
+    if q.dim() != (3 if varlen else 4) or k.dim() != q.dim() or v.shape != k.shape:
+        raise ValueError(f"q is {'(total, H, D)' if varlen else '(B, S, H, D)'}, k and v the same with H_KV heads "
+                         f"(got q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)})")
+    if k.shape[:-2] != q.shape[:-2] or k.shape[-1] != D or q.shape[-2] % k.shape[-2]:
+        raise ValueError(f"k and v {tuple(k.shape)} do not match q {tuple(q.shape)}: same leading sizes and head dim, "
+                         "and a head count that divides q's")
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError(f"q, k and v must be bf16 or fp16, and the same type (got {q.dtype}, {k.dtype}, {v.dtype})")
+    if any(t.stride(-1) != 1 for t in (q, k, v)) or k.device != q.device or v.device != q.device:
+        raise ValueError("q, k and v are on one device with a contiguous head dim")
+    if varlen and (cu_seqlens.dtype != torch.int32 or cu_seqlens.device != q.device):
+        raise ValueError("cu_seqlens is int32 on q's device")
     sm = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
     o = torch.empty_like(q)
     if varlen:

@@ -9,9 +9,10 @@
 //   O += P V     A = P from TMEM, B = V as stored (MN-major), 8 steps of 16 keys -> TMEM fp32
 //
 // The two tiles share each K/V stage and take turns on the tensor core: while one tile's
-// rows are in their softmax, the other's scores or P V product run. The running maximum
-// only ever rises; O is rescaled in TMEM when a row's maximum rose (skipped by warps in
-// which no row's did), after the tile's previous product has retired.
+// rows are in their softmax, the other's scores or P V product run. A row's softmax
+// reference only ever rises, and only when the row's maximum passed it by more than 2^8; O is
+// rescaled in TMEM when a row's reference moved (skipped, with the wait for the tile's previous
+// product, by warps in which no row's did).
 //
 // Warps: 0 TMA producer, 1 MMA issuer (owns all 512 TMEM columns), 4-7 and 8-11 the two
 // tiles' softmax, O rescale and epilogue. Every wait is bounded (about a second); on expiry
@@ -32,6 +33,7 @@ constexpr int BM = 128, BN = 128;   // a query tile, a key tile
 constexpr int CTA_M = 2 * BM;       // a CTA owns two query tiles
 constexpr int NTHREADS = 384;
 constexpr long long WAIT_CYCLES = 1ll << 31;
+constexpr float LAZY = 8.0f;        // log2 of how far a row's maximum may pass its softmax reference before the reference moves
 
 // shared memory map (1024-aligned base)
 constexpr int SM_Q = 0;                        // 2 tiles x [2 boxes of 64 channels][128 rows][128 B]
@@ -326,10 +328,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) mxv = max3f(mxv, __uint_as_float(sv[e]), __uint_as_float(sv[e + 1]));
             }
-            const float m_new = fmaxf(m_run, mxv * c2);
+            // The reference point only moves when the row's maximum rose by more than 2^LAZY: weights
+            // up to 2^LAZY are as exact in 16 bits as weights up to 1, the final O / l cancels the
+            // choice, and a row whose reference stays has alpha = 1 exactly, so its warp neither
+            // waits for the previous product nor rescales O. After a sequence's first tiles that is
+            // nearly every warp.
+            const float m_cand = fmaxf(m_run, mxv * c2);
+            const float m_new = m_cand > m_run + LAZY ? m_cand : m_run;
             // a row that sees no key yet keeps m = -inf; its weights are exp2(-inf) = 0
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = ex2f(m_run - m_use);   // 0 on the first tile that holds a key
+            const float alpha = ex2f(m_run - m_use);   // 0 on the first tile that holds a key, 1 where the reference stays
             // pass 2: weights over the scores as packed bf16 (P chunk c lands on columns the row's
             // thread has already read), and their sum
             uint64_t sum2 = 0ull;   // two partial sums, added at the end of the tile
@@ -360,10 +368,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fwd_sm100_kernel(const Params p, 
             l_run = l_run * alpha + (sum_e + sum_o);
             m_run = m_new;
             // O was last written by key tile j-1's product: rescale it where a row's maximum rose
-            if (j > 0) {
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
                 mbar_wait(bar(B_ODONE + x), (j - 1) & 1, abort_flag, p.status);
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t ov[32];

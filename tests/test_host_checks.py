@@ -42,3 +42,38 @@ def test_status_text():
         check_status(torch.tensor([3], dtype=torch.int32), "x")
     with pytest.raises(_lib.FoldLibraryError, match="refused its arguments"):
         check_status(torch.tensor([1], dtype=torch.int32), "x")
+
+
+def test_the_forward_and_backward_refuse_tensors_that_do_not_match_q():
+    """The kernels index k, v, o, do and lse by q's sizes, so a mismatch is refused on the host
+    (CPU tensors here: the checks come before any launch)."""
+    from fold_attention_b200.backward.launch import attention_forward, prepare_backward
+
+    B, S, H, HKV, D = 2, 16, 4, 2, 64
+    q = torch.zeros(B, S, H, D, dtype=torch.bfloat16)
+    k = torch.zeros(B, S, HKV, D, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="do not match q"):
+        attention_forward(q, k[:, :8], k[:, :8], causal=True)          # a shorter k: would be read past its end
+    with pytest.raises(ValueError, match="do not match q"):
+        attention_forward(q.transpose(1, 2), k, k, causal=True)        # (B, H, S, D) passed where (B, S, H, D) goes
+    with pytest.raises(ValueError, match="H_KV heads"):
+        attention_forward(q, k, k[:, :, :1], causal=True)
+    with pytest.raises(ValueError, match="same type"):
+        attention_forward(q, k.half(), k.half(), causal=True)
+    with pytest.raises(ValueError, match="contiguous head dim"):
+        attention_forward(q.transpose(-1, -2).contiguous().transpose(-1, -2), k, k, causal=True)
+    with pytest.raises(ValueError, match="int32"):
+        attention_forward(q[0], k[0], k[0], causal=True, cu_seqlens=torch.tensor([0, 16]), max_seqlen=16)
+
+    qb, kb = q.transpose(1, 2), k.transpose(1, 2)                      # the backward's (B, H, S, D) views
+    lse = torch.zeros(B, H, S)
+    with pytest.raises(ValueError, match="do not match q"):
+        prepare_backward(qb, kb[:1], kb[:1], qb, qb, lse, causal=True)
+    with pytest.raises(ValueError, match="o and do are q's shape"):
+        prepare_backward(qb, kb, kb, qb[:, :2], qb, lse, causal=True)
+    with pytest.raises(ValueError, match=r"lse is \(B, H, S\)"):
+        prepare_backward(qb, kb, kb, qb, qb, lse[:, :, :8], causal=True)
+    with pytest.raises(ValueError, match="same 16-bit type"):
+        prepare_backward(qb, kb, kb, qb.half(), qb, lse, causal=True)
+    with pytest.raises(NotImplementedError, match="self-attention"):
+        prepare_backward(qb, kb[:, :, :8], kb[:, :, :8], qb, qb, lse, causal=True)
