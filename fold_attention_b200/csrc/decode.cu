@@ -46,6 +46,13 @@ struct DecodeParams {
     // the tail (bf16 V, truncating): one bf16 row per 64 pool rows, each row group's int8
     // projection (16, D) and map back (D, 16); all null without a tail, u and vr null at rank 0
     const uint16_t* tail_rows; const int8_t* tail_u; const float* tail_vr;
+    // levels and layouts beyond the single-level step (all neutral by default):
+    const int* req_map;     // request -> row of page_table / seq_lens (a cascade's shared level: its prefix); null: itself
+    const int* tree;        // (NBH, G) int32, bit j of a row: draft node j is visible to it; null without a draft
+    int q_len;              // draft nodes: the cache's last q_len keys; 0 without a draft
+    int gsub;               // row groups per KV head (a group wider than 8 rows runs as gsub groups of 8)
+    int slots_total, slot_off;   // partial slot of (row group, split sp): bh * slots_total + slot_off + sp
+    int row_cut;            // 1: a key enters a row only if that row keeps it (drafts, cascades); 0: if any row of the group does
     int bh_limit;   // > 0: the partial buffers hold this many row groups; an `order` entry outside is refused
 };
 
@@ -131,8 +138,12 @@ struct DecSmem {
 // its 64-key block's row plus the part of its V its K predicts: y = (plane A . u) ek / 256 comes
 // out of the coarse logit's own matmul (u's rows are two more B operands), the dropped weights
 // meet it in one bf16 mma per 8 ranks, and the epilogue maps the rank sums back through vr.
-template <int D, bool V8, bool W2, bool TRUNC, int TR>
+// EX: the layouts beyond the single-level step (a cascade's shared level, split row groups, a
+// draft's visibility words, a row's own cut); a build of its own, so the step's builds keep
+// their registers.
+template <int D, bool V8, bool W2, bool TRUNC, int TR, bool EX = false>
 __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams p) {
+    static_assert(!EX || TR < 0, "the tail runs on single-level steps");
     static_assert(TR < 0 || (TRUNC && !V8), "the tail re-enters truncated mass on a bf16 V");
     static_assert(TR == -1 || TR == 0 || TR == 16, "tail ranks: none, 0, 16");
     using L = DecSmem<D, V8>;
@@ -147,8 +158,10 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
         if (tid == 0) atomicExch(p.status, FOLD_ERR_ARGUMENT);
         return;
     }
-    const int breq = bh / p.hkv, hkv = bh % p.hkv;
-    const int slen = p.seq_lens[breq];
+    const int bhk = EX ? bh / p.gsub : bh;             // the KV head's row group in the cache's numbering
+    const int breq = bhk / p.hkv, hkv = bhk % p.hkv;
+    const int preq = (EX && p.req_map) ? p.req_map[breq] : breq;
+    const int slen = p.seq_lens[preq];
     const int G = p.G, PS = p.page_size;
 
     // this split's tiles: interleaved (tile sp, sp + split, ...) or a fixed chunk
@@ -166,7 +179,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
         const int all = (slen + BNK - 1) / BNK;
         n_tiles = all > sp ? (all - sp + p.split - 1) / p.split : 0;
     }
-    const int64_t pix = static_cast<int64_t>(bh) * p.split + sp;
+    const int64_t pix = EX ? static_cast<int64_t>(bh) * p.slots_total + p.slot_off + sp : static_cast<int64_t>(bh) * p.split + sp;
 
     float rk = p.rk, rv = p.rv;
     if (p.banded) {
@@ -186,7 +199,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
     }
     __syncthreads();
 
-    const int* ptab = p.page_table + static_cast<int64_t>(breq) * p.ppr;
+    const int* ptab = p.page_table + static_cast<int64_t>(preq) * p.ppr;
     // pool row of position `pos` of this row group
     auto pool_row = [&](int pos) -> int64_t {
         return (static_cast<int64_t>(__ldg(ptab + pos / PS)) * p.hkv + hkv) * PS + pos % PS;
@@ -242,6 +255,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
     // the two rows this lane's logit registers belong to
     float eqr[2], zr[2], cutr[2];
     bool rowok[2];
+    uint32_t treer[2] = {~0u, ~0u};
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
         const int g = 2 * tq + j;
@@ -250,7 +264,13 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
         eqr[j] = p.eq[ix];
         zr[j] = p.z[ix];
         cutr[j] = -p.cut[ix];
+        if (EX && p.tree) treer[j] = static_cast<uint32_t>(p.tree[ix]);
     }
+    // a draft: the cache's last q_len keys are the draft's own nodes, and a row sees node j only
+    // if bit j of its word is set (a chain's row t sees nodes 0..t)
+    const int node0 = (EX && p.q_len > 0) ? slen - p.q_len : (1 << 30);
+    auto sees = [&](int j, int kabs) { return !EX || kabs < node0 || ((treer[j] >> (kabs - node0)) & 1u) != 0u; };
+    (void)treer; (void)node0;
 
     float acc[NT][4];
 #pragma unroll
@@ -261,7 +281,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
     int nlive = 0, nref = 0;
 
     float s_old[4] = {0, 0, 0, 0}, tk_old[4] = {0, 0, 0, 0};
-    int b_old[2] = {0, 0}, nrow_old = 0;
+    int b_old[2] = {0, 0}, nrow_old = 0, base_old = 0;
     bool failed = false;
 
     for (int t = 0; t <= n_tiles; ++t) {
@@ -308,7 +328,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                     y_new[4 + i] = ky < nrow ? static_cast<float>(cy2[i]) * ekf : 0.f;
                 }
                 float s1 = -INFINITY;
-                if (rowok[i & 1] && ky < nrow) {
+                if (rowok[i & 1] && ky < nrow && sees(i & 1, base + ky)) {
                     s1 = fmaf(static_cast<float>(c1[i] * 256 + c2[i]), tk, -zr[i & 1]);
                     if (TRUNC && s1 >= cutr[i & 1]) pk |= 1 << (3 * (i >> 1));
                     dg[i >> 1] = fmaxf(dg[i >> 1], s1);
@@ -419,8 +439,9 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int ky = 16 * warp + gid + 8 * (i >> 1);
-                const bool valid = rowok[i & 1] && ky < nrow_old;
-                const bool live = (b_old[i >> 1] & 1) != 0;
+                const bool valid = rowok[i & 1] && ky < nrow_old && sees(i & 1, base_old + ky);
+                // under a row's own cut a gathered key enters only the rows that keep it
+                const bool live = (b_old[i >> 1] & 1) != 0 && (!EX || !p.row_cut || s_old[i] >= cutr[i & 1]);
                 float s = s_old[i];
                 if (b_old[i >> 1] & 2)
                     s = s + (static_cast<float>(c3a[i]) + static_cast<float>(c3b[i]) * (1.0f / 256.0f)) * tk_old[i];
@@ -548,6 +569,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
         b_old[0] = b_new[0];
         b_old[1] = b_new[1];
         nrow_old = nrow_new;
+        base_old = lo + t * tstep;
     }
     cp_async_wait<0>();
     __syncthreads();
@@ -602,7 +624,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
             m += sRed[w2 * 8 + g];
         }
         if (V8) x *= E4O;
-        if (TR < 0 && TRUNC && p.vmean) x += m * p.vmean[static_cast<int64_t>(bh) * D + c];
+        if (TR < 0 && TRUNC && p.vmean) x += m * p.vmean[(static_cast<int64_t>(preq) * p.hkv + hkv) * D + c];
         if constexpr (TR > 0) {
             const float4* vr = reinterpret_cast<const float4*>(p.tail_vr + (static_cast<int64_t>(bh) * D + c) * TR);
 #pragma unroll
@@ -673,12 +695,14 @@ template <int D>
 __global__ void __launch_bounds__(DEC_THREADS) mass_z_kernel(
     const int8_t* __restrict__ qa, const int8_t* __restrict__ qb, const float* __restrict__ eq,
     const int8_t* __restrict__ ka, const uint16_t* __restrict__ ek, const int* __restrict__ page_table,
-    const int* __restrict__ seq_lens, int G, int hkv, int ppr, int PS, float* __restrict__ z) {
+    const int* __restrict__ seq_lens, int G, int hkv, int ppr, int PS, float* __restrict__ z,
+    const int* __restrict__ req_map, int gsub, const int* __restrict__ tree, int q_len) {
     __shared__ __align__(16) int8_t sQ[2][8][D];
     __shared__ float sS[MASS_ROWS][8];
     __shared__ int sKey[MASS_ROWS];
     __shared__ int sClass[MASS_ROWS];   // 0 unused, 1 exact, 2 sample
-    const int bh = blockIdx.x, breq = bh / hkv, h = bh % hkv, tid = threadIdx.x;
+    const int bh = blockIdx.x, bhk = bh / gsub, h = bhk % hkv, tid = threadIdx.x;
+    const int breq = req_map ? req_map[bhk / hkv] : bhk / hkv;   // the row of page_table / seq_lens this group reads
     const int n = seq_lens[breq];
     for (int i = tid; i < G * D / 4; i += DEC_THREADS) {
         reinterpret_cast<uint32_t*>(&sQ[0][0][0])[i] = reinterpret_cast<const uint32_t*>(qa + static_cast<int64_t>(bh) * G * D)[i];
@@ -728,8 +752,13 @@ __global__ void __launch_bounds__(DEC_THREADS) mass_z_kernel(
             }
         }
         const float ekf = bf16_bits_to_float(ek[prow]) * (1.0f / 256.0f);
-        for (int g = 0; g < G; ++g)
-            sS[r][g] = static_cast<float>(c1[g] * 256 + c2[g]) * (eq[static_cast<int64_t>(bh) * G + g] * ekf);
+        for (int g = 0; g < G; ++g) {
+            float sg = static_cast<float>(c1[g] * 256 + c2[g]) * (eq[static_cast<int64_t>(bh) * G + g] * ekf);
+            // a draft node the row does not see weighs nothing (the nodes are the newest keys: all in the exact window)
+            if (q_len > 0 && pos >= n - q_len && !((static_cast<uint32_t>(tree[static_cast<int64_t>(bh) * G + g]) >> (pos - (n - q_len))) & 1u))
+                sg = -INFINITY;
+            sS[r][g] = sg;
+        }
     }
     __syncthreads();
     // one warp per query row (rows g = warp, warp + 4)
@@ -794,10 +823,10 @@ using namespace fold;
 
 namespace {
 
-template <int D, bool V8, bool W2, bool TRUNC, int TR = -1>
+template <int D, bool V8, bool W2, bool TRUNC, int TR = -1, bool EX = false>
 int launch_decode(const DecodeParams& p, cudaStream_t st) {
     using L = DecSmem<D, V8>;
-    auto kern = decode_kernel<D, V8, W2, TRUNC, TR>;
+    auto kern = decode_kernel<D, V8, W2, TRUNC, TR, EX>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES);
     kern<<<p.nbh * p.split, DEC_THREADS, L::BYTES, st>>>(p);
     return check_launch("fold_decode_run");
@@ -807,6 +836,12 @@ template <int D>
 int launch_decode_tail(const DecodeParams& p, int w2, cudaStream_t st) {
     if (p.tail_u) return w2 ? launch_decode<D, false, true, true, 16>(p, st) : launch_decode<D, false, false, true, 16>(p, st);
     return w2 ? launch_decode<D, false, true, true, 0>(p, st) : launch_decode<D, false, false, true, 0>(p, st);
+}
+
+template <int D, bool V8>
+int launch_decode_ex(const DecodeParams& p, int w2, cudaStream_t st) {
+    if (p.truncate) return w2 ? launch_decode<D, V8, true, true, -1, true>(p, st) : launch_decode<D, V8, false, true, -1, true>(p, st);
+    return w2 ? launch_decode<D, V8, true, false, -1, true>(p, st) : launch_decode<D, V8, false, false, -1, true>(p, st);
 }
 
 template <int D, bool V8>
@@ -827,10 +862,32 @@ extern "C" int fold_mass_z(const int8_t* qa, const int8_t* qb, const float* eq, 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint16_t* ekp = static_cast<const uint16_t*>(ek);
     if (head_dim == 128)
-        mass_z_kernel<128><<<n_groups, DEC_THREADS, 0, st>>>(qa, qb, eq, ka, ekp, page_table, seq_lens, group, n_kv_heads, pages_per_request, page_size, z);
+        mass_z_kernel<128><<<n_groups, DEC_THREADS, 0, st>>>(qa, qb, eq, ka, ekp, page_table, seq_lens, group, n_kv_heads, pages_per_request, page_size, z, nullptr, 1, nullptr, 0);
     else
-        mass_z_kernel<64><<<n_groups, DEC_THREADS, 0, st>>>(qa, qb, eq, ka, ekp, page_table, seq_lens, group, n_kv_heads, pages_per_request, page_size, z);
+        mass_z_kernel<64><<<n_groups, DEC_THREADS, 0, st>>>(qa, qb, eq, ka, ekp, page_table, seq_lens, group, n_kv_heads, pages_per_request, page_size, z, nullptr, 1, nullptr, 0);
     return check_launch("fold_mass_z");
+}
+
+// The mass reference for the layouts fold_decode_run_ex takes: a cascade's shared level
+// (`req_map`), row groups wider than 8 rows (`group_split`), a draft's rows (`tree`, `draft_len`).
+extern "C" int fold_mass_z_ex(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                              const void* ek, const int32_t* page_table, const int32_t* seq_lens,
+                              int n_groups, int group, int n_kv_heads, int head_dim,
+                              int pages_per_request, int page_size, float* z, const int32_t* req_map,
+                              int group_split, const int32_t* tree, int draft_len, void* stream) {
+    FOLD_CHECK_ARG(qa && qb && eq && ka && ek && page_table && seq_lens && z, "fold_mass_z_ex: null pointer");
+    FOLD_CHECK_ARG(group >= 1 && group <= 8, "a row group of %d rows: 1..8 are supported", group);
+    FOLD_CHECK_ARG(head_dim == 64 || head_dim == 128, "head_dim %d: the decode takes 64 or 128", head_dim);
+    FOLD_CHECK_ARG(group_split >= 1 && n_groups % group_split == 0, "group_split %d does not divide %d row groups", group_split, n_groups);
+    FOLD_CHECK_ARG(draft_len >= 0 && draft_len <= 32 && (draft_len == 0) == (tree == nullptr),
+                   "a draft is its node count (1..32) and its rows' visibility words");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint16_t* ekp = static_cast<const uint16_t*>(ek);
+    if (head_dim == 128)
+        mass_z_kernel<128><<<n_groups, DEC_THREADS, 0, st>>>(qa, qb, eq, ka, ekp, page_table, seq_lens, group, n_kv_heads, pages_per_request, page_size, z, req_map, group_split, tree, draft_len);
+    else
+        mass_z_kernel<64><<<n_groups, DEC_THREADS, 0, st>>>(qa, qb, eq, ka, ekp, page_table, seq_lens, group, n_kv_heads, pages_per_request, page_size, z, req_map, group_split, tree, draft_len);
+    return check_launch("fold_mass_z_ex");
 }
 
 static int decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
@@ -844,7 +901,18 @@ static int decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const
                       float* o_part, float* den_part, int32_t* cnt_part, void* out,
                       int out_dtype, float* den, int32_t* counts, int32_t* status,
                       int bh_limit, void* stream, const void* tail_rows = nullptr,
-                      const int8_t* tail_u = nullptr, const float* tail_vr = nullptr, int tail_rank = -1) {
+                      const int8_t* tail_u = nullptr, const float* tail_vr = nullptr, int tail_rank = -1,
+                      const int32_t* req_map = nullptr, int group_split = 1, const int32_t* tree = nullptr,
+                      int draft_len = 0, int slots_total = 0, int slot_off = 0, int row_cut = 0) {
+    if (slots_total <= 0) slots_total = split;
+    FOLD_CHECK_ARG(group_split >= 1 && n_groups % group_split == 0, "group_split %d does not divide %d row groups", group_split, n_groups);
+    FOLD_CHECK_ARG(draft_len >= 0 && draft_len <= 32 && (draft_len == 0) == (tree == nullptr),
+                   "a draft is its node count (1..32) and its rows' visibility words");
+    FOLD_CHECK_ARG(slot_off >= 0 && slot_off + split <= slots_total, "splits %d..%d of %d partial slots", slot_off, slot_off + split, slots_total);
+    FOLD_CHECK_ARG(slots_total == split || (chunk_keys == 0 && !out),
+                   "a level of several writes its own slots of uncombined partials, with interleaved splits (chunk_keys 0, out NULL)");
+    FOLD_CHECK_ARG(tail_rank < 0 || (!req_map && !tree && group_split == 1 && !row_cut),
+                   "the tail runs on single-level steps with the group's cut");
     if (tail_rank >= 0) {
         FOLD_CHECK_ARG(tail_rank == 0 || tail_rank == 16, "tail rank %d: 0 (block rows alone) or 16", tail_rank);
         FOLD_CHECK_ARG(tail_rows && (tail_rank == 0 ? (!tail_u && !tail_vr) : (tail_u && tail_vr)),
@@ -884,16 +952,21 @@ static int decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const
     p.status = status;
     p.bh_limit = bh_limit;
     p.tail_rows = static_cast<const uint16_t*>(tail_rows); p.tail_u = tail_u; p.tail_vr = tail_vr;
+    p.req_map = req_map; p.tree = tree; p.q_len = draft_len; p.gsub = group_split;
+    p.slots_total = slots_total; p.slot_off = slot_off; p.row_cut = row_cut;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool v8 = vb != nullptr;
     int rc;
+    const bool ex = req_map || tree || group_split > 1 || slots_total != split || slot_off || row_cut;
     if (tail_rank >= 0) rc = head_dim == 128 ? launch_decode_tail<128>(p, weight_terms == 2, st) : launch_decode_tail<64>(p, weight_terms == 2, st);
+    else if (ex && head_dim == 128) rc = v8 ? launch_decode_ex<128, true>(p, weight_terms == 2, st) : launch_decode_ex<128, false>(p, weight_terms == 2, st);
+    else if (ex) rc = v8 ? launch_decode_ex<64, true>(p, weight_terms == 2, st) : launch_decode_ex<64, false>(p, weight_terms == 2, st);
     else if (head_dim == 128) rc = v8 ? launch_decode_d<128, true>(p, weight_terms == 2, st) : launch_decode_d<128, false>(p, weight_terms == 2, st);
     else rc = v8 ? launch_decode_d<64, true>(p, weight_terms == 2, st) : launch_decode_d<64, false>(p, weight_terms == 2, st);
     if (rc) return rc;
     if (!out) return FOLD_OK;   // partials only: the caller combines
     const int threads = 256;
-#define FOLD_COMBINE(OUT) decode_combine_kernel<OUT><<<n_groups, threads, 0, st>>>(o_part, den_part, cnt_part, seq_lens, out, den, counts, group, head_dim, n_kv_heads, split, chunk_keys, v_scale)
+#define FOLD_COMBINE(OUT) decode_combine_kernel<OUT><<<n_groups, threads, 0, st>>>(o_part, den_part, cnt_part, seq_lens, out, den, counts, group, head_dim, n_kv_heads * group_split, split, chunk_keys, v_scale)
     if (out_dtype == 0) FOLD_COMBINE(0);
     else if (out_dtype == 1) FOLD_COMBINE(1);
     else FOLD_COMBINE(2);
@@ -937,6 +1010,30 @@ extern "C" int fold_decode_run_tail(const int8_t* qa, const int8_t* qb, const fl
                       group, n_kv_heads, head_dim, pages_per_request, page_size, split, chunk_keys, /*truncate=*/1,
                       weight_terms, refine_k, 0.f, nullptr, 1.0f, o_part, den_part, cnt_part, out,
                       out_dtype, den, counts, status, /*bh_limit=*/0, stream, tail_rows, tail_u, tail_vr, tail_rank);
+}
+
+// fold_decode_run for the layouts beyond the single-level step: a cascade's shared level reads
+// another cache through `req_map` and writes its own slots of a partial buffer several levels
+// share; a row group wider than 8 rows runs as `group_split` groups of 8 on one KV head; a
+// draft's rows see the cache's last `draft_len` keys through `tree`; `row_cut` keeps each row's
+// own cut. Warp-level kernel only.
+extern "C" int fold_decode_run_ex(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                                  const int8_t* kb, const void* ek, const void* va, const void* vb,
+                                  const float* vmean, const float* z, const float* cut,
+                                  const int32_t* page_table, const int32_t* seq_lens,
+                                  const int32_t* order, int n_groups, int group, int n_kv_heads,
+                                  int head_dim, int pages_per_request, int page_size, int split,
+                                  int chunk_keys, int truncate, int weight_terms, float refine_k,
+                                  float refine_v, const float* refine_bands, float v_scale,
+                                  float* o_part, float* den_part, int32_t* cnt_part, void* out,
+                                  int out_dtype, float* den, int32_t* counts, int32_t* status,
+                                  const int32_t* req_map, int group_split, const int32_t* tree,
+                                  int draft_len, int slots_total, int slot_off, int row_cut, void* stream) {
+    return decode_run(qa, qb, eq, ka, kb, ek, va, vb, vmean, z, cut, page_table, seq_lens, order, n_groups,
+                      group, n_kv_heads, head_dim, pages_per_request, page_size, split, chunk_keys, truncate,
+                      weight_terms, refine_k, refine_v, refine_bands, v_scale, o_part, den_part, cnt_part, out,
+                      out_dtype, den, counts, status, /*bh_limit=*/0, stream, nullptr, nullptr, nullptr, -1,
+                      req_map, group_split, tree, draft_len, slots_total, slot_off, row_cut);
 }
 
 // The combine alone, for decode kernels that fill the same partial buffers.

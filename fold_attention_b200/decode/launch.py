@@ -10,11 +10,13 @@ returns `(out, den, counts)`, the same tensors every call.
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 
 import torch
 
 from .. import _lib
 from ..utils import Launch
+from .rows import pack_tree
 
 P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _lib.register("fold_mass_z", [P, P, P, P, P, P, P, I, I, I, I, I, I, P, P])
@@ -32,6 +34,11 @@ _lib.register(
     "fold_decode_run_tail",
     [P] * 10 + [I] + [P] * 5 + [I] * 9 + [F] + [P, P, P, P, I, P, P, P, P],
 )
+_lib.register(
+    "fold_decode_run_ex",
+    [P] * 14 + [I] * 10 + [F, F, P, F] + [P, P, P, P, I, P, P, P] + [P, I, P, I, I, I, I, P],
+)
+_lib.register("fold_mass_z_ex", [P, P, P, P, P, P, P, I, I, I, I, I, I, P, P, I, P, I, P])
 _lib.register("fold_decode_combine", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P])
 
 _OUT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
@@ -42,9 +49,57 @@ class DecodeLaunch(Launch):
     pass
 
 
-def mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z):
-    """Each query row's estimated log-sum-exp (base 2) into `z` (NBH, G)."""
+@dataclass
+class SharedPrefix:
+    """One shared level of a cascade: a prefix cache that several requests
+    attend before their own keys, whose partials the combine adds to the
+    unique level's under the rows' one reference.
+
+    `ka`, `kb`, `ek`, `v` (and `v2`, V's second e4m3 plane) are the prefix's own
+    paged pool in the cache's format, `page_table` `(n_prefixes, pages)` and
+    `seq_lens` `(n_prefixes,)` its pages and lengths, read when the launch is
+    prepared (a prefix does not grow). `req_map` `(requests,)` int32 names the
+    prefix each request holds (-1: none; None: every request holds prefix 0).
+    `vmean` `(n_prefixes * H_KV, D)` is the prefix's dropped-mass direction,
+    given exactly when the unique level has one. Both levels share V's scale.
+
+    The reference's `SharedPrefix` (src/fold_attention/decode/launch.py:48-80)
+    names the requests' stacked rows (`cascade_rows`) and reads a prefix once
+    for up to 64 of them; here every request's row group reads its prefix
+    itself (the pages are the same, so L2 serves the repeats), which keeps a
+    request's result independent of the requests it shares the prefix with.
+    """
+
+    ka: torch.Tensor
+    kb: torch.Tensor
+    ek: torch.Tensor
+    v: torch.Tensor
+    page_table: torch.Tensor
+    seq_lens: torch.Tensor
+    page_size: int
+    req_map: torch.Tensor | None = None
+    v2: torch.Tensor | None = None
+    vmean: torch.Tensor | None = None
+    split: int = 1
+
+
+def mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z, *, req_map=None, tree=None, draft_len=0):
+    """Each query row's estimated log-sum-exp (base 2) into `z` (NBH, G).
+    A group of 16, 24 or 32 rows is estimated as groups of 8; `req_map` reads
+    another cache's rows (a cascade's shared level), `tree` with `draft_len`
+    hides the draft nodes a row does not see."""
     NBH, G, D = qa.shape
+    gsub = 1 if G <= 8 else G // 8
+    if G > 8 and (G % 8 or G > 32):
+        raise NotImplementedError(f"a row group of {G} rows: 1..8, 16, 24 or 32 are supported")
+    if gsub > 1 or req_map is not None or tree is not None:
+        _lib.call(
+            "fold_mass_z_ex", qa.data_ptr(), qb.data_ptr(), eq.data_ptr(), ka.data_ptr(), ek.data_ptr(),
+            page_table.data_ptr(), seq_lens.data_ptr(), NBH * gsub, G // gsub, n_kv_heads, D, page_table.shape[1],
+            int(page_size), z.data_ptr(), _lib.ptr(req_map), gsub, _lib.ptr(tree), int(draft_len) if tree is not None else 0,
+            _lib.stream(qa.device),
+        )
+        return z
     _lib.call(
         "fold_mass_z", qa.data_ptr(), qb.data_ptr(), eq.data_ptr(), ka.data_ptr(), ek.data_ptr(),
         page_table.data_ptr(), seq_lens.data_ptr(), NBH, G, n_kv_heads, D, page_table.shape[1],
@@ -58,7 +113,7 @@ def prepare_fold_decode(
     split=1, truncate=False, refine_k=10.0, refine_v=10.0, v8=False, v2=None, v_scale=1.0,
     vmean=None, page_table, page_size, seq_lens, n_kv_heads, reference="given", weight_terms=1,
     order=None, out_dtype=torch.float32, refine_bands=(), chunk_keys=0, out=None, kernel="mma",
-    short_slots=0, tail=None,
+    short_slots=0, tail=None, draft_len=1, causal=False, mask=None, shared=None, group_cut="auto",
 ):
     """Bind one decode over a paged cache and return its launch.
 
@@ -74,6 +129,16 @@ def prepare_fold_decode(
     With an `order`, its first `short_slots` slots stay on the warp-level kernel
     when the tcgen05 one takes the rest (requests too short for it to pay), and
     one combine follows both.
+    `draft_len` with `causal` or `mask` verifies a draft: a row group is
+    `G // draft_len` query heads at `draft_len` positions (`rows.pack_rows`),
+    the draft's keys are the cache's last `draft_len`, and a row sees the nodes
+    its word names (`rows.pack_tree`, `rows.draft_mask`). `shared` is a
+    cascade: a `SharedPrefix` or a list of them. `group_cut` lets a gathered key
+    enter every row of its group at its true weight; "auto" takes it for a
+    single-level step and not for drafts and cascades, where each row keeps its
+    own cut (reference: launch.py:602-640). Groups of 16, 24 or 32 rows run
+    as groups of 8 on one KV head (an `order` then names those: `NBH * G / 8`
+    slots). All of these run on the warp-level kernel.
     `tail` (a `tail.TailState`, or anything with `rows`, `u`, `vr` and `rank`)
     replaces `vmean` as where dropped mass re-enters: each 64-key block's row
     and, at rank 16, the part of a key's V its K predicts. It needs a
@@ -81,8 +146,45 @@ def prepare_fold_decode(
     warp-level kernel (reference: decode/launch.py:380-500, `tail=`).
     """
     NBH, G, D = qa.shape
-    if G > 8:
-        raise NotImplementedError(f"a row group of {G} rows: 1..8 are supported")
+    if G > 8 and (G % 8 or G > 32):
+        raise NotImplementedError(f"a row group of {G} rows: 1..8, 16, 24 or 32 are supported")
+    gsub = 1 if G <= 8 else G // 8
+    q_len = int(draft_len)
+    if q_len < 1:
+        raise ValueError("draft_len is the number of draft positions per query head")
+    if G % q_len:
+        raise ValueError(f"G={G} is not a multiple of draft_len={q_len}: a row group is G // draft_len query heads at "
+                         "draft_len positions each, row g * draft_len + t (see rows.pack_rows)")
+    if causal and mask is not None:
+        raise ValueError("causal=True and mask= are two answers to one question: put the chain in the bits or drop the mask")
+    if q_len > 1 and gsub > 1:
+        raise NotImplementedError("a draft's rows share one group of at most 8")
+    levels = [] if shared is None else (list(shared) if isinstance(shared, (list, tuple)) else [shared])
+    for lv in levels:
+        if not isinstance(lv, SharedPrefix):
+            raise TypeError("shared is a SharedPrefix or a list of them")
+        if (lv.vmean is None) != (vmean is None):
+            raise ValueError("vmean for both levels or neither")
+        if (lv.v2 is None) != (not v8):
+            raise ValueError("a shared level's V has the unique level's format")
+        if lv.page_size < 16 or lv.page_size % 16 or (lv.page_size % 64 and 64 % lv.page_size):
+            raise ValueError(f"a shared level's page_size={lv.page_size}: a multiple of 64, or 16 or 32")
+    if group_cut == "auto":
+        group_cut = bool(truncate) and G > 1 and q_len == 1 and not levels
+    if group_cut not in (0, 1, False, True):
+        raise ValueError('group_cut is True, False or "auto"')
+    row_cut = bool(truncate) and not bool(group_cut) and G > 1
+    tree = pack_tree(mask, bool(causal), q_len, G, NBH, qa.device) if (q_len > 1 and (causal or mask is not None)) else None
+    ex = gsub > 1 or tree is not None or bool(levels) or row_cut
+    if ex and (tail is not None or kernel == "sm100" or short_slots):
+        raise NotImplementedError("drafts, cascades, wide row groups and a row's own cut run on the warp-level kernel "
+                                  "(kernel='mma' or 'auto'), without a tail")
+    if ex and levels and chunk_keys:
+        raise ValueError("a cascade's levels interleave their splits: no fixed chunk")
+    if ex and any(not t.is_contiguous() for t in (qa, qb, eq, z, cut)):
+        raise ValueError("qa, qb, eq, z and cut are contiguous (NBH, G, ...) tensors")
+    if gsub > 1 and order is not None and order.numel() != NBH * gsub:
+        raise ValueError(f"an order over groups of {G} rows names the {NBH * gsub} groups of 8 they run as")
     if D not in (64, 128):
         raise NotImplementedError(f"head_dim {D}: the decode takes 64 or 128")
     if v8 and v2 is None:
@@ -118,22 +220,23 @@ def prepare_fold_decode(
     if kernel == "sm100" and not can:
         raise NotImplementedError(
             "the tcgen05 decode takes head_dim 128, pages and chunks of a multiple of 128 keys")
-    use_sm100 = can and kernel in ("auto", "sm100")
+    use_sm100 = can and kernel in ("auto", "sm100") and not ex
     dev = qa.device
     split = int(split)
-    o_part = torch.empty((NBH * split, G, D), device=dev, dtype=torch.float32)
-    den_part = torch.empty((NBH * split, G), device=dev, dtype=torch.float32)
-    cnt_part = torch.empty((NBH * split, 2), device=dev, dtype=torch.int32)
+    slots = split + sum(int(lv.split) for lv in levels)
+    o_part = torch.empty((NBH * slots, G, D), device=dev, dtype=torch.float32)
+    den_part = torch.empty((NBH * slots, G), device=dev, dtype=torch.float32)
+    cnt_part = torch.empty((NBH * gsub * slots, 2), device=dev, dtype=torch.int32)
     out_t = torch.empty((NBH, G, D), device=dev, dtype=out_dtype) if out is None else out
     den = torch.empty((NBH, G), device=dev, dtype=torch.float32)
-    counts = torch.empty((NBH, 2), device=dev, dtype=torch.int32)
+    counts = torch.empty((NBH * gsub, 2), device=dev, dtype=torch.int32)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
     bands = (ctypes.c_float * 6)(*refine_bands) if refine_bands else None
     fixed = (
         qa.data_ptr(), qb.data_ptr(), eq.data_ptr(), ka.data_ptr(), kb.data_ptr(), ek.data_ptr(),
         v.data_ptr(), _lib.ptr(v2) if v8 else None, _lib.ptr(vmean) if truncate else None,
         z.data_ptr(), cut.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(), _lib.ptr(order),
-        NBH, G, int(n_kv_heads), D, page_table.shape[1], int(page_size), split, int(chunk_keys),
+        NBH * gsub, G // gsub, int(n_kv_heads), D, page_table.shape[1], int(page_size), split, int(chunk_keys),
         int(bool(truncate)), int(weight_terms), float(refine_k), float(refine_v),
         ctypes.addressof(bands) if bands is not None else None, float(v_scale),
         o_part.data_ptr(), den_part.data_ptr(), cnt_part.data_ptr(),
@@ -156,6 +259,52 @@ def prepare_fold_decode(
               den.data_ptr(), counts.data_ptr(), status.data_ptr(), _lib.stream(dev)]
         return a
 
+    # ---- the layouts beyond the single-level step (fold_decode_run_ex) ----
+    keep = []           # tensors the level calls read
+    level_calls = []
+    if ex:
+        off = split
+        for lv in levels:
+            n_pre = lv.page_table.shape[0]
+            rm = lv.req_map if lv.req_map is not None else torch.zeros(NBH // n_kv_heads, device=dev, dtype=torch.int32)
+            # a request that holds no prefix reads an empty one appended to the level's tables
+            pt = torch.cat([lv.page_table, torch.zeros_like(lv.page_table[:1])]).contiguous()
+            sl = torch.cat([lv.seq_lens.to(torch.int32), torch.zeros(1, device=dev, dtype=torch.int32)]).contiguous()
+            rm = torch.where(rm < 0, torch.full_like(rm, n_pre), rm).to(torch.int32).contiguous()
+            vm = None
+            if truncate and lv.vmean is not None:      # the empty prefix's direction: it has no mass to send there
+                vm = torch.cat([lv.vmean.float(), torch.zeros((int(n_kv_heads), D), device=dev)]).contiguous()
+            if rm.numel() != NBH // int(n_kv_heads) or int(rm.max()) > n_pre:
+                raise ValueError(f"req_map names a prefix (or -1) for each of the {NBH // int(n_kv_heads)} requests")
+            keep += [pt, sl, rm, vm, lv]
+            level_calls.append((
+                qa.data_ptr(), qb.data_ptr(), eq.data_ptr(), lv.ka.data_ptr(), lv.kb.data_ptr(), lv.ek.data_ptr(),
+                lv.v.data_ptr(), _lib.ptr(lv.v2) if v8 else None, _lib.ptr(vm),
+                z.data_ptr(), cut.data_ptr(), pt.data_ptr(), sl.data_ptr(), None,
+                NBH * gsub, G // gsub, int(n_kv_heads), D, pt.shape[1], int(lv.page_size), int(lv.split), 0,
+                int(bool(truncate)), int(weight_terms), float(refine_k), float(refine_v),
+                ctypes.addressof(bands) if bands is not None else None, float(v_scale),
+                o_part.data_ptr(), den_part.data_ptr(), cnt_part.data_ptr(), None, 0, den.data_ptr(), counts.data_ptr(),
+                status.data_ptr(), rm.data_ptr(), gsub, None, 0, slots, off, int(row_cut), _lib.stream(dev),
+            ))
+            off += int(lv.split)
+
+    def ex_args(o):
+        """The unique level: combined in the call when it is the only level."""
+        a = list(fixed)
+        a += [o.data_ptr() if not levels else None, _OUT[o.dtype], den.data_ptr(), counts.data_ptr(), status.data_ptr(),
+              None, gsub, _lib.ptr(tree), q_len if tree is not None else 0, slots, 0, int(row_cut), _lib.stream(dev)]
+        return a
+
+    def run_mass():
+        mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z, tree=tree, draft_len=q_len)
+        for lv, call in zip(levels, level_calls):
+            zl = torch.empty_like(z)
+            _lib.call("fold_mass_z_ex", qa.data_ptr(), qb.data_ptr(), eq.data_ptr(), lv.ka.data_ptr(), lv.ek.data_ptr(),
+                      call[11], call[12], NBH * gsub, G // gsub, int(n_kv_heads), D, call[18], int(lv.page_size), zl.data_ptr(),
+                      call[36], gsub, None, 0, _lib.stream(dev))
+            z.copy_(torch.logaddexp2(z, zl))      # the rows' mass over both levels
+
     def tail_args(o):
         return [
             qa.data_ptr(), qb.data_ptr(), eq.data_ptr(), ka.data_ptr(), kb.data_ptr(), ek.data_ptr(), v.data_ptr(),
@@ -169,8 +318,22 @@ def prepare_fold_decode(
     def run(out=None):
         o = out_t if out is None else out
         if reference == "mass":
-            mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z)
-        if tail is not None:
+            run_mass()
+        if ex:
+            _lib.call("fold_decode_run_ex", *ex_args(o))
+            if levels:
+                for call in level_calls:
+                    _lib.call("fold_decode_run_ex", *call)
+                _lib.call(
+                    "fold_decode_combine", o_part.data_ptr(), den_part.data_ptr(), cnt_part.data_ptr(),
+                    seq_lens.data_ptr(), o.data_ptr(), _OUT[o.dtype], den.data_ptr(), counts.data_ptr(), NBH * gsub, G // gsub, D,
+                    int(n_kv_heads) * gsub, slots, 0, float(v_scale), _lib.stream(dev),
+                )
+                # the combine counted every level's keys: keep the unique level's, and the shared levels' apart
+                per = cnt_part.view(NBH * gsub, slots, 2)
+                launch.counts_shared = per[:, split:].sum(1, dtype=torch.int32)
+                counts.copy_(per[:, :split].sum(1, dtype=torch.int32))
+        elif tail is not None:
             _lib.call("fold_decode_run_tail", *tail_args(o))
         elif use_sm100 and short_slots:
             _lib.call("fold_decode_run_sm100", *args(short_slots, NBH - short_slots, True, None))
@@ -189,9 +352,11 @@ def prepare_fold_decode(
     launch = DecodeLaunch(
         run,
         (qa, qb, eq, ka, kb, ek, v, v2, vmean, z, cut, page_table, seq_lens, order, o_part,
-         den_part, cnt_part, out_t, den, counts, status, bands, tail),
+         den_part, cnt_part, out_t, den, counts, status, bands, tail, tree, keep),
     )
+    launch.counts_shared = None
     launch.z = z
     launch.status = status
     launch.kernel = ("sm100+mma" if short_slots else "sm100") if use_sm100 else "mma"
+    launch.tree = tree
     return launch

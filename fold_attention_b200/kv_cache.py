@@ -119,8 +119,14 @@ class FoldKVCache:
         self.mix_kernels = False
         if head_dim not in (64, 128):
             raise NotImplementedError(f"head_dim {head_dim}: the cache takes 64 or 128")
-        if self.group > 8:
-            raise NotImplementedError(f"a row group of {self.group} rows: 1..8 are supported")
+        if self.group > 8 and (self.group % 8 or self.group > 32):
+            raise NotImplementedError(f"a row group of {self.group} rows: 1..8, 16, 24 or 32 are supported")
+        # a group wider than 8 rows runs as groups of 8 on one KV head, on the warp-level kernel
+        self._gsub = 1 if self.group <= 8 else self.group // 8
+        if self._gsub > 1:
+            if kernel == "sm100":
+                raise NotImplementedError("row groups wider than 8 run on the warp-level kernel: kernel='mma' or 'auto'")
+            self.kernel = "mma"
         if page_size < 16 or page_size % 16 or (page_size % 64 and 64 % page_size):
             raise ValueError(f"page_size={page_size}: a multiple of 64, or 16 or 32")
 
@@ -143,7 +149,7 @@ class FoldKVCache:
         self._v_scale = float(v_scale) if (self.v8 and v_scale is not None) else 1.0
         self.seq_lens = torch.zeros((batch,), device=dev, dtype=torch.int32)
         self.lens = [0] * batch
-        self.order = torch.arange(self.n_groups, device=dev, dtype=torch.int32)
+        self.order = torch.arange(self.n_groups * self._gsub, device=dev, dtype=torch.int32)
         self.vsum = torch.zeros((self.n_groups, D), device=dev, dtype=torch.float32)
         self.vmean = torch.zeros_like(self.vsum)
         self.qa = torch.zeros((self.n_groups, self.group, D), device=dev, dtype=torch.int8)
@@ -154,7 +160,7 @@ class FoldKVCache:
         self.cut = torch.full_like(self.z, 1e4 if depth is None else float(depth))
         if tail == "auto":
             tail = tail_rank_for(D, self.group, self.v8) if depth is not None else -1
-            if page_size % tail_fit.TAIL_BLOCK or kernel == "sm100":
+            if page_size % tail_fit.TAIL_BLOCK or kernel == "sm100" or self._gsub > 1:
                 tail = -1
         self.tail_rank = -1 if tail is None else int(tail)
         self.tail = None
@@ -167,6 +173,8 @@ class FoldKVCache:
                 raise ValueError(f"page_size={page_size}: the tail keeps one row per 64 keys, so a page must hold whole blocks")
             if kernel == "sm100":
                 raise NotImplementedError("the tail runs on the warp-level kernel: kernel='mma' or 'auto'")
+            if self._gsub > 1:
+                raise NotImplementedError("the tail takes row groups of at most 8 rows")
             tail_fit.check_rank(self.tail_rank, D)
             R, nblk = self.tail_rank, rows // tail_fit.TAIL_BLOCK
             self.tail = tail_fit.TailState(
@@ -458,13 +466,13 @@ class FoldKVCache:
         keys and are the slowest, and should not be what the grid ends on."""
         sign = 1 if self.chunk else -1
         rank = sorted(range(self.batch), key=lambda b: (sign * self.lens[b], b))
-        order = [r * self.n_kv_heads + h for r in rank for h in range(self.n_kv_heads)]
+        order = [(r * self.n_kv_heads + h) * self._gsub + s for r in rank for h in range(self.n_kv_heads) for s in range(self._gsub)]
         self.order.copy_(torch.tensor(order, dtype=torch.int32), non_blocking=True)
 
     def _auto_split(self):
         mean = sum(self.lens) / self.batch
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        return pick_split(self.n_groups, max(1, int(mean)), max_len=max(self.lens), sms=sms)
+        return pick_split(self.n_groups * self._gsub, max(1, int(mean)), max_len=max(self.lens), sms=sms)
 
     def _resolve_split(self, split):
         if self.chunk is not None:

@@ -148,6 +148,42 @@ int fold_decode_run_tail(const int8_t* qa, const int8_t* qb, const float* eq, co
                          int32_t* cnt_part, void* out, int out_dtype, float* den, int32_t* counts,
                          int32_t* status, void* stream);
 
+/* fold_decode_run and fold_mass_z for the layouts beyond the single-level step (warp-level
+ * kernel only). Replaces: the draft, cascade and row-cut paths of
+ * src/fold_attention/decode/launch.py:509-1252 (_prepare with draft_len / mask / shared /
+ * group_cut), decode/rows.py:19-184 and the level loop of decode/combine.py.
+ *   req_map      int32 (requests,) or NULL: the row of page_table / seq_lens a request reads
+ *                (a cascade's shared level: the prefix the request holds; vmean is then
+ *                indexed by that row and KV head)
+ *   group_split  row groups per KV head: a group of 16, 24 or 32 query rows runs as 2, 3 or 4
+ *                groups of 8 (qa, z, ... are then (n_groups, 8, ..) with n_groups counting them)
+ *   tree         int32 (n_groups, group) or NULL: bit j of a row's word says the row sees
+ *                draft node j; the nodes are the cache's last draft_len keys (1..32), which a
+ *                row otherwise would all see. NULL with draft_len 0.
+ *   slots_total, slot_off   the partial buffers hold slots_total slots per row group and this
+ *                call's splits take slots slot_off .. slot_off + split - 1 (a cascade's levels
+ *                share the buffers and one fold_decode_combine with split = slots_total adds
+ *                them); a call that does not own every slot takes chunk_keys 0 and out NULL.
+ *                slots_total 0 means split.
+ *   row_cut      1: a key enters a row only if that row keeps it (the reference's choice for
+ *                drafts and cascades); 0: if any row of its group keeps it */
+int fold_decode_run_ex(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                       const int8_t* kb, const void* ek, const void* va, const void* vb,
+                       const float* vmean, const float* z, const float* cut,
+                       const int32_t* page_table, const int32_t* seq_lens, const int32_t* order,
+                       int n_groups, int group, int n_kv_heads, int head_dim, int pages_per_request,
+                       int page_size, int split, int chunk_keys, int truncate, int weight_terms,
+                       float refine_k, float refine_v, const float* refine_bands /* host */,
+                       float v_scale, float* o_part, float* den_part, int32_t* cnt_part, void* out,
+                       int out_dtype, float* den, int32_t* counts, int32_t* status,
+                       const int32_t* req_map, int group_split, const int32_t* tree, int draft_len,
+                       int slots_total, int slot_off, int row_cut, void* stream);
+int fold_mass_z_ex(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
+                   const void* ek, const int32_t* page_table, const int32_t* seq_lens, int n_groups,
+                   int group, int n_kv_heads, int head_dim, int pages_per_request, int page_size,
+                   float* z, const int32_t* req_map, int group_split, const int32_t* tree,
+                   int draft_len, void* stream);
+
 /* The same decode on tcgen05 tensor cores (TMEM accumulators, the E4M3 V planes
  * read by the tensor core as stored; weights carried as four E5M2 terms). K's
  * and V's first planes stream whole through shared memory; V's second plane is

@@ -81,17 +81,24 @@ def truncated_softmax(s, z, v, cut):
     return (p @ v) / p.sum(-1, keepdim=True), p
 
 
-def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, vmean=None, reentry=None):
+def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, vmean=None, reentry=None,
+                 visible=None, row_cut=False):
     """One row group's decode in float64 on the cache's own (unswizzled)
     planes: `ka`, `kb` (S, D) int8, `ek` (S,), `va` (S, D) float (bf16 values
     or plane A in scale units), `vb` plane B or None. `depth` None keeps every
     key. `reentry` (S, D), instead of `vmean`: where each key's mass re-enters if it is
     dropped (the tail: its block's row plus its projection mapped back, `oracle.tail.reentry`).
+    `visible` (G, >= n) bool hides keys from rows (a draft's tree: a hidden key weighs nothing
+    in that row and takes no part in its verdicts); `row_cut` lets a gathered key enter only
+    the rows that keep it themselves (src/fold_attention/decode/launch.py:602-627, `group_cut`
+    off), the others count it as dropped.
     Returns (out (G, D), den (G,), live count, refined count)."""
     ka, kb, va = ka[:n], kb[:n], va[:n].double()
     ek = ek[:n]
     G = qa.shape[0]
     s1 = coarse_logits(qa[None], qb[None], eq[None], ka[None], ek[None], z[None])[0]  # (G, n) float32
+    if visible is not None:
+        s1 = torch.where(visible[:, :n].to(s1.device), s1, torch.full_like(s1, float("-inf")))
     if depth is None:
         live = torch.ones(n, dtype=torch.bool, device=s1.device)
     else:
@@ -104,8 +111,11 @@ def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, v
     c3b = torch.einsum("gd,sd->gs", qb.double(), kb.double())
     s = s1.double() + torch.where(refk[None], (c3a + c3b / KBR) * tk, torch.zeros_like(tk))
     e = torch.exp2(s)
-    w = torch.where(live[None], e, torch.zeros_like(e))
-    m = torch.where(live[None], torch.zeros_like(e), e).sum(-1)
+    keeps = live[None].expand_as(e)
+    if row_cut and depth is not None:
+        keeps = keeps & (s1 >= -depth)
+    w = torch.where(keeps, e, torch.zeros_like(e))
+    m = torch.where(keeps, torch.zeros_like(e), e).sum(-1)
     vt = va
     if vb is not None:
         vt = va + torch.where(refv[:, None], vb[:n].double() / 8.0, torch.zeros_like(va))
@@ -113,7 +123,7 @@ def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, v
     if vmean is not None and depth is not None:
         num = num + m[:, None] * vmean.double()[None, :]
     if reentry is not None and depth is not None:
-        num = num + torch.where(live[None], torch.zeros_like(e), e) @ reentry[:n].double().to(e.device)
+        num = num + torch.where(keeps, torch.zeros_like(e), e) @ reentry[:n].double().to(e.device)
     den = w.sum(-1) + m
     return num * v_scale / den[:, None], den, int(live.sum()), int(refk.sum())
 
