@@ -595,6 +595,112 @@ def decode_extra(device, kind="config5", ids=None, steps=64, kernel="auto", tail
     return res
 
 
+def levels_extra(device, B=64, steps=20):
+    """The decode's layouts beyond the single-level step, timed on the warp-level kernel that
+    runs them (CUDA events around `steps` launches of mass reference + decode + combine): a
+    two-position draft verified against a bf16 cache (GQA 32/8: 4 query heads x 2 positions a row
+    group), the same cache's single-token step beside it, and a cascade of `B` requests sharing
+    one 16384-key prefix before 2048 keys of their own, beside the same keys as one flat cache per
+    request. Each with the error of sampled rows against FP32 attention over the keys they see."""
+    from fold_attention_b200 import FoldKVCache
+    from fold_attention_b200.decode import write
+    from fold_attention_b200.decode.launch import SharedPrefix, prepare_fold_decode
+    from fold_attention_b200.decode.rows import pack_rows
+
+    H, HKV, D = 32, 8, 128
+    G = H // HKV
+    g = torch.Generator(device=device).manual_seed(31)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(run):
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps * 1e3
+
+    def filled(lens, seed):
+        c = FoldKVCache(len(lens), H, HKV, D, max(lens) + 8, device=device, kernel="mma")
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=device, dtype=torch.int32)
+        k = torch.empty(sum(lens), HKV, D, device=device, dtype=torch.bfloat16)
+        v = torch.empty_like(k)
+        at = 0
+        for i, n in enumerate(lens):
+            k[at:at + n], v[at:at + n] = request_kv(n, HKV, D, device, seed + i)
+            at += n
+        c.write_prompt(k, v, cu, lens)
+        return c, k, v, cu
+
+    def quantise(c, rows):
+        qa = torch.zeros(rows.shape, device=device, dtype=torch.int8)
+        qb, eq = torch.zeros_like(qa), torch.ones(rows.shape[:2], device=device, dtype=torch.float32)
+        write.step(rows.reshape(-1, D).contiguous(), None, None, qa.view(-1, D), qb.view(-1, D), eq.view(-1), c.ek, c.page_table,
+                   c.page_size, c.seq_lens, c.ka, c.kb, c.va, c.vb, 1.0, c.vsum, c.vmean, c.seq_lens)
+        return qa, qb, eq
+
+    def attend(q, kk, vv):
+        w = torch.softmax((q.float() @ kk.float().T) / D**0.5, -1)
+        return w @ vv.float()
+
+    res = {}
+    # ---- a two-position draft on config 4's lengths ----
+    lens = decode_lengths("config4", B, 7)
+    c, k, v, cu = filled(lens, 7000)
+    q = torch.randn(B, 2, H, D, device=device, generator=g).bfloat16()
+    common = dict(split=c._auto_split(), refine_k=10.0, refine_v=10.0, v_scale=1.0, page_table=c.page_table, page_size=c.page_size,
+                  seq_lens=c.seq_lens, n_kv_heads=HKV, reference="mass", weight_terms=2, kernel="mma")
+    qa, qb, eq = quantise(c, pack_rows(q, HKV, 2))
+    z = torch.empty((B * HKV, 2 * G), device=device)
+    draft = prepare_fold_decode(qa, qb, eq, c.ka, c.kb, c.ek, c.va, z, torch.full_like(z, 1e4), draft_len=2, causal=True, **common)
+    qa1, qb1, eq1 = quantise(c, pack_rows(q[:, 1:], HKV, 1))
+    z1 = torch.empty((B * HKV, G), device=device)
+    single = prepare_fold_decode(qa1, qb1, eq1, c.ka, c.kb, c.ek, c.va, z1, torch.full_like(z1, 1e4), **common)
+    us_d, us_s = timed(draft), timed(single)
+    out = draft()[0]
+    errs = []
+    for b in (0, B // 2, B - 1):
+        a, n = int(cu[b]), lens[b]
+        for t in range(2):
+            want = attend(q[b, t, :G], k[a:a + n - 1 + t, 0], v[a:a + n - 1 + t, 0])
+            errs.append(((out[b * HKV, t::2].float() - want).norm() / want.norm()).item())
+    res["draft"] = dict(workload=f"bf16 dense B{B} H32/8 D128 lens U[1024,32768], 2 draft positions (8 rows a group), warp-level kernel",
+                        us_per_step=us_d, single_token_us_per_step=us_s, keys=sum(lens) * HKV, rel_l2_vs_fp32=max(errs),
+                        status=int(draft.status))
+    del c, k, v, draft, single
+    torch.cuda.empty_cache()
+    # ---- a cascade: one 16384-key prefix, 2048 keys of each request's own ----
+    PL, UL = 16384, 2048
+    P, kp, vp, _ = filled([PL], 8000)
+    U, ku, vu, cuu = filled([UL] * B, 8100)
+    F, kf, vf, _ = filled([PL + UL] * 8, 8200)          # the flat comparison at B8: the same keys per request, eight copies
+    q = torch.randn(B, H, D, device=device, generator=g).bfloat16()
+    qa, qb, eq = quantise(U, pack_rows(q[:, None], HKV, 1))
+    z = torch.empty((B * HKV, G), device=device)
+    level = SharedPrefix(P.ka, P.kb, P.ek, P.va, P.page_table, P.seq_lens, P.page_size, split=8)
+    common.update(page_table=U.page_table, page_size=U.page_size, seq_lens=U.seq_lens, split=2)
+    casc = prepare_fold_decode(qa, qb, eq, U.ka, U.kb, U.ek, U.va, z, torch.full_like(z, 1e4), shared=level, **common)
+    qa8, qb8, eq8 = quantise(F, pack_rows(q[:8, None], HKV, 1))
+    z8 = torch.empty((8 * HKV, G), device=device)
+    common.update(page_table=F.page_table, page_size=F.page_size, seq_lens=F.seq_lens, split=F._auto_split())
+    flat = prepare_fold_decode(qa8, qb8, eq8, F.ka, F.kb, F.ek, F.va, z8, torch.full_like(z8, 1e4), **common)
+    us_c, us_f = timed(casc), timed(flat)
+    out = casc()[0]
+    errs = []
+    for b in (0, B - 1):
+        a = int(cuu[b])
+        want = attend(q[b, :G], torch.cat([kp[:, 0], ku[a:a + UL, 0]]), torch.cat([vp[:, 0], vu[a:a + UL, 0]]))
+        errs.append(((out[b * HKV].float() - want).norm() / want.norm()).item())
+    res["cascade"] = dict(workload=f"bf16 dense B{B} H32/8 D128: one shared prefix of {PL} keys + {UL} own keys a request, warp-level kernel",
+                          us_per_step=us_c, keys_attended=B * HKV * (PL + UL), keys_stored=HKV * (PL + B * UL),
+                          flat_b8_us_per_step=us_f, flat_b8_keys=8 * HKV * (PL + UL), rel_l2_vs_fp32=max(errs), status=int(casc.status),
+                          note="every request's row group reads the prefix itself; its pages are shared, so the repeats are L2 hits")
+    return res
+
+
 def write_prompt_extra(device):
     """The prompt writer on the shape the reference publishes a row for (235 us on H100, eager, with
     host planning: 32 prompts of 2048 tokens, 4 KV heads, D128, 8-bit V)."""
@@ -742,6 +848,7 @@ def main():
     ap.add_argument("--decode-kernel", default="auto", choices=("auto", "mma", "sm100"))
     ap.add_argument("--decode-dense", action="store_true", help="config 4's shape instead of config 5's")
     ap.add_argument("--decode-tail", action="store_true", help="heavy-tailed keys: few live keys at depth 16")
+    ap.add_argument("--decode-levels", action="store_true", help="run only the draft / cascade extra and print its dict")
     ap.add_argument("--decode-bf16-depth", default=None, choices=("auto", "rows", "mean"),
                     help="the bf16-V depth-12 extra instead: with the rank-16 tail, the block rows alone, or V's mean")
     args = ap.parse_args()
@@ -750,6 +857,10 @@ def main():
         run_reference(args)
         return
     args.warmup = max(args.warmup, 3)
+    if args.decode_levels:
+        torch.cuda.set_device(0)
+        print(json.dumps(levels_extra(torch.device("cuda", 0))), flush=True)
+        return
     if args.decode_only:
         torch.cuda.set_device(0)
         kind = "bf16depth" if args.decode_bf16_depth else "config4" if args.decode_dense else "config5"
@@ -829,6 +940,7 @@ def main():
                         ("decode_config5", lambda: decode_extra(device, "config5")),
                         ("decode_config4", lambda: decode_extra(device, "config4")),
                         ("decode_config5_few_live_keys", lambda: decode_extra(device, "config5", B=64, tail=True, with_e2e=False)),
+                        ("decode_levels", lambda: levels_extra(device)),
                         ("decode_bf16_depth12_tail16", lambda: decode_extra(device, "bf16depth", with_e2e=False)),
                         ("decode_bf16_depth12_vmean", lambda: decode_extra(device, "bf16depth", with_e2e=False, tail_rank=None, kernel="mma"))):
             try:
