@@ -187,6 +187,8 @@ def prepare_fold_decode(
         raise ValueError(f"an order over groups of {G} rows names the {NBH * gsub} groups of 8 they run as")
     if D not in (64, 128):
         raise NotImplementedError(f"head_dim {D}: the decode takes 64 or 128")
+    if vmean is not None and (vmean.dim() != 2 or vmean.shape[-1] != D or vmean.dtype != torch.float32):
+        raise NotImplementedError(f"vmean is fp32 (row groups, {D}), one direction per KV head: a direction per query row is not built")
     if v8 and v2 is None:
         raise ValueError("an 8-bit V has two planes: pass v2")
     if not v8 and v.dtype != torch.bfloat16:
@@ -261,6 +263,9 @@ def prepare_fold_decode(
 
     # ---- the layouts beyond the single-level step (fold_decode_run_ex) ----
     keep = []           # tensors the level calls read
+    # the shared levels' key counts, the same tensor every call (the launch's closure must not hold the
+    # launch itself: a reference cycle would keep a cache's pools alive until the collector runs)
+    counts_shared = torch.zeros((NBH * gsub, 2), device=dev, dtype=torch.int32) if levels else None
     level_calls = []
     if ex:
         off = split
@@ -331,7 +336,7 @@ def prepare_fold_decode(
                 )
                 # the combine counted every level's keys: keep the unique level's, and the shared levels' apart
                 per = cnt_part.view(NBH * gsub, slots, 2)
-                launch.counts_shared = per[:, split:].sum(1, dtype=torch.int32)
+                counts_shared.copy_(per[:, split:].sum(1, dtype=torch.int32))
                 counts.copy_(per[:, :split].sum(1, dtype=torch.int32))
         elif tail is not None:
             _lib.call("fold_decode_run_tail", *tail_args(o))
@@ -354,7 +359,7 @@ def prepare_fold_decode(
         (qa, qb, eq, ka, kb, ek, v, v2, vmean, z, cut, page_table, seq_lens, order, o_part,
          den_part, cnt_part, out_t, den, counts, status, bands, tail, tree, keep),
     )
-    launch.counts_shared = None
+    launch.counts_shared = counts_shared
     launch.z = z
     launch.status = status
     launch.kernel = ("sm100+mma" if short_slots else "sm100") if use_sm100 else "mma"

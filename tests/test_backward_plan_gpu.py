@@ -195,15 +195,16 @@ def test_the_mma_main_loop_refuses_a_folding_plan():
         prepare_backward(q, k, v, o, do, lse, causal=True, plan=Plan(3, 0))
 
 
-def test_mqa_and_small_batch_shapes_fold_by_default_and_stay_accurate():
-    """The shapes whole-group items cannot balance (B2 H32/1, B1 H32/8 at S 8192 in the reference's
-    GQA sweep) take a folding plan by default; checked here at S 2048 with the plan they would get."""
+def test_mqa_and_small_batch_shapes_plan_by_default_and_stay_accurate():
+    """A shape whose whole-group items cannot balance (B2 H32/1 at S 8192 in the reference's GQA
+    sweep) takes a folding plan by default, and B1 H32/8 is where a folding plan (two heads at a
+    time) and the private one (the default there) meet; checked here at S 2048 with those plans."""
     from fold_attention_b200.backward.plan import plan_dense
 
     _, prepare_backward, Plan = _api()
     assert plan_dense(2, 32, 1, 8192, 128, True) == Plan(4, 0)
-    assert plan_dense(1, 32, 8, 8192, 128, True) == Plan(2, 0)
-    for (B, H, HKV), plan in (((2, 32, 1), Plan(4, 0)), ((1, 32, 8), Plan(2, 0))):
+    assert plan_dense(1, 32, 8, 8192, 128, True) == Plan(4, 0)
+    for (B, H, HKV), plan in (((2, 32, 1), Plan(4, 0)), ((1, 32, 8), Plan(2, 0)), ((1, 32, 8), Plan(4, 0))):
         (q, k, v, o, do), lse = _dense(B, H, HKV, 2048, seed=6)
         run = prepare_backward(q, k, v, o, do, lse, causal=True, plan=plan)
         got = tuple(x.clone() for x in run())
