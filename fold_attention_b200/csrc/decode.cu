@@ -53,6 +53,9 @@ struct DecodeParams {
     int gsub;               // row groups per KV head (a group wider than 8 rows runs as gsub groups of 8)
     int slots_total, slot_off;   // partial slot of (row group, split sp): bh * slots_total + slot_off + sp
     int row_cut;            // 1: a key enters a row only if that row keeps it (drafts, cascades); 0: if any row of the group does
+    const float* sound;     // (NBH, G) or null: eq * sum_d (128 |qa_d| + |qb_d| / 2), the bound on what plane B of K can
+                            // add to a row's logit per unit of the key's ek / 256; the verdict then tests s1 + bound
+    int vmean_rows;         // 1: vmean is (NBH, G, D), a direction per query row
     int bh_limit;   // > 0: the partial buffers hold this many row groups; an `order` entry outside is refused
 };
 
@@ -256,6 +259,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
     float eqr[2], zr[2], cutr[2];
     bool rowok[2];
     uint32_t treer[2] = {~0u, ~0u};
+    float soundr[2] = {0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
         const int g = 2 * tq + j;
@@ -265,12 +269,14 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
         zr[j] = p.z[ix];
         cutr[j] = -p.cut[ix];
         if (EX && p.tree) treer[j] = static_cast<uint32_t>(p.tree[ix]);
+        if (EX && p.sound) soundr[j] = p.sound[ix];
     }
     // a draft: the cache's last q_len keys are the draft's own nodes, and a row sees node j only
     // if bit j of its word is set (a chain's row t sees nodes 0..t)
     const int node0 = (EX && p.q_len > 0) ? slen - p.q_len : (1 << 30);
     auto sees = [&](int j, int kabs) { return !EX || kabs < node0 || ((treer[j] >> (kabs - node0)) & 1u) != 0u; };
-    (void)treer; (void)node0;
+    (void)treer; (void)node0; (void)soundr;
+    int kb_old = 0;     // bit i: this lane's row i & 1 itself keeps its key i >> 1 (read under a row's own cut)
 
     float acc[NT][4];
 #pragma unroll
@@ -286,7 +292,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
 
     for (int t = 0; t <= n_tiles; ++t) {
         float s_new[4] = {0, 0, 0, 0}, tk_new[4] = {0, 0, 0, 0};
-        int b_new[2] = {0, 0}, nrow_new = 0;
+        int b_new[2] = {0, 0}, nrow_new = 0, kb_new = 0;
         float y_new[TR > 0 ? 8 : 1] = {};
         (void)y_new;
         if (t < n_tiles) {
@@ -330,7 +336,12 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                 float s1 = -INFINITY;
                 if (rowok[i & 1] && ky < nrow && sees(i & 1, base + ky)) {
                     s1 = fmaf(static_cast<float>(c1[i] * 256 + c2[i]), tk, -zr[i & 1]);
-                    if (TRUNC && s1 >= cutr[i & 1]) pk |= 1 << (3 * (i >> 1));
+                    // (a sound cut adds what plane B of K could still add to this row's logit)
+                    const float s1c = (EX && p.sound) ? fmaf(soundr[i & 1], ekf, s1) : s1;
+                    if (TRUNC && s1c >= cutr[i & 1]) {
+                        pk |= 1 << (3 * (i >> 1));
+                        kb_new |= 1 << i;
+                    }
                     dg[i >> 1] = fmaxf(dg[i >> 1], s1);
                 }
                 s_new[i] = s1;
@@ -441,7 +452,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
                 const int ky = 16 * warp + gid + 8 * (i >> 1);
                 const bool valid = rowok[i & 1] && ky < nrow_old && sees(i & 1, base_old + ky);
                 // under a row's own cut a gathered key enters only the rows that keep it
-                const bool live = (b_old[i >> 1] & 1) != 0 && (!EX || !p.row_cut || s_old[i] >= cutr[i & 1]);
+                const bool live = (b_old[i >> 1] & 1) != 0 && (!EX || !p.row_cut || ((kb_old >> i) & 1) != 0);
                 float s = s_old[i];
                 if (b_old[i >> 1] & 2)
                     s = s + (static_cast<float>(c3a[i]) + static_cast<float>(c3b[i]) * (1.0f / 256.0f)) * tk_old[i];
@@ -569,6 +580,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
         b_old[0] = b_new[0];
         b_old[1] = b_new[1];
         nrow_old = nrow_new;
+        kb_old = kb_new;
         base_old = lo + t * tstep;
     }
     cp_async_wait<0>();
@@ -624,7 +636,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(const DecodeParams 
             m += sRed[w2 * 8 + g];
         }
         if (V8) x *= E4O;
-        if (TR < 0 && TRUNC && p.vmean) x += m * p.vmean[(static_cast<int64_t>(preq) * p.hkv + hkv) * D + c];
+        if (TR < 0 && TRUNC && p.vmean)
+            x += m * p.vmean[((EX && p.vmean_rows) ? static_cast<int64_t>(bh) * G + g : static_cast<int64_t>(preq) * p.hkv + hkv) * D + c];
         if constexpr (TR > 0) {
             const float4* vr = reinterpret_cast<const float4*>(p.tail_vr + (static_cast<int64_t>(bh) * D + c) * TR);
 #pragma unroll
@@ -903,7 +916,9 @@ static int decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const
                       int bh_limit, void* stream, const void* tail_rows = nullptr,
                       const int8_t* tail_u = nullptr, const float* tail_vr = nullptr, int tail_rank = -1,
                       const int32_t* req_map = nullptr, int group_split = 1, const int32_t* tree = nullptr,
-                      int draft_len = 0, int slots_total = 0, int slot_off = 0, int row_cut = 0) {
+                      int draft_len = 0, int slots_total = 0, int slot_off = 0, int row_cut = 0,
+                      const float* sound = nullptr, int vmean_per_row = 0) {
+    FOLD_CHECK_ARG(!vmean_per_row || (vmean && !req_map), "a direction per query row belongs to the unique level's vmean");
     if (slots_total <= 0) slots_total = split;
     FOLD_CHECK_ARG(group_split >= 1 && n_groups % group_split == 0, "group_split %d does not divide %d row groups", group_split, n_groups);
     FOLD_CHECK_ARG(draft_len >= 0 && draft_len <= 32 && (draft_len == 0) == (tree == nullptr),
@@ -911,7 +926,7 @@ static int decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const
     FOLD_CHECK_ARG(slot_off >= 0 && slot_off + split <= slots_total, "splits %d..%d of %d partial slots", slot_off, slot_off + split, slots_total);
     FOLD_CHECK_ARG(slots_total == split || (chunk_keys == 0 && !out),
                    "a level of several writes its own slots of uncombined partials, with interleaved splits (chunk_keys 0, out NULL)");
-    FOLD_CHECK_ARG(tail_rank < 0 || (!req_map && !tree && group_split == 1 && !row_cut),
+    FOLD_CHECK_ARG(tail_rank < 0 || (!req_map && !tree && group_split == 1 && !row_cut && !sound && !vmean_per_row),
                    "the tail runs on single-level steps with the group's cut");
     if (tail_rank >= 0) {
         FOLD_CHECK_ARG(tail_rank == 0 || tail_rank == 16, "tail rank %d: 0 (block rows alone) or 16", tail_rank);
@@ -954,10 +969,11 @@ static int decode_run(const int8_t* qa, const int8_t* qb, const float* eq, const
     p.tail_rows = static_cast<const uint16_t*>(tail_rows); p.tail_u = tail_u; p.tail_vr = tail_vr;
     p.req_map = req_map; p.tree = tree; p.q_len = draft_len; p.gsub = group_split;
     p.slots_total = slots_total; p.slot_off = slot_off; p.row_cut = row_cut;
+    p.sound = sound; p.vmean_rows = vmean_per_row;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool v8 = vb != nullptr;
     int rc;
-    const bool ex = req_map || tree || group_split > 1 || slots_total != split || slot_off || row_cut;
+    const bool ex = req_map || tree || group_split > 1 || slots_total != split || slot_off || row_cut || sound || vmean_per_row;
     if (tail_rank >= 0) rc = head_dim == 128 ? launch_decode_tail<128>(p, weight_terms == 2, st) : launch_decode_tail<64>(p, weight_terms == 2, st);
     else if (ex && head_dim == 128) rc = v8 ? launch_decode_ex<128, true>(p, weight_terms == 2, st) : launch_decode_ex<128, false>(p, weight_terms == 2, st);
     else if (ex) rc = v8 ? launch_decode_ex<64, true>(p, weight_terms == 2, st) : launch_decode_ex<64, false>(p, weight_terms == 2, st);
@@ -1028,12 +1044,13 @@ extern "C" int fold_decode_run_ex(const int8_t* qa, const int8_t* qb, const floa
                                   float* o_part, float* den_part, int32_t* cnt_part, void* out,
                                   int out_dtype, float* den, int32_t* counts, int32_t* status,
                                   const int32_t* req_map, int group_split, const int32_t* tree,
-                                  int draft_len, int slots_total, int slot_off, int row_cut, void* stream) {
+                                  int draft_len, int slots_total, int slot_off, int row_cut,
+                                  const float* sound, int vmean_per_row, void* stream) {
     return decode_run(qa, qb, eq, ka, kb, ek, va, vb, vmean, z, cut, page_table, seq_lens, order, n_groups,
                       group, n_kv_heads, head_dim, pages_per_request, page_size, split, chunk_keys, truncate,
                       weight_terms, refine_k, refine_v, refine_bands, v_scale, o_part, den_part, cnt_part, out,
                       out_dtype, den, counts, status, /*bh_limit=*/0, stream, nullptr, nullptr, nullptr, -1,
-                      req_map, group_split, tree, draft_len, slots_total, slot_off, row_cut);
+                      req_map, group_split, tree, draft_len, slots_total, slot_off, row_cut, sound, vmean_per_row);
 }
 
 // The combine alone, for decode kernels that fill the same partial buffers.

@@ -36,7 +36,7 @@ _lib.register(
 )
 _lib.register(
     "fold_decode_run_ex",
-    [P] * 14 + [I] * 10 + [F, F, P, F] + [P, P, P, P, I, P, P, P] + [P, I, P, I, I, I, I, P],
+    [P] * 14 + [I] * 10 + [F, F, P, F] + [P, P, P, P, I, P, P, P] + [P, I, P, I, I, I, I, P, I, P],
 )
 _lib.register("fold_mass_z_ex", [P, P, P, P, P, P, P, I, I, I, I, I, I, P, P, I, P, I, P])
 _lib.register("fold_decode_combine", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P])
@@ -113,7 +113,7 @@ def prepare_fold_decode(
     split=1, truncate=False, refine_k=10.0, refine_v=10.0, v8=False, v2=None, v_scale=1.0,
     vmean=None, page_table, page_size, seq_lens, n_kv_heads, reference="given", weight_terms=1,
     order=None, out_dtype=torch.float32, refine_bands=(), chunk_keys=0, out=None, kernel="mma",
-    short_slots=0, tail=None, draft_len=1, causal=False, mask=None, shared=None, group_cut="auto",
+    short_slots=0, tail=None, draft_len=1, causal=False, mask=None, shared=None, group_cut="auto", sound=False,
 ):
     """Bind one decode over a paged cache and return its launch.
 
@@ -138,7 +138,10 @@ def prepare_fold_decode(
     single-level step and not for drafts and cascades, where each row keeps its
     own cut (reference: launch.py:602-640). Groups of 16, 24 or 32 rows run
     as groups of 8 on one KV head (an `order` then names those: `NBH * G / 8`
-    slots). All of these run on the warp-level kernel.
+    slots). `sound` shifts the cut by the bound on what K's second plane can
+    still add to a row's logit, so the screen drops only keys the full logit
+    would drop too; `vmean` may be `(NBH, G, D)`, a direction per query row
+    (single level). All of these run on the warp-level kernel.
     `tail` (a `tail.TailState`, or anything with `rows`, `u`, `vr` and `rank`)
     replaces `vmean` as where dropped mass re-enters: each 64-key block's row
     and, at rank 16, the part of a key's V its K predicts. It needs a
@@ -169,13 +172,21 @@ def prepare_fold_decode(
             raise ValueError("a shared level's V has the unique level's format")
         if lv.page_size < 16 or lv.page_size % 16 or (lv.page_size % 64 and 64 % lv.page_size):
             raise ValueError(f"a shared level's page_size={lv.page_size}: a multiple of 64, or 16 or 32")
+    vmean_rows = vmean is not None and vmean.dim() == 3
+    if vmean is not None and (vmean.dtype != torch.float32 or not vmean.is_contiguous()
+                              or tuple(vmean.shape) not in ((NBH, D), (NBH, G, D))):
+        raise ValueError(f"vmean is contiguous fp32 ({NBH}, {D}), a direction per KV head, or ({NBH}, {G}, {D}), one per query row")
+    if vmean_rows and levels:
+        raise NotImplementedError("a cascade's levels each take one direction per KV head")
     if group_cut == "auto":
         group_cut = bool(truncate) and G > 1 and q_len == 1 and not levels
     if group_cut not in (0, 1, False, True):
         raise ValueError('group_cut is True, False or "auto"')
     row_cut = bool(truncate) and not bool(group_cut) and G > 1
     tree = pack_tree(mask, bool(causal), q_len, G, NBH, qa.device) if (q_len > 1 and (causal or mask is not None)) else None
-    ex = gsub > 1 or tree is not None or bool(levels) or row_cut
+    sound = bool(sound) and bool(truncate)
+    ex = gsub > 1 or tree is not None or bool(levels) or row_cut or sound or vmean_rows
+    bound = torch.empty((NBH, G), device=qa.device, dtype=torch.float32) if sound else None
     if ex and (tail is not None or kernel == "sm100" or short_slots):
         raise NotImplementedError("drafts, cascades, wide row groups and a row's own cut run on the warp-level kernel "
                                   "(kernel='mma' or 'auto'), without a tail")
@@ -187,8 +198,6 @@ def prepare_fold_decode(
         raise ValueError(f"an order over groups of {G} rows names the {NBH * gsub} groups of 8 they run as")
     if D not in (64, 128):
         raise NotImplementedError(f"head_dim {D}: the decode takes 64 or 128")
-    if vmean is not None and (vmean.dim() != 2 or vmean.shape[-1] != D or vmean.dtype != torch.float32):
-        raise NotImplementedError(f"vmean is fp32 (row groups, {D}), one direction per KV head: a direction per query row is not built")
     if v8 and v2 is None:
         raise ValueError("an 8-bit V has two planes: pass v2")
     if not v8 and v.dtype != torch.bfloat16:
@@ -290,7 +299,7 @@ def prepare_fold_decode(
                 int(bool(truncate)), int(weight_terms), float(refine_k), float(refine_v),
                 ctypes.addressof(bands) if bands is not None else None, float(v_scale),
                 o_part.data_ptr(), den_part.data_ptr(), cnt_part.data_ptr(), None, 0, den.data_ptr(), counts.data_ptr(),
-                status.data_ptr(), rm.data_ptr(), gsub, None, 0, slots, off, int(row_cut), _lib.stream(dev),
+                status.data_ptr(), rm.data_ptr(), gsub, None, 0, slots, off, int(row_cut), _lib.ptr(bound), 0, _lib.stream(dev),
             ))
             off += int(lv.split)
 
@@ -298,7 +307,8 @@ def prepare_fold_decode(
         """The unique level: combined in the call when it is the only level."""
         a = list(fixed)
         a += [o.data_ptr() if not levels else None, _OUT[o.dtype], den.data_ptr(), counts.data_ptr(), status.data_ptr(),
-              None, gsub, _lib.ptr(tree), q_len if tree is not None else 0, slots, 0, int(row_cut), _lib.stream(dev)]
+              None, gsub, _lib.ptr(tree), q_len if tree is not None else 0, slots, 0, int(row_cut), _lib.ptr(bound),
+              int(vmean_rows), _lib.stream(dev)]
         return a
 
     def run_mass():
@@ -324,6 +334,8 @@ def prepare_fold_decode(
         o = out_t if out is None else out
         if reference == "mass":
             run_mass()
+        if sound:   # the planes are this step's: the bound is too
+            bound.copy_(eq * (qa.float().abs().sum(-1) * 128.0 + qb.float().abs().sum(-1) * 0.5))
         if ex:
             _lib.call("fold_decode_run_ex", *ex_args(o))
             if levels:
@@ -357,7 +369,7 @@ def prepare_fold_decode(
     launch = DecodeLaunch(
         run,
         (qa, qb, eq, ka, kb, ek, v, v2, vmean, z, cut, page_table, seq_lens, order, o_part,
-         den_part, cnt_part, out_t, den, counts, status, bands, tail, tree, keep),
+         den_part, cnt_part, out_t, den, counts, status, bands, tail, tree, keep, bound),
     )
     launch.counts_shared = counts_shared
     launch.z = z

@@ -166,7 +166,12 @@ int fold_decode_run_tail(const int8_t* qa, const int8_t* qb, const float* eq, co
  *                them); a call that does not own every slot takes chunk_keys 0 and out NULL.
  *                slots_total 0 means split.
  *   row_cut      1: a key enters a row only if that row keeps it (the reference's choice for
- *                drafts and cascades); 0: if any row of its group keeps it */
+ *                drafts and cascades); 0: if any row of its group keeps it
+ *   sound        fp32 (n_groups, group) or NULL: per row eq * sum_d (128 |qa_d| + |qb_d| / 2);
+ *                the verdict then tests the coarse logit plus sound * ek / 256, a bound on what
+ *                K's second plane can add, so only keys the full logit would also drop are
+ *                dropped (decode/kernel.py:573-612, 797-834)
+ *   vmean_per_row  1: vmean is (n_groups, group, head_dim), a direction per query row */
 int fold_decode_run_ex(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
                        const int8_t* kb, const void* ek, const void* va, const void* vb,
                        const float* vmean, const float* z, const float* cut,
@@ -177,7 +182,8 @@ int fold_decode_run_ex(const int8_t* qa, const int8_t* qb, const float* eq, cons
                        float v_scale, float* o_part, float* den_part, int32_t* cnt_part, void* out,
                        int out_dtype, float* den, int32_t* counts, int32_t* status,
                        const int32_t* req_map, int group_split, const int32_t* tree, int draft_len,
-                       int slots_total, int slot_off, int row_cut, void* stream);
+                       int slots_total, int slot_off, int row_cut, const float* sound,
+                       int vmean_per_row, void* stream);
 int fold_mass_z_ex(const int8_t* qa, const int8_t* qb, const float* eq, const int8_t* ka,
                    const void* ek, const int32_t* page_table, const int32_t* seq_lens, int n_groups,
                    int group, int n_kv_heads, int head_dim, int pages_per_request, int page_size,

@@ -82,7 +82,7 @@ def truncated_softmax(s, z, v, cut):
 
 
 def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, vmean=None, reentry=None,
-                 visible=None, row_cut=False):
+                 visible=None, row_cut=False, sound=False):
     """One row group's decode in float64 on the cache's own (unswizzled)
     planes: `ka`, `kb` (S, D) int8, `ek` (S,), `va` (S, D) float (bf16 values
     or plane A in scale units), `vb` plane B or None. `depth` None keeps every
@@ -91,7 +91,8 @@ def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, v
     `visible` (G, >= n) bool hides keys from rows (a draft's tree: a hidden key weighs nothing
     in that row and takes no part in its verdicts); `row_cut` lets a gathered key enter only
     the rows that keep it themselves (src/fold_attention/decode/launch.py:602-627, `group_cut`
-    off), the others count it as dropped.
+    off), the others count it as dropped. `sound` tests the coarse logit plus the bound on what
+    plane B of K could add, `eq sum_d (128 |qa_d| + |qb_d| / 2) ek / 256` (decode/kernel.py:573-612).
     Returns (out (G, D), den (G,), live count, refined count)."""
     ka, kb, va = ka[:n], kb[:n], va[:n].double()
     ek = ek[:n]
@@ -99,10 +100,14 @@ def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, v
     s1 = coarse_logits(qa[None], qb[None], eq[None], ka[None], ek[None], z[None])[0]  # (G, n) float32
     if visible is not None:
         s1 = torch.where(visible[:, :n].to(s1.device), s1, torch.full_like(s1, float("-inf")))
+    s1c = s1
+    if sound:
+        bound = eq.float() * (qa.float().abs().sum(-1) * 128.0 + qb.float().abs().sum(-1) * 0.5)
+        s1c = _fma(bound[:, None].expand_as(s1), (ek.float() * (1.0 / KBR))[None, :].expand_as(s1), s1)
     if depth is None:
         live = torch.ones(n, dtype=torch.bool, device=s1.device)
     else:
-        live = (s1 >= -depth).any(0)
+        live = (s1c >= -depth).any(0)
     top = s1.amax(0)
     refk = live & (top >= -rk)
     refv = live & (top >= -rv) if vb is not None else torch.zeros_like(live)
@@ -113,7 +118,7 @@ def decode_model(qa, qb, eq, ka, kb, ek, va, vb, v_scale, z, depth, rk, rv, n, v
     e = torch.exp2(s)
     keeps = live[None].expand_as(e)
     if row_cut and depth is not None:
-        keeps = keeps & (s1 >= -depth)
+        keeps = keeps & (s1c >= -depth)
     w = torch.where(keeps, e, torch.zeros_like(e))
     m = torch.where(keeps, torch.zeros_like(e), e).sum(-1)
     vt = va

@@ -366,3 +366,75 @@ def test_the_levels_are_refused_where_they_cannot_run():
         fa.FoldKVCache(2, 40, 2, 128, 256)
     with pytest.raises(NotImplementedError, match="warp-level"):
         fa.FoldKVCache(2, 32, 2, 128, 256, kernel="sm100", page_size=128)
+
+
+@pytest.mark.parametrize("D,G,v8", [(128, 8, False), (64, 4, True)])
+def test_a_sound_cut_drops_only_what_the_full_logit_drops(D, G, v8):
+    from fold_attention_b200.decode.launch import prepare_fold_decode
+
+    HKV = 2
+    lens = [1200, 400]
+    k, v, cu = _kv(lens, HKV, D, 71)
+    c = _cache(lens, HKV * G, HKV, D, 71, depth=6.0, v8=v8, tail=None, v_scale=2.0 ** -3 if v8 else None)
+    c.write_prompt(k, v, cu, lens)
+    q = torch.randn(2, HKV * G, D, device="cuda").bfloat16()
+    c._step(q, None, None)
+    z = (torch.ceil(c.z * 16) / 16).contiguous()
+    live = {}
+    for snd in (False, True):
+        run = prepare_fold_decode(
+            c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, c.cut, split=2, truncate=True, refine_k=8.0, refine_v=8.0, v8=v8, v2=c.vb,
+            v_scale=c.v_scale, vmean=c.vmean, page_table=c.page_table, page_size=c.page_size, seq_lens=c.seq_lens, n_kv_heads=HKV,
+            weight_terms=2, sound=snd)
+        out, den, counts = run()
+        torch.cuda.synchronize()
+        assert int(run.status) == 0
+        live[snd] = counts[:, 0].clone()
+        for b, n in enumerate(lens):
+            for h in range(HKV):
+                bh = b * HKV + h
+                ka, kb, ek, va, vb = _planes(c, b, h, n)
+                want, wden, nlive, nref = od.decode_model(c.qa[bh], c.qb[bh], c.eq[bh], ka, kb, ek, va, vb, c.v_scale, z[bh], 6.0, 8.0, 8.0, n,
+                                                          vmean=c.vmean[bh], sound=snd)
+                assert counts[bh].tolist() == [nlive, nref], (snd, b, h)
+                assert _l2(out[bh], want) < 2e-3
+                if snd:
+                    # soundness: a key whose full two-plane logit clears some row's cut is live
+                    s1 = od.coarse_logits(c.qa[bh][None], c.qb[bh][None], c.eq[bh][None], ka[None], ek[None], z[bh][None])[0]
+                    tk = (c.eq[bh].float()[:, None] * (ek.float()[None, :] / 256.0)).double()
+                    full = s1.double() + (torch.einsum("gd,sd->gs", c.qa[bh].double(), kb.double())
+                                          + torch.einsum("gd,sd->gs", c.qb[bh].double(), kb.double()) / 256.0) * tk
+                    bound = (c.eq[bh].float() * (c.qa[bh].float().abs().sum(-1) * 128.0 + c.qb[bh].float().abs().sum(-1) * 0.5)).double()
+                    kept = (s1.double() + bound[:, None] * (ek.double()[None, :] / 256.0) >= -6.0).any(0)
+                    assert bool(kept[(full >= -6.0).any(0)].all())
+    assert bool((live[True] >= live[False]).all()) and int(live[True].sum()) > int(live[False].sum())
+
+
+def test_a_direction_per_query_row():
+    from fold_attention_b200.decode.launch import prepare_fold_decode
+
+    D, G, HKV = 128, 4, 2
+    lens = [900, 250]
+    k, v, cu = _kv(lens, HKV, D, 81)
+    c = _cache(lens, HKV * G, HKV, D, 81, depth=6.0, tail=None)
+    c.write_prompt(k, v, cu, lens)
+    q = torch.randn(2, HKV * G, D, device="cuda").bfloat16()
+    c._step(q, None, None)
+    z = (torch.ceil(c.z * 16) / 16).contiguous()
+    vm = torch.randn(2 * HKV, G, D, device="cuda")
+    run = prepare_fold_decode(
+        c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, c.cut, split=3, truncate=True, refine_k=8.0, refine_v=8.0, v_scale=1.0, vmean=vm,
+        page_table=c.page_table, page_size=c.page_size, seq_lens=c.seq_lens, n_kv_heads=HKV, weight_terms=2)
+    out, den, counts = run()
+    torch.cuda.synchronize()
+    for b, n in enumerate(lens):
+        for h in range(HKV):
+            bh = b * HKV + h
+            ka, kb, ek, va, vb = _planes(c, b, h, n)
+            for g in range(G):   # the model takes one direction: a row at a time, with the group's verdicts
+                want, _, nlive, nref = od.decode_model(c.qa[bh], c.qb[bh], c.eq[bh], ka, kb, ek, va, vb, 1.0, z[bh], 6.0, 8.0, 8.0, n, vmean=vm[bh, g])
+                assert _l2(out[bh, g], want[g]) < 2e-3
+            assert counts[bh].tolist() == [nlive, nref]
+    with pytest.raises(ValueError, match="one per query row"):
+        prepare_fold_decode(c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, c.cut, truncate=True, vmean=vm[:, :2], page_table=c.page_table,
+                            page_size=c.page_size, seq_lens=c.seq_lens, n_kv_heads=HKV)

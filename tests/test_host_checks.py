@@ -77,3 +77,30 @@ def test_the_forward_and_backward_refuse_tensors_that_do_not_match_q():
         prepare_backward(qb, kb, kb, qb.half(), qb, lse, causal=True)
     with pytest.raises(NotImplementedError, match="self-attention"):
         prepare_backward(qb, kb[:, :, :8], kb[:, :, :8], qb, qb, lse, causal=True)
+
+
+def test_a_decode_launch_binds_on_the_host_for_every_layout():
+    """`prepare_fold_decode` validates and binds without touching the GPU: every layout it takes
+    builds a launch from CPU tensors (nothing is run), and the mismatches are refused."""
+    from fold_attention_b200.decode.launch import prepare_fold_decode
+
+    def planes(NBH, G, D=128):
+        return (torch.zeros(NBH, G, D, dtype=torch.int8), torch.zeros(NBH, G, D, dtype=torch.int8), torch.ones(NBH, G),
+                torch.zeros(1024, D, dtype=torch.int8), torch.zeros(1024, D, dtype=torch.int8), torch.zeros(1024, dtype=torch.bfloat16),
+                torch.zeros(1024, D, dtype=torch.bfloat16), torch.zeros(NBH, G), torch.full((NBH, G), 8.0))
+
+    kw = dict(page_table=torch.zeros(2, 4, dtype=torch.int32), page_size=64, seq_lens=torch.zeros(2, dtype=torch.int32), n_kv_heads=2)
+    assert prepare_fold_decode(*planes(4, 8), truncate=True, vmean=torch.zeros(4, 128), **kw).kernel in ("mma", "sm100")
+    assert prepare_fold_decode(*planes(4, 8), truncate=True, vmean=torch.zeros(4, 128), draft_len=4, causal=True, **kw).tree.shape == (4, 8)
+    assert prepare_fold_decode(*planes(4, 8), truncate=True, vmean=torch.zeros(4, 8, 128), **kw).kernel == "mma"
+    assert prepare_fold_decode(*planes(4, 8), truncate=True, vmean=torch.zeros(4, 128), sound=True, **kw).kernel == "mma"
+    assert prepare_fold_decode(*planes(4, 8), truncate=True, vmean=torch.zeros(4, 128), group_cut=False, **kw).kernel == "mma"
+    assert prepare_fold_decode(*planes(4, 32), split=2, **kw).kernel == "mma"      # 16 groups of 8 on the warp-level kernel
+    with pytest.raises(ValueError, match="one per query row"):
+        prepare_fold_decode(*planes(4, 8), truncate=True, vmean=torch.zeros(4, 4, 128), **kw)
+    with pytest.raises(NotImplementedError, match="16, 24 or 32"):
+        prepare_fold_decode(*planes(4, 12), **kw)
+    with pytest.raises(NotImplementedError, match="one group of at most 8"):
+        prepare_fold_decode(*planes(4, 16), draft_len=2, causal=True, **kw)
+    with pytest.raises(ValueError, match="names the 16 groups of 8"):
+        prepare_fold_decode(*planes(4, 32), order=torch.arange(4, dtype=torch.int32), **kw)
