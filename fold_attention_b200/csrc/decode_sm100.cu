@@ -74,7 +74,10 @@ constexpr int NHELP = 4;
 constexpr int HSLOT = 528;       // a staging slot: Ka, Kb, Va, Vb rows of 128 bytes, the scale's word, the key's note
 constexpr int NBQ = 8;            // tiles of quarter flags (and their barrier) in flight: more than the key threads can lead by
 constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weights) in flight
-constexpr int DENSE_MIN = 4;     // refine-V keys in a 32-key quarter from which the quarter's plane B is fetched whole
+#ifndef FOLD_DEC_DENSE_MIN
+#define FOLD_DEC_DENSE_MIN 3
+#endif
+constexpr int DENSE_MIN = FOLD_DEC_DENSE_MIN;   // refine-V keys in a 32-key quarter from which the quarter's plane B is fetched whole
 constexpr int NTHREADS = 512;
 constexpr long long WAIT_CYCLES = 1ll << 31;
 constexpr float BIG_TOP = 8.0f;  // a key whose weight could pass 2^8 is summed in fp32 by a helper
