@@ -377,3 +377,39 @@ def prepare_fold_decode(
     launch.kernel = ("sm100+mma" if short_slots else "sm100") if use_sm100 else "mma"
     launch.tree = tree
     return launch
+
+
+def fold_decode(qa, qb, eq, ka, kb, ek, v, z, cut, **kw):
+    """One decode step: `prepare_fold_decode(...)()`, returning `(out, den, counts)`
+    (reference: decode/launch.py:503-506)."""
+    return prepare_fold_decode(qa, qb, eq, ka, kb, ek, v, z, cut, **kw)()
+
+
+def capture_decode(launch, warmup=3):
+    """A prepared decode captured in a CUDA graph; the returned launch replays it.
+
+    The replay reads and writes the tensors `launch` was bound to: their
+    contents may change between replays, the tensors themselves may not. A
+    launch that was bound with `sound=True` or a cascade under the mass
+    reference runs a few torch kernels of its own, which are captured too
+    (reference: decode/launch.py:1333-1360)."""
+    for _ in range(int(warmup)):
+        launch()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            result = launch()
+    torch.cuda.synchronize()
+
+    def replay(out=None):
+        if out is not None:
+            raise ValueError("a captured decode writes the output it was captured with")
+        graph.replay()
+        return result
+
+    captured = DecodeLaunch(replay, (launch, side, graph))
+    for name in ("z", "status", "kernel", "tree", "counts_shared"):
+        setattr(captured, name, getattr(launch, name, None))
+    return captured

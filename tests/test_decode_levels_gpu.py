@@ -438,3 +438,33 @@ def test_a_direction_per_query_row():
     with pytest.raises(ValueError, match="one per query row"):
         prepare_fold_decode(c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, c.cut, truncate=True, vmean=vm[:, :2], page_table=c.page_table,
                             page_size=c.page_size, seq_lens=c.seq_lens, n_kv_heads=HKV)
+
+
+def test_a_captured_decode_replays_the_launch_it_was_made_from():
+    from fold_attention_b200.decode import capture_decode, fold_decode, prepare_fold_decode
+
+    D, H, HKV = 128, 8, 2
+    lens = [500, 130]
+    k, v, cu = _kv(lens, HKV, D, 91)
+    c = _cache(lens, H, HKV, D, 91, depth=8.0, tail=None)
+    c.write_prompt(k, v, cu, lens)
+    q = torch.randn(2, H, D, device="cuda").bfloat16()
+    c._step(q, None, None)
+    args = (c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, c.z, c.cut)
+    kw = dict(split=2, truncate=True, v_scale=1.0, vmean=c.vmean, page_table=c.page_table, page_size=c.page_size, seq_lens=c.seq_lens,
+              n_kv_heads=HKV, reference="mass", weight_terms=2, sound=True, group_cut=False)
+    want = tuple(t.clone() for t in fold_decode(*args, **kw))
+    launch = prepare_fold_decode(*args, **kw)
+    cap = capture_decode(launch)
+    for _ in range(2):
+        got = cap()
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(got, want))
+    assert int(cap.status) == 0 and cap.kernel == "mma"
+    # the bound tensors' contents may change between replays
+    q2 = torch.randn(2, H, D, device="cuda").bfloat16()
+    c._step(q2, None, None)
+    want2 = tuple(t.clone() for t in launch())
+    got2 = cap()
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(got2, want2)) and not torch.equal(want2[0], want[0])
