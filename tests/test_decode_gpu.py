@@ -300,3 +300,46 @@ def test_check_range_reruns_the_rows_whose_reference_was_off(v8, depth, kernel):
     off.z[1::2] += 6.0
     off._run(q, None)
     assert bool((off.den[1::2] < lo).any())   # without the check such rows stay as they came out
+
+
+@pytest.mark.parametrize("kernel,v8,depth", [("mma", False, None), ("mma", True, 12.0), ("sm100", True, 16.0), ("sm100", False, None)])
+def test_where_the_pages_lie_changes_no_bit(kernel, v8, depth):
+    """A shuffled page table, the identity one and another page size give the same bits and the
+    same counts (the reference's paged-equals-contiguous check, tests/test_decode.py:555-597), and
+    a key under the cut weighs exactly nothing: moving V of the dropped keys moves no bit either
+    once their mass re-enters nowhere (a zero direction)."""
+    lens = [1500, 260, 3000]
+    B, H, HKV, D = len(lens), 16, 2, 128
+    q, k, v, cu = _layer(B, H, HKV, D, lens, seed=12)
+    outs = []
+    for shuffle, ps, seed in ((False, 128, 0), (True, 128, 1), (True, 256, 2), (True, 128, 3)):
+        c = _cache(B, H, HKV, D, lens, ps=ps, shuffle=shuffle, seed=seed, v8=v8, depth=depth, kernel=kernel, chunk=1024,
+                   tail=None, v_scale=2.0 ** -3 if v8 else None)
+        c.write_prompt(k, v, cu, lens)
+        outs.append((c.attend(q).clone(), c.counts.clone(), c.den.clone()))
+    for o, cnt, den in outs[1:]:
+        assert torch.equal(o, outs[0][0]) and torch.equal(cnt, outs[0][1]) and torch.equal(den, outs[0][2])
+    if depth is not None:
+        from fold_attention_b200.decode.launch import prepare_fold_decode
+
+        c = _cache(B, H, HKV, D, lens, ps=128, v8=v8, depth=depth, kernel=kernel, tail=None, v_scale=2.0 ** -3)
+        c.write_prompt(k, v, cu, lens)
+        c._step(q, None, None)
+        cut = torch.full_like(c.z, 4.0)
+        kw = dict(split=2, truncate=True, refine_k=2.0, refine_v=2.0, v8=True, v2=c.vb, v_scale=c.v_scale, vmean=torch.zeros_like(c.vmean),
+                  page_table=c.page_table, page_size=128, seq_lens=c.seq_lens, n_kv_heads=HKV, weight_terms=2, kernel=kernel)
+        z = (torch.ceil(c.z * 16) / 16).contiguous()
+        base, _, counts = (t.clone() for t in prepare_fold_decode(c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, cut, **kw)())
+        assert int(counts[:, 0].sum()) < 0.5 * sum(lens) * HKV
+        # scramble V of every key no row keeps: the model's live set, from the coarse logits
+        for b, n in enumerate(lens):
+            for h in range(HKV):
+                bh = b * HKV + h
+                ka, _, ek, _, _ = _planes(c, b, h, n)
+                s1 = od.coarse_logits(c.qa[bh][None], c.qb[bh][None], c.eq[bh][None], ka[None], ek[None], z[bh][None])[0]
+                dead = ~(s1 >= -4.0).any(0)
+                rows, _ = _rows(c, b, h, n)
+                c.va.view(torch.uint8)[rows[dead]] = 0x38      # e4m3 1.0 everywhere
+                c.vb.view(torch.uint8)[rows[dead]] = 0x38
+        again = prepare_fold_decode(c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, cut, **kw)()[0]
+        assert torch.equal(again, base)
