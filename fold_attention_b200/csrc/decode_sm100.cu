@@ -80,6 +80,20 @@ constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weig
 constexpr int DENSE_MIN = FOLD_DEC_DENSE_MIN;   // refine-V keys in a 32-key quarter from which the quarter's plane B is fetched whole
 constexpr int NTHREADS = 512;
 constexpr long long WAIT_CYCLES = 1ll << 31;
+// -DFOLD_DEC_COUNTERS: every role adds the cycles it spends in each of its waits, and in all, to
+// global counters fold_decode_counters returns (a measurement build: the waits cost two clock reads)
+#ifdef FOLD_DEC_COUNTERS
+__device__ unsigned long long g_dec_counters[32];
+#define CW(slot, call) do { const long long cw_t = clock64(); call; cntl[slot] += clock64() - cw_t; } while (0)
+#define CW_DECL long long cntl[32] = {}; const long long cw_t0 = clock64(); (void)cw_t0
+#define CW_FLUSH(total_slot) do { cntl[total_slot] += clock64() - cw_t0; for (int cw_i = 0; cw_i < 32; ++cw_i) if (cntl[cw_i]) atomicAdd(&g_dec_counters[cw_i], static_cast<unsigned long long>(cntl[cw_i])); } while (0)
+#define CW_ADD(slot, v) cntl[slot] += (v)
+#else
+#define CW(slot, call) call
+#define CW_DECL
+#define CW_FLUSH(total_slot)
+#define CW_ADD(slot, v)
+#endif
 constexpr float BIG_TOP = 8.0f;  // a key whose weight could pass 2^8 is summed in fp32 by a helper
 constexpr int W_BIAS = 6;        // weights are stored times 2^6: under 2^14 on the tensor-core path
 
@@ -405,26 +419,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
     if (warp == 0) {
         // ================= producer: K's plane A =================
         if (lane == 0) {
+            CW_DECL;
+            CW_ADD(0, 1);
             for (int t = 0; t < n_tiles; ++t) {
                 const int s = t % NA;
-                if (t >= NA) mbar_wait(bar(B_LFULL + s), ((t / NA) - 1) & 1, abort_flag, p.status);
+                if (t >= NA) CW(12, mbar_wait(bar(B_LFULL + s), ((t / NA) - 1) & 1, abort_flag, p.status));
                 const int64_t r = tile_row(lo + t * tstep);
                 mbar_expect_tx(bar(B_AFULL + s), 16384);
                 bulk_load(base + SM_KA + s * 16384, p.ka + r * HD, 16384, bar(B_AFULL + s));
             }
+            CW_FLUSH(13);
         }
     } else if (warp == 2) {
         // ================= producer: V's plane A and the key scales =================
         if (lane == 0) {
+            CW_DECL;
             for (int t = 0; t < n_tiles; ++t) {
                 const int s = t % NV;
-                if (t >= NV) mbar_wait(bar(B_VEMPTY + s), ((t / NV) - 1) & 1, abort_flag, p.status);
+                if (t >= NV) CW(14, mbar_wait(bar(B_VEMPTY + s), ((t / NV) - 1) & 1, abort_flag, p.status));
                 const int64_t r = tile_row(lo + t * tstep);
                 mbar_expect_tx(bar(B_VFULL + s), VBYTES + 256);
                 bulk_load(base + SM_KS + s * 256, p.ek + r, 256, bar(B_VFULL + s));
                 tma_load_2d(base + SM_VA + s * VBYTES, &vmap, 0, static_cast<int>(r), bar(B_VFULL + s));
                 if (!V8) tma_load_2d(base + SM_VA + s * VBYTES + 16384, &vmap, 64, static_cast<int>(r), bar(B_VFULL + s));
             }
+            CW_FLUSH(15);
         }
     } else if (warp == 1) {
         // ================= MMA issuer: logits =================
@@ -433,16 +452,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             // descriptors of slot 0; a slot or K step further is an addition
             const uint64_t dq = smem_desc(base + SM_Q, 16, 1024, 2);
             const uint64_t dka = smem_desc(base + SM_KA, 16, 1024, 2);
+            CW_DECL;
             for (int t = 0; t < n_tiles; ++t) {
                 const int s = t % NA;
                 // the TMEM slot was tile t-NA's: its value MMAs retired, so its weights were done and
                 // its logits read
-                if (t >= NA) mbar_wait(bar(B_VEMPTY + (t - NA) % NV), ((t - NA) / NV) & 1, abort_flag, p.status);
-                mbar_wait(bar(B_AFULL + s), (t / NA) & 1, abort_flag, p.status);
+                if (t >= NA) CW(16, mbar_wait(bar(B_VEMPTY + (t - NA) % NV), ((t - NA) / NV) & 1, abort_flag, p.status));
+                CW(17, mbar_wait(bar(B_AFULL + s), (t / NA) & 1, abort_flag, p.status));
                 tc_fence_after();
                 mma4_i8<2, 2>(tmem + T_L + 16 * s, dka + s * 1024, dq, ID_L, 0u);   // 32 bytes per K step
                 tc_commit(bar(B_LFULL + s));
             }
+            CW_FLUSH(18);
         }
     } else if (warp == 3) {
         // ================= MMA issuer: values =================
@@ -455,6 +476,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             const uint64_t dw = smem_desc(base + SM_W, 128, 2048, 0);
             const uint64_t dw2 = smem_desc(base + SM_W2, 128, 2048, 0);
             bool acc2_started = false;
+            CW_DECL;
             // iteration j: plane B of V of tile j-2 (its quarters were asked for two tiles ago), then
             // the value product of tile j. The order matters: a key thread of tile t waits for the
             // value MMAs of t-2 and then, by parity, for the plane-B buffer of t-2; the commit for
@@ -462,7 +484,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             for (int j = 0; j < n_tiles + 2; ++j) {
                 if (V8 && j >= 2) {
                     const int t = j - 2, b2 = t % NB2;
-                    mbar_wait(bar(B_BFULL + t % NBQ), (t / NBQ) & 1, abort_flag, p.status);
+                    CW(19, mbar_wait(bar(B_BFULL + t % NBQ), (t / NBQ) & 1, abort_flag, p.status));
                     const volatile uint32_t* qfp = reinterpret_cast<const volatile uint32_t*>(smem + SM_QF + (t % NBQ) * 16);
                     const uint32_t f[4] = {qfp[0], qfp[1], qfp[2], qfp[3]};
                     if (f[0] | f[1] | f[2] | f[3]) {
@@ -479,8 +501,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 }
                 if (j < n_tiles) {
                     const int t = j, s = t % NV;
-                    mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status);
-                    mbar_wait(bar(B_WREADY + (t & 1)), (t >> 1) & 1, abort_flag, p.status);
+                    CW(20, mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status));
+                    CW(21, mbar_wait(bar(B_WREADY + (t & 1)), (t >> 1) & 1, abort_flag, p.status));
                     tc_fence_after();
                     if (V8) {
                         // 32 keys per K step: 4096 bytes of V, 512 bytes of weights
@@ -494,6 +516,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 }
             }
             tc_commit(bar(B_ALLDONE));
+            CW_FLUSH(22);
         }
     } else if (warp >= 4 && warp < 12) {
         // ================= one thread per key; two groups take the even and the odd tiles =================
@@ -514,12 +537,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
         int nlive = 0, nref = 0;
         bool any_dense = false;
         uint32_t* qm = reinterpret_cast<uint32_t*>(smem + SM_QM);
+        CW_DECL;
         for (int t = wg; t < n_tiles; t += 2) {
+            if ((warp & 3) == 0) CW_ADD(1, 1);
             const int s = t % NV;
             const int tb = lo + t * tstep;
             const int nrow = min(TK, hi - tb);
-            mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status);   // the scales ride with V
-            mbar_wait(bar(B_LFULL + t % NA), (t / NA) & 1, abort_flag, p.status);
+            CW(3, mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status));   // the scales ride with V
+            CW(4, mbar_wait(bar(B_LFULL + t % NA), (t / NA) & 1, abort_flag, p.status));
             tc_fence_after();
             uint32_t c[16];
             tmem_ld16(tmem + lane_addr + T_L + 16 * (t % NA), c);
@@ -562,7 +587,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             const unsigned mk = __ballot_sync(0xffffffffu, refk);
             const unsigned mv = __ballot_sync(0xffffffffu, refv);
             const unsigned mh = __ballot_sync(0xffffffffu, helped);
-            if (t >= 2) mbar_wait(bar(B_VEMPTY + (t - 2) % NV), ((t - 2) / NV) & 1, abort_flag, p.status);   // the weight buffer is free
+            if (t >= 2) CW(5, mbar_wait(bar(B_VEMPTY + (t - 2) % NV), ((t - 2) / NV) & 1, abort_flag, p.status));   // the weight buffer is free
             float w[8];
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
@@ -621,7 +646,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             if (V8) {
                 const int b2 = t % NB2, bq = t % NBQ;
                 if (dense) {
-                    if (lane == 0 && t >= NB2) mbar_wait(bar(B_BFREE + b2), ((t / NB2) - 1) & 1, abort_flag, p.status);
+                    if (lane == 0 && t >= NB2) CW(6, mbar_wait(bar(B_BFREE + b2), ((t / NB2) - 1) & 1, abort_flag, p.status));
                     __syncwarp();
                     uint8_t* w2dst = smem + SM_W2 + b2 * 4096 + k * 16;
                     *reinterpret_cast<uint4*>(w2dst) = dv ? make_uint4(wb[0], wb[1], wb[2], wb[3]) : make_uint4(0, 0, 0, 0);
@@ -643,7 +668,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             // hand the keys that need fp32 to the tile's helper
             if (lane == 0) {
                 const int q = t % QD;
-                if (t >= QD) mbar_wait(bar(B_QFREE + q), ((t / QD) - 1) & 1, abort_flag, p.status);
+                if (t >= QD) CW(7, mbar_wait(bar(B_QFREE + q), ((t / QD) - 1) & 1, abort_flag, p.status));
                 qm[q * 12 + (warp & 3)] = mk;
                 qm[q * 12 + 4 + (warp & 3)] = mv;
                 qm[q * 12 + 8 + (warp & 3)] = mh;
@@ -653,7 +678,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
         }
 
         // ---- epilogue: the first group's thread k is channel k of the output ----
-        if (n_tiles > 0) mbar_wait(bar(B_ALLDONE), 0, abort_flag, p.status);
+        if (lane == 0) CW_FLUSH(2);
+        if (n_tiles > 0) CW(23, mbar_wait(bar(B_ALLDONE), 0, abort_flag, p.status));
         tc_fence_after();
         float* sRed = reinterpret_cast<float*>(smem + SM_RED);
         const int kk2 = wg * 128 + k;
@@ -775,6 +801,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
         const int row_bytes_l = (!V8 && part >= 2) ? 256 : HD;
 
         // issue side: the tile whose marked keys are being handed out
+        CW_DECL;
         int it = h;                       // next tile to open
         uint32_t mK[4] = {0, 0, 0, 0}, mV[4] = {0, 0, 0, 0}, mH[4] = {0, 0, 0, 0};
         int wi = 4;                       // word of mH in hand (4: none left)
@@ -793,11 +820,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 }
                 if (rem != 0u) break;
                 if (!open_tiles) return false;
+#ifdef FOLD_DEC_COUNTERS
+                const long long cw_o0 = clock64();
+#endif
                 // open the next tile's masks
                 const int q = it % QD;
                 if (!mbar_try(bar(B_QFULL + q), (it / QD) & 1)) {
                     if (!block) return false;
-                    mbar_wait(bar(B_QFULL + q), (it / QD) & 1, abort_flag, p.status);
+                    CW(9, mbar_wait(bar(B_QFULL + q), (it / QD) & 1, abort_flag, p.status));
                     if (*abort_flag) { open_tiles = false; return false; }
                 }
 #pragma unroll
@@ -813,7 +843,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 rem = mH[0];
                 it += NHELP;
                 open_tiles = it < n_tiles;
+#ifdef FOLD_DEC_COUNTERS
+                cntl[26] += clock64() - cw_o0;
+                cntl[28] += 1;
+#endif
             }
+#ifdef FOLD_DEC_COUNTERS
+            const long long cw_k0 = clock64();
+#endif
             const int b = __ffs(rem) - 1;
             rem &= rem - 1;
             const int kk = 32 * wi + b;
@@ -836,6 +873,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
             ++issued;
+#ifdef FOLD_DEC_COUNTERS
+            cntl[27] += clock64() - cw_k0;
+#endif
             return true;
         };
         auto dot8 = [&](const uint4& lo4, const uint4& hi4, const int (&qw)[8]) -> int {
@@ -853,8 +893,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
         };
         while (true) {
             // keep the slots full as far as keys are to be had now; wait for one only when idle
+#ifdef FOLD_DEC_COUNTERS
+            const long long cw_i0 = clock64();
+#endif
             while (issued - taken < HD_KEYS && issue_one(false)) {}
             if (issued == taken && !issue_one(true)) break;
+#ifdef FOLD_DEC_COUNTERS
+            cntl[24] += clock64() - cw_i0;
+            const long long cw_c0 = clock64();
+#endif
             // Several keys a pass when that many are in flight: their dot products, shuffles and
             // conversions do not depend on each other, which a lone warp's in-order issue needs to
             // stay busy. The sums still take the keys in order. (Measured: a gain on a bf16 V, where a
@@ -863,6 +910,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             const int avail = issued - taken;
             const int take = (HPASS >= 4 && avail >= 4) ? 4 : ((HPASS >= 2 && avail >= 2) ? 2 : 1);
             {   // the younger copies may still be in flight
+#ifdef FOLD_DEC_COUNTERS
+                const long long cw_w = clock64();
+#endif
                 const int pending = avail - take;
                 switch (pending < 15 ? pending : 15) {   // the instruction takes its count as an immediate
 #define FOLD_WAIT_CASE(n) case n: asm volatile("cp.async.wait_group " #n ";" ::: "memory"); break;
@@ -872,6 +922,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                     default: asm volatile("cp.async.wait_group 15;" ::: "memory"); break;
 #undef FOLD_WAIT_CASE
                 }
+#ifdef FOLD_DEC_COUNTERS
+                cntl[10] += clock64() - cw_w;
+#endif
             }
             __syncwarp();
             auto consume = [&](auto n_keys) {
@@ -946,8 +999,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             else if (take == 2) consume(std::integral_constant<int, (HPASS >= 2 ? 2 : 1)>{});
             else consume(std::integral_constant<int, 1>{});
             __syncwarp();   // the slots are read out before the next copies may land in them
+#ifdef FOLD_DEC_COUNTERS
+            cntl[25] += clock64() - cw_c0;
+#endif
             taken += take;
+            CW_ADD(11, take);
         }
+        if (lane == 0) CW_FLUSH(8);
         // the sums go where V's ring was: wait until nothing reads or fills it any more
         if (n_tiles > 0) mbar_wait(bar(B_ALLDONE), 0, abort_flag, p.status);
         float* hout = reinterpret_cast<float*>(smem + SM_HOUT) + h * (HOUT / 4);
@@ -1080,4 +1138,32 @@ extern "C" int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const f
     if (!out) return FOLD_OK;   // partials only: the caller combines
     return fold_decode_combine(o_part, den_part, cnt_part, seq_lens, out, out_dtype, den, counts, n_groups, group,
                                head_dim, n_kv_heads, split, chunk_keys, v_scale, stream);
+}
+
+// The role counters of a -DFOLD_DEC_COUNTERS build (cycles, summed over CTAs and over each role's
+// counting lanes): 0 CTAs, 1 tiles; key threads (8 warps) 2 all, 3-7 waits for V and scales,
+// logits, the weight buffer, a plane-B buffer, the mask ring; helpers (4 warps) 8 all, 9 waiting
+// for a tile's masks, 10 waiting for rows, 11 keys; 12-13 K producer (slot free, all); 14-15 V
+// producer; 16-18 logit MMA thread (TMEM slot free, K landed, all); 19-22 value MMA thread (plane B
+// landed, V landed, weights ready, all); 23 key threads' wait for the last product; helpers again:
+// 24 handing out keys (opening tiles' masks, starting copies), 25 waiting for rows and summing,
+// 26 inside tile opens (a try_wait that sleeps until the masks are published counts here), 27 starting
+// a key's copies, 28 tiles opened.
+extern "C" int fold_decode_counters(uint64_t* out32, int reset) {
+#ifdef FOLD_DEC_COUNTERS
+    FOLD_CHECK_ARG(out32, "fold_decode_counters: null pointer");
+    unsigned long long h[32];
+    if (cudaMemcpyFromSymbol(h, fold::dsm100::g_dec_counters, sizeof(h)) != cudaSuccess) return fold::check_launch("fold_decode_counters");
+    for (int i = 0; i < 32; ++i) out32[i] = h[i];
+    if (reset) {
+        memset(h, 0, sizeof(h));
+        if (cudaMemcpyToSymbol(fold::dsm100::g_dec_counters, h, sizeof(h)) != cudaSuccess) return fold::check_launch("fold_decode_counters");
+    }
+    return FOLD_OK;
+#else
+    (void)out32;
+    (void)reset;
+    fold::set_error("fold_decode_counters: the library was built without -DFOLD_DEC_COUNTERS");
+    return FOLD_ERR_UNSUPPORTED;
+#endif
 }

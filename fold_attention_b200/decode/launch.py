@@ -39,6 +39,7 @@ _lib.register(
     [P] * 14 + [I] * 10 + [F, F, P, F] + [P, P, P, P, I, P, P, P] + [P, I, P, I, I, I, I, P, I, P],
 )
 _lib.register("fold_mass_z_ex", [P, P, P, P, P, P, P, I, I, I, I, I, I, P, P, I, P, I, P])
+_lib.register("fold_decode_counters", [P, I])
 _lib.register("fold_decode_combine", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P])
 
 _OUT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}

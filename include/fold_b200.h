@@ -219,6 +219,11 @@ int fold_decode_run_sm100(const int8_t* qa, const int8_t* qb, const float* eq, c
                           float* den_part, int32_t* cnt_part, void* out, int out_dtype, float* den,
                           int32_t* counts, int32_t* status, void* stream);
 
+/* Where the tcgen05 decode kernel's roles spend their cycles: 32 counters (listed beside the
+ * entry in csrc/decode_sm100.cu) that a library built with -DFOLD_DEC_COUNTERS accumulates;
+ * FOLD_ERR_UNSUPPORTED from any other build. No counterpart in the reference. */
+int fold_decode_counters(uint64_t* out32, int reset);
+
 /* The combine step alone: out = (sum over splits of o_part) * v_scale / (sum of
  * den_part), in slot order. Replaces src/fold_attention/decode/combine.py:10-162. */
 int fold_decode_combine(const float* o_part, const float* den_part, const int32_t* cnt_part,
