@@ -5,7 +5,7 @@ layouts, under the reference's names where it has them
 from .heuristics import pick_split
 from .launch import SharedPrefix, capture_decode, fold_decode, mass_z, prepare_fold_decode
 from .rows import draft_mask, pack_rows, pack_tree, unpack_rows
-from .tail import TailState
+from .tail import TailState, tail_model
 
 __all__ = [
     "SharedPrefix",
@@ -18,5 +18,6 @@ __all__ = [
     "pack_tree",
     "pick_split",
     "prepare_fold_decode",
+    "tail_model",
     "unpack_rows",
 ]

@@ -112,7 +112,7 @@ def mass_z(qa, qb, eq, ka, ek, page_table, page_size, seq_lens, n_kv_heads, z, *
 def prepare_fold_decode(
     qa, qb, eq, ka, kb, ek, v, z, cut, *,
     split=1, truncate=False, refine_k=10.0, refine_v=10.0, v8=False, v2=None, v_scale=1.0,
-    vmean=None, page_table, page_size, seq_lens, n_kv_heads, reference="given", weight_terms=1,
+    vmean=None, page_table=None, page_size=0, seq_lens=None, n_kv_heads=1, reference="given", weight_terms=1,
     order=None, out_dtype=torch.float32, refine_bands=(), chunk_keys=0, out=None, kernel="mma",
     short_slots=0, tail=None, draft_len=1, causal=False, mask=None, shared=None, group_cut="auto", sound=False,
 ):
@@ -123,6 +123,9 @@ def prepare_fold_decode(
     reference (written by the launch when `reference="mass"`) and `cut` its
     depth below `z` under which a key is dropped (`truncate`). Calling the
     launch returns `(out (NBH, G, D), den (NBH, G), counts (NBH, 2))`.
+    Without a `page_table` the cache is contiguous: `ka`, `kb`, `v` `(NBH, S, D)`
+    and `ek` `(NBH, S)`, every row group `S` keys long unless `seq_lens` `(NBH,)`
+    says otherwise (S a multiple of 64).
     `kernel` picks the split-KV kernel: "mma" (warp-level, every shape), "sm100"
     (tcgen05; D = 128, pages and chunks of a multiple of 128 keys; its weights are
     four E5M2 terms on an 8-bit V and two bf16 terms on a bf16 V, whatever
@@ -150,6 +153,24 @@ def prepare_fold_decode(
     warp-level kernel (reference: decode/launch.py:380-500, `tail=`).
     """
     NBH, G, D = qa.shape
+    if page_table is None:
+        # a contiguous cache `(NBH, S, D)` is a paged one whose pages are the row groups themselves
+        if ka.dim() != 3 or ka.shape[0] != NBH:
+            raise ValueError(f"without a page table K's planes are ({NBH}, S, {D}) (got {tuple(ka.shape)})")
+        S = ka.shape[1]
+        if S % 64 and S not in (16, 32):
+            raise NotImplementedError(f"a contiguous cache of {S} keys a row group: a multiple of 64 (or 16, 32); page it otherwise")
+        page_table = torch.arange(NBH, device=qa.device, dtype=torch.int32).view(NBH, 1)
+        page_size, n_kv_heads = S, 1
+        if seq_lens is None:
+            seq_lens = torch.full((NBH,), S, device=qa.device, dtype=torch.int32)
+        elif seq_lens.numel() != NBH:
+            raise ValueError(f"a contiguous cache's seq_lens has one length per row group ({NBH})")
+        ka, kb, ek, v = ka.reshape(NBH * S, D), kb.reshape(NBH * S, D), ek.reshape(NBH * S), v.reshape(NBH * S, D)
+        if v2 is not None:
+            v2 = v2.reshape(NBH * S, D)
+    elif seq_lens is None or page_size <= 0:
+        raise ValueError("a paged cache is ragged: pass seq_lens and page_size")
     if G > 8 and (G % 8 or G > 32):
         raise NotImplementedError(f"a row group of {G} rows: 1..8, 16, 24 or 32 are supported")
     gsub = 1 if G <= 8 else G // 8

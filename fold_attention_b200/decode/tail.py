@@ -150,3 +150,43 @@ def fit_prompt(kint, ek, v, rank, lam=1e-3, fit=None):
     ysum, _ = block_sums(project(kint, ek, u))
     rows = rows - (ysum / cntf) @ vr.transpose(1, 2)
     return u, vr, vsum, ysum, rows
+
+
+def tail_model(ka, ek, v, *, rank=0, lam=1e-3, fit=None):
+    """A contiguous cache's tail, as `prepare_fold_decode(tail=)` takes it: `ka`
+    `(NBH, S, D)` plane A as the cache stores it (swizzled by position), `ek`
+    `(NBH, S)` the keys' scales, `v` `(NBH, S, D)` the bf16 values; S a multiple
+    of 64. Same call as the reference's `cache.tail_model`
+    (src/fold_attention/decode/cache.py:307-337); `paged` moves the rows to a
+    paged pool's blocks."""
+    NBH, S, D = v.shape
+    pos = torch.arange(S, device=v.device)
+    prow = torch.arange(NBH, device=v.device)[:, None] * S + pos[None, :]
+    kint = plane_rows(ka.reshape(NBH * S, D), prow, pos, D)
+    u, vr, vsum, ysum, rows = fit_prompt(kint, ek.reshape(NBH, S), v, rank, lam, fit)
+    return TailState(rows=rows.to(torch.bfloat16).reshape(-1, D).contiguous(), vsum=vsum.reshape(-1, D).contiguous(),
+                     ysum=None if ysum is None else ysum.reshape(-1, rank).contiguous(), u=u, vr=vr)
+
+
+def paged(tail, page_table, page_size, n_kv_heads, blocks_per_group):
+    """A contiguous cache's tail (`tail_model`) for the same cache paged through
+    `page_table` `(requests, pages)`: block `j` of row group `(b, h)` moves to
+    the pool block of its first key (a page holds whole blocks)."""
+    if page_size % TAIL_BLOCK:
+        raise ValueError(f"page_size={page_size}: the tail keeps one row per {TAIL_BLOCK} keys, so a page must hold whole blocks")
+    B = page_table.shape[0]
+    pb = page_size // TAIL_BLOCK
+    j = torch.arange(blocks_per_group, device=page_table.device)
+    pg = page_table[:, (j // pb).clamp(max=page_table.shape[1] - 1)].long()                   # (B, blocks)
+    h = torch.arange(n_kv_heads, device=page_table.device)
+    dst = ((pg[:, None, :] * n_kv_heads + h[None, :, None]) * pb + (j % pb)[None, None, :]).reshape(-1)
+    n_pool = (int(page_table.max()) + 1) * n_kv_heads * pb
+
+    def move(x):
+        if x is None:
+            return None
+        out = x.new_zeros((n_pool, x.shape[-1]))
+        out[dst] = x.reshape(B * n_kv_heads * blocks_per_group, -1)
+        return out
+
+    return TailState(rows=move(tail.rows), vsum=move(tail.vsum), ysum=move(tail.ysum), u=tail.u, vr=tail.vr)

@@ -468,3 +468,47 @@ def test_a_captured_decode_replays_the_launch_it_was_made_from():
     got2 = cap()
     torch.cuda.synchronize()
     assert all(torch.equal(a, b) for a, b in zip(got2, want2)) and not torch.equal(want2[0], want[0])
+
+
+def test_a_contiguous_cache_is_its_paged_self():
+    """Without a page table the planes are `(NBH, S, D)`; the same keys paged give the same bits,
+    with a tail too (`tail_model`, then `paged`)."""
+    from fold_attention_b200.decode import prepare_fold_decode, tail_model
+    from fold_attention_b200.decode.tail import paged
+
+    D, H, HKV, S = 128, 8, 2, 1024
+    B = 3
+    k, v, cu = _kv([S] * B, HKV, D, 101)
+    c = _cache([S] * B, H, HKV, D, 101, shuffle=True, page_size=128, depth=8.0, tail=None)
+    c.write_prompt(k, v, cu, [S] * B)
+    q = torch.randn(B, H, D, device="cuda").bfloat16()
+    c._step(q, None, None)
+    NBH, G = B * HKV, H // HKV
+    # the same cache, contiguous: gather every row group's pool rows (a row's swizzle depends on its slot
+    # in the page, and page slots repeat every 128: position s sits at slot s % 128, the same 8-period)
+    rows = torch.stack([_rows(c, b, h, S)[0] for b in range(B) for h in range(HKV)])          # (NBH, S)
+    ka, kb, ek, va = c.ka[rows], c.kb[rows], c.ek[rows], c.va[rows]
+    z = (torch.ceil(c.z * 16) / 16).contiguous()
+    kw = dict(split=2, truncate=True, refine_k=8.0, refine_v=8.0, v_scale=1.0, weight_terms=2)
+    paged_run = prepare_fold_decode(c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, c.cut, vmean=c.vmean, page_table=c.page_table,
+                                    page_size=c.page_size, seq_lens=c.seq_lens, n_kv_heads=HKV, kernel="mma", **kw)
+    flat_run = prepare_fold_decode(c.qa, c.qb, c.eq, ka, kb, ek, va, z, c.cut, vmean=c.vmean, kernel="mma", **kw)
+    a, b_ = paged_run(), flat_run()
+    torch.cuda.synchronize()
+    assert all(torch.equal(x, y) for x, y in zip(a, b_))
+    # a shorter length per row group, and the tail
+    lens = torch.tensor([S, 700, 64, S, 900, 130], device="cuda", dtype=torch.int32)
+    t = tail_model(ka, ek, va, rank=16)
+    flat_t = prepare_fold_decode(c.qa, c.qb, c.eq, ka, kb, ek, va, z, c.cut, tail=t, seq_lens=lens, **kw)()
+    tp = paged(t, c.page_table, c.page_size, HKV, S // 64)
+    assert tp.rows.shape[0] == c.ka.shape[0] // 64
+    seq = lens.view(B, HKV)
+    # paged lengths are per request: compare the row groups whose length is their request's
+    c.seq_lens.copy_(seq[:, 0])
+    paged_t = prepare_fold_decode(c.qa, c.qb, c.eq, c.ka, c.kb, c.ek, c.va, z, c.cut, tail=tp, page_table=c.page_table,
+                                  page_size=c.page_size, seq_lens=c.seq_lens, n_kv_heads=HKV, **kw)()
+    torch.cuda.synchronize()
+    for bh in range(0, NBH, HKV):
+        assert torch.equal(flat_t[0][bh], paged_t[0][bh])
+    with pytest.raises(NotImplementedError, match="multiple of 64"):
+        prepare_fold_decode(c.qa, c.qb, c.eq, ka[:, :1000], kb[:, :1000], ek[:, :1000], va[:, :1000], z, c.cut, **kw)
