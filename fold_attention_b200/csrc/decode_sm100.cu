@@ -74,6 +74,10 @@ constexpr int NHELP = 4;
 constexpr int HSLOT = 528;       // a staging slot: Ka, Kb, Va, Vb rows of 128 bytes, the scale's word, the key's note
 constexpr int NBQ = 8;            // tiles of quarter flags (and their barrier) in flight: more than the key threads can lead by
 constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weights) in flight
+// 1: groups of exactly eight rows take a build of their own
+#ifndef FOLD_DEC_G8
+#define FOLD_DEC_G8 1
+#endif
 #ifndef FOLD_DEC_DENSE_MIN
 #define FOLD_DEC_DENSE_MIN 3
 #endif
@@ -312,7 +316,11 @@ __host__ __device__ constexpr uint32_t instr_desc(int c_fmt, int a_fmt, int b_fm
            (static_cast<uint32_t>(M >> 4) << 24);
 }
 
-template <bool TRUNC, bool V8>
+// GC: the group's rows when the kernel is compiled for them (8: the per-row guards fold away, and the key
+// threads' instruction stream is what the tile rate comes to: -6.6 % step time on an 8-bit V at depth 16),
+// 0: read from p. A build for groups of four measured no gain on a dense bf16 V, which is HBM-bound, and a
+// build of the tile body without the last tile's row guards lost 1 % to its size.
+template <bool TRUNC, bool V8, int GC = 0>
 __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params p, const __grid_constant__ CUtensorMap vmap,
                                                                    const __grid_constant__ CUtensorMap vbmap) {
     using L = Lay<V8>;
@@ -334,7 +342,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
     const int bh = p.order ? p.order[slot] : slot;
     const int breq = bh / p.hkv, hkv = bh % p.hkv;
     const int slen = p.seq_lens[breq];
-    const int G = p.G, PS = p.page_size;
+    const int G = GC ? GC : p.G, PS = p.page_size;
 
     int lo, hi, tstep, n_tiles;
     if (p.chunk_keys > 0) {
@@ -588,13 +596,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             const unsigned mv = __ballot_sync(0xffffffffu, refv);
             const unsigned mh = __ballot_sync(0xffffffffu, helped);
             if (t >= 2) CW(5, mbar_wait(bar(B_VEMPTY + (t - 2) % NV), ((t - 2) / NV) & 1, abort_flag, p.status));   // the weight buffer is free
+            // a row past the group and a key past the tile have s1 = -inf: weight 0 without a guard. A key's
+            // eight weights all go one way: to the dropped mass, to a helper, or into W and the denominator
             float w[8];
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                const float e = (g < G && valid) ? ex2f(s1[g]) : 0.f;
-                if (TRUNC) rM[g] += live ? 0.f : e;
-                w[g] = (live && !helped) ? e : 0.f;
-                rN[g] += w[g];
+            for (int g = 0; g < 8; ++g) w[g] = ex2f(s1[g]);
+            const bool plain = live && !helped;
+            if (TRUNC && !live) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) rM[g] += w[g];
+            }
+            if (plain) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) rN[g] += w[g];
             }
             uint32_t wb[8];
             if (V8) {
@@ -602,7 +616,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 // at a time: an E5M2 number is the high byte of an fp16, the differences are exact
 #pragma unroll
                 for (int g = 0; g < 8; g += 2) {
-                    __half2 r = __floats2half2_rn(w[g] * static_cast<float>(1 << W_BIAS), w[g + 1] * static_cast<float>(1 << W_BIAS));
+                    __half2 r = plain ? __floats2half2_rn(w[g] * static_cast<float>(1 << W_BIAS), w[g + 1] * static_cast<float>(1 << W_BIAS))
+                                      : __floats2half2_rn(0.f, 0.f);
 #pragma unroll
                     for (int term = 0; term < 4; ++term) {
                         uint16_t pk;
@@ -618,8 +633,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 // rows' hi, unit 1 their lo (decode/kernel.py:1181-1189)
 #pragma unroll
                 for (int g = 0; g < 8; g += 2) {
-                    const uint32_t hi = pack_bf16x2(w[g], w[g + 1]);
-                    const float r0 = w[g] - __uint_as_float(hi << 16), r1 = w[g + 1] - __uint_as_float(hi & 0xFFFF0000u);
+                    const float w0 = plain ? w[g] : 0.f, w1 = plain ? w[g + 1] : 0.f;
+                    const uint32_t hi = pack_bf16x2(w0, w1);
+                    const float r0 = w0 - __uint_as_float(hi << 16), r1 = w1 - __uint_as_float(hi & 0xFFFF0000u);
                     wb[g >> 1] = hi;
                     wb[4 + (g >> 1)] = pack_bf16x2(r0, r1);
                 }
@@ -675,7 +691,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 mbar_arrive(bar(B_QFULL + q));
             }
             __syncwarp();
-        }
+                }
 
         // ---- epilogue: the first group's thread k is channel k of the output ----
         if (lane == 0) CW_FLUSH(2);
@@ -1062,11 +1078,17 @@ bool make_v_map(CUtensorMap* m, const void* v, int row_bytes, int box_rows) {
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool TRUNC, bool V8>
-void launch(const dsm100::Params& p, const CUtensorMap& vmap, const CUtensorMap& vbmap, int ctas, cudaStream_t st) {
-    auto kern = dsm100::decode_sm100_kernel<TRUNC, V8>;
+template <bool TRUNC, bool V8, int GC>
+void launch_g(const dsm100::Params& p, const CUtensorMap& vmap, const CUtensorMap& vbmap, int ctas, cudaStream_t st) {
+    auto kern = dsm100::decode_sm100_kernel<TRUNC, V8, GC>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dsm100::Lay<V8>::SMEM_BYTES);
     kern<<<ctas, dsm100::NTHREADS, dsm100::Lay<V8>::SMEM_BYTES, st>>>(p, vmap, vbmap);
+}
+
+template <bool TRUNC, bool V8>
+void launch(const dsm100::Params& p, const CUtensorMap& vmap, const CUtensorMap& vbmap, int ctas, cudaStream_t st) {
+    if (p.G == 8 && FOLD_DEC_G8) launch_g<TRUNC, V8, 8>(p, vmap, vbmap, ctas, st);
+    else launch_g<TRUNC, V8, 0>(p, vmap, vbmap, ctas, st);
 }
 
 }  // namespace
