@@ -121,10 +121,11 @@ struct Lay {
     static constexpr int SM_KS = SM_VB + NB2E * 16384;           // NV x 128 bf16 scales
     static constexpr int SM_W = SM_KS + NV * 256;                // 2 x [2 units][128 keys][16 B] weights
     static constexpr int SM_W2 = SM_W + 2 * 4096;                // NB2 x the same, masked to the dense refine-V keys
-    static constexpr int SM_QM = SM_W2 + NB2E * 4096;            // QD x { refine-K, refine-V, helper } x 4 mask words
-    static constexpr int SM_QF = SM_QM + QD * 48;                // NBQ x 4 quarter flags
+    static constexpr int SM_QM = SM_W2 + NB2E * 4096;            // QD x { refine-K, refine-V, helper } x 4 mask words, the tile's first pool row
+    static constexpr int SM_QF = SM_QM + QD * 64;                // NBQ x 4 quarter flags
     static constexpr int SM_EQZ = SM_QF + NBQ * 16;              // eq[8], z[8] of the row group
-    static constexpr int SM_HST = (SM_EQZ + 64 + 15) / 16 * 16;  // NHELP x HD_KEYS staging slots
+    static constexpr int SM_ROW = SM_EQZ + 64;                   // NV x the first pool row of the tile in the V slot (the producer's page lookup, shared)
+    static constexpr int SM_HST = (SM_ROW + 8 * NV + 15) / 16 * 16;  // NHELP x HD_KEYS staging slots
     static constexpr int SM_BAR = SM_HST + NHELP * HD_KEYS * HSLOT;
     // after the last MMA the rings are dead and hold the final reduction: 256 x 16 row sums,
     // 8 x 16 partial and 16 full column sums, per-warp counters; and the helpers' sums
@@ -326,7 +327,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
     using L = Lay<V8>;
     constexpr int NA = L::NA, NV = L::NV, VBYTES = L::VBYTES, HD_KEYS = L::HD_KEYS, HPASS = L::HPASS;
     constexpr int SM_KA = L::SM_KA, SM_VA = L::SM_VA, SM_VB = L::SM_VB, SM_KS = L::SM_KS, SM_W = L::SM_W, SM_W2 = L::SM_W2,
-                  SM_QM = L::SM_QM, SM_QF = L::SM_QF, SM_EQZ = L::SM_EQZ, SM_HST = L::SM_HST, SM_BAR = L::SM_BAR,
+                  SM_QM = L::SM_QM, SM_QF = L::SM_QF, SM_EQZ = L::SM_EQZ, SM_ROW = L::SM_ROW, SM_HST = L::SM_HST, SM_BAR = L::SM_BAR,
                   SM_RED = L::SM_RED, SM_CNT = L::SM_CNT, SM_HOUT = L::SM_HOUT;
     constexpr int B_AFULL = L::B_AFULL, B_LFULL = L::B_LFULL, B_VFULL = L::B_VFULL, B_VEMPTY = L::B_VEMPTY,
                   B_WREADY = L::B_WREADY, B_QFULL = L::B_QFULL, B_QFREE = L::B_QFREE, B_BFULL = L::B_BFULL,
@@ -446,6 +447,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 const int s = t % NV;
                 if (t >= NV) CW(14, mbar_wait(bar(B_VEMPTY + s), ((t / NV) - 1) & 1, abort_flag, p.status));
                 const int64_t r = tile_row(lo + t * tstep);
+                reinterpret_cast<volatile int64_t*>(smem + SM_ROW)[s] = r;   // released by the arrive below, read after the wait on it
                 mbar_expect_tx(bar(B_VFULL + s), VBYTES + 256);
                 bulk_load(base + SM_KS + s * 256, p.ek + r, 256, bar(B_VFULL + s));
                 tma_load_2d(base + SM_VA + s * VBYTES, &vmap, 0, static_cast<int>(r), bar(B_VFULL + s));
@@ -559,6 +561,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             tmem_wait_ld();
             tc_fence_before();
             const bool valid = k < nrow;
+            const int64_t tile_row0 = reinterpret_cast<const volatile int64_t*>(smem + SM_ROW)[s];
             const float ek = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(smem + SM_KS + s * 256)[k]) * (1.0f / 256.0f);
             float s1[8];
             float top = -INFINITY;
@@ -588,7 +591,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             nref += refk ? 1 : 0;
             // a helper will want this key's second planes some tiles from now: start them towards L2
             if (refk || refv) {
-                const int64_t row = tile_row(tb) + k;
+                const int64_t row = tile_row0 + k;
                 if (refk) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kb + row * HD));
                 if (V8 && refv && !dense) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vb + row * HD));
             }
@@ -675,7 +678,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                     if (dense) {
                         mbar_expect_tx(bar(B_BFULL + bq), 4096);
                         tma_load_2d(base + SM_VB + b2 * 16384 + 4096 * (warp & 3), &vbmap, 0,
-                                    static_cast<int>(tile_row(tb)) + 32 * (warp & 3), bar(B_BFULL + bq));
+                                    static_cast<int>(tile_row0) + 32 * (warp & 3), bar(B_BFULL + bq));
                     } else {
                         mbar_arrive(bar(B_BFULL + bq));
                     }
@@ -685,9 +688,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             if (lane == 0) {
                 const int q = t % QD;
                 if (t >= QD) CW(7, mbar_wait(bar(B_QFREE + q), ((t / QD) - 1) & 1, abort_flag, p.status));
-                qm[q * 12 + (warp & 3)] = mk;
-                qm[q * 12 + 4 + (warp & 3)] = mv;
-                qm[q * 12 + 8 + (warp & 3)] = mh;
+                qm[q * 16 + (warp & 3)] = mk;
+                qm[q * 16 + 4 + (warp & 3)] = mv;
+                qm[q * 16 + 8 + (warp & 3)] = mh;
+                if ((warp & 3) == 0) *reinterpret_cast<int64_t*>(qm + q * 16 + 12) = tile_row0;   // the helper's page lookup, done
                 mbar_arrive(bar(B_QFULL + q));
             }
             __syncwarp();
@@ -848,13 +852,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    mK[i] = qm[q * 12 + i];
-                    mV[i] = qm[q * 12 + 4 + i];
-                    mH[i] = qm[q * 12 + 8 + i];
+                    mK[i] = qm[q * 16 + i];
+                    mV[i] = qm[q * 16 + 4 + i];
+                    mH[i] = qm[q * 16 + 8 + i];
                 }
+                row0 = *reinterpret_cast<const int64_t*>(qm + q * 16 + 12);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_QFREE + q));
-                row0 = tile_row(lo + it * tstep);
                 wi = 0;
                 rem = mH[0];
                 it += NHELP;
