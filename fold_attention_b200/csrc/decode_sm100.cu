@@ -31,15 +31,18 @@
 // refine-K gate (its logits need plane B of K), a key inside the refine-V gate in a
 // quarter with few of them, or a key whose weight could pass 2^8 (E5M2 ends at
 // 57344) gets weight zero in W and is handed, tile by tile through bit masks in
-// shared memory, to four helper warps. A helper
+// shared memory, to the helper warps (seven for an 8-bit V, four for a 16-bit one). A helper
 // recomputes the key's logits from both planes with dp4a, takes the weight in
 // fp32 and adds w (Va + Vb/8) into its own fp32 accumulators; tile t always goes
-// to helper t mod 4 and keys are taken in position order, so the sums are the
-// same on every run. The partial is the tensor-core sum plus the four helpers' sums.
+// to helper t mod NHELP and keys are taken in position order, so the sums are the
+// same on every run. The partial is the tensor-core sum plus the helpers' sums.
+// The helper count is what a CTA of a short request waits for: there a tenth or
+// more of the keys are inside the gates, the stream is done long before the
+// helpers, and the other warps idle until the helpers' last key.
 //
-// Warps: 0 and 2 producers (two 5-slot rings: K's plane A by bulk copy; plane A of V
+// Warps: 0 and 2 producers (a 4-slot and a 5-slot ring: K's plane A by bulk copy; plane A of V
 // by TMA with the 128-byte swizzle, with the key scales), 1 and 3 MMA issuers (logits; values. 256 TMEM
-// columns), 4-7 and 8-11 one thread per key of the even and of the odd tiles, 12-15
+// columns), 4-7 and 8-11 one thread per key of the even and of the odd tiles, 12 and up the
 // helpers. A K slot is free again as soon as its logits are out, a V slot when its
 // value product has retired. Every wait is bounded (about a second); on expiry
 // a status word is raised, nobody waits any more, TMEM is freed and the kernel returns.
@@ -70,7 +73,15 @@ constexpr int HD = 128;
 // tiles of helper masks in flight: how far a helper may fall behind the key threads (its tiles come
 // every NHELP-th, with a bursty number of keys each) before they have to wait for it
 constexpr int QD = FOLD_DEC_QD;
-constexpr int NHELP = 4;
+#ifndef FOLD_DEC_HPASS
+#define FOLD_DEC_HPASS 1
+#endif
+#ifndef FOLD_DEC_NHELP
+#define FOLD_DEC_NHELP 7
+#endif
+#ifndef FOLD_DEC_RING_K
+#define FOLD_DEC_RING_K 4
+#endif
 constexpr int HSLOT = 528;       // a staging slot: Ka, Kb, Va, Vb rows of 128 bytes, the scale's word, the key's note
 constexpr int NBQ = 8;            // tiles of quarter flags (and their barrier) in flight: more than the key threads can lead by
 constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weights) in flight
@@ -82,7 +93,6 @@ constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weig
 #define FOLD_DEC_DENSE_MIN 3
 #endif
 constexpr int DENSE_MIN = FOLD_DEC_DENSE_MIN;   // refine-V keys in a 32-key quarter from which the quarter's plane B is fetched whole
-constexpr int NTHREADS = 512;
 constexpr long long WAIT_CYCLES = 1ll << 31;
 // -DFOLD_DEC_COUNTERS: every role adds the cycles it spends in each of its waits, and in all, to
 // global counters fold_decode_counters returns (a measurement build: the waits cost two clock reads)
@@ -107,14 +117,16 @@ constexpr int SM_Q = 0;                               // [16 rows][128 B] int8, 
 constexpr int HOUT = (8 * 128 + 8) * 4;               // a helper's sums: [8 rows][128 channels], [8] floats
 template <bool V8>
 struct Lay {
-    static constexpr int NA = V8 ? FOLD_DEC_RING : 4;   // ring slots of K's plane A
+    static constexpr int NA = V8 ? FOLD_DEC_RING_K : 4; // ring slots of K's plane A (and logit buffers in TMEM)
+    static constexpr int NHELP = V8 ? FOLD_DEC_NHELP : 4;   // helper warps
+    static constexpr int NTHREADS = 384 + 32 * NHELP;
     static constexpr int NV = V8 ? FOLD_DEC_RING : 4;   // ring slots of V (plane A) and the key scales
     static constexpr int VBYTES = V8 ? 16384 : 32768; // a V slot: [128 keys][128 B], or two 64-channel boxes of that
     static constexpr int NB2E = V8 ? NB2 : 0;
     // keys whose rows a helper has in flight into its staging slots: four random 128-byte reads a key, each
     // about a microsecond away, so the depth of this queue is what the helpers' rate comes to
     static constexpr int HD_KEYS = V8 ? FOLD_DEC_HDK : 8;
-    static constexpr int HPASS = V8 ? 1 : 4;          // keys a helper takes in one pass, when that many are in flight
+    static constexpr int HPASS = V8 ? FOLD_DEC_HPASS : 4;          // keys a helper takes in one pass, when that many are in flight
     static constexpr int SM_KA = 2048;                           // NA x Ka [128 keys][128 B]
     static constexpr int SM_VA = SM_KA + NA * 16384;             // NV x V slots
     static constexpr int SM_VB = SM_VA + NV * VBYTES;            // NB2 x Vb [128 keys][128 B], fetched by quarters
@@ -322,10 +334,10 @@ __host__ __device__ constexpr uint32_t instr_desc(int c_fmt, int a_fmt, int b_fm
 // 0: read from p. A build for groups of four measured no gain on a dense bf16 V, which is HBM-bound, and a
 // build of the tile body without the last tile's row guards lost 1 % to its size.
 template <bool TRUNC, bool V8, int GC = 0>
-__global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params p, const __grid_constant__ CUtensorMap vmap,
+__global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(const Params p, const __grid_constant__ CUtensorMap vmap,
                                                                    const __grid_constant__ CUtensorMap vbmap) {
     using L = Lay<V8>;
-    constexpr int NA = L::NA, NV = L::NV, VBYTES = L::VBYTES, HD_KEYS = L::HD_KEYS, HPASS = L::HPASS;
+    constexpr int NA = L::NA, NHELP = L::NHELP, NV = L::NV, VBYTES = L::VBYTES, HD_KEYS = L::HD_KEYS, HPASS = L::HPASS;
     constexpr int SM_KA = L::SM_KA, SM_VA = L::SM_VA, SM_VB = L::SM_VB, SM_KS = L::SM_KS, SM_W = L::SM_W, SM_W2 = L::SM_W2,
                   SM_QM = L::SM_QM, SM_QF = L::SM_QF, SM_EQZ = L::SM_EQZ, SM_ROW = L::SM_ROW, SM_HST = L::SM_HST, SM_BAR = L::SM_BAR,
                   SM_RED = L::SM_RED, SM_CNT = L::SM_CNT, SM_HOUT = L::SM_HOUT;
@@ -717,7 +729,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
                 sCnt[3 * (warp - 4) + 2] = any_dense ? 1 : 0;
             }
         }
-        asm volatile("bar.sync 2, 384;" ::: "memory");   // both groups' sums, and the helpers'
+        asm volatile("bar.sync 2, %0;" ::"n"(256 + 32 * NHELP) : "memory");   // both groups' sums, and the helpers'
         if (wg == 0) {
             // column sums in a fixed order: 8 runs of 32 entries, then the 8 partial sums
             {
@@ -1034,7 +1046,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_sm100_kernel(const Params 
             *reinterpret_cast<float4*>(hout + g * 128 + 4 * lane) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
             if (lane == g) hout[8 * 128 + g] = hden;   // lane g sums row g's weights
         }
-        asm volatile("bar.sync 2, 384;" ::: "memory");
+        asm volatile("bar.sync 2, %0;" ::"n"(256 + 32 * NHELP) : "memory");
     }
     __syncthreads();
     if (warp == 1) {
@@ -1086,7 +1098,7 @@ template <bool TRUNC, bool V8, int GC>
 void launch_g(const dsm100::Params& p, const CUtensorMap& vmap, const CUtensorMap& vbmap, int ctas, cudaStream_t st) {
     auto kern = dsm100::decode_sm100_kernel<TRUNC, V8, GC>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dsm100::Lay<V8>::SMEM_BYTES);
-    kern<<<ctas, dsm100::NTHREADS, dsm100::Lay<V8>::SMEM_BYTES, st>>>(p, vmap, vbmap);
+    kern<<<ctas, dsm100::Lay<V8>::NTHREADS, dsm100::Lay<V8>::SMEM_BYTES, st>>>(p, vmap, vbmap);
 }
 
 template <bool TRUNC, bool V8>
