@@ -92,6 +92,14 @@ constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weig
 #ifndef FOLD_DEC_DENSE_MIN
 #define FOLD_DEC_DENSE_MIN 3
 #endif
+// refine-K keys in a 32-key quarter from which their threads refine them in place (33: never). Never for an
+// 8-bit V: that build runs 19 warps at 96 registers, and the call's presence alone costs its loop a quarter
+#ifndef FOLD_DEC_INL
+#define FOLD_DEC_INL 8
+#endif
+#ifndef FOLD_DEC_INL_V8
+#define FOLD_DEC_INL_V8 33
+#endif
 constexpr int DENSE_MIN = FOLD_DEC_DENSE_MIN;   // refine-V keys in a 32-key quarter from which the quarter's plane B is fetched whole
 constexpr long long WAIT_CYCLES = 1ll << 31;
 // -DFOLD_DEC_COUNTERS: every role adds the cycles it spends in each of its waits, and in all, to
@@ -333,6 +341,46 @@ __host__ __device__ constexpr uint32_t instr_desc(int c_fmt, int a_fmt, int b_fm
 // threads' instruction stream is what the tile rate comes to: -6.6 % step time on an 8-bit V at depth 16),
 // 0: read from p. A build for groups of four measured no gain on a dense bf16 V, which is HBM-bound, and a
 // build of the tile body without the last tile's row guards lost 1 % to its size.
+// A key's part of its eight logits that comes from K's plane B: kb . qa + kb . qb / 256 per query row, as
+// the helpers compute it. A call of its own, so that the registers it needs are found on the rare path
+// that takes it and not in the key threads' loop.
+struct Corr8 { float v[8]; };
+__device__ __noinline__ Corr8 refine_k(const uint4* kbrow, const uint8_t* q, int k, int G) {
+    int ca[8], cb[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) ca[g] = cb[g] = 0;
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+        uint4 kb4[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kb4[j] = __ldg(kbrow + 4 * half + j);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int lu = (4 * half + j) ^ (k & 7);   // the row's 16-byte units are stored swizzled by its slot
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                if (g < G) {
+                    const int off = g * 128 + ((lu ^ g) << 4);
+                    const uint4 qa4 = *reinterpret_cast<const uint4*>(q + off);
+                    const uint4 qb4 = *reinterpret_cast<const uint4*>(q + 1024 + off);
+                    ca[g] = __dp4a(static_cast<int>(kb4[j].x), static_cast<int>(qa4.x), ca[g]);
+                    ca[g] = __dp4a(static_cast<int>(kb4[j].y), static_cast<int>(qa4.y), ca[g]);
+                    ca[g] = __dp4a(static_cast<int>(kb4[j].z), static_cast<int>(qa4.z), ca[g]);
+                    ca[g] = __dp4a(static_cast<int>(kb4[j].w), static_cast<int>(qa4.w), ca[g]);
+                    cb[g] = __dp4a(static_cast<int>(kb4[j].x), static_cast<int>(qb4.x), cb[g]);
+                    cb[g] = __dp4a(static_cast<int>(kb4[j].y), static_cast<int>(qb4.y), cb[g]);
+                    cb[g] = __dp4a(static_cast<int>(kb4[j].z), static_cast<int>(qb4.z), cb[g]);
+                    cb[g] = __dp4a(static_cast<int>(kb4[j].w), static_cast<int>(qb4.w), cb[g]);
+                }
+            }
+        }
+    }
+    Corr8 x;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) x.v[g] = static_cast<float>(ca[g]) + static_cast<float>(cb[g]) * (1.0f / 256.0f);
+    return x;
+}
+
 template <bool TRUNC, bool V8, int GC = 0>
 __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(const Params p, const __grid_constant__ CUtensorMap vmap,
                                                                    const __grid_constant__ CUtensorMap vbmap) {
@@ -590,21 +638,43 @@ __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(cons
             }
             live = live && valid;
             const bool refk = live && top >= -rk;
+            // A quarter (this warp's 32 keys) with enough refine-K keys refines them in place: each such
+            // key's thread reads its own row of K's plane B and adds the second plane's part to its eight
+            // logits (the helper's arithmetic, on lanes that would wait for the helper otherwise); the
+            // key then stays on the tensor-core path. Which keys do depends on the logits alone.
+            bool refined_here = false;
+            constexpr int INL_MIN = V8 ? FOLD_DEC_INL_V8 : FOLD_DEC_INL;
+            if (INL_MIN <= 32 && nrow == TK && __popc(__ballot_sync(0xffffffffu, refk)) >= INL_MIN) {
+                if (refk) {
+                    const Corr8 x = refine_k(reinterpret_cast<const uint4*>(p.kb + (tile_row0 + k) * HD), smem + SM_Q, k, G);
+                    top = -INFINITY;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        if (g < G) {
+                            s1[g] = s1[g] + x.v[g] * (eqr[g] * ek);
+                            top = fmaxf(top, s1[g]);
+                        }
+                    }
+                    refined_here = true;
+                }
+                __syncwarp();
+            }
+            const bool needk = refk && !refined_here;   // still needs plane B of K: a helper's
             // a 16-bit V has no second plane, and bf16 weights no range to run out of
             const bool refv = V8 && live && top >= -rv;
             const bool big = V8 && live && top >= BIG_TOP;
-            // a quarter (this warp's 32 keys) with enough refine-V keys fetches its plane B whole;
+            // a quarter with enough refine-V keys fetches its plane B whole;
             // the last, partial tile does not (rows past the range are not V's to read)
-            const bool dv = refv && !refk && !big;
+            const bool dv = refv && !needk && !big;
             const bool dense = nrow == TK && __popc(__ballot_sync(0xffffffffu, dv)) >= DENSE_MIN;
             any_dense = any_dense || dense;
-            const bool helped = refk || big || (refv && !dense);
+            const bool helped = needk || big || (refv && !dense);
             nlive += live ? 1 : 0;
             nref += refk ? 1 : 0;
             // a helper will want this key's second planes some tiles from now: start them towards L2
-            if (refk || refv) {
+            if (needk || refv) {
                 const int64_t row = tile_row0 + k;
-                if (refk) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kb + row * HD));
+                if (needk) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kb + row * HD));
                 if (V8 && refv && !dense) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vb + row * HD));
             }
             const unsigned mk = __ballot_sync(0xffffffffu, refk);
