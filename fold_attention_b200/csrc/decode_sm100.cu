@@ -76,6 +76,12 @@ constexpr int QD = FOLD_DEC_QD;
 #ifndef FOLD_DEC_HPASS
 #define FOLD_DEC_HPASS 1
 #endif
+// requests up to this many keys stream both planes of K: their gates are the wide ones (a tenth of the keys
+// inside refine-K), and the second plane's logits from the tensor core cost less than the helpers (0: never)
+#ifndef FOLD_DEC_BOTHK
+#define FOLD_DEC_BOTHK 8192
+#endif
+constexpr int BOTHK_LEN = FOLD_DEC_BOTHK;
 #ifndef FOLD_DEC_NHELP
 #define FOLD_DEC_NHELP 7
 #endif
@@ -154,6 +160,7 @@ struct Lay {
     static constexpr int SM_HOUT = SM_VA;
     static constexpr int SMEM_BYTES = SM_BAR + (QD > 8 ? 1024 : 512);
     static_assert(SMEM_BYTES <= 232448, "over the 227 KB a CTA may hold");
+    static_assert(NA == 4, "four logit buffers of 32 TMEM columns; with both planes of K the ring is two pairs of slots");
     static_assert(NA * 16384 >= SM_CNT - SM_KA + 1024 && NV * VBYTES >= NHELP * HOUT, "the final reduction fits the dead rings");
     enum {
         B_AFULL = 0,                 // [NA] K's plane A has landed
@@ -170,7 +177,7 @@ struct Lay {
     };
 };
 
-constexpr uint32_t T_L = 0, T_ACC = 96, T_ACC2 = 128;   // TMEM columns: NA logit buffers of 16, then the accumulators
+constexpr uint32_t T_L = 0, T_ACC = 128, T_ACC2 = 160;   // TMEM columns: 4 logit buffers of 16 + 16 (plane A of K, plane B), then the accumulators
 
 struct Params {
     const int8_t* qa; const int8_t* qb; const float* eq;
@@ -381,9 +388,12 @@ __device__ __noinline__ Corr8 refine_k(const uint4* kbrow, const uint8_t* q, int
     return x;
 }
 
-template <bool TRUNC, bool V8, int GC = 0>
-__global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(const Params p, const __grid_constant__ CUtensorMap vmap,
-                                                                   const __grid_constant__ CUtensorMap vbmap) {
+// The kernel's body, built twice: for requests that stream plane A of K alone, and (BOTHK) for short
+// requests, which stream both planes. Two bodies and a branch at the kernel's top, because the first
+// one's loop, at the 96 registers its 19 warps leave, loses a quarter of its speed to the second's code
+// when the two share a body.
+template <bool TRUNC, bool V8, int GC, bool BOTHK>
+__device__ __forceinline__ void decode_sm100_body(const Params& p, const CUtensorMap* vmap_p, const CUtensorMap* vbmap_p) {
     using L = Lay<V8>;
     constexpr int NA = L::NA, NHELP = L::NHELP, NV = L::NV, VBYTES = L::VBYTES, HD_KEYS = L::HD_KEYS, HPASS = L::HPASS;
     constexpr int SM_KA = L::SM_KA, SM_VA = L::SM_VA, SM_VB = L::SM_VB, SM_KS = L::SM_KS, SM_W = L::SM_W, SM_W2 = L::SM_W2,
@@ -429,6 +439,10 @@ __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(cons
         rk = slen > static_cast<int>(p.band_e1) ? p.rk2 : (slen > static_cast<int>(p.band_e0) ? p.rk1 : p.rk);
         rv = slen > static_cast<int>(p.band_e1) ? p.rv2 : (slen > static_cast<int>(p.band_e0) ? p.rv1 : p.rv);
     }
+
+    // both planes of K for a short request: a tile takes a pair of ring slots (plane A, plane B), its
+    // logits 32 TMEM columns; the refine-K keys' second-plane part is read from there
+    constexpr bool bothk = BOTHK;
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -491,11 +505,21 @@ __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(cons
             CW_DECL;
             CW_ADD(0, 1);
             for (int t = 0; t < n_tiles; ++t) {
-                const int s = t % NA;
-                if (t >= NA) CW(12, mbar_wait(bar(B_LFULL + s), ((t / NA) - 1) & 1, abort_flag, p.status));
                 const int64_t r = tile_row(lo + t * tstep);
-                mbar_expect_tx(bar(B_AFULL + s), 16384);
-                bulk_load(base + SM_KA + s * 16384, p.ka + r * HD, 16384, bar(B_AFULL + s));
+                if (bothk) {
+                    // the pair was tile t-2's, free once that tile's logits are out (tile t+2, which shares
+                    // the barrier, cannot have run: its K is not loaded yet)
+                    const int s = 2 * (t & 1);
+                    if (t >= 2) CW(12, mbar_wait(bar(B_LFULL + (t - 2) % NA), ((t - 2) / NA) & 1, abort_flag, p.status));
+                    mbar_expect_tx(bar(B_AFULL + s), 32768);
+                    bulk_load(base + SM_KA + s * 16384, p.ka + r * HD, 16384, bar(B_AFULL + s));
+                    bulk_load(base + SM_KA + (s + 1) * 16384, p.kb + r * HD, 16384, bar(B_AFULL + s));
+                } else {
+                    const int s = t % NA;
+                    if (t >= NA) CW(12, mbar_wait(bar(B_LFULL + s), ((t / NA) - 1) & 1, abort_flag, p.status));
+                    mbar_expect_tx(bar(B_AFULL + s), 16384);
+                    bulk_load(base + SM_KA + s * 16384, p.ka + r * HD, 16384, bar(B_AFULL + s));
+                }
             }
             CW_FLUSH(13);
         }
@@ -510,8 +534,8 @@ __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(cons
                 reinterpret_cast<volatile int64_t*>(smem + SM_ROW)[s] = r;   // released by the arrive below, read after the wait on it
                 mbar_expect_tx(bar(B_VFULL + s), VBYTES + 256);
                 bulk_load(base + SM_KS + s * 256, p.ek + r, 256, bar(B_VFULL + s));
-                tma_load_2d(base + SM_VA + s * VBYTES, &vmap, 0, static_cast<int>(r), bar(B_VFULL + s));
-                if (!V8) tma_load_2d(base + SM_VA + s * VBYTES + 16384, &vmap, 64, static_cast<int>(r), bar(B_VFULL + s));
+                tma_load_2d(base + SM_VA + s * VBYTES, vmap_p, 0, static_cast<int>(r), bar(B_VFULL + s));
+                if (!V8) tma_load_2d(base + SM_VA + s * VBYTES + 16384, vmap_p, 64, static_cast<int>(r), bar(B_VFULL + s));
             }
             CW_FLUSH(15);
         }
@@ -524,14 +548,23 @@ __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(cons
             const uint64_t dka = smem_desc(base + SM_KA, 16, 1024, 2);
             CW_DECL;
             for (int t = 0; t < n_tiles; ++t) {
-                const int s = t % NA;
-                // the TMEM slot was tile t-NA's: its value MMAs retired, so its weights were done and
+                const int lb = t % NA;   // the logit buffer
+                // the TMEM buffer was tile t-NA's: its value MMAs retired, so its weights were done and
                 // its logits read
                 if (t >= NA) CW(16, mbar_wait(bar(B_VEMPTY + (t - NA) % NV), ((t - NA) / NV) & 1, abort_flag, p.status));
-                CW(17, mbar_wait(bar(B_AFULL + s), (t / NA) & 1, abort_flag, p.status));
-                tc_fence_after();
-                mma4_i8<2, 2>(tmem + T_L + 16 * s, dka + s * 1024, dq, ID_L, 0u);   // 32 bytes per K step
-                tc_commit(bar(B_LFULL + s));
+                if (bothk) {
+                    const int s = 2 * (t & 1);
+                    CW(17, mbar_wait(bar(B_AFULL + s), (t >> 1) & 1, abort_flag, p.status));
+                    tc_fence_after();
+                    mma4_i8<2, 2>(tmem + T_L + 32 * lb, dka + s * 1024, dq, ID_L, 0u);
+                    mma4_i8<2, 2>(tmem + T_L + 32 * lb + 16, dka + (s + 1) * 1024, dq, ID_L, 0u);
+                } else {
+                    const int s = t % NA;
+                    CW(17, mbar_wait(bar(B_AFULL + s), (t / NA) & 1, abort_flag, p.status));
+                    tc_fence_after();
+                    mma4_i8<2, 2>(tmem + T_L + 32 * lb, dka + s * 1024, dq, ID_L, 0u);   // 32 bytes per K step
+                }
+                tc_commit(bar(B_LFULL + lb));
             }
             CW_FLUSH(18);
         }
@@ -617,7 +650,7 @@ __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(cons
             CW(4, mbar_wait(bar(B_LFULL + t % NA), (t / NA) & 1, abort_flag, p.status));
             tc_fence_after();
             uint32_t c[16];
-            tmem_ld16(tmem + lane_addr + T_L + 16 * (t % NA), c);
+            tmem_ld16(tmem + lane_addr + T_L + 32 * (t % NA), c);
             tmem_wait_ld();
             tc_fence_before();
             const bool valid = k < nrow;
@@ -643,8 +676,27 @@ __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(cons
             // logits (the helper's arithmetic, on lanes that would wait for the helper otherwise); the
             // key then stays on the tensor-core path. Which keys do depends on the logits alone.
             bool refined_here = false;
+            if (bothk && __any_sync(0xffffffffu, refk)) {
+                // the second plane's logits are in the buffer's other 16 columns: kb . qa and kb . qb per row
+                tc_fence_after();
+                tmem_ld16(tmem + lane_addr + T_L + 32 * (t % NA) + 16, c);
+                tmem_wait_ld();
+                tc_fence_before();
+                if (refk) {
+                    top = -INFINITY;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        if (g < G) {
+                            const float x = static_cast<float>(static_cast<int>(c[g])) + static_cast<float>(static_cast<int>(c[8 + g])) * (1.0f / 256.0f);
+                            s1[g] = s1[g] + x * (eqr[g] * ek);
+                            top = fmaxf(top, s1[g]);
+                        }
+                    }
+                    refined_here = true;
+                }
+            }
             constexpr int INL_MIN = V8 ? FOLD_DEC_INL_V8 : FOLD_DEC_INL;
-            if (INL_MIN <= 32 && nrow == TK && __popc(__ballot_sync(0xffffffffu, refk)) >= INL_MIN) {
+            if (INL_MIN <= 32 && !bothk && nrow == TK && __popc(__ballot_sync(0xffffffffu, refk)) >= INL_MIN) {
                 if (refk) {
                     const Corr8 x = refine_k(reinterpret_cast<const uint4*>(p.kb + (tile_row0 + k) * HD), smem + SM_Q, k, G);
                     top = -INFINITY;
@@ -759,7 +811,7 @@ __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(cons
                     reinterpret_cast<volatile int*>(smem + SM_QF + bq * 16)[warp & 3] = dense ? 1 : 0;
                     if (dense) {
                         mbar_expect_tx(bar(B_BFULL + bq), 4096);
-                        tma_load_2d(base + SM_VB + b2 * 16384 + 4096 * (warp & 3), &vbmap, 0,
+                        tma_load_2d(base + SM_VB + b2 * 16384 + 4096 * (warp & 3), vbmap_p, 0,
                                     static_cast<int>(tile_row0) + 32 * (warp & 3), bar(B_BFULL + bq));
                     } else {
                         mbar_arrive(bar(B_BFULL + bq));
@@ -1122,6 +1174,15 @@ __global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(cons
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
     }
+}
+
+template <bool TRUNC, bool V8, int GC = 0>
+__global__ void __launch_bounds__(Lay<V8>::NTHREADS, 1) decode_sm100_kernel(const Params p, const __grid_constant__ CUtensorMap vmap,
+                                                                   const __grid_constant__ CUtensorMap vbmap) {
+    const int slot = blockIdx.x / p.split;
+    const int bh = p.order ? p.order[slot] : slot;
+    if (BOTHK_LEN > 0 && p.seq_lens[bh / p.hkv] <= BOTHK_LEN) decode_sm100_body<TRUNC, V8, GC, true>(p, &vmap, &vbmap);
+    else decode_sm100_body<TRUNC, V8, GC, false>(p, &vmap, &vbmap);
 }
 
 }  // namespace dsm100
