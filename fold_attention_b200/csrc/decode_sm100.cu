@@ -39,6 +39,10 @@
 // The helper count is what a CTA of a short request waits for: there a tenth or
 // more of the keys are inside the gates, the stream is done long before the
 // helpers, and the other warps idle until the helpers' last key.
+// So a request of up to 8192 keys streams both planes of K (a pair of ring slots a
+// tile, 32 TMEM columns of logits): its refine-K keys read their second-plane
+// logits from TMEM and stay on the tensor-core path. That is a second build of the
+// kernel's body, chosen at the kernel's top by the request's length alone.
 //
 // Warps: 0 and 2 producers (a 4-slot and a 5-slot ring: K's plane A by bulk copy; plane A of V
 // by TMA with the 128-byte swizzle, with the key scales), 1 and 3 MMA issuers (logits; values. 256 TMEM
