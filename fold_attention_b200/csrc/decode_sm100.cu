@@ -64,7 +64,7 @@ namespace fold {
 namespace dsm100 {
 
 #ifndef FOLD_DEC_RING
-#define FOLD_DEC_RING 5
+#define FOLD_DEC_RING 4
 #endif
 #ifndef FOLD_DEC_HDK
 #define FOLD_DEC_HDK 4
@@ -94,7 +94,12 @@ constexpr int BOTHK_LEN = FOLD_DEC_BOTHK;
 #endif
 constexpr int HSLOT = 528;       // a staging slot: Ka, Kb, Va, Vb rows of 128 bytes, the scale's word, the key's note
 constexpr int NBQ = 8;            // tiles of quarter flags (and their barrier) in flight: more than the key threads can lead by
-constexpr int NB2 = 2;           // tiles of plane B of V (and their masked weights) in flight
+#ifndef FOLD_DEC_NB2
+#define FOLD_DEC_NB2 3
+#endif
+// tiles of plane B of V (and their masked weights) in flight. A key group takes every other tile; with two
+// buffers it would need its own last tile's buffer back, whose quarters are a DRAM latency away
+constexpr int NB2 = FOLD_DEC_NB2;
 // 1: groups of exactly eight rows take a build of their own
 #ifndef FOLD_DEC_G8
 #define FOLD_DEC_G8 1
