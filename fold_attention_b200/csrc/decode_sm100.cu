@@ -47,7 +47,7 @@
 // Warps: 0 and 2 producers (a 4-slot and a 5-slot ring: K's plane A by bulk copy; plane A of V
 // by TMA with the 128-byte swizzle, with the key scales), 1 and 3 MMA issuers (logits; values. 256 TMEM
 // columns), 4-7 and 8-11 one thread per key of the even and of the odd tiles, 12 and up the
-// helpers. A K slot is free again as soon as its logits are out, a V slot when its
+// helpers, and for an 8-bit V one more warp that issues plane B's MMAs as its quarters land. A K slot is free again as soon as its logits are out, a V slot when its
 // value product has retired. Every wait is bounded (about a second); on expiry
 // a status word is raised, nobody waits any more, TMEM is freed and the kernel returns.
 // Arithmetic contract: src/fold_attention/decode/kernel.py:774-870, 1032-1201,
@@ -142,7 +142,7 @@ template <bool V8>
 struct Lay {
     static constexpr int NA = V8 ? FOLD_DEC_RING_K : 4; // ring slots of K's plane A (and logit buffers in TMEM)
     static constexpr int NHELP = V8 ? FOLD_DEC_NHELP : 4;   // helper warps
-    static constexpr int NTHREADS = 384 + 32 * NHELP;
+    static constexpr int NTHREADS = 384 + 32 * NHELP + (V8 ? 32 : 0);   // an 8-bit V: one more warp issues plane B's MMAs
     static constexpr int NV = V8 ? FOLD_DEC_RING : 4;   // ring slots of V (plane A) and the key scales
     static constexpr int VBYTES = V8 ? 16384 : 32768; // a V slot: [128 keys][128 B], or two 64-channel boxes of that
     static constexpr int NB2E = V8 ? NB2 : 0;
@@ -470,7 +470,7 @@ __device__ __forceinline__ void decode_sm100_body(const Params& p, const CUtenso
         }
         for (int i = 0; i < NBQ; ++i) mbar_init(bar(B_BFULL + i), 4);
         for (int i = 0; i < NB2; ++i) mbar_init(bar(B_BFREE + i), 1);
-        mbar_init(bar(B_ALLDONE), 1);
+        mbar_init(bar(B_ALLDONE), V8 ? 2 : 1);   // the value MMA thread's commit, and the plane-B thread's
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // Q planes -> shared, 16 rows of 128 bytes with the 128-byte swizzle; rows
@@ -584,35 +584,11 @@ __device__ __forceinline__ void decode_sm100_body(const Params& p, const CUtenso
             // both operands MN-major
             constexpr uint32_t ID_V = V8 ? instr_desc(1, 0, 1, 1, 1, 32, 128) : instr_desc(1, 1, 1, 1, 1, 16, 128);
             const uint64_t dva = smem_desc(base + SM_VA, 16384, 1024, 2);
-            const uint64_t dvb = smem_desc(base + SM_VB, 16384, 1024, 2);
             const uint64_t dw = smem_desc(base + SM_W, 128, 2048, 0);
-            const uint64_t dw2 = smem_desc(base + SM_W2, 128, 2048, 0);
-            bool acc2_started = false;
             CW_DECL;
-            // iteration j: plane B of V of tile j-2 (its quarters were asked for two tiles ago), then
-            // the value product of tile j. The order matters: a key thread of tile t waits for the
-            // value MMAs of t-2 and then, by parity, for the plane-B buffer of t-2; the commit for
-            // t-4's buffer must be the older of the two or that parity test passes a phase early
-            for (int j = 0; j < n_tiles + 2; ++j) {
-                if (V8 && j >= 2) {
-                    const int t = j - 2, b2 = t % NB2;
-                    CW(19, mbar_wait(bar(B_BFULL + t % NBQ), (t / NBQ) & 1, abort_flag, p.status));
-                    const volatile uint32_t* qfp = reinterpret_cast<const volatile uint32_t*>(smem + SM_QF + (t % NBQ) * 16);
-                    const uint32_t f[4] = {qfp[0], qfp[1], qfp[2], qfp[3]};
-                    if (f[0] | f[1] | f[2] | f[3]) {
-                        tc_fence_after();
-#pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) {
-                            if (f[ks]) {
-                                mma_f8(tmem + T_ACC2, dvb + b2 * 1024 + ks * 256, dw2 + b2 * 256 + ks * 32, ID_V, acc2_started);
-                                acc2_started = true;
-                            }
-                        }
-                    }
-                    tc_commit(bar(B_BFREE + b2));
-                }
-                if (j < n_tiles) {
-                    const int t = j, s = t % NV;
+            for (int t = 0; t < n_tiles; ++t) {
+                {
+                    const int s = t % NV;
                     CW(20, mbar_wait(bar(B_VFULL + s), (t / NV) & 1, abort_flag, p.status));
                     CW(21, mbar_wait(bar(B_WREADY + (t & 1)), (t >> 1) & 1, abort_flag, p.status));
                     tc_fence_after();
@@ -807,9 +783,13 @@ __device__ __forceinline__ void decode_sm100_body(const Params& p, const CUtenso
             // logits); only the data buffers, two tiles deep, are waited for, and only when used
             if (V8) {
                 const int b2 = t % NB2, bq = t % NBQ;
+                // Every tile waits for the plane-B thread to be done with tile t-NB2, dense or not: that is
+                // what bounds its lag (the flags' ring is deeper), and what keeps the parity test honest:
+                // this group waited for t-NB2+1's buffer a tile ago, the thread commits in order, so
+                // t-2*NB2's phase is complete and the test cannot pass a phase early
+                if (lane == 0 && t >= NB2) CW(6, mbar_wait(bar(B_BFREE + b2), ((t / NB2) - 1) & 1, abort_flag, p.status));
+                __syncwarp();
                 if (dense) {
-                    if (lane == 0 && t >= NB2) CW(6, mbar_wait(bar(B_BFREE + b2), ((t / NB2) - 1) & 1, abort_flag, p.status));
-                    __syncwarp();
                     uint8_t* w2dst = smem + SM_W2 + b2 * 4096 + k * 16;
                     *reinterpret_cast<uint4*>(w2dst) = dv ? make_uint4(wb[0], wb[1], wb[2], wb[3]) : make_uint4(0, 0, 0, 0);
                     *reinterpret_cast<uint4*>(w2dst + 2048) = dv ? make_uint4(wb[4], wb[5], wb[6], wb[7]) : make_uint4(0, 0, 0, 0);
@@ -927,7 +907,37 @@ __device__ __forceinline__ void decode_sm100_body(const Params& p, const CUtenso
                 p.cnt_part[pix * 2 + 1] = bcount;
             }
         }
-    } else if (warp >= 12) {
+    } else if (V8 && warp == 12 + NHELP) {
+        // ================= MMA issuer: plane B of V, tile by tile as its quarters land =================
+        // A thread of its own: behind the value products in one thread, a quarter still on its way held
+        // the next tile's value product back, and with it the key threads' weight buffer.
+        if (lane == 0) {
+            constexpr uint32_t ID_V = instr_desc(1, 0, 1, 1, 1, 32, 128);
+            const uint64_t dvb = smem_desc(base + SM_VB, 16384, 1024, 2);
+            const uint64_t dw2 = smem_desc(base + SM_W2, 128, 2048, 0);
+            bool acc2_started = false;
+            CW_DECL;
+            for (int t = 0; t < n_tiles; ++t) {
+                const int b2 = t % NB2;
+                CW(19, mbar_wait(bar(B_BFULL + t % NBQ), (t / NBQ) & 1, abort_flag, p.status));
+                const volatile uint32_t* qfp = reinterpret_cast<const volatile uint32_t*>(smem + SM_QF + (t % NBQ) * 16);
+                const uint32_t f[4] = {qfp[0], qfp[1], qfp[2], qfp[3]};
+                if (f[0] | f[1] | f[2] | f[3]) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        if (f[ks]) {
+                            mma_f8(tmem + T_ACC2, dvb + b2 * 1024 + ks * 256, dw2 + b2 * 256 + ks * 32, ID_V, acc2_started);
+                            acc2_started = true;
+                        }
+                    }
+                }
+                tc_commit(bar(B_BFREE + b2));
+            }
+            tc_commit(bar(B_ALLDONE));
+            CW_FLUSH(29);
+        }
+    } else if (warp >= 12 && warp < 12 + NHELP) {
         // ================= helpers: the keys that need both planes or an fp32 weight =================
         // The whole warp works on one key. Its four rows (both planes of K and of V) come into a
         // staging slot with one 16-byte copy per lane, four keys ahead of their use. For the
