@@ -58,9 +58,10 @@ class FoldKVCache:
     (head_dim 128, pages and chunks of a multiple of 128 keys), which
     streams K's first plane and V whole and is the faster the longer the
     contexts are; "auto" takes "sm100" where it applies, for
-    the requests of 12288 keys or more (shorter requests keep too many keys
-    inside the refine gates, and those leave its tensor-core path): the batch
-    goes where most of its keys would. With `mix_kernels` set (and a `chunk`)
+    the requests of 2048 keys or more (measured faster from 1024 keys up, on
+    an 8-bit and on a 16-bit V, since requests of up to 8192 keys stream both
+    planes of K there; a CTA's fixed cost is what very short requests would
+    pay): the batch goes where most of its keys would. With `mix_kernels` set (and a `chunk`)
     the short requests of a batch go to "mma" and the long ones to "sm100" in
     the same step; on one B200 that measured slower up to 128 requests (the
     short requests' launch cannot fill the GPU by itself), so it is off.
@@ -77,7 +78,7 @@ class FoldKVCache:
     outside `[0.5, 2^60]` (`2^100` on a bf16 V) of their mass.
     """
 
-    SM100_MIN_KEYS = 12288   # requests shorter than this stay on the warp-level kernel under kernel="auto"
+    SM100_MIN_KEYS = 2048    # requests shorter than this stay on the warp-level kernel under kernel="auto"
 
     def __init__(
         self,

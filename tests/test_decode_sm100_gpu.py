@@ -142,7 +142,7 @@ def test_a_batch_splits_between_the_kernels_by_request_length():
     both; every request's output is the bits its own kernel gives it alone."""
     from fold_attention_b200 import FoldKVCache
 
-    lens = [13000, 500, 12288, 4000]
+    lens = [13000, 500, 12288, 1500]
     B, H, HKV, D = len(lens), 16, 2, 128
     q, k, v, cu = _layer(B, H, HKV, D, lens, seed=11)
     kw = dict(ps=128, v8=True, depth=16.0, chunk=2048, v_scale=0.03125)
@@ -162,10 +162,10 @@ def test_a_batch_splits_between_the_kernels_by_request_length():
         assert torch.equal(o_one[0], o[b]), b
         assert torch.equal(one.counts, both.counts[b * HKV:(b + 1) * HKV])
     # a batch of short requests only: the warp-level kernel takes all of it
-    short = _cache(2, H, HKV, D, [500, 4000], kernel="auto", **kw)
+    short = _cache(2, H, HKV, D, [500, 1500], kernel="auto", **kw)
     short.mix_kernels = True
-    short.write_prompt(torch.cat([k[13000:13500], k[-4000:]]), torch.cat([v[13000:13500], v[-4000:]]),
-                       torch.tensor([0, 500, 4500], device="cuda", dtype=torch.int32), [500, 4000])
+    short.write_prompt(torch.cat([k[13000:13500], k[-1500:]]), torch.cat([v[13000:13500], v[-1500:]]),
+                       torch.tensor([0, 500, 2000], device="cuda", dtype=torch.int32), [500, 1500])
     short.attend(q[[1, 3]])
     assert next(iter(short._launches.values())).kernel == "mma"
 
