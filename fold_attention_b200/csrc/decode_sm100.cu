@@ -700,10 +700,10 @@ __device__ __forceinline__ void decode_sm100_body(const Params& p, const CUtenso
             // a 16-bit V has no second plane, and bf16 weights no range to run out of
             const bool refv = V8 && live && top >= -rv;
             const bool big = V8 && live && top >= BIG_TOP;
-            // a quarter with enough refine-V keys fetches its plane B whole;
-            // the last, partial tile does not (rows past the range are not V's to read)
+            // a quarter with enough refine-V keys fetches its plane B whole; so does one of the last,
+            // partial tile (its rows past the range lie in the tile's page; the plane-B thread clears them)
             const bool dv = refv && !needk && !big;
-            const bool dense = nrow == TK && __popc(__ballot_sync(0xffffffffu, dv)) >= DENSE_MIN;
+            const bool dense = __popc(__ballot_sync(0xffffffffu, dv)) >= DENSE_MIN;
             any_dense = any_dense || dense;
             const bool helped = needk || big || (refv && !dense);
             nlive += live ? 1 : 0;
@@ -911,31 +911,48 @@ __device__ __forceinline__ void decode_sm100_body(const Params& p, const CUtenso
         // ================= MMA issuer: plane B of V, tile by tile as its quarters land =================
         // A thread of its own: behind the value products in one thread, a quarter still on its way held
         // the next tile's value product back, and with it the key threads' weight buffer.
-        if (lane == 0) {
+        // Lane 0 waits and issues; the whole warp clears the rows past the range in the last, partial
+        // tile's buffer once they have landed (what the pool holds there may read as an E4M3 NaN, and a
+        // NaN times a zero weight is a NaN): without it that tile's refine-V keys, a third of a short
+        // request's last tile, would all be one helper's, after everything else is done.
+        {
             constexpr uint32_t ID_V = instr_desc(1, 0, 1, 1, 1, 32, 128);
             const uint64_t dvb = smem_desc(base + SM_VB, 16384, 1024, 2);
             const uint64_t dw2 = smem_desc(base + SM_W2, 128, 2048, 0);
             bool acc2_started = false;
+            const int nrow_last = n_tiles > 0 ? min(TK, hi - (lo + (n_tiles - 1) * tstep)) : TK;
             CW_DECL;
             for (int t = 0; t < n_tiles; ++t) {
                 const int b2 = t % NB2;
-                CW(19, mbar_wait(bar(B_BFULL + t % NBQ), (t / NBQ) & 1, abort_flag, p.status));
+                if (lane == 0) CW(19, mbar_wait(bar(B_BFULL + t % NBQ), (t / NBQ) & 1, abort_flag, p.status));
+                __syncwarp();
                 const volatile uint32_t* qfp = reinterpret_cast<const volatile uint32_t*>(smem + SM_QF + (t % NBQ) * 16);
                 const uint32_t f[4] = {qfp[0], qfp[1], qfp[2], qfp[3]};
-                if (f[0] | f[1] | f[2] | f[3]) {
-                    tc_fence_after();
+                const bool any = (f[0] | f[1] | f[2] | f[3]) != 0u;
+                if (any && t == n_tiles - 1 && nrow_last < TK) {
+                    uint4* vbrow = reinterpret_cast<uint4*>(smem + SM_VB + b2 * 16384);   // [128 keys][8 units], swizzled within a row
+                    for (int i = nrow_last * 8 + lane; i < TK * 8; i += 32) vbrow[i] = make_uint4(0, 0, 0, 0);
+                    fence_async_smem();
+                    __syncwarp();
+                }
+                if (lane == 0) {
+                    if (any) {
+                        tc_fence_after();
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        if (f[ks]) {
-                            mma_f8(tmem + T_ACC2, dvb + b2 * 1024 + ks * 256, dw2 + b2 * 256 + ks * 32, ID_V, acc2_started);
-                            acc2_started = true;
+                        for (int ks = 0; ks < 4; ++ks) {
+                            if (f[ks]) {
+                                mma_f8(tmem + T_ACC2, dvb + b2 * 1024 + ks * 256, dw2 + b2 * 256 + ks * 32, ID_V, acc2_started);
+                                acc2_started = true;
+                            }
                         }
                     }
+                    tc_commit(bar(B_BFREE + b2));
                 }
-                tc_commit(bar(B_BFREE + b2));
             }
-            tc_commit(bar(B_ALLDONE));
-            CW_FLUSH(29);
+            if (lane == 0) {
+                tc_commit(bar(B_ALLDONE));
+                CW_FLUSH(29);
+            }
         }
     } else if (warp >= 12 && warp < 12 + NHELP) {
         // ================= helpers: the keys that need both planes or an fp32 weight =================
