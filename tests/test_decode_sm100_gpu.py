@@ -73,6 +73,53 @@ def test_the_tcgen05_kernel_is_the_model(depth, ps, G, lens, split, chunk, v8):
                 assert ((den[bh].double() - wden).abs() / wden).max().item() < 1e-3
 
 
+@pytest.mark.parametrize("v8", [True, False])
+def test_what_the_pool_holds_past_a_requests_end_changes_no_bit(v8):
+    """The kernel reads whole tiles; the rows of a last, partial tile past the request's end hold
+    whatever the pool holds. Filled with 0xFF (an E4M3 NaN, a bf16 NaN, -1 in the int8 planes) in
+    every plane they must leave every bit of the result as it was: the stream's V rows, the
+    plane-B quarters of V and both planes of K are all read there."""
+    HKV, G, D, ps = 2, 8, 128, 256
+    lens = [1500, 700, 64, 2049, 9000]
+    B = len(lens)
+    q, k, v, cu = _layer(B, HKV * G, HKV, D, lens, seed=4, vmu=0.5)
+    c = _cache(B, HKV * G, HKV, D, lens, ps=ps, v8=v8, depth=16.0)
+    c.write_prompt(k, v, cu, lens)
+    c.attend(q)
+    z = (torch.ceil(c.z * 16) / 16).contiguous()
+    lens_now = [int(n) for n in c.seq_lens.tolist()]
+    for rk, rv in [(10.0, 10.0), (2.0, 14.0), (14.0, 14.0)]:
+        run = _launch(c, z, depth=16.0, rk=rk, rv=rv, split=1, chunk=0, HKV=HKV, ps=ps, kernel="sm100")
+        out, den, counts = (t.clone() for t in run())
+        torch.cuda.synchronize()
+        saved = {}
+        for b in range(B):
+            n = lens_now[b]
+            last = -(-n // ps) * ps            # the end of the request's last page
+            if last == n:
+                continue
+            for h in range(HKV):
+                pos = torch.arange(n, last, device="cuda")
+                pg = c.page_table[b, pos // ps].long()
+                rows = (pg * HKV + h) * ps + pos % ps
+                for name in ("ka", "kb", "ek", "va", "vb"):
+                    t = getattr(c, name)
+                    if t is None:
+                        continue
+                    raw = t.view(torch.uint8).view(t.shape[0], -1)
+                    saved[(b, h, name)] = (rows, raw[rows].clone())
+                    raw[rows] = 0xFF
+        assert saved
+        out2, den2, counts2 = run()
+        torch.cuda.synchronize()
+        assert int(run.status) == 0
+        assert torch.isfinite(out2).all() and torch.isfinite(den2).all()
+        assert torch.equal(out2, out) and torch.equal(den2, den) and torch.equal(counts2, counts), (rk, rv)
+        for (b, h, name), (rows, old) in saved.items():
+            t = getattr(c, name)
+            t.view(torch.uint8).view(t.shape[0], -1)[rows] = old
+
+
 def test_the_cache_serves_through_either_kernel():
     """FoldKVCache with kernel="sm100": append + attend tracks the softmax, a
     request's output under a fixed chunk is the same bits alone and in a batch."""
