@@ -98,7 +98,12 @@ def tail_rank_for(D, G, v8):
 
 def pick_split(n_groups, seq_len, *, max_len=None, sms=148, resident=3):
     """CTAs per row group on B200: enough CTAs for two waves of `resident`
-    per SM, but at least eight 64-key tiles each so the pipeline fills."""
-    want = -(-2 * sms * resident // max(1, n_groups))
+    per SM, but at least eight 64-key tiles each so the pipeline fills.
+    `resident` is 3 for the warp-level kernel; the tcgen05 kernel holds one
+    CTA an SM and pays a fixed cost per CTA, and measured best at about three
+    waves in all (`resident=1.5`: config 5's shape at 32 / 64 / 128 requests
+    takes 550 / 1031 / 1892 us a step with 2 / 1 / 1 CTAs a row group, against
+    705 with 1 at 32 requests and 1058 with 2 at 64)."""
+    want = -int(-2 * sms * resident // max(1, n_groups))
     cap = max(1, seq_len // 512)
     return int(max(1, min(want, cap, 64)))

@@ -473,7 +473,10 @@ class FoldKVCache:
     def _auto_split(self):
         mean = sum(self.lens) / self.batch
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        return pick_split(self.n_groups * self._gsub, max(1, int(mean)), max_len=max(self.lens), sms=sms)
+        sm100 = self.kernel == "sm100" or (
+            self.kernel == "auto" and 2 * sum(n for n in self.lens if n >= self.SM100_MIN_KEYS) >= sum(self.lens))
+        return pick_split(self.n_groups * self._gsub, max(1, int(mean)), max_len=max(self.lens), sms=sms,
+                          resident=1.5 if sm100 else 3)
 
     def _resolve_split(self, split):
         if self.chunk is not None:
