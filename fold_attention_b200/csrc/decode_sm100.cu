@@ -44,7 +44,7 @@
 // logits from TMEM and stay on the tensor-core path. That is a second build of the
 // kernel's body, chosen at the kernel's top by the request's length alone.
 //
-// Warps: 0 and 2 producers (a 4-slot and a 5-slot ring: K's plane A by bulk copy; plane A of V
+// Warps: 0 and 2 producers (two 4-slot rings: K's plane A by bulk copy; plane A of V
 // by TMA with the 128-byte swizzle, with the key scales), 1 and 3 MMA issuers (logits; values. 256 TMEM
 // columns), 4-7 and 8-11 one thread per key of the even and of the odd tiles, 12 and up the
 // helpers, and for an 8-bit V one more warp that issues plane B's MMAs as its quarters land. A K slot is free again as soon as its logits are out, a V slot when its
@@ -779,8 +779,8 @@ __device__ __forceinline__ void decode_sm100_body(const Params& p, const CUtenso
             fence_async_smem();
             mbar_arrive(bar(B_WREADY + (t & 1)));
             // plane B of V for this quarter, and the weights it meets. The flags and their barrier
-            // have more slots than the key threads can run ahead of the MMA issuer (they need its
-            // logits); only the data buffers, two tiles deep, are waited for, and only when used
+            // have more slots than the key threads can run ahead of the plane-B thread; the data
+            // buffers are three tiles deep
             if (V8) {
                 const int b2 = t % NB2, bq = t % NBQ;
                 // Every tile waits for the plane-B thread to be done with tile t-NB2, dense or not: that is
