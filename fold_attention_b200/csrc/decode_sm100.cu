@@ -785,8 +785,8 @@ __device__ __forceinline__ void decode_sm100_body(const Params& p, const CUtenso
                 const int b2 = t % NB2, bq = t % NBQ;
                 // Every tile waits for the plane-B thread to be done with tile t-NB2, dense or not: that is
                 // what bounds its lag (the flags' ring is deeper), and what keeps the parity test honest:
-                // this group waited for t-NB2+1's buffer a tile ago, the thread commits in order, so
-                // t-2*NB2's phase is complete and the test cannot pass a phase early
+                // at its last tile, t-2, this group waited for tile t-2-NB2's buffer; the thread commits in
+                // order, so the older tile t-2*NB2's phase is complete and the test cannot pass a phase early
                 if (lane == 0 && t >= NB2) CW(6, mbar_wait(bar(B_BFREE + b2), ((t / NB2) - 1) & 1, abort_flag, p.status));
                 __syncwarp();
                 if (dense) {
